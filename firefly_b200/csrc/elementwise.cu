@@ -1,0 +1,179 @@
+// Row-wise and element-wise kernels: embedding gather, (residual add +) RMSNorm,
+// SiLU-gate product, casts.  Statistics and sums are 32-bit whatever the storage.
+//
+// Arithmetic follows the reference's kernels (src/kernels/embedding.cu:19-37,
+// src/kernels/norm.cu:73-131, src/kernels/activation.cu:15-19, src/kernels/add.cu:33-39)
+// but the residual add is folded into the norm and the residual stream is kept in
+// 32-bit, so a layer's output is rounded once.
+#include "common.cuh"
+
+namespace ff {
+
+// ---------------------------------------------------------------- embedding --
+template <typename TT>
+__global__ void embedding_kernel(const int* __restrict__ ids, const TT* __restrict__ table,
+                                 float* __restrict__ out, int H, int V, int* __restrict__ status) {
+    const int t = blockIdx.x;
+    int id = ids[t];
+    if (id < 0 || id >= V) {  // never read outside the table; report it
+        if (threadIdx.x == 0) atomicExch(status, 1);
+        id = 0;
+    }
+    const TT* src = table + (size_t)id * H;
+    float* dst = out + (size_t)t * H;
+    for (int i = threadIdx.x; i < H; i += blockDim.x) dst[i] = to_float(src[i]);
+}
+
+// ------------------------------------------------------ residual add + norm --
+// residual[src,:] (+= delta[src,:]);  out[r,:] = v * rsqrt(mean(v^2)+eps) * w
+// src = row_idx ? row_idx[r] : r.  With row_idx the residual is not written back.
+template <typename TD, typename TO>
+__global__ void add_rms_norm_kernel(float* __restrict__ residual, const TD* __restrict__ delta,
+                                    const int* __restrict__ row_idx, const float* __restrict__ w,
+                                    float eps, TO* __restrict__ out, int H, int write_residual,
+                                    int use_smem) {
+    extern __shared__ float row[];
+    __shared__ float scratch[32];
+    const int r = blockIdx.x;
+    const int src = row_idx ? row_idx[r] : r;
+    float* res = residual + (size_t)src * H;
+    const TD* dl = delta ? delta + (size_t)src * H : nullptr;
+    float ss = 0.f;
+    for (int i = threadIdx.x; i < H; i += blockDim.x) {
+        float v = res[i];
+        if (dl) v += to_float(dl[i]);
+        if (use_smem) row[i] = v;
+        if (dl && write_residual) res[i] = v;
+        ss += v * v;
+    }
+    ss = block_sum(ss, scratch);
+    const float inv = 1.0f / sqrtf(ss / (float)H + eps);
+    TO* o = out + (size_t)r * H;
+    for (int i = threadIdx.x; i < H; i += blockDim.x) {
+        float v;
+        if (use_smem) v = row[i];
+        else { v = res[i]; if (dl && !write_residual) v += to_float(dl[i]); }
+        o[i] = from_float<TO>(v * inv * w[i]);
+    }
+}
+
+// ------------------------------------------------------------------ SwiGLU --
+// out[t,i] = silu(gu[t,i]) * gu[t,I+i]
+template <typename T>
+__global__ void silu_mul_kernel(const T* __restrict__ gu, T* __restrict__ out, int I, size_t total) {
+    size_t idx = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
+    if (idx >= total) return;
+    size_t t = idx / I;
+    int i = (int)(idx - t * I);
+    float g = to_float(gu[t * 2 * I + i]);
+    float u = to_float(gu[t * 2 * I + I + i]);
+    out[idx] = from_float<T>(g / (1.0f + expf(-g)) * u);
+}
+
+template <typename TI, typename TO>
+__global__ void cast_kernel(const TI* __restrict__ in, TO* __restrict__ out, size_t n) {
+    size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
+    if (i < n) out[i] = from_float<TO>(to_float(in[i]));
+}
+
+// out[r,:] += delta[r,:]   (32-bit residual, delta of either type)
+template <typename TD>
+__global__ void add_kernel(float* __restrict__ res, const TD* __restrict__ delta, size_t n) {
+    size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
+    if (i < n) res[i] += to_float(delta[i]);
+}
+
+static inline int norm_threads(int H) {
+    int t = (H + 3) / 4;
+    t = ((t + 31) / 32) * 32;
+    if (t < 32) t = 32;
+    if (t > 1024) t = 1024;
+    return t;
+}
+
+}  // namespace ff
+
+using namespace ff;
+
+// dtype codes: 0 = float32, 1 = bfloat16
+FF_EXPORT int ff_embedding(const int* ids, const void* table, int table_dtype, float* out, int T,
+                           int H, int V, int* status, cudaStream_t stream) {
+    if (T <= 0) return 0;
+    int threads = H >= 1024 ? 256 : (H >= 256 ? 128 : 64);
+    if (table_dtype == 0)
+        embedding_kernel<float><<<T, threads, 0, stream>>>(ids, (const float*)table, out, H, V, status);
+    else if (table_dtype == 1)
+        embedding_kernel<bf16><<<T, threads, 0, stream>>>(ids, (const bf16*)table, out, H, V, status);
+    else
+        return FF_ERR_BAD_ARG;
+    FF_LAUNCH_CHECK();
+    return 0;
+}
+
+template <typename TD, typename TO>
+static int launch_add_rms_norm(float* residual, const void* delta, const int* row_idx, const float* w,
+                               float eps, void* out, int rows, int H, int write_residual,
+                               cudaStream_t stream) {
+    size_t smem = (size_t)H * sizeof(float);
+    int use_smem = smem <= 200 * 1024;
+    if (!use_smem) smem = 0;
+    auto kern = add_rms_norm_kernel<TD, TO>;
+    if (smem > 48 * 1024) {
+        cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+        if (e != cudaSuccess) return (int)e;
+    }
+    kern<<<rows, norm_threads(H), smem, stream>>>(residual, (const TD*)delta, row_idx, w, eps, (TO*)out,
+                                                  H, write_residual, use_smem);
+    FF_LAUNCH_CHECK();
+    return 0;
+}
+
+// delta may be null (plain norm).  delta_dtype / out_dtype: 0 f32, 1 bf16.
+FF_EXPORT int ff_add_rms_norm(float* residual, const void* delta, int delta_dtype, const int* row_idx,
+                              const float* w, float eps, void* out, int out_dtype, int rows, int H,
+                              int write_residual, cudaStream_t stream) {
+    if (rows <= 0) return 0;
+    if (H <= 0) return FF_ERR_BAD_ARG;
+    if (delta_dtype == 0 && out_dtype == 0)
+        return launch_add_rms_norm<float, float>(residual, delta, row_idx, w, eps, out, rows, H, write_residual, stream);
+    if (delta_dtype == 1 && out_dtype == 1)
+        return launch_add_rms_norm<bf16, bf16>(residual, delta, row_idx, w, eps, out, rows, H, write_residual, stream);
+    if (delta_dtype == 0 && out_dtype == 1)
+        return launch_add_rms_norm<float, bf16>(residual, delta, row_idx, w, eps, out, rows, H, write_residual, stream);
+    if (delta_dtype == 1 && out_dtype == 0)
+        return launch_add_rms_norm<bf16, float>(residual, delta, row_idx, w, eps, out, rows, H, write_residual, stream);
+    return FF_ERR_BAD_ARG;
+}
+
+FF_EXPORT int ff_silu_mul(const void* gate_up, void* out, int dtype, int T, int I, cudaStream_t stream) {
+    size_t total = (size_t)T * I;
+    if (total == 0) return 0;
+    unsigned blocks = (unsigned)((total + 255) / 256);
+    if (dtype == 0) silu_mul_kernel<float><<<blocks, 256, 0, stream>>>((const float*)gate_up, (float*)out, I, total);
+    else if (dtype == 1) silu_mul_kernel<bf16><<<blocks, 256, 0, stream>>>((const bf16*)gate_up, (bf16*)out, I, total);
+    else return FF_ERR_BAD_ARG;
+    FF_LAUNCH_CHECK();
+    return 0;
+}
+
+FF_EXPORT int ff_cast(const void* in, int in_dtype, void* out, int out_dtype, size_t n, cudaStream_t stream) {
+    if (n == 0) return 0;
+    unsigned blocks = (unsigned)((n + 255) / 256);
+    if (in_dtype == 0 && out_dtype == 1) cast_kernel<float, bf16><<<blocks, 256, 0, stream>>>((const float*)in, (bf16*)out, n);
+    else if (in_dtype == 1 && out_dtype == 0) cast_kernel<bf16, float><<<blocks, 256, 0, stream>>>((const bf16*)in, (float*)out, n);
+    else if (in_dtype == 0 && out_dtype == 0) cast_kernel<float, float><<<blocks, 256, 0, stream>>>((const float*)in, (float*)out, n);
+    else if (in_dtype == 1 && out_dtype == 1) cast_kernel<bf16, bf16><<<blocks, 256, 0, stream>>>((const bf16*)in, (bf16*)out, n);
+    else return FF_ERR_BAD_ARG;
+    FF_LAUNCH_CHECK();
+    return 0;
+}
+
+FF_EXPORT int ff_residual_add(float* residual, const void* delta, int delta_dtype, size_t n, cudaStream_t stream) {
+    if (n == 0) return 0;
+    unsigned blocks = (unsigned)((n + 255) / 256);
+    if (delta_dtype == 0) add_kernel<float><<<blocks, 256, 0, stream>>>(residual, (const float*)delta, n);
+    else if (delta_dtype == 1) add_kernel<bf16><<<blocks, 256, 0, stream>>>(residual, (const bf16*)delta, n);
+    else return FF_ERR_BAD_ARG;
+    FF_LAUNCH_CHECK();
+    return 0;
+}

@@ -1,0 +1,113 @@
+// Per-head RMSNorm of q and k, rotary position encoding, and the write of k and v
+// into the paged cache, in one pass over the projection's output.
+//
+// The reference does this in four launches: two rms_norm calls with a row = one
+// head (src/model/qwen_model.cu:124-128), apply_rope (src/kernels/rope.cu:22-137)
+// and append_kv_cache (src/model/qwen_model.cu:21-47).  Here one warp owns one
+// (token, head): it normalises in 32-bit, rotates with cosines and sines taken from
+// a table built on the host in double precision, and rounds once on the way out.
+// q is rewritten in place; k (normalised, rotated) and v (raw) go to their page.
+//
+// Cache layout of one slot: [num_blocks][2 (k,v)][n_kv_heads][block_size][head_dim].
+#include "common.cuh"
+
+namespace ff {
+
+constexpr int QKR_WARPS = 4;
+constexpr int QKR_MAX_D = 256;
+
+template <typename T>
+__global__ void qk_norm_rope_store_kernel(
+    T* __restrict__ qkv, int row_width, int T_tokens, int nq, int nkv, int d,
+    const float* __restrict__ q_norm_w, const float* __restrict__ k_norm_w, float eps,
+    const float* __restrict__ cos_sin, int rotary_dim, int max_positions,
+    const int* __restrict__ positions, const int* __restrict__ token_seq,
+    const int* __restrict__ block_table, int max_blocks, int block_size, int num_blocks,
+    T* __restrict__ cache, int* __restrict__ status) {
+    __shared__ float bufs[QKR_WARPS][QKR_MAX_D];
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+    const int heads = nq + 2 * nkv;
+    const long long item = (long long)blockIdx.x * QKR_WARPS + warp;
+    if (item >= (long long)T_tokens * heads) return;
+    const int t = (int)(item / heads), hh = (int)(item % heads);
+    float* buf = bufs[warp];
+    T* src = qkv + (size_t)t * row_width + (size_t)hh * d;
+    const int kind = hh < nq ? 0 : (hh < nq + nkv ? 1 : 2);  // q, k, v
+    const int pos = positions[t];
+
+    float ss = 0.f;
+    for (int i = lane; i < d; i += 32) {
+        float v = to_float(src[i]);
+        buf[i] = v;
+        ss += v * v;
+    }
+    const float* nw = kind == 0 ? q_norm_w : (kind == 1 ? k_norm_w : nullptr);
+    if (nw) {
+        ss = warp_sum(ss);
+        const float inv = 1.0f / sqrtf(ss / (float)d + eps);
+        for (int i = lane; i < d; i += 32) buf[i] = buf[i] * inv * nw[i];
+    }
+    __syncwarp();
+
+    T* dst = src;
+    if (kind != 0) {
+        const int seq = token_seq[t];
+        const int page = block_table[(size_t)seq * max_blocks + pos / block_size];
+        if (page < 0 || page >= num_blocks) {
+            if (lane == 0) atomicExch(status, 2);
+            return;
+        }
+        const int kh = kind == 1 ? hh - nq : hh - nq - nkv;
+        dst = cache + ((((size_t)page * 2 + (kind == 2)) * nkv + kh) * block_size + pos % block_size) * d;
+    }
+    if (kind != 2 && cos_sin) {
+        if (pos < 0 || pos >= max_positions) {
+            if (lane == 0) atomicExch(status, 3);
+            return;
+        }
+        const int half = rotary_dim / 2;
+        const float* cs = cos_sin + (size_t)pos * rotary_dim;  // [half][2]
+        for (int i = lane; i < half; i += 32) {
+            const float c = cs[2 * i], s = cs[2 * i + 1];
+            const float lo = buf[i], hi = buf[i + half];
+            dst[i] = from_float<T>(lo * c - hi * s);
+            dst[i + half] = from_float<T>(hi * c + lo * s);
+        }
+        for (int i = rotary_dim + lane; i < d; i += 32) dst[i] = from_float<T>(buf[i]);
+    } else {
+        for (int i = lane; i < d; i += 32) dst[i] = from_float<T>(buf[i]);
+    }
+}
+
+}  // namespace ff
+
+using namespace ff;
+
+// nkv may be 0: a run that only reads another layer's cache has q heads alone.
+FF_EXPORT int ff_qk_norm_rope_store(void* qkv, int dtype, int row_width, int T, int nq, int nkv, int d,
+                                    const float* q_norm_w, const float* k_norm_w, float eps,
+                                    const float* cos_sin, int rotary_dim, int max_positions,
+                                    const int* positions, const int* token_seq, const int* block_table,
+                                    int max_blocks, int block_size, int num_blocks, void* cache,
+                                    int* status, cudaStream_t stream) {
+    if (T <= 0) return 0;
+    if (d <= 0 || d > QKR_MAX_D) return FF_ERR_UNSUPPORTED;
+    if (cos_sin && (rotary_dim <= 0 || rotary_dim > d || (rotary_dim & 1))) return FF_ERR_BAD_ARG;
+    if (row_width < (nq + 2 * nkv) * d) return FF_ERR_BAD_ARG;
+    const long long items = (long long)T * (nq + 2 * nkv);
+    const unsigned blocks = (unsigned)((items + QKR_WARPS - 1) / QKR_WARPS);
+    if (dtype == 0)
+        qk_norm_rope_store_kernel<float><<<blocks, QKR_WARPS * 32, 0, stream>>>(
+            (float*)qkv, row_width, T, nq, nkv, d, q_norm_w, k_norm_w, eps, cos_sin, rotary_dim,
+            max_positions, positions, token_seq, block_table, max_blocks, block_size, num_blocks,
+            (float*)cache, status);
+    else if (dtype == 1)
+        qk_norm_rope_store_kernel<bf16><<<blocks, QKR_WARPS * 32, 0, stream>>>(
+            (bf16*)qkv, row_width, T, nq, nkv, d, q_norm_w, k_norm_w, eps, cos_sin, rotary_dim,
+            max_positions, positions, token_seq, block_table, max_blocks, block_size, num_blocks,
+            (bf16*)cache, status);
+    else
+        return FF_ERR_BAD_ARG;
+    FF_LAUNCH_CHECK();
+    return 0;
+}

@@ -1,0 +1,78 @@
+"""What one step looks like to the parts of a model: the batch's metadata on the
+device, the caches, and scratch memory.
+
+A step is a flat list of tokens from several requests.  Each token knows its
+request (``token_seq``, an index into this step's sequences) and its absolute
+position; that is all the kernels need to find its keys, whatever the cut.
+"""
+from __future__ import annotations
+
+from dataclasses import dataclass, field
+from typing import Dict, List, Optional, Sequence, Tuple
+
+import torch
+
+
+class Workspace:
+    """Named scratch buffers, reused from layer to layer and from step to step.
+
+    A buffer grows when a larger one is asked for, unless the workspace is
+    frozen (while a CUDA graph that uses its addresses exists)."""
+
+    def __init__(self, device):
+        self.device = torch.device(device)
+        self._bufs: Dict[Tuple[str, torch.dtype], torch.Tensor] = {}
+        self.frozen = False
+
+    def get(self, tag: str, shape: Sequence[int], dtype: torch.dtype) -> torch.Tensor:
+        n = 1
+        for s in shape:
+            n *= int(s)
+        key = (tag, dtype)
+        buf = self._bufs.get(key)
+        if buf is None or buf.numel() < n:
+            if self.frozen:
+                raise RuntimeError(f"workspace buffer '{tag}' would have to grow to {n} elements "
+                                   "while a captured graph uses it")
+            buf = torch.empty(max(n, 1), dtype=dtype, device=self.device)
+            self._bufs[key] = buf
+        return buf[:n].view(*shape)
+
+    def reserve(self, tag: str, numel: int, dtype: torch.dtype) -> None:
+        self.get(tag, (numel,), dtype)
+
+    def bytes(self) -> int:
+        return sum(b.numel() * b.element_size() for b in self._bufs.values())
+
+
+@dataclass
+class StepContext:
+    num_tokens: int
+    num_seqs: int
+    token_ids: torch.Tensor            # int32 [T]
+    positions: torch.Tensor            # int32 [T] absolute position of each token
+    token_seq: torch.Tensor            # int32 [T] index of the token's sequence in this step
+    cu_q: torch.Tensor                 # int32 [n+1] token offsets of the sequences
+    ctx_lens: torch.Tensor             # int32 [n] tokens already in the cache
+    state_slots: torch.Tensor          # int32 [n] fixed-size state slot of each sequence
+    seq_fresh: torch.Tensor            # int32 [n] 1 when this is the request's first step
+    logits_rows: torch.Tensor          # int32 [r] tokens whose logits are wanted
+    block_tables: List[torch.Tensor]   # per KV group: int32 [n, max_blocks]
+    q_lens: List[int]                  # host copies
+    ctx_lens_host: List[int]
+    max_q_len: int
+    max_kv_len: int
+    workspace: Workspace
+    status: torch.Tensor               # int32 [1], set by a kernel that met a bad index
+    cache: object                      # CacheManager
+    dtype: torch.dtype                 # activation type of this engine
+    pure_decode: bool = False
+
+    def kv(self, slot: int) -> Tuple[torch.Tensor, torch.Tensor]:
+        """Pages of cache slot ``slot`` and the block table of its group."""
+        pages, g = self.cache.kv_view(slot)
+        return pages, self.block_tables[g]
+
+    def state(self, slot: int) -> torch.Tensor:
+        """Fixed-size state tensor of cache slot ``slot``: [1+max_requests, *shape]."""
+        return self.cache.state_storage[slot]

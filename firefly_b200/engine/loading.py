@@ -1,0 +1,65 @@
+"""From a model folder (or a configuration and a seed) to a bound model."""
+from __future__ import annotations
+
+from typing import Optional, Tuple
+
+import torch
+
+from ..config.base import ModelConfig
+from ..models.decoder import DecoderModel
+from ..models.registry import load_config, spec_for
+from ..ops import kernels as K
+from ..parts import Runtime
+from ..weights.loader import load_weights
+from ..weights.random_init import random_weights
+
+_DTYPES = {"bfloat16": torch.bfloat16, "bf16": torch.bfloat16, "float32": torch.float32,
+           "fp32": torch.float32, "f32": torch.float32}
+
+
+def parse_dtype(d) -> torch.dtype:
+    if isinstance(d, torch.dtype):
+        if d not in (torch.bfloat16, torch.float32):
+            raise ValueError(f"engine dtype must be bfloat16 or float32, got {d}")
+        return d
+    try:
+        return _DTYPES[str(d).lower()]
+    except KeyError:
+        raise ValueError(f"engine dtype must be bfloat16 or float32, got {d!r}") from None
+
+
+def require_cuda(device) -> torch.device:
+    dev = torch.device(device)
+    if dev.type != "cuda":
+        raise RuntimeError("firefly_b200 runs on a CUDA device only (there is no CPU path)")
+    if not torch.cuda.is_available():
+        raise RuntimeError("firefly_b200 needs a CUDA device and none is available")
+    return dev
+
+
+def load_model(model_dir: str, *, dtype="bfloat16", device="cuda:0") -> Tuple[DecoderModel, ModelConfig]:
+    """Read ``config.json``, pick the model by its architecture name, bind the
+    tensors of ``model.safetensors`` by name."""
+    dt = parse_dtype(dtype)
+    dev = require_cuda(device)
+    K.set_exact_matmul()
+    config = load_config(model_dir)
+    model = DecoderModel(spec_for(config), Runtime(dev, dt))
+    tensors = load_weights(model_dir, model.weight_specs(), dtype=dt, device=dev)
+    model.bind(tensors)
+    del tensors
+    return model, config
+
+
+def random_model(config: ModelConfig, seed: int, *, dtype="bfloat16", device="cuda:0",
+                 num_layers: Optional[int] = None) -> DecoderModel:
+    """A model of ``config``'s shape with seeded random weights drawn on the
+    device (no folder is written)."""
+    dt = parse_dtype(dtype)
+    dev = require_cuda(device)
+    K.set_exact_matmul()
+    model = DecoderModel(spec_for(config), Runtime(dev, dt))
+    tensors = random_weights(model.weight_specs(), seed, dtype=dt, device=dev)
+    model.bind(tensors)
+    del tensors
+    return model

@@ -1,0 +1,197 @@
+"""The step function: a batch of (request, its next tokens) through the model.
+
+``ModelRunner.step(entries)`` runs exactly the tokens it is given, as one batch,
+against the cache that earlier steps left, and returns 32-bit logits at the
+wanted places.  Portions of prompts and single decoded tokens may sit side by
+side, cut anywhere.  The reference instead runs each prefill portion as a call
+of its own and all decodes as another (src/engine.cc:238-342) through a
+rectangular ``forward(input_ids[B,S], context_lens[B], ...)``
+(include/firefly/model/model.h:45-46).
+
+Per step the host packs all integer metadata (token ids, positions, the token ->
+sequence map, block tables, wanted rows) into one pinned buffer and uploads it
+with one copy.
+"""
+from __future__ import annotations
+
+from dataclasses import dataclass, field
+from typing import Dict, List, Optional, Sequence, Tuple
+
+import numpy as np
+import torch
+
+from ..cache.manager import SCRATCH_PAGE, CacheManager, OutOfPages, RequestCache
+from ..models.decoder import DecoderModel
+from ..ops import kernels as K
+from .context import StepContext, Workspace
+
+
+@dataclass
+class StepEntry:
+    """One request's share of a step: its next tokens and the places among them
+    (indices into ``tokens``) whose logits are wanted."""
+
+    cache: RequestCache
+    tokens: Sequence[int]
+    want: Sequence[int] = ()
+
+
+class StepError(RuntimeError):
+    pass
+
+
+_STATUS = {1: "a token id outside the vocabulary reached the embedding kernel",
+           2: "a token's cache page is missing from its block table (write)",
+           3: "a position beyond the rotary table",
+           4: "a key's cache page is missing from a block table (read)"}
+
+
+class MetaLayout:
+    """Where each integer array of a step lies in the packed metadata buffer."""
+
+    def __init__(self, T: int, n: int, r: int, n_groups: int, max_blocks: int):
+        self.T, self.n, self.r, self.n_groups, self.max_blocks = T, n, r, n_groups, max_blocks
+        off = 0
+
+        def take(count):
+            nonlocal off
+            lo = off
+            off += (count + 3) // 4 * 4     # keep every array 16-byte aligned
+            return lo
+        self.token_ids = take(T)
+        self.positions = take(T)
+        self.token_seq = take(T)
+        self.cu_q = take(n + 1)
+        self.ctx_lens = take(n)
+        self.state_slots = take(n)
+        self.seq_fresh = take(n)
+        self.logits_rows = take(r)
+        self.tables = [take(n * max_blocks) for _ in range(n_groups)]
+        self.size = off
+
+
+class ModelRunner:
+    def __init__(self, model: DecoderModel, cache: CacheManager, *, max_model_len: int,
+                 max_batched_tokens: int = 8192, max_seqs: int = 256):
+        self.model = model
+        self.cache = cache
+        self.device = model.rt.device
+        self.dtype = model.rt.dtype
+        self.vocab_size = model.spec.vocab_size
+        self.max_model_len = max_model_len
+        self.block_size = cache.block_size
+        self.max_blocks_per_seq = -(-max_model_len // cache.block_size)
+        self.workspace = Workspace(self.device)
+        self.status = torch.zeros(1, dtype=torch.int32, device=self.device)
+        self._meta_cap = 0
+        self._meta_host: Optional[torch.Tensor] = None
+        self._meta_dev: Optional[torch.Tensor] = None
+        self._ensure_meta(MetaLayout(max_batched_tokens, max_seqs, max_seqs, len(cache.groups),
+                                     self.max_blocks_per_seq).size)
+        self.steps_run = 0
+        self.kernel_launches = 0
+
+    # ------------------------------------------------------------------------------
+    def _ensure_meta(self, size: int) -> None:
+        if size > self._meta_cap:
+            self._meta_cap = size
+            self._meta_host = torch.empty(size, dtype=torch.int32).pin_memory()
+            self._meta_dev = torch.empty(size, dtype=torch.int32, device=self.device)
+
+    def build_context(self, entries: Sequence[StepEntry], *, meta_host: Optional[torch.Tensor] = None,
+                      meta_dev: Optional[torch.Tensor] = None, upload: bool = True) -> StepContext:
+        n = len(entries)
+        q_lens = [len(e.tokens) for e in entries]
+        T = sum(q_lens)
+        ctx_lens = [e.cache.num_tokens for e in entries]
+        wants: List[int] = []
+        start = 0
+        for e, ql in zip(entries, q_lens):
+            for w in e.want:
+                if not (0 <= w < ql):
+                    raise StepError(f"request {e.cache.request_id!r}: wanted place {w} is outside its "
+                                    f"{ql} tokens of this step")
+                wants.append(start + w)
+            start += ql
+        lay = MetaLayout(T, n, len(wants), len(self.cache.groups), self.max_blocks_per_seq)
+        if meta_host is None:
+            self._ensure_meta(lay.size)
+            meta_host, meta_dev = self._meta_host, self._meta_dev
+        elif lay.size > meta_host.numel():
+            raise StepError("metadata buffer too small for this step")
+        h = meta_host.numpy()
+        pos = 0
+        for i, (e, ql, cl) in enumerate(zip(entries, q_lens, ctx_lens)):
+            toks = np.asarray(e.tokens, dtype=np.int64)
+            if toks.size and (toks.min() < 0 or toks.max() >= self.vocab_size):
+                raise StepError(f"request {e.cache.request_id!r}: token id outside [0, {self.vocab_size})")
+            if cl + ql > self.max_model_len:
+                raise StepError(f"request {e.cache.request_id!r}: {cl + ql} tokens exceed the engine's "
+                                f"max_model_len {self.max_model_len}")
+            h[lay.token_ids + pos: lay.token_ids + pos + ql] = toks
+            h[lay.positions + pos: lay.positions + pos + ql] = np.arange(cl, cl + ql)
+            h[lay.token_seq + pos: lay.token_seq + pos + ql] = i
+            h[lay.cu_q + i] = pos
+            h[lay.ctx_lens + i] = cl
+            h[lay.state_slots + i] = e.cache.state_slot
+            h[lay.seq_fresh + i] = 1 if e.cache.fresh else 0
+            need_pages = -(-(cl + ql) // self.block_size)
+            for g, table in enumerate(e.cache.tables):
+                if len(table) < need_pages:
+                    raise OutOfPages(f"request {e.cache.request_id!r} has {len(table)} pages in group "
+                                     f"{g}, this step needs {need_pages}")
+                row = lay.tables[g] + i * self.max_blocks_per_seq
+                h[row: row + len(table)] = table
+                h[row + len(table): row + self.max_blocks_per_seq] = -1
+            pos += ql
+        h[lay.cu_q + n] = pos
+        if wants:
+            h[lay.logits_rows: lay.logits_rows + len(wants)] = wants
+        if upload:
+            meta_dev[:lay.size].copy_(meta_host[:lay.size], non_blocking=True)
+        return self.context_from_layout(lay, meta_dev, q_lens, ctx_lens)
+
+    def context_from_layout(self, lay: MetaLayout, meta_dev: torch.Tensor, q_lens: List[int],
+                            ctx_lens: List[int]) -> StepContext:
+        d = meta_dev
+
+        def sl(off, count):
+            return d[off: off + count]
+        return StepContext(
+            num_tokens=lay.T, num_seqs=lay.n,
+            token_ids=sl(lay.token_ids, lay.T), positions=sl(lay.positions, lay.T),
+            token_seq=sl(lay.token_seq, lay.T), cu_q=sl(lay.cu_q, lay.n + 1),
+            ctx_lens=sl(lay.ctx_lens, lay.n), state_slots=sl(lay.state_slots, lay.n),
+            seq_fresh=sl(lay.seq_fresh, lay.n), logits_rows=sl(lay.logits_rows, lay.r),
+            block_tables=[sl(o, lay.n * lay.max_blocks).view(lay.n, lay.max_blocks) for o in lay.tables],
+            q_lens=list(q_lens), ctx_lens_host=list(ctx_lens),
+            max_q_len=max(q_lens, default=0),
+            max_kv_len=max((c + q for c, q in zip(ctx_lens, q_lens)), default=0),
+            workspace=self.workspace, status=self.status, cache=self.cache, dtype=self.dtype,
+            pure_decode=all(q == 1 for q in q_lens))
+
+    # ------------------------------------------------------------------------------
+    def step(self, entries: Sequence[StepEntry]) -> torch.Tensor:
+        """Run the entries' tokens as one batch.  Returns float32 logits
+        [number of wanted places, vocab] in the order of the entries and of each
+        entry's ``want`` (a view of scratch memory: valid until the next step).
+        Every entry's request must already hold the pages for its new tokens."""
+        entries = [e for e in entries if len(e.tokens)]
+        if not entries:
+            return torch.empty((0, self.vocab_size), dtype=torch.float32, device=self.device)
+        ids = [id(e.cache) for e in entries]
+        if len(set(ids)) != len(ids):
+            raise StepError("a request appears twice in one step")
+        ctx = self.build_context(entries)
+        logits = self.model.forward(ctx)
+        for e in entries:
+            self.cache.advance(e.cache, len(e.tokens))
+        self.steps_run += 1
+        return logits
+
+    def check_status(self) -> None:
+        """Raise if a kernel met a bad index since the last check (synchronises)."""
+        code = int(self.status.item())
+        if code:
+            self.status.zero_()
+            raise StepError(f"device status {code}: {_STATUS.get(code, 'unknown')}")

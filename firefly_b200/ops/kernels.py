@@ -1,0 +1,235 @@
+"""Python faces of the CUDA kernels in ``csrc/``.
+
+Every function takes CUDA tensors, launches on torch's current stream (so the
+calls can be captured into a CUDA graph) and writes into buffers the caller
+provides; nothing is allocated here.  There is no CPU or library fallback: a
+tensor that is not on a CUDA device, or a kernel that cannot be built, raises.
+"""
+from __future__ import annotations
+
+import ctypes
+from ctypes import c_float, c_int, c_longlong, c_size_t, c_void_p
+from typing import Optional
+
+import torch
+
+from .build import KernelBuildError, compile_many, load_module
+
+_DT = {torch.float32: 0, torch.bfloat16: 1}
+
+
+class KernelError(RuntimeError):
+    pass
+
+
+def _p(t: Optional[torch.Tensor]) -> c_void_p:
+    return c_void_p(0 if t is None else t.data_ptr())
+
+
+def _stream() -> c_void_p:
+    return c_void_p(torch.cuda.current_stream().cuda_stream)
+
+
+def _dt(t: torch.Tensor) -> int:
+    try:
+        return _DT[t.dtype]
+    except KeyError:
+        raise KernelError(f"unsupported element type {t.dtype}") from None
+
+
+def _need_cuda(*tensors: Optional[torch.Tensor]) -> None:
+    for t in tensors:
+        if t is not None:
+            if not t.is_cuda:
+                raise KernelError("firefly_b200 kernels run on a CUDA device only; got a "
+                                  f"{t.device} tensor (there is no CPU implementation)")
+            if not t.is_contiguous():
+                raise KernelError("kernel operand must be contiguous")
+
+
+def _check(code: int, what: str) -> None:
+    if code == 0:
+        return
+    if code == -1:
+        raise KernelError(f"{what}: bad argument")
+    if code == -2:
+        raise KernelError(f"{what}: size not supported by this kernel")
+    raise KernelError(f"{what}: CUDA error {code}")
+
+
+_MODULES = {
+    "elementwise": ("elementwise.cu", None),
+    "qk_rope_store": ("qk_rope_store.cu", None),
+    "attention_simt": ("attention_simt.cu", None),
+    "sampling": ("sampling.cu", None),
+}
+
+
+def _lib(name: str) -> ctypes.CDLL:
+    src, defs = _MODULES[name]
+    return load_module(src, defs)
+
+
+def build_all(extra=()) -> None:
+    """Compile every module (used by the build check; needs no GPU)."""
+    mods = list(_MODULES.values()) + list(extra)
+    compile_many(mods)
+
+
+# --------------------------------------------------------------------------- #
+def embedding(ids: torch.Tensor, table: torch.Tensor, out: torch.Tensor, status: torch.Tensor) -> None:
+    """out[t,:] = float(table[ids[t],:]); ids int32 [T], out float32 [T,H]."""
+    _need_cuda(ids, table, out, status)
+    assert ids.dtype == torch.int32 and out.dtype == torch.float32
+    T, H = out.shape
+    V = table.shape[0]
+    assert table.shape[1] == H and ids.numel() == T
+    _check(_lib("elementwise").ff_embedding(_p(ids), _p(table), c_int(_dt(table)), _p(out), c_int(T),
+                                           c_int(H), c_int(V), _p(status), _stream()), "embedding")
+
+
+def add_rms_norm(residual: torch.Tensor, delta: Optional[torch.Tensor], weight: torch.Tensor,
+                 eps: float, out: torch.Tensor, row_idx: Optional[torch.Tensor] = None) -> None:
+    """residual (+= delta), out = rms_norm(residual) * weight.
+
+    residual float32 [T,H], updated in place when ``delta`` is given and
+    ``row_idx`` is not.  With ``row_idx`` (int32 [n]) only those rows are
+    normalised, into ``out`` [n,H], and the residual is left as it is.
+    """
+    _need_cuda(residual, delta, weight, out, row_idx)
+    assert residual.dtype == torch.float32 and weight.dtype == torch.float32
+    H = residual.shape[-1]
+    rows = out.shape[0]
+    assert out.shape[-1] == H and weight.numel() == H
+    if row_idx is None:
+        assert rows == residual.shape[0]
+    else:
+        assert row_idx.dtype == torch.int32 and row_idx.numel() == rows
+    if delta is not None:
+        assert delta.shape == residual.shape
+    _check(_lib("elementwise").ff_add_rms_norm(
+        _p(residual), _p(delta), c_int(_dt(delta) if delta is not None else _dt(out)), _p(row_idx),
+        _p(weight), c_float(eps), _p(out), c_int(_dt(out)), c_int(rows), c_int(H),
+        c_int(1 if row_idx is None else 0), _stream()), "add_rms_norm")
+
+
+def residual_add(residual: torch.Tensor, delta: torch.Tensor) -> None:
+    _need_cuda(residual, delta)
+    assert residual.dtype == torch.float32 and residual.shape == delta.shape
+    _check(_lib("elementwise").ff_residual_add(_p(residual), _p(delta), c_int(_dt(delta)),
+                                              c_size_t(residual.numel()), _stream()), "residual_add")
+
+
+def silu_mul(gate_up: torch.Tensor, out: torch.Tensor) -> None:
+    """out[t,i] = silu(gate_up[t,i]) * gate_up[t,I+i]."""
+    _need_cuda(gate_up, out)
+    T, I = out.shape
+    assert gate_up.shape == (T, 2 * I) and gate_up.dtype == out.dtype
+    _check(_lib("elementwise").ff_silu_mul(_p(gate_up), _p(out), c_int(_dt(out)), c_int(T), c_int(I),
+                                          _stream()), "silu_mul")
+
+
+def cast(src: torch.Tensor, out: torch.Tensor) -> None:
+    _need_cuda(src, out)
+    assert src.numel() == out.numel()
+    _check(_lib("elementwise").ff_cast(_p(src), c_int(_dt(src)), _p(out), c_int(_dt(out)),
+                                      c_size_t(src.numel()), _stream()), "cast")
+
+
+def qk_norm_rope_store(qkv: torch.Tensor, nq: int, nkv: int, d: int, q_norm_w, k_norm_w, eps: float,
+                       cos_sin: Optional[torch.Tensor], rotary_dim: int, positions: torch.Tensor,
+                       token_seq: torch.Tensor, block_table: Optional[torch.Tensor],
+                       cache: Optional[torch.Tensor], status: torch.Tensor) -> None:
+    """Per-head RMSNorm of q and k, rotation, and the write of k, v into the
+    paged cache ``[blocks, 2, nkv, block_size, d]``; q is rewritten in place in
+    ``qkv`` [T, (nq+2nkv)*d].  ``nkv == 0``: q only, no cache write."""
+    _need_cuda(qkv, q_norm_w, k_norm_w, cos_sin, positions, token_seq, block_table, cache, status)
+    T, width = qkv.shape
+    if nkv:
+        assert cache is not None and block_table is not None and cache.dtype == qkv.dtype
+        num_blocks, two, ckv, block_size, cd = cache.shape
+        assert two == 2 and ckv == nkv and cd == d
+        max_blocks = block_table.shape[1]
+    else:
+        num_blocks = block_size = max_blocks = 1
+    max_pos = cos_sin.shape[0] if cos_sin is not None else 0
+    if cos_sin is not None:
+        assert cos_sin.dtype == torch.float32 and cos_sin.shape[1] * cos_sin.shape[2] == rotary_dim
+    _check(_lib("qk_rope_store").ff_qk_norm_rope_store(
+        _p(qkv), c_int(_dt(qkv)), c_int(width), c_int(T), c_int(nq), c_int(nkv), c_int(d),
+        _p(q_norm_w), _p(k_norm_w), c_float(eps), _p(cos_sin), c_int(rotary_dim), c_int(max_pos),
+        _p(positions), _p(token_seq), _p(block_table), c_int(max_blocks), c_int(block_size),
+        c_int(num_blocks), _p(cache), _p(status), _stream()), "qk_norm_rope_store")
+
+
+def paged_attention_simt(q: torch.Tensor, q_stride: int, cache: torch.Tensor, block_table: torch.Tensor,
+                         token_seq: torch.Tensor, positions: torch.Tensor, out: torch.Tensor,
+                         nq: int, nkv: int, d: int, scale: float, window: int,
+                         status: torch.Tensor) -> None:
+    """Attention of every query token over its sequence's cached keys 0..pos
+    (or the last ``window`` of them; 0 = all).  ``q`` is read with row stride
+    ``q_stride`` elements (it may be the head of a wider qkv buffer)."""
+    _need_cuda(cache, block_table, token_seq, positions, out, status)
+    if not q.is_cuda:
+        raise KernelError("firefly_b200 kernels run on a CUDA device only")
+    T = out.shape[0]
+    num_blocks, two, ckv, block_size, cd = cache.shape
+    assert two == 2 and ckv == nkv and cd == d and cache.dtype == q.dtype == out.dtype
+    _check(_lib("attention_simt").ff_paged_attention_simt(
+        _p(q), c_int(_dt(q)), c_int(q_stride), _p(cache), _p(block_table), c_int(block_table.shape[1]),
+        _p(token_seq), _p(positions), _p(out), c_int(out.shape[1]), c_int(T), c_int(nq), c_int(nkv),
+        c_int(d), c_int(block_size), c_int(num_blocks), c_float(scale), c_int(window), _p(status),
+        _stream()), "paged_attention_simt")
+
+
+def sample(logits: torch.Tensor, out: torch.Tensor, temperature: Optional[torch.Tensor] = None,
+           seeds: Optional[torch.Tensor] = None, counters: Optional[torch.Tensor] = None) -> None:
+    """out[r] = arg-max of logits[r] (lowest index on ties), or, where
+    temperature[r] > 0, a draw from softmax(logits[r] / temperature[r]) with the
+    random numbers of (seeds[r], counters[r])."""
+    _need_cuda(logits, out, temperature, seeds, counters)
+    assert logits.dtype == torch.float32 and out.dtype == torch.int32 and logits.dim() == 2
+    rows, V = logits.shape
+    if temperature is not None:
+        assert temperature.dtype == torch.float32 and seeds.dtype == torch.int64 \
+            and counters.dtype == torch.int64
+    _check(_lib("sampling").ff_sample(_p(logits), c_int(rows), c_int(V), c_size_t(logits.stride(0)),
+                                     _p(temperature), _p(seeds), _p(counters), _p(out), _stream()),
+           "sample")
+
+
+# --------------------------------------------------------------------------- #
+# matrix products: a library routine (cuBLAS through torch), as the reference
+# uses a library (CUTLASS, src/kernels/linear.cu:15-104) for them.
+def linear(x: torch.Tensor, weight: torch.Tensor, out: torch.Tensor) -> None:
+    """out = x @ weight^T with 32-bit accumulation.  ``weight`` [N,K] row-major
+    as stored in checkpoints.  ``out`` may be float32 for bfloat16 operands."""
+    _need_cuda(x, weight, out)
+    if x.dtype != weight.dtype:
+        raise KernelError(f"linear: operand types differ ({x.dtype} vs {weight.dtype})")
+    if out.dtype == x.dtype:
+        torch.mm(x, weight.t(), out=out)
+    elif out.dtype == torch.float32:
+        torch.mm(x, weight.t(), out_dtype=torch.float32, out=out)
+    else:
+        raise KernelError(f"linear: cannot write {out.dtype} from {x.dtype}")
+
+
+def set_exact_matmul() -> None:
+    """No reduced-precision matrix mode anywhere: 32-bit products are true
+    32-bit (no TF32), 16-bit products accumulate and reduce in 32-bit."""
+    torch.backends.cuda.matmul.allow_tf32 = False
+    torch.backends.cudnn.allow_tf32 = False
+    torch.backends.cuda.matmul.allow_bf16_reduced_precision_reduction = False
+    torch.backends.cuda.matmul.allow_fp16_reduced_precision_reduction = False
+    try:
+        torch.set_float32_matmul_precision("highest")
+    except Exception:  # noqa: BLE001
+        pass
+
+
+def paged_attention(q: torch.Tensor, q_stride: int, pages: torch.Tensor, table: torch.Tensor, ctx,
+                    out: torch.Tensor, nq: int, nkv: int, d: int, scale: float, window: int) -> None:
+    """Attention of a step's tokens over the paged cache; picks the kernel."""
+    paged_attention_simt(q, q_stride, pages, table, ctx.token_seq, ctx.positions, out, nq, nkv, d,
+                         scale, window, ctx.status)

@@ -1,0 +1,62 @@
+"""Arrangements: how a layer's parts are joined into a block.
+
+``pre_norm`` is the reference's (src/model/qwen_model.cu:106-175):
+    h += mixer(norm_0(h));  h += feed_forward(norm_1(h))
+The residual stream ``h`` is 32-bit.  A part's output is not added at once: it is
+handed on as ``pending`` and the next norm adds it while it reads the row, so
+each sum is done once, in 32-bit, without a pass of its own.
+"""
+from __future__ import annotations
+
+from typing import List, Mapping, Optional, Tuple
+
+import torch
+
+from ..weights.loader import WeightSpec
+from .base import Part, Runtime, build_part, register_part
+
+
+class Block:
+    """Base of arrangements: owns the built parts of one layer."""
+
+    n_norms = 2
+
+    def __init__(self, layer_spec, rt: Runtime):
+        self.layer_spec = layer_spec
+        self.position = build_part("position", layer_spec.position, rt) \
+            if layer_spec.position is not None else None
+        self.mixer = build_part("mixer", layer_spec.mixer, rt, position=self.position)
+        self.feed_forward = build_part("feed_forward", layer_spec.feed_forward, rt)
+        if len(layer_spec.norms) != self.n_norms:
+            raise ValueError(f"arrangement '{layer_spec.arrangement}' needs {self.n_norms} norms, "
+                             f"got {len(layer_spec.norms)}")
+        self.norms = [build_part("norm", n, rt) for n in layer_spec.norms]
+
+    def parts(self) -> List[Part]:
+        out = [self.mixer, self.feed_forward, *self.norms]
+        if self.position is not None:
+            out.append(self.position)
+        return out
+
+    def weight_specs(self) -> List[WeightSpec]:
+        return [w for p in self.parts() for w in p.weight_specs()]
+
+    def bind(self, tensors: Mapping[str, torch.Tensor]) -> None:
+        for p in self.parts():
+            p.bind(tensors)
+
+    def cache_spec(self):
+        return self.mixer.cache_spec()
+
+
+class PreNormBlock(Block):
+    def forward(self, residual: torch.Tensor, pending: Optional[torch.Tensor], ctx, slot: int,
+                write_cache: bool) -> Tuple[torch.Tensor, Optional[torch.Tensor]]:
+        x = self.norms[0].forward(residual, pending, ctx)
+        a = self.mixer.forward(x, ctx, slot, write_cache)
+        x = self.norms[1].forward(residual, a, ctx)
+        f = self.feed_forward.forward(x, ctx)
+        return residual, f
+
+
+register_part("arrangement", "pre_norm", PreNormBlock)

@@ -1,0 +1,89 @@
+"""Replay on the GPU: the same requests whole, with the last 32 tokens decoded one
+by one, in portions of changing size, and mixed with other requests on a pool so
+small that pages are used again; in 32-bit and in bfloat16; all compared with the
+plain implementation."""
+import json
+import os
+import subprocess
+import sys
+
+import numpy as np
+import pytest
+import torch
+
+import plain_qwen3 as P
+import replay_util as U
+
+pytestmark = pytest.mark.gpu
+
+CONFIGS = {"A": (P.TINY_A, 0, 16, [40, 100, 1, 77, 128, 33]),
+           "B": (P.TINY_B, 1, 8, [70, 3, 200, 45, 256, 129, 17]),
+           "C": (P.TINY_C, 2, 32, [150, 64, 65, 300, 2, 97])}
+
+
+@pytest.fixture(scope="module")
+def folders(tmp_path_factory):
+    out = {}
+    for name, (cfg, seed, block, lengths) in CONFIGS.items():
+        for dtype, tdt in (("float32", torch.float32), ("bfloat16", torch.bfloat16)):
+            w = P.random_weights(cfg, seed, dtype=tdt, scale=0.05)
+            path = str(tmp_path_factory.mktemp(f"model{name}_{dtype}"))
+            U.write_model_dir(path, cfg, w, tdt)
+            reqs = U.make_requests(cfg["vocab_size"], lengths, seed + 10)
+            plain = U.plain_all(cfg, w, reqs)     # the plain model sees the stored (rounded) weights
+            out[(name, dtype)] = (path, cfg, block, reqs, plain)
+    return out
+
+
+def _session(path, dtype, max_tokens, block):
+    from firefly_b200.replay import ReplaySession
+    return ReplaySession(path, dtype=dtype, max_tokens=max_tokens, block_size=block)
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+@pytest.mark.parametrize("name", list(CONFIGS))
+@pytest.mark.parametrize("family", ["whole", "tail", "portions", "mixed"])
+def test_replay_family(folders, name, dtype, family):
+    path, cfg, block, reqs, plain = folders[(name, dtype)]
+    steps = {"whole": U.trace_whole, "tail": U.trace_tail_decode, "portions": U.trace_portions,
+             "mixed": U.trace_mixed}[family](reqs)
+    peak = U.peak_tokens(steps)
+    sess = _session(path, dtype, peak, block)
+    got = U.run_trace(sess, steps)
+    assert len(got.rows) == sum(len(t) for t in reqs.values())
+    U.compare(got, plain, U.TOL[dtype], f"{name}/{dtype}/{family}")
+    sess.cache.check()
+    assert not sess.cache.live
+    if family == "mixed":
+        # the pool held fewer tokens than the requests have: pages were used again
+        assert peak < sum(-(-len(t) // 64) * 64 for t in reqs.values())
+
+
+def test_trace_run_program(folders, tmp_path):
+    """The program itself: stdin protocol, files, 'done' lines, exit code."""
+    path, cfg, block, reqs, plain = folders[("B", "float32")]
+    steps = U.trace_mixed(reqs, seed=3)
+    exe = os.path.join(os.path.dirname(__file__), "..", "bin", "trace_run")
+    out = tmp_path / "out"
+    proc = subprocess.Popen([sys.executable, exe, "--model", path, "--dtype", "float32", "--out", str(out),
+                             "--max-tokens", str(U.peak_tokens(steps)), "--block-size", str(block)],
+                            stdin=subprocess.PIPE, stdout=subprocess.PIPE, text=True)
+    got = U.Collected()
+    done = {}
+    V = cfg["vocab_size"]
+    for rec in steps:
+        proc.stdin.write(json.dumps(rec) + "\n")
+        proc.stdin.flush()
+        line = proc.stdout.readline().strip()
+        assert line == f"done {rec['step']}", line
+        arr = np.fromfile(out / f"{rec['step']}.f32", dtype="<f4").reshape(-1, V)
+        k = 0
+        for ent in rec["entries"]:
+            base = done.get(ent["id"], 0)
+            for w in ent["want"]:
+                got.add(ent["id"], base + w, arr[k])
+                k += 1
+            done[ent["id"]] = base + len(ent["tokens"])
+    proc.stdin.close()
+    assert proc.wait(timeout=60) == 0
+    U.compare(got, plain, U.TOL["float32"], "trace_run program")
