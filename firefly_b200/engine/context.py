@@ -67,6 +67,7 @@ class StepContext:
     cache: object                      # CacheManager
     dtype: torch.dtype                 # activation type of this engine
     pure_decode: bool = False
+    captured: bool = False             # being captured into a CUDA graph: launch shapes must be static
 
     def kv(self, slot: int) -> Tuple[torch.Tensor, torch.Tensor]:
         """Pages of cache slot ``slot`` and the block table of its group."""

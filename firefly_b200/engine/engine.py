@@ -1,0 +1,266 @@
+"""The engine loop: schedule, step, sample, finish; and its public faces.
+
+``Engine`` follows the reference's class of that name (include/firefly/engine.h:16-73,
+src/engine.cc): ``async_generate(id, input_ids, max_tokens)`` queues a request
+from any thread, ``start()`` / ``stop()`` run the loop in a background thread and
+results arrive on a ``ResultQueue`` as (request id, new token ids, is_finished)
+— token ids where the reference pushes text, since text is outside this engine.
+``max_prefill_chunk_size`` has the reference's meaning and default (256).
+One iteration is ``Engine.step()``: the scheduler picks portions and decode
+tokens, the step function runs them as one batch, the sampler picks next tokens.
+"""
+from __future__ import annotations
+
+import json
+import os
+import queue
+import threading
+import time
+from dataclasses import dataclass, field
+from typing import Dict, Iterable, List, Optional, Sequence, Tuple
+
+import torch
+
+from ..cache.manager import CacheManager
+from ..config.base import ModelConfig
+from ..models.decoder import DecoderModel
+from ..sampling.params import SamplingParams
+from ..sampling.sampler import Sampler
+from .loading import load_model, parse_dtype, random_model
+from .request import GenerationRequest, RequestStatus
+from .runner import ModelRunner, StepEntry
+from .scheduler import Scheduler, SchedulerBatch
+
+
+@dataclass
+class StepOutput:
+    request_id: str
+    new_tokens: List[int]
+    is_finished: bool
+    finish_reason: Optional[str] = None
+
+
+class ResultQueue:
+    """Thread-safe queue of ``StepOutput`` (the reference's ResultQueue carries
+    {req_id, text, is_finished}, include/firefly/queue.h:11-57)."""
+
+    def __init__(self):
+        self._q: "queue.Queue[StepOutput]" = queue.Queue()
+
+    def push(self, item: StepOutput) -> None:
+        self._q.put(item)
+
+    def pop(self, timeout: Optional[float] = None) -> Optional[StepOutput]:
+        try:
+            return self._q.get(timeout=timeout)
+        except queue.Empty:
+            return None
+
+
+@dataclass
+class EngineOptions:
+    max_prefill_chunk_size: int = 256       # the reference's --max-prefill-chunk-size
+    max_batch_size_limit: int = 64          # most active requests (reference: 64)
+    max_num_batched_tokens: int = 8192      # tokens of one step, all requests together
+    kv_block_size: int = 16                 # tokens per cache page (reference: 16)
+    num_kv_blocks: Optional[int] = None     # pages per cache group; None: from memory_fraction
+    memory_fraction: float = 0.90           # of free device memory, for pages (reference: 0.90)
+    max_model_len: Optional[int] = None     # None: the model's max positions
+    eos_token_ids: Optional[Sequence[int]] = None   # None: config.json's eos_token_id, if any
+    use_cuda_graphs: bool = True
+    graph_batch_sizes: Sequence[int] = (1, 2, 4, 8, 16, 32, 64)   # reference: engine.h:72
+
+
+class Engine:
+    def __init__(self, model: DecoderModel, config: Optional[ModelConfig] = None,
+                 result_queue: Optional[ResultQueue] = None, max_prefill_chunk_size: int = 256,
+                 options: Optional[EngineOptions] = None, raw_config: Optional[dict] = None):
+        opts = options or EngineOptions()
+        if options is None:
+            opts.max_prefill_chunk_size = max_prefill_chunk_size
+        self.options = opts
+        self.model = model
+        self.config = config
+        self.result_queue = result_queue
+        self.device = model.rt.device
+        max_len = opts.max_model_len or model.spec.max_positions
+        max_len = min(max_len, model.spec.max_positions)
+        slot_specs = model.cache_slot_specs()
+        probe = CacheManager(slot_specs, block_size=opts.kv_block_size, num_blocks=0, max_requests=1)
+        per_block = max(1, probe.bytes_per_block(model.rt.dtype))
+        if opts.num_kv_blocks is not None:
+            num_blocks = opts.num_kv_blocks
+        else:
+            free, _ = torch.cuda.mem_get_info(self.device)
+            reserve = 4 << 30       # scratch memory of the largest step and the library's own
+            num_blocks = int(max(0, free - reserve) * opts.memory_fraction) // per_block
+            # no request can use more than max_model_len tokens
+            num_blocks = min(num_blocks, opts.max_batch_size_limit * (-(-max_len // opts.kv_block_size)))
+        if num_blocks < 1:
+            raise RuntimeError("no memory left for cache pages")
+        self.cache = CacheManager(slot_specs, block_size=opts.kv_block_size, num_blocks=num_blocks,
+                                  max_requests=opts.max_batch_size_limit)
+        self.cache.allocate_storage(model.rt.dtype, self.device)
+        self.max_model_len = min(max_len, num_blocks * opts.kv_block_size) \
+            if not all(g.spec.window is not None for g in self.cache.groups) or not self.cache.groups \
+            else max_len
+        self.runner = ModelRunner(model, self.cache, max_model_len=self.max_model_len,
+                                  max_batched_tokens=opts.max_num_batched_tokens,
+                                  max_seqs=opts.max_batch_size_limit)
+        eos = opts.eos_token_ids
+        if eos is None:
+            e = (raw_config or {}).get("eos_token_id")
+            eos = [] if e is None else ([int(x) for x in e] if isinstance(e, list) else [int(e)])
+        self.scheduler = Scheduler(self.cache, max_batch_size_limit=opts.max_batch_size_limit,
+                                   max_prefill_chunk_size=opts.max_prefill_chunk_size,
+                                   max_num_batched_tokens=opts.max_num_batched_tokens,
+                                   max_model_len=self.max_model_len, eos_token_ids=eos)
+        self.sampler = Sampler(self.device, opts.max_batch_size_limit)
+        self.graphs = None
+        if opts.use_cuda_graphs:
+            from .graphs import DecodeGraphs
+            self.graphs = DecodeGraphs(self.runner, opts.graph_batch_sizes)
+        self._inbox: "queue.Queue[GenerationRequest]" = queue.Queue()
+        self._thread: Optional[threading.Thread] = None
+        self._running = False
+        self.requests: Dict[str, GenerationRequest] = {}
+        self.stats = {"steps": 0, "graph_steps": 0, "tokens": 0, "preemptions": 0}
+
+    # ---- the reference's interface ----------------------------------------------
+    def async_generate(self, id: str, input_ids: Sequence[int], max_tokens: int = 512,
+                       sampling: Optional[SamplingParams] = None) -> None:
+        """Queue a request; thread-safe."""
+        sp = sampling or SamplingParams(max_tokens=max_tokens)
+        self._inbox.put(GenerationRequest(str(id), [int(t) for t in input_ids], sp))
+
+    def start(self) -> None:
+        if self._thread is not None:
+            return
+        self._running = True
+        self._thread = threading.Thread(target=self._loop, name="firefly-engine", daemon=True)
+        self._thread.start()
+
+    def stop(self) -> None:
+        self._running = False
+        if self._thread is not None:
+            self._thread.join()
+            self._thread = None
+
+    def _loop(self) -> None:
+        torch.cuda.set_device(self.device)
+        while self._running:
+            self._drain_inbox()
+            if not self.scheduler.has_unfinished_requests():
+                time.sleep(0.0005)
+                continue
+            for out in self.step():
+                if self.result_queue is not None:
+                    self.result_queue.push(out)
+
+    def _drain_inbox(self) -> None:
+        while True:
+            try:
+                req = self._inbox.get_nowait()
+            except queue.Empty:
+                return
+            try:
+                self.add_request(req)
+            except ValueError as e:
+                req.status = RequestStatus.FINISHED
+                req.finish_reason = f"error: {e}"
+                if self.result_queue is not None:
+                    self.result_queue.push(StepOutput(req.id, [], True, req.finish_reason))
+
+    # ---- synchronous core ----------------------------------------------------------
+    def add_request(self, req: GenerationRequest) -> None:
+        V = self.model.spec.vocab_size
+        if any(t < 0 or t >= V for t in req.prompt_tokens):
+            raise ValueError(f"request {req.id!r}: token id outside [0, {V})")
+        self.scheduler.add_request(req)
+        self.requests[req.id] = req
+
+    def has_unfinished_requests(self) -> bool:
+        return self.scheduler.has_unfinished_requests() or not self._inbox.empty()
+
+    def step(self) -> List[StepOutput]:
+        """One iteration: returns what each affected request produced."""
+        batch = self.scheduler.step()
+        outputs: List[StepOutput] = []
+        for req in batch.failed:
+            outputs.append(StepOutput(req.id, [], True, req.finish_reason))
+            self.requests.pop(req.id, None)
+        self.stats["preemptions"] += len(batch.preempted)
+        if not batch.items:
+            return outputs
+        sampling_items = [it for it in batch.items if it.samples]
+        entries = [StepEntry(it.request.cache,
+                             it.request.tokens_between(it.start, it.start + it.num_tokens),
+                             [it.num_tokens - 1] if it.samples else []) for it in batch.items]
+        params = [it.request.sampling for it in sampling_items]
+        counters = [len(it.request.generated_tokens) for it in sampling_items]
+        tokens = None
+        if (self.graphs is not None and len(sampling_items) == len(batch.items)
+                and all(it.num_tokens == 1 for it in batch.items)
+                and self.graphs.supports(len(entries))):
+            greedy = all(p.temperature <= 0 for p in params)
+            logits, tokens = self.graphs.run(entries, want_tokens=greedy)
+            self.stats["graph_steps"] += 1
+        else:
+            logits = self.runner.step(entries)
+        if tokens is None:
+            tokens = self.sampler.sample(logits, params, counters)
+        self.stats["steps"] += 1
+        self.stats["tokens"] += batch.num_tokens
+        for it, tok in zip(sampling_items, tokens):
+            done = self.scheduler.append_token(it.request, tok)
+            outputs.append(StepOutput(it.request.id, [int(tok)], done, it.request.finish_reason))
+            if done:
+                self.requests.pop(it.request.id, None)
+        return outputs
+
+
+class LLM:
+    """The Python entry point: ids in, ids out.
+
+        llm = LLM("/path/to/model", dtype="bfloat16")
+        outs = llm.generate([[1, 2, 3], [4, 5]], max_tokens=16)
+    """
+
+    def __init__(self, model, *, dtype="bfloat16", device="cuda:0", seed: int = 0,
+                 max_prefill_chunk_size: int = 256, **options):
+        """``model``: a folder with config.json and model.safetensors, or a typed
+        configuration (random weights drawn from ``seed``)."""
+        raw = None
+        if isinstance(model, (str, os.PathLike)):
+            self.model, self.config = load_model(str(model), dtype=dtype, device=device)
+            with open(os.path.join(str(model), "config.json")) as fh:
+                raw = json.load(fh)
+        elif isinstance(model, ModelConfig):
+            self.config = model
+            self.model = random_model(model, seed, dtype=dtype, device=device)
+        else:
+            raise TypeError("model must be a folder or a ModelConfig")
+        opts = EngineOptions(max_prefill_chunk_size=max_prefill_chunk_size, **options)
+        self.engine = Engine(self.model, self.config, options=opts, raw_config=raw)
+        self._next_id = 0
+
+    def generate(self, prompts: Sequence[Sequence[int]], max_tokens: int = 512, temperature: float = 0.0,
+                 seed: int = 0, ignore_eos: bool = False,
+                 sampling: Optional[Sequence[SamplingParams]] = None) -> List[List[int]]:
+        """Generate for every prompt (lists of token ids); returns the new token
+        ids of each, in order."""
+        reqs = []
+        for i, p in enumerate(prompts):
+            sp = sampling[i] if sampling is not None else SamplingParams(
+                temperature=temperature, seed=seed + i, max_tokens=max_tokens, ignore_eos=ignore_eos)
+            req = GenerationRequest(f"gen-{self._next_id}", [int(t) for t in p], sp)
+            self._next_id += 1
+            self.engine.add_request(req)
+            reqs.append(req)
+        while self.engine.scheduler.has_unfinished_requests():
+            self.engine.step()
+        self.engine.runner.check_status()
+        for r in reqs:
+            if r.finish_reason and r.finish_reason.startswith("error"):
+                raise RuntimeError(f"request {r.id}: {r.finish_reason}")
+        return [list(r.generated_tokens) for r in reqs]

@@ -1,0 +1,136 @@
+"""Decode steps replayed from CUDA graphs.
+
+A step in which every request decodes one token has the same launches whatever
+the requests are; only the integer metadata differs.  For each batch-size bucket
+(the reference's {1,2,4,8,16,32,64}, include/firefly/engine.h:72, captured in
+src/engine.cc:121-169) the model's forward and the arg-max are captured once
+over a static metadata buffer; a decode step then fills that buffer, uploads it
+with one copy and replays.  Unused lanes of a bucket decode a dummy token at
+position 0 into the reserved scratch page, so they never touch a live page.
+Unlike the reference, the block-table rows are bounded by the model length, not
+by the size of the whole pool, and nothing is allocated inside the capture.
+"""
+from __future__ import annotations
+
+from typing import Dict, List, Optional, Sequence, Tuple
+
+import numpy as np
+import torch
+
+from ..cache.manager import SCRATCH_PAGE
+from ..ops import kernels as K
+from .context import Workspace
+from .runner import MetaLayout, ModelRunner, StepEntry
+
+
+class _Bucket:
+    __slots__ = ("size", "layout", "meta_host", "meta_dev", "graph", "logits", "tokens", "h_tokens")
+
+
+class DecodeGraphs:
+    def __init__(self, runner: ModelRunner, batch_sizes: Sequence[int]):
+        self.runner = runner
+        self.sizes = sorted(set(int(b) for b in batch_sizes))
+        self.workspace = Workspace(runner.device)
+        self.buckets: Dict[int, _Bucket] = {}
+        self.replays = 0
+
+    def supports(self, n: int) -> bool:
+        return bool(self.sizes) and n <= self.sizes[-1]
+
+    def _bucket_for(self, n: int) -> _Bucket:
+        size = next(b for b in self.sizes if b >= n)
+        if size not in self.buckets:
+            # capture from the largest bucket down, so scratch buffers never grow afterwards
+            for s in reversed(self.sizes):
+                if s >= size and s not in self.buckets:
+                    self.buckets[s] = self._capture(s)
+        return self.buckets[size]
+
+    def _fill(self, b: _Bucket, entries: Sequence[StepEntry]) -> None:
+        r, lay = self.runner, b.layout
+        h = b.meta_host.numpy()
+        n = len(entries)
+        mb = r.max_blocks_per_seq
+        # padding lanes first (whole arrays), then the live lanes
+        h[lay.token_ids: lay.token_ids + b.size] = 0
+        h[lay.positions: lay.positions + b.size] = 0
+        h[lay.token_seq: lay.token_seq + b.size] = np.arange(b.size)
+        h[lay.cu_q: lay.cu_q + b.size + 1] = np.arange(b.size + 1)
+        h[lay.ctx_lens: lay.ctx_lens + b.size] = 0
+        h[lay.state_slots: lay.state_slots + b.size] = 0
+        h[lay.seq_fresh: lay.seq_fresh + b.size] = 0
+        h[lay.logits_rows: lay.logits_rows + b.size] = np.arange(b.size)
+        for off in lay.tables:
+            tab = h[off: off + b.size * mb].reshape(b.size, mb)
+            tab[n:, 0] = SCRATCH_PAGE
+            tab[n:, 1:] = -1
+        for i, e in enumerate(entries):
+            cl = e.cache.num_tokens
+            tok = int(e.tokens[0])
+            if not (0 <= tok < r.vocab_size):
+                raise ValueError(f"token id {tok} outside the vocabulary")
+            if cl + 1 > r.max_model_len:
+                raise ValueError(f"request {e.cache.request_id!r} exceeds max_model_len")
+            h[lay.token_ids + i] = tok
+            h[lay.positions + i] = cl
+            h[lay.ctx_lens + i] = cl
+            h[lay.state_slots + i] = e.cache.state_slot
+            h[lay.seq_fresh + i] = 1 if e.cache.fresh else 0
+            for g, table in enumerate(e.cache.tables):
+                row = lay.tables[g] + i * mb
+                h[row: row + len(table)] = table
+                h[row + len(table): row + mb] = -1
+
+    def _capture(self, size: int) -> _Bucket:
+        r = self.runner
+        b = _Bucket()
+        b.size = size
+        b.layout = MetaLayout(size, size, size, len(r.cache.groups), r.max_blocks_per_seq)
+        b.meta_host = torch.zeros(b.layout.size, dtype=torch.int32).pin_memory()
+        b.meta_dev = torch.zeros(b.layout.size, dtype=torch.int32, device=r.device)
+        b.tokens = torch.zeros(size, dtype=torch.int32, device=r.device)
+        b.h_tokens = torch.zeros(size, dtype=torch.int32).pin_memory()
+        self._fill(b, [])
+        b.meta_dev.copy_(b.meta_host)
+        ctx = r.context_from_layout(b.layout, b.meta_dev, [1] * size, [0] * size)
+        ctx.workspace = self.workspace
+        ctx.max_kv_len = r.max_model_len      # launch shapes must not depend on the requests
+        ctx.captured = True
+        self.workspace.frozen = False
+        side = torch.cuda.Stream(device=r.device)
+        side.wait_stream(torch.cuda.current_stream())
+        with torch.cuda.stream(side):
+            for _ in range(2):                # warm-up: library handles, lazy module loads
+                logits = r.model.forward(ctx)
+                K.sample(logits, b.tokens)
+        torch.cuda.current_stream().wait_stream(side)
+        torch.cuda.synchronize(r.device)
+        b.graph = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(b.graph):
+            b.logits = r.model.forward(ctx)
+            K.sample(b.logits, b.tokens)
+        self.workspace.frozen = True
+        return b
+
+    def run(self, entries: Sequence[StepEntry], want_tokens: bool = True
+            ) -> Tuple[torch.Tensor, Optional[List[int]]]:
+        """One decode step for ``entries`` (one token each).  Returns the logits
+        [n, vocab] (valid until the next replay of this bucket) and, when asked,
+        the arg-max tokens already copied to the host."""
+        n = len(entries)
+        b = self._bucket_for(n)
+        self._fill(b, entries)
+        b.meta_dev.copy_(b.meta_host, non_blocking=True)
+        b.graph.replay()
+        self.replays += 1
+        tokens = None
+        if want_tokens:
+            b.h_tokens[:n].copy_(b.tokens[:n], non_blocking=True)
+            torch.cuda.current_stream().synchronize()
+            tokens = b.h_tokens[:n].tolist()
+        for e in entries:
+            r_cache = e.cache
+            self.runner.cache.advance(r_cache, 1)
+        self.runner.steps_run += 1
+        return b.logits[:n], tokens

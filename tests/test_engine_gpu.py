@@ -1,0 +1,142 @@
+"""Generation through the Python entry point on the GPU, compared with the plain
+implementation: greedy tokens, scarcity of pages, captured graphs, sampling."""
+import numpy as np
+import pytest
+import torch
+
+import plain_qwen3 as P
+import replay_util as U
+
+pytestmark = pytest.mark.gpu
+
+
+@pytest.fixture(scope="module")
+def models(tmp_path_factory):
+    out = {}
+    for name, cfg, seed in (("A", P.TINY_A, 0), ("B", P.TINY_B, 1)):
+        w = P.random_weights(cfg, seed, dtype=torch.float32, scale=0.05)
+        path = str(tmp_path_factory.mktemp(f"gen{name}"))
+        U.write_model_dir(path, cfg, w, torch.float32)
+        out[name] = (path, cfg, w)
+    return out
+
+
+def _llm(path, **kw):
+    from firefly_b200 import LLM
+    return LLM(path, **kw)
+
+
+@pytest.mark.parametrize("name,block,chunk", [("A", 16, 256), ("B", 8, 17)])
+@pytest.mark.parametrize("graphs", [False, True])
+def test_greedy_generation_matches_plain(models, name, block, chunk, graphs):
+    path, cfg, w = models[name]
+    rng = np.random.RandomState(5)
+    prompts = [list(map(int, rng.randint(0, cfg["vocab_size"], size=n))) for n in (1, 2, 40, 23, 9)]
+    llm = _llm(path, dtype="float32", kv_block_size=block, max_prefill_chunk_size=chunk,
+               num_kv_blocks=64, use_cuda_graphs=graphs)
+    got = llm.generate(prompts, max_tokens=12)
+    for p, g in zip(prompts, got):
+        assert g == P.greedy_generate(cfg, w, p, 12)
+    if graphs:
+        assert llm.engine.stats["graph_steps"] > 0
+    llm.engine.cache.check()
+    assert not llm.engine.cache.live
+
+
+def test_few_pages_preempt_and_still_match(models):
+    path, cfg, w = models["B"]
+    rng = np.random.RandomState(7)
+    prompts = [list(map(int, rng.randint(0, cfg["vocab_size"], size=n))) for n in (30, 30, 21, 5)]
+    llm = _llm(path, dtype="float32", kv_block_size=8, num_kv_blocks=10, max_prefill_chunk_size=16)
+    got = llm.generate(prompts, max_tokens=14)
+    assert llm.engine.stats["preemptions"] > 0
+    for p, g in zip(prompts, got):
+        assert g == P.greedy_generate(cfg, w, p, 14)
+
+
+def test_long_decoding_and_first_tokens(models):
+    path, cfg, w = models["A"]
+    llm = _llm(path, dtype="float32", num_kv_blocks=16)
+    got = llm.generate([[7]], max_tokens=120)[0]          # from one token up to the model's length
+    assert len(got) == 120
+    assert got == P.greedy_generate(cfg, w, [7], 120)
+
+
+def test_bfloat16_generation_picks_a_top_token(models):
+    """bfloat16 may break a near tie the other way: every token it picks must be
+    within rounding of the plain implementation's best at that place."""
+    path, cfg, w = models["B"]
+    rng = np.random.RandomState(9)
+    prompts = [list(map(int, rng.randint(0, cfg["vocab_size"], size=n))) for n in (12, 33)]
+    got = _llm(path, dtype="bfloat16", kv_block_size=8, num_kv_blocks=64).generate(prompts, max_tokens=8)
+    for p, g in zip(prompts, got):
+        assert len(g) == 8
+        ids = list(p)
+        for t in g:
+            row = P.forward(cfg, w, ids)[-1]
+            assert float(row.max() - row[t]) <= U.TOL["bfloat16"] * float(row.abs().max())
+            ids.append(t)
+
+
+def test_temperature_sampling_is_seeded_and_follows_softmax(models):
+    path, cfg, w = models["A"]
+    llm = _llm(path, dtype="float32", num_kv_blocks=32)
+    a = llm.generate([[1, 2, 3]] * 2, max_tokens=10, temperature=0.8, seed=11)
+    b = llm.generate([[1, 2, 3]] * 2, max_tokens=10, temperature=0.8, seed=11)
+    c = llm.generate([[1, 2, 3]], max_tokens=10, temperature=0.8, seed=12)
+    assert a == b and a[0] != a[1] and c[0] == a[1]        # request i uses seed + i
+    # the kernel alone: frequencies follow softmax(logits / T)
+    from firefly_b200.ops import kernels as K
+    V, n, T = 37, 20000, 0.7
+    logits = torch.randn(V, device="cuda") * 2
+    rows = logits[None, :].expand(n, V).contiguous()
+    out = torch.empty(n, dtype=torch.int32, device="cuda")
+    temp = torch.full((n,), T, device="cuda")
+    seeds = torch.full((n,), 5, dtype=torch.int64, device="cuda")
+    counters = torch.arange(n, dtype=torch.int64, device="cuda")
+    K.sample(rows, out, temp, seeds, counters)
+    freq = torch.bincount(out.long(), minlength=V).double().cpu() / n
+    want = torch.softmax(logits.double().cpu() / T, dim=0)
+    assert float((freq - want).abs().max()) < 0.015
+    out2 = torch.empty_like(out)
+    K.sample(rows, out2, temp, seeds, counters)
+    assert torch.equal(out, out2)
+    K.sample(rows, out2)                                   # no temperature: arg-max
+    assert int(out2[0]) == int(torch.argmax(logits))
+
+
+def test_argmax_ties_go_to_lowest_index():
+    from firefly_b200.ops import kernels as K
+    V = 151936 + 5
+    x = torch.full((3, V), -1.0, device="cuda")
+    x[0, 70000] = 2.0
+    x[0, 150000] = 2.0
+    x[1, V - 1] = 3.0
+    x[2, :] = 0.5
+    out = torch.empty(3, dtype=torch.int32, device="cuda")
+    K.sample(x, out)
+    assert out.tolist() == [70000, V - 1, 0]
+
+
+def test_async_engine_interface(models):
+    path, cfg, w = models["A"]
+    from firefly_b200 import Engine, ResultQueue
+    from firefly_b200.engine import load_model
+    model, config = load_model(path, dtype="float32")
+    q = ResultQueue()
+    eng = Engine(model, config, q, max_prefill_chunk_size=8)
+    assert eng.options.max_prefill_chunk_size == 8
+    eng.start()
+    eng.async_generate("x", [3, 1, 4, 1, 5, 9, 2, 6, 5, 3, 5], 6)
+    eng.async_generate("y", [2, 7], 4)
+    toks = {"x": [], "y": []}
+    finished = set()
+    while len(finished) < 2:
+        out = q.pop(timeout=30)
+        assert out is not None
+        toks[out.request_id] += out.new_tokens
+        if out.is_finished:
+            finished.add(out.request_id)
+    eng.stop()
+    assert toks["x"] == P.greedy_generate(cfg, w, [3, 1, 4, 1, 5, 9, 2, 6, 5, 3, 5], 6)
+    assert toks["y"] == P.greedy_generate(cfg, w, [2, 7], 4)
