@@ -1,0 +1,331 @@
+#!/usr/bin/env python3
+"""Benchmark of firefly_b200 on one B200: decode tokens per second of a
+Qwen3-8B-shaped model (random weights, synthetic token ids), plus prefill
+throughput, the decode step's memory roofline and batch-1 / batch-64 points.
+
+    python bench.py [--gpus 1] [--steps K] [--warmup W] [--batch 8] [--layers N] [--impl ours|reference]
+
+One JSON line is printed.  ``value`` is device-timed (CUDA events around K
+decode steps that run back to back from CUDA graphs, the sampled tokens fed to
+the next step on the device); ``e2e`` is the same K steps through the Python
+entry point's engine loop, with token ids going host -> device and sampled
+tokens device -> host every step.  The decode step streams ~15 GB of weights, far
+more than the 126 MB L2, so no extra flush is needed between timed iterations.
+"""
+from __future__ import annotations
+
+import argparse
+import json
+import os
+import statistics
+import subprocess
+import sys
+import tempfile
+import time
+
+ROOT = os.path.dirname(os.path.abspath(__file__))
+if ROOT not in sys.path:
+    sys.path.insert(0, ROOT)
+
+FALLBACK_PEAKS = {"hbm_gbs": 6650.0, "bf16_tflops": 1590.0, "bf16_tflops_sustained": 1400.0}
+
+
+def load_shape():
+    """Layer sizes of BASELINE.json's configs[2] (Qwen3-8B-shaped), as config.json keys."""
+    return dict(architectures=["Qwen3ForCausalLM"], hidden_size=4096, intermediate_size=12288,
+                num_hidden_layers=36, num_attention_heads=32, num_key_value_heads=8, head_dim=128,
+                vocab_size=151936, max_position_embeddings=4096, rms_norm_eps=1e-6, rope_theta=1e6,
+                tie_word_embeddings=False)
+
+
+def peaks():
+    path = os.path.join(ROOT, "MEASURED_PEAKS.json")
+    if os.path.isfile(path):
+        try:
+            with open(path) as fh:
+                raw = json.load(fh)
+            out = dict(FALLBACK_PEAKS)
+            for k in out:
+                if isinstance(raw.get(k), (int, float)):
+                    out[k] = float(raw[k])
+            out["source"] = "measured"
+            return out
+        except Exception:  # noqa: BLE001
+            pass
+    out = dict(FALLBACK_PEAKS)
+    out["source"] = "fallback"
+    return out
+
+
+class ClockSampler:
+    QUERY = ("index,clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.active,"
+             "clocks_event_reasons.hw_slowdown,clocks_event_reasons.hw_thermal_slowdown,"
+             "clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap")
+
+    def __init__(self):
+        self.proc = None
+        self.path = None
+
+    def start(self):
+        try:
+            fd, self.path = tempfile.mkstemp(suffix=".csv")
+            os.close(fd)
+            self.fh = open(self.path, "w")
+            self.proc = subprocess.Popen(["nvidia-smi", f"--query-gpu={self.QUERY}", "--format=csv,noheader,nounits",
+                                          "-i", "0", "-lms", "200"], stdout=self.fh, stderr=subprocess.DEVNULL)
+        except Exception:  # noqa: BLE001
+            self.proc = None
+
+    def stop(self):
+        if self.proc is None:
+            return None
+        self.proc.terminate()
+        try:
+            self.proc.wait(timeout=5)
+        except Exception:  # noqa: BLE001
+            self.proc.kill()
+        self.fh.close()
+        sm, mx, reasons = [], [], set()
+        names = ["hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"]
+        with open(self.path) as fh:
+            for line in fh:
+                parts = [p.strip() for p in line.split(",")]
+                if len(parts) < 9:
+                    continue
+                try:
+                    sm.append(float(parts[1]))
+                    mx.append(float(parts[2]))
+                except ValueError:
+                    continue
+                for name, val in zip(names, parts[5:9]):
+                    if val.lower().startswith("active"):
+                        reasons.add(name)
+        os.unlink(self.path)
+        if not sm:
+            return None
+        return {"sm_mhz": statistics.median(sm), "sm_max_mhz": max(mx), "reasons": sorted(reasons),
+                "samples": len(sm)}
+
+
+def reference_arm():
+    # The reference is a CMake/C++/CUDA server with no Python package: there is nothing pip can
+    # install from it, its build fetches CUTLASS/mdspan/json/googletest over the network and needs
+    # gRPC, and it has no sm_100 kernels.
+    print(json.dumps({"impl": "reference",
+                      "unavailable": "gallnut/firefly is a C++/CMake gRPC server without a Python package "
+                                     "(pip install finds no setup.py/pyproject.toml); its build needs network "
+                                     "fetches (CPM: CUTLASS, mdspan, json) and gRPC, none available offline"}))
+    return 0
+
+
+def main() -> int:
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=96)
+    ap.add_argument("--warmup", type=int, default=8)
+    ap.add_argument("--batch", type=int, default=8)
+    ap.add_argument("--layers", type=int, default=None, help="fewer layers than the configuration (named in config)")
+    ap.add_argument("--prompt-len", type=int, default=2048)
+    ap.add_argument("--context", type=int, default=4096)
+    ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
+    ap.add_argument("--no-points", action="store_true", help="skip the batch-1 and batch-64 points")
+    ap.add_argument("--dtype", default="bfloat16", choices=["bfloat16", "float32"])
+    args = ap.parse_args()
+    if args.impl == "reference":
+        return reference_arm()
+    if args.gpus != 1:
+        print(f"bench.py: this engine runs on one GPU; --gpus {args.gpus} is not supported")
+        return 2
+    if args.warmup < 3:
+        args.warmup = 3
+
+    import torch
+    from firefly_b200.engine.engine import Engine, EngineOptions
+    from firefly_b200.engine.loading import random_model
+    from firefly_b200.engine.request import GenerationRequest
+    from firefly_b200.engine.runner import StepEntry
+    from firefly_b200.models import config_from_dict
+    from firefly_b200.ops import kernels as K
+    from firefly_b200.sampling import SamplingParams
+
+    shape = load_shape()
+    full_layers = shape["num_hidden_layers"]
+    if args.layers:
+        shape["num_hidden_layers"] = args.layers
+    cfg = config_from_dict(shape)
+    dev = torch.device("cuda:0")
+    torch.cuda.set_device(dev)
+    pk = peaks()
+    es = 2 if args.dtype == "bfloat16" else 4
+
+    t0 = time.time()
+    model = random_model(cfg, seed=0, dtype=args.dtype, device=dev)
+    torch.cuda.synchronize()
+    build_s = time.time() - t0
+
+    L, H, I, V = cfg.num_hidden_layers, cfg.hidden_size, cfg.intermediate_size, cfg.vocab_size
+    nq, nkv, d = cfg.num_attention_heads, cfg.num_key_value_heads, cfg.head_dim
+    layer_params = (nq + 2 * nkv) * d * H + nq * d * H + 3 * H * I
+    weight_bytes = (L * layer_params + V * H) * es + (2 * L + 1) * H * 4
+    kv_bytes_per_token = L * 2 * nkv * d * es
+    P = args.prompt_len
+    K_steps, W = args.steps, args.warmup
+    need_new = 1 + W + 2 * K_steps + 2
+    if P + need_new > args.context:
+        print(f"bench.py: {P} prompt + {need_new} decode tokens exceed the context {args.context}")
+        return 2
+    gen = torch.Generator().manual_seed(1234)
+
+    def make_engine(B):
+        opts = EngineOptions(max_prefill_chunk_size=P, max_batch_size_limit=max(B, 1),
+                             max_num_batched_tokens=max(P, B), kv_block_size=16,
+                             num_kv_blocks=B * (-(-args.context // 16)), max_model_len=args.context,
+                             eos_token_ids=[], graph_batch_sizes=(1, 2, 4, 8, 16, 32, 64))
+        return Engine(model, cfg, options=opts)
+
+    def start_requests(eng, B):
+        reqs = []
+        for i in range(B):
+            ids = torch.randint(0, V, (P,), generator=gen).tolist()
+            r = GenerationRequest(f"b{i}", ids, SamplingParams(max_tokens=max(256, need_new), ignore_eos=True))
+            eng.add_request(r)
+            reqs.append(r)
+        while any(len(r.generated_tokens) == 0 for r in reqs):   # prompts in, first token sampled
+            eng.step()
+        return reqs
+
+    def device_timed_decode(eng, reqs, steps):
+        """``steps`` decode steps back to back on the device.  Returns (ms, own kernel launches)."""
+        g = eng.graphs
+        n = len(reqs)
+        b = g._bucket_for(n)
+        lay = b.layout
+        for r in reqs:
+            assert eng.cache.grow(r.cache, r.cache.num_tokens + steps + 1)
+        entries = [StepEntry(r.cache, [r.generated_tokens[-1]], [0]) for r in reqs]
+        staged_h = torch.empty((steps, lay.size), dtype=torch.int32).pin_memory()
+        base = [r.cache.num_tokens for r in reqs]
+        for s in range(steps):
+            for r, c in zip(reqs, base):
+                r.cache.num_tokens = c + s          # positions of this step
+            g._fill(b, entries)
+            staged_h[s].copy_(b.meta_host)
+        for r, c in zip(reqs, base):
+            r.cache.num_tokens = c
+        staged = staged_h.to(dev, non_blocking=True)
+        toks = torch.empty((steps, n), dtype=torch.int32, device=dev)
+        ev0, ev1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        torch.cuda.synchronize()
+        ev0.record()
+        for s in range(steps):
+            b.meta_dev.copy_(staged[s], non_blocking=True)
+            if s:
+                b.meta_dev[lay.token_ids: lay.token_ids + n].copy_(toks[s - 1], non_blocking=True)
+            b.graph.replay()
+            toks[s].copy_(b.tokens[:n], non_blocking=True)
+        ev1.record()
+        torch.cuda.synchronize()
+        ms = ev0.elapsed_time(ev1)
+        host = toks.cpu().tolist()
+        for s in range(steps):                      # keep the engine's books right
+            for r, t in zip(reqs, host[s]):
+                eng.cache.advance(r.cache, 1)
+                eng.scheduler.append_token(r, t)
+        return ms, steps * b.launches
+
+    def e2e_decode(eng, reqs, steps):
+        n = len(reqs)
+        b = eng.graphs._bucket_for(n)
+        torch.cuda.synchronize()
+        t = time.perf_counter()
+        for _ in range(steps):
+            outs = eng.step()
+            assert len(outs) == n
+        torch.cuda.synchronize()
+        dt = time.perf_counter() - t
+        return dt, b.layout.size * 4, n * 4
+
+    def decode_point(B, steps, with_e2e):
+        eng = make_engine(B)
+        reqs = start_requests(eng, B)
+        for _ in range(W):
+            eng.step()
+        assert eng.stats["graph_steps"] >= W, "decode did not run from CUDA graphs"
+        ctx0 = reqs[0].cache.num_tokens
+        ms, launches = device_timed_decode(eng, reqs, steps)
+        res = {"B": B, "ms_per_step": ms / steps, "tok_s": B * steps / (ms / 1e3), "launches": launches,
+               "ctx_mean": ctx0 + steps / 2}
+        if with_e2e:
+            dt, h2d, d2h = e2e_decode(eng, reqs, steps)
+            res["e2e"] = {"value": B * steps / dt, "unit": "tok/s", "h2d_bytes_per_step": h2d,
+                          "d2h_bytes_per_step": d2h}
+        eng.runner.check_status()
+        del eng
+        torch.cuda.empty_cache()
+        return res
+
+    def prefill_point():
+        eng = make_engine(1)
+        times = []
+        for it in range(3 + 5):
+            ids = torch.randint(0, V, (P,), generator=gen).tolist()
+            rc = eng.cache.admit(f"p{it}")
+            assert eng.cache.grow(rc, P)
+            ev0, ev1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            torch.cuda.synchronize()
+            ev0.record()
+            eng.runner.step([StepEntry(rc, ids, [P - 1])])
+            ev1.record()
+            torch.cuda.synchronize()
+            if it >= 3:
+                times.append(ev0.elapsed_time(ev1))
+            eng.cache.free(rc)
+        eng.runner.check_status()
+        del eng
+        torch.cuda.empty_cache()
+        ms = statistics.median(times)
+        flops = 2.0 * P * L * layer_params + 2.0 * V * H + L * 4.0 * nq * d * (P * (P + 1) / 2)
+        return {"value": P / (ms / 1e3), "tokens": P, "ms": ms,
+                "frac": flops / (ms / 1e3) / (pk["bf16_tflops_sustained" if False else "bf16_tflops"] * 1e12),
+                "tflops": flops / (ms / 1e3) / 1e12}
+
+    clocks = ClockSampler()
+    clocks.start()
+    main_res = decode_point(args.batch, K_steps, with_e2e=True)
+    clock_info = clocks.stop()
+    prefill = prefill_point()
+    points = {}
+    if not args.no_points:
+        for B in (1, 64):
+            r = decode_point(B, min(K_steps, 64), with_e2e=False)
+            points[f"decode_b{B}"] = r["tok_s"]
+            points[f"decode_b{B}_ms_per_step"] = r["ms_per_step"]
+
+    step_bytes = weight_bytes + args.batch * main_res["ctx_mean"] * kv_bytes_per_token
+    achieved = step_bytes / (main_res["ms_per_step"] / 1e3) / 1e9
+    out = {
+        "metric": "decode tok/s at batch 8 (Qwen3-8B-shaped bf16, 2048-token prompts)",
+        "value": main_res["tok_s"], "unit": "tok/s", "n_gpus": 1, "steps": K_steps, "warmup": W,
+        "ms_per_step": main_res["ms_per_step"], "higher_is_better": True, "scaling": "weak",
+        "vs_baseline": None, "dtype": "bf16" if args.dtype == "bfloat16" else "fp32", "data": "synthetic",
+        "impl": "ours",
+        "config": {"model": "Qwen3-8B-shaped random weights", "global_batch": args.batch, "seq_len": args.context,
+                   "parallelism": "single GPU", "layers": L, "layers_of_config": full_layers, "hidden": H,
+                   "q_heads": nq, "kv_heads": nkv, "head_dim": d, "intermediate": I, "vocab": V,
+                   "prompt_len": P, "new_tokens": need_new, "kv_block": 16, "cuda_graphs": True,
+                   "l2": "inputs>L2: each step streams all weights (>15 GB)",
+                   "peaks": pk["source"], "model_build_s": round(build_s, 1)},
+        "clocks": clock_info,
+        "e2e": main_res["e2e"],
+        "gpu_launches": main_res["launches"],
+        "prefill": prefill,
+        "roofline": {"bound": "hbm", "achieved": achieved, "peak": pk["hbm_gbs"], "unit": "GB/s",
+                     "frac": achieved / pk["hbm_gbs"]},
+        "points": points,
+    }
+    print(json.dumps(out))
+    return 0
+
+
+if __name__ == "__main__":
+    sys.exit(main())

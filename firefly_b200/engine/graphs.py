@@ -24,7 +24,7 @@ from .runner import MetaLayout, ModelRunner, StepEntry
 
 
 class _Bucket:
-    __slots__ = ("size", "layout", "meta_host", "meta_dev", "graph", "logits", "tokens", "h_tokens")
+    __slots__ = ("size", "layout", "meta_host", "meta_dev", "graph", "logits", "tokens", "h_tokens", "launches")
 
 
 class DecodeGraphs:
@@ -34,6 +34,7 @@ class DecodeGraphs:
         self.workspace = Workspace(runner.device)
         self.buckets: Dict[int, _Bucket] = {}
         self.replays = 0
+        self.kernel_launches = 0
 
     def supports(self, n: int) -> bool:
         return bool(self.sizes) and n <= self.sizes[-1]
@@ -107,9 +108,11 @@ class DecodeGraphs:
         torch.cuda.current_stream().wait_stream(side)
         torch.cuda.synchronize(r.device)
         b.graph = torch.cuda.CUDAGraph()
+        before = K.LAUNCHES
         with torch.cuda.graph(b.graph):
             b.logits = r.model.forward(ctx)
             K.sample(b.logits, b.tokens)
+        b.launches = K.LAUNCHES - before      # own kernels in one replay
         self.workspace.frozen = True
         return b
 
@@ -124,6 +127,7 @@ class DecodeGraphs:
         b.meta_dev.copy_(b.meta_host, non_blocking=True)
         b.graph.replay()
         self.replays += 1
+        self.kernel_launches += b.launches
         tokens = None
         if want_tokens:
             b.h_tokens[:n].copy_(b.tokens[:n], non_blocking=True)

@@ -47,8 +47,13 @@ def _need_cuda(*tensors: Optional[torch.Tensor]) -> None:
                 raise KernelError("kernel operand must be contiguous")
 
 
+LAUNCHES = 0   # launches of this package's own kernels (library products are not counted)
+
+
 def _check(code: int, what: str) -> None:
+    global LAUNCHES
     if code == 0:
+        LAUNCHES += 1
         return
     if code == -1:
         raise KernelError(f"{what}: bad argument")
