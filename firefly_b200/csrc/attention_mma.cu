@@ -1,0 +1,508 @@
+// Tensor-core attention over the paged cache for bfloat16: a tiled kernel for
+// portions of prompts (and any mix of sequences), a split-KV kernel for steps in
+// which every sequence decodes one token, and the kernel that joins the splits.
+//
+// Both kernels pack the query heads of one kv head into the rows of a tile
+// (row = token * G + head-in-group, G = num_heads / num_kv_heads), so a key or
+// value is fetched once for the whole group; the reference's decode kernel re-reads
+// it per q head (src/kernels/attention.cu:291-447) and its prefill kernel works on
+// the portion's own k and v instead of the cache (src/model/qwen_model.cu:147-151).
+// Scores, running max and sum, and the output accumulator are 32-bit; q.k and p.v
+// run on mma.sync m16n8k16 with bfloat16 operands.  Keys come from the pages by
+// absolute position: a query at position p sees keys max(0, p-W+1)..p.
+//
+// Compiled once per head size: -DFF_HEAD_DIM=<multiple of 16, up to 256>.
+// Cache layout of a slot: [num_blocks][2 (k,v)][n_kv_heads][block_size][head_dim].
+#include "common.cuh"
+#include <math_constants.h>
+
+#ifndef FF_HEAD_DIM
+#define FF_HEAD_DIM 128
+#endif
+
+namespace ff {
+
+constexpr int D = FF_HEAD_DIM;
+static_assert(D % 16 == 0 && D >= 16 && D <= 256, "head size must be a multiple of 16, at most 256");
+constexpr int KSTR = D + 8;            // padded row: ldmatrix rows fall in distinct banks
+constexpr int BN = 64;                 // keys per tile
+constexpr int BM = 64;                 // rows per tile of the tiled kernel (4 warps x 16)
+constexpr int NTHREADS = 128;
+constexpr int CHUNKS = D / 8;          // 16-byte pieces per row
+constexpr float LOG2E = 1.4426950408889634f;
+
+__device__ __forceinline__ uint32_t smem_u32(const void* p) {
+    return (uint32_t)__cvta_generic_to_shared(p);
+}
+__device__ __forceinline__ void cp_async16(void* dst, const void* src, bool valid) {
+    const int n = valid ? 16 : 0;      // n = 0: the 16 bytes are zero-filled
+    asm volatile("cp.async.cg.shared.global [%0], [%1], 16, %2;\n" ::"r"(smem_u32(dst)), "l"(src), "r"(n));
+}
+__device__ __forceinline__ void cp_async_commit() { asm volatile("cp.async.commit_group;\n" ::); }
+template <int N> __device__ __forceinline__ void cp_async_wait() {
+    asm volatile("cp.async.wait_group %0;\n" ::"n"(N));
+}
+__device__ __forceinline__ void ldsm_x4(uint32_t (&r)[4], const void* p) {
+    asm volatile("ldmatrix.sync.aligned.m8n8.x4.shared.b16 {%0,%1,%2,%3}, [%4];\n"
+                 : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]) : "r"(smem_u32(p)));
+}
+__device__ __forceinline__ void ldsm_x4_t(uint32_t (&r)[4], const void* p) {
+    asm volatile("ldmatrix.sync.aligned.m8n8.x4.trans.shared.b16 {%0,%1,%2,%3}, [%4];\n"
+                 : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]) : "r"(smem_u32(p)));
+}
+__device__ __forceinline__ void mma_bf16(float (&c)[4], const uint32_t (&a)[4], uint32_t b0, uint32_t b1) {
+    asm volatile("mma.sync.aligned.m16n8k16.row.col.f32.bf16.bf16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};\n"
+                 : "+f"(c[0]), "+f"(c[1]), "+f"(c[2]), "+f"(c[3])
+                 : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b0), "r"(b1));
+}
+__device__ __forceinline__ uint32_t pack_bf16(float lo, float hi) {
+    __nv_bfloat162 v = __floats2bfloat162_rn(lo, hi);
+    return *reinterpret_cast<uint32_t*>(&v);
+}
+
+// Copy keys [key0, key0+BN) of one kv head into smem tiles (K and V), zero-filling
+// keys outside [kv_lo, kv_hi) and keys whose page is missing.
+__device__ __forceinline__ void load_kv_tile(bf16* Ks, bf16* Vs, const bf16* __restrict__ cache,
+                                             const int* __restrict__ bt, int max_blocks, int num_blocks,
+                                             int nkv, int kh, int block_size, int key0, int kv_lo, int kv_hi) {
+    for (int c = threadIdx.x; c < BN * CHUNKS; c += NTHREADS) {
+        const int row = c / CHUNKS, ch = c % CHUNKS;
+        const int key = key0 + row;
+        bool ok = key >= kv_lo && key < kv_hi;
+        const bf16* ksrc = cache;
+        const bf16* vsrc = cache;
+        if (ok) {
+            const int pi = key / block_size;
+            const int page = pi < max_blocks ? bt[pi] : -1;
+            ok = page >= 0 && page < num_blocks;
+            if (ok) {
+                ksrc = cache + ((((size_t)page * 2) * nkv + kh) * block_size + key % block_size) * D + ch * 8;
+                vsrc = ksrc + (size_t)nkv * block_size * D;
+            }
+        }
+        cp_async16(Ks + row * KSTR + ch * 8, ksrc, ok);
+        cp_async16(Vs + row * KSTR + ch * 8, vsrc, ok);
+    }
+}
+
+// One warp's attention state for 16 rows: running max / sum and the output tile.
+// `KN` keys of each tile belong to this warp.
+template <int KN>
+struct WarpState {
+    float o[D / 8][4];
+    float m[2], l[2];
+
+    __device__ __forceinline__ void init() {
+#pragma unroll
+        for (int i = 0; i < D / 8; ++i) { o[i][0] = o[i][1] = o[i][2] = o[i][3] = 0.f; }
+        m[0] = m[1] = -CUDART_INF_F;
+        l[0] = l[1] = 0.f;
+    }
+
+    // Qs: this warp's 16 rows of q in smem ([16][KSTR]); Ks/Vs: this warp's KN keys.
+    // key0: absolute index of the warp's first key.  Row r of the fragment (g, g+8)
+    // sees keys in [lo[r], hi[r]); scores are multiplied by scale_log2 (= scale*log2 e).
+    __device__ __forceinline__ void step(const bf16* Qs, const bf16* Ks, const bf16* Vs, int key0,
+                                         const int (&lo)[2], const int (&hi)[2], float scale_log2,
+                                         bool need_mask) {
+        const int lane = threadIdx.x & 31;
+        float s[KN / 8][4];
+#pragma unroll
+        for (int j = 0; j < KN / 8; ++j) { s[j][0] = s[j][1] = s[j][2] = s[j][3] = 0.f; }
+        // S = Q K^T
+#pragma unroll
+        for (int kk = 0; kk < D / 16; ++kk) {
+            uint32_t a[4];
+            ldsm_x4(a, Qs + ((lane & 7) + 8 * ((lane >> 3) & 1)) * KSTR + kk * 16 + 8 * (lane >> 4));
+#pragma unroll
+            for (int jj = 0; jj < KN / 16; ++jj) {
+                uint32_t b[4];
+                ldsm_x4(b, Ks + (jj * 16 + (lane & 7) + 8 * (lane >> 4)) * KSTR + kk * 16 + 8 * ((lane >> 3) & 1));
+                mma_bf16(s[2 * jj], a, b[0], b[1]);
+                mma_bf16(s[2 * jj + 1], a, b[2], b[3]);
+            }
+        }
+        // scale, mask, running max
+        const int t4 = lane & 3;
+        float mx[2] = {-CUDART_INF_F, -CUDART_INF_F};
+#pragma unroll
+        for (int j = 0; j < KN / 8; ++j) {
+#pragma unroll
+            for (int e = 0; e < 4; ++e) {
+                const int r = e >> 1;
+                float v = s[j][e] * scale_log2;
+                if (need_mask) {
+                    const int key = key0 + j * 8 + 2 * t4 + (e & 1);
+                    if (key < lo[r] || key >= hi[r]) v = -CUDART_INF_F;
+                }
+                s[j][e] = v;
+                mx[r] = fmaxf(mx[r], v);
+            }
+        }
+        float corr[2], msafe[2];
+#pragma unroll
+        for (int r = 0; r < 2; ++r) {
+            mx[r] = fmaxf(mx[r], __shfl_xor_sync(0xffffffffu, mx[r], 1));
+            mx[r] = fmaxf(mx[r], __shfl_xor_sync(0xffffffffu, mx[r], 2));
+            const float m_new = fmaxf(m[r], mx[r]);
+            msafe[r] = m_new == -CUDART_INF_F ? 0.f : m_new;
+            corr[r] = exp2f(m[r] - msafe[r]);      // m = -inf: 0
+            m[r] = m_new;
+            l[r] *= corr[r];
+        }
+#pragma unroll
+        for (int i = 0; i < D / 8; ++i) {
+            o[i][0] *= corr[0]; o[i][1] *= corr[0];
+            o[i][2] *= corr[1]; o[i][3] *= corr[1];
+        }
+        // P = exp2(S - m), row sums (per thread; joined over the quad at the end)
+#pragma unroll
+        for (int j = 0; j < KN / 8; ++j) {
+#pragma unroll
+            for (int e = 0; e < 4; ++e) {
+                const int r = e >> 1;
+                const float p = exp2f(s[j][e] - msafe[r]);
+                s[j][e] = p;
+                l[r] += p;
+            }
+        }
+        // O += P V
+#pragma unroll
+        for (int kk = 0; kk < KN / 16; ++kk) {
+            uint32_t a[4];
+            a[0] = pack_bf16(s[2 * kk][0], s[2 * kk][1]);
+            a[1] = pack_bf16(s[2 * kk][2], s[2 * kk][3]);
+            a[2] = pack_bf16(s[2 * kk + 1][0], s[2 * kk + 1][1]);
+            a[3] = pack_bf16(s[2 * kk + 1][2], s[2 * kk + 1][3]);
+#pragma unroll
+            for (int nn = 0; nn < D / 16; ++nn) {
+                uint32_t b[4];
+                ldsm_x4_t(b, Vs + (kk * 16 + (lane & 7) + 8 * ((lane >> 3) & 1)) * KSTR + nn * 16 + 8 * (lane >> 4));
+                mma_bf16(o[2 * nn], a, b[0], b[1]);
+                mma_bf16(o[2 * nn + 1], a, b[2], b[3]);
+            }
+        }
+    }
+
+    __device__ __forceinline__ void finish_sums() {
+#pragma unroll
+        for (int r = 0; r < 2; ++r) {
+            l[r] += __shfl_xor_sync(0xffffffffu, l[r], 1);
+            l[r] += __shfl_xor_sync(0xffffffffu, l[r], 2);
+        }
+    }
+};
+
+// ------------------------------------------------------------------ tiled kernel --
+// grid.x: tiles of BM rows over all sequences (row = token*G + head in group),
+// grid.y: kv heads.  Tile -> sequence by a scan of the per-sequence tile counts.
+__global__ void __launch_bounds__(NTHREADS)
+attn_tiled_kernel(const bf16* __restrict__ q, int q_stride, const bf16* __restrict__ cache,
+                  const int* __restrict__ block_table, int max_blocks, const int* __restrict__ cu_q,
+                  const int* __restrict__ ctx_lens, int n_seqs, bf16* __restrict__ out, int out_stride,
+                  int nq, int nkv, int block_size, int num_blocks, float scale_log2, int window) {
+    extern __shared__ __align__(16) unsigned char smem_raw[];
+    bf16* Qs = reinterpret_cast<bf16*>(smem_raw);                 // [BM][KSTR]
+    bf16* Ks = Qs + BM * KSTR;                                    // [2][BN][KSTR]
+    bf16* Vs = Ks + 2 * BN * KSTR;                                // [2][BN][KSTR]
+    __shared__ int s_seq, s_tile;
+    const int G = nq / nkv;
+    const int kh = blockIdx.y;
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+
+    if (warp == 0) {   // which sequence owns tile blockIdx.x
+        int base = 0, found_seq = -1, found_tile = 0;
+        for (int s0 = 0; s0 < n_seqs && found_seq < 0; s0 += 32) {
+            const int s = s0 + lane;
+            const int cnt = s < n_seqs ? ((cu_q[s + 1] - cu_q[s]) * G + BM - 1) / BM : 0;
+            int incl = cnt;
+#pragma unroll
+            for (int o = 1; o < 32; o <<= 1) {
+                const int v = __shfl_up_sync(0xffffffffu, incl, o);
+                if (lane >= o) incl += v;
+            }
+            const int total = __shfl_sync(0xffffffffu, incl, 31);
+            const unsigned hit = __ballot_sync(0xffffffffu, base + incl > (int)blockIdx.x);
+            if (hit) {
+                const int l0 = __ffs(hit) - 1;
+                found_seq = s0 + l0;
+                const int incl0 = __shfl_sync(0xffffffffu, incl, l0);
+                const int cnt0 = __shfl_sync(0xffffffffu, cnt, l0);
+                found_tile = (int)blockIdx.x - (base + incl0 - cnt0);
+            }
+            base += total;
+        }
+        if (lane == 0) { s_seq = found_seq; s_tile = found_tile; }
+    }
+    __syncthreads();
+    const int seq = s_seq, tile = s_tile;
+    if (seq < 0) return;
+    const int tok0 = cu_q[seq], q_len = cu_q[seq + 1] - tok0, ctx = ctx_lens[seq];
+    const int rows = q_len * G;
+    const int row0 = tile * BM;
+    const int* bt = block_table + (size_t)seq * max_blocks;
+
+    // q tile -> smem
+    for (int c = threadIdx.x; c < BM * CHUNKS; c += NTHREADS) {
+        const int r = c / CHUNKS, ch = c % CHUNKS;
+        const int rg = row0 + r;
+        const bool ok = rg < rows;
+        const bf16* src = q;
+        if (ok) src = q + (size_t)(tok0 + rg / G) * q_stride + (size_t)(kh * G + rg % G) * D + ch * 8;
+        cp_async16(Qs + r * KSTR + ch * 8, src, ok);
+    }
+    // visible keys of the tile
+    const int first_tok = row0 / G;
+    const int last_tok = min(q_len - 1, (row0 + BM - 1) / G);
+    const int kv_hi = ctx + last_tok + 1;
+    const int kv_lo = window > 0 ? max(0, ctx + first_tok - window + 1) : 0;
+    const int t_begin = kv_lo / BN, t_end = (kv_hi + BN - 1) / BN;
+
+    load_kv_tile(Ks, Vs, cache, bt, max_blocks, num_blocks, nkv, kh, block_size, t_begin * BN, kv_lo, kv_hi);
+    cp_async_commit();
+
+    // this thread's two rows
+    const int g = lane >> 2;
+    int lo[2], hi[2];
+#pragma unroll
+    for (int r = 0; r < 2; ++r) {
+        const int rg = row0 + warp * 16 + g + 8 * r;
+        const int pos = ctx + min(rg, rows - 1) / G;
+        hi[r] = pos + 1;
+        lo[r] = window > 0 ? max(0, pos - window + 1) : 0;
+    }
+    const bool warp_active = row0 + warp * 16 < rows;
+    // keys below this are visible to every row of the warp, keys at or above need the mask
+    const int warp_first_pos = ctx + min(row0 + warp * 16, rows - 1) / G;
+    const int warp_last_pos = ctx + min(row0 + warp * 16 + 15, rows - 1) / G;
+    const int full_lo = window > 0 ? max(0, warp_last_pos - window + 1) : 0;
+    const int warp_lo = window > 0 ? max(0, warp_first_pos - window + 1) : 0;   // first key any row sees
+
+    WarpState<BN> st;
+    st.init();
+    for (int t = t_begin; t < t_end; ++t) {
+        const int buf = (t - t_begin) & 1;
+        if (t + 1 < t_end) {
+            load_kv_tile(Ks + (buf ^ 1) * BN * KSTR, Vs + (buf ^ 1) * BN * KSTR, cache, bt, max_blocks,
+                         num_blocks, nkv, kh, block_size, (t + 1) * BN, kv_lo, kv_hi);
+            cp_async_commit();
+            cp_async_wait<1>();
+        } else {
+            cp_async_wait<0>();
+        }
+        __syncthreads();
+        const int key0 = t * BN;
+        if (warp_active && key0 <= warp_last_pos && key0 + BN > warp_lo) {   // warp-uniform
+            const bool need_mask = key0 + BN > warp_first_pos + 1 || key0 < full_lo || key0 < kv_lo;
+            st.step(Qs + warp * 16 * KSTR, Ks + buf * BN * KSTR, Vs + buf * BN * KSTR, key0, lo, hi,
+                    scale_log2, need_mask);
+        }
+        __syncthreads();
+    }
+    st.finish_sums();
+    if (!warp_active) return;
+    const int t4 = lane & 3;
+#pragma unroll
+    for (int r = 0; r < 2; ++r) {
+        const int rg = row0 + warp * 16 + g + 8 * r;
+        if (rg >= rows) continue;
+        const float inv = 1.0f / st.l[r];
+        bf16* dst = out + (size_t)(tok0 + rg / G) * out_stride + (size_t)(kh * G + rg % G) * D;
+#pragma unroll
+        for (int i = 0; i < D / 8; ++i) {
+            __nv_bfloat162 v = __floats2bfloat162_rn(st.o[i][2 * r] * inv, st.o[i][2 * r + 1] * inv);
+            *reinterpret_cast<__nv_bfloat162*>(dst + i * 8 + 2 * t4) = v;
+        }
+    }
+}
+
+// ----------------------------------------------------------------- decode kernel --
+// One token per sequence.  grid (sequence, kv head, split).  The block's four warps
+// share each tile of 64 keys, 16 keys a warp, and join their states at the end.
+// With one split the output is final; else partial (o, m, l) go to scratch memory.
+__global__ void __launch_bounds__(NTHREADS)
+attn_decode_kernel(const bf16* __restrict__ q, int q_stride, const bf16* __restrict__ cache,
+                   const int* __restrict__ block_table, int max_blocks, const int* __restrict__ cu_q,
+                   const int* __restrict__ ctx_lens, bf16* __restrict__ out, int out_stride,
+                   float* __restrict__ part_o, float* __restrict__ part_ml, int nq, int nkv,
+                   int block_size, int num_blocks, float scale_log2, int window, int num_splits) {
+    extern __shared__ __align__(16) unsigned char smem_raw[];
+    bf16* Qs = reinterpret_cast<bf16*>(smem_raw);                 // [16][KSTR]
+    bf16* Ks = Qs + 16 * KSTR;                                    // [2][BN][KSTR]
+    bf16* Vs = Ks + 2 * BN * KSTR;                                // [2][BN][KSTR]
+    const int G = nq / nkv;
+    const int seq = blockIdx.x, kh = blockIdx.y, split = blockIdx.z;
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+    const int tok = cu_q[seq];
+    const int pos = ctx_lens[seq];
+    const int kv_hi = pos + 1;
+    const int kv_lo = window > 0 ? max(0, pos - window + 1) : 0;
+    const int* bt = block_table + (size_t)seq * max_blocks;
+    const int t0 = kv_lo / BN, t1 = (kv_hi + BN - 1) / BN;
+    const int per = (t1 - t0 + num_splits - 1) / num_splits;
+    const int t_begin = t0 + split * per, t_end = min(t1, t_begin + per);
+
+    for (int c = threadIdx.x; c < 16 * CHUNKS; c += NTHREADS) {
+        const int r = c / CHUNKS, ch = c % CHUNKS;
+        const bool ok = r < G;
+        const bf16* src = ok ? q + (size_t)tok * q_stride + (size_t)(kh * G + r) * D + ch * 8 : q;
+        cp_async16(Qs + r * KSTR + ch * 8, src, ok);
+    }
+    if (t_begin < t_end)
+        load_kv_tile(Ks, Vs, cache, bt, max_blocks, num_blocks, nkv, kh, block_size, t_begin * BN, kv_lo, kv_hi);
+    cp_async_commit();
+
+    int lo[2] = {kv_lo, kv_lo}, hi[2] = {kv_hi, kv_hi};
+    WarpState<16> st;
+    st.init();
+    for (int t = t_begin; t < t_end; ++t) {
+        const int buf = (t - t_begin) & 1;
+        if (t + 1 < t_end) {
+            load_kv_tile(Ks + (buf ^ 1) * BN * KSTR, Vs + (buf ^ 1) * BN * KSTR, cache, bt, max_blocks,
+                         num_blocks, nkv, kh, block_size, (t + 1) * BN, kv_lo, kv_hi);
+            cp_async_commit();
+            cp_async_wait<1>();
+        } else {
+            cp_async_wait<0>();
+        }
+        __syncthreads();
+        const int key0 = t * BN + warp * 16;
+        if (key0 < kv_hi && key0 + 16 > kv_lo) {
+            const bool need_mask = key0 + 16 > kv_hi || key0 < kv_lo;
+            st.step(Qs, Ks + (buf * BN + warp * 16) * KSTR, Vs + (buf * BN + warp * 16) * KSTR, key0, lo, hi,
+                    scale_log2, need_mask);
+        }
+        __syncthreads();
+    }
+    cp_async_wait<0>();
+    st.finish_sums();
+    __syncthreads();
+    // join the four warps (rows g and g+8 of each; only rows < G matter)
+    float* sm_o = reinterpret_cast<float*>(Ks);                   // [4][16][D]
+    float* sm_m = sm_o + 4 * 16 * D;                              // [4][16]
+    float* sm_l = sm_m + 4 * 16;                                  // [4][16]
+    const int g = lane >> 2, t4 = lane & 3;
+#pragma unroll
+    for (int r = 0; r < 2; ++r) {
+        const int row = g + 8 * r;
+        if (t4 == 0) { sm_m[warp * 16 + row] = st.m[r]; sm_l[warp * 16 + row] = st.l[r]; }
+#pragma unroll
+        for (int i = 0; i < D / 8; ++i) {
+            sm_o[(warp * 16 + row) * D + i * 8 + 2 * t4] = st.o[i][2 * r];
+            sm_o[(warp * 16 + row) * D + i * 8 + 2 * t4 + 1] = st.o[i][2 * r + 1];
+        }
+    }
+    __syncthreads();
+    for (int idx = threadIdx.x; idx < G * D; idx += NTHREADS) {
+        const int row = idx / D, col = idx % D;
+        float M = -CUDART_INF_F;
+#pragma unroll
+        for (int w = 0; w < 4; ++w) M = fmaxf(M, sm_m[w * 16 + row]);
+        float L = 0.f, O = 0.f;
+#pragma unroll
+        for (int w = 0; w < 4; ++w) {
+            const float mw = sm_m[w * 16 + row];
+            const float wt = mw == -CUDART_INF_F ? 0.f : exp2f(mw - M);
+            L += wt * sm_l[w * 16 + row];
+            O += wt * sm_o[(w * 16 + row) * D + col];
+        }
+        const int head = kh * G + row;
+        if (num_splits == 1) {
+            out[(size_t)tok * out_stride + (size_t)head * D + col] = __float2bfloat16_rn(O / L);
+        } else {
+            const size_t p = ((size_t)seq * nq + head) * num_splits + split;
+            part_o[p * D + col] = O;
+            if (col == 0) { part_ml[p * 2] = M; part_ml[p * 2 + 1] = L; }
+        }
+    }
+}
+
+// out[token of seq, head, :] = sum_s w_s o_s / sum_s w_s l_s,  w_s = 2^(m_s - max m)
+__global__ void attn_combine_kernel(const float* __restrict__ part_o, const float* __restrict__ part_ml,
+                                    const int* __restrict__ cu_q, bf16* __restrict__ out, int out_stride,
+                                    int nq, int num_splits) {
+    const int seq = blockIdx.x, head = blockIdx.y;
+    const size_t base = ((size_t)seq * nq + head) * num_splits;
+    float M = -CUDART_INF_F;
+    for (int s = 0; s < num_splits; ++s) M = fmaxf(M, part_ml[(base + s) * 2]);
+    float L = 0.f;
+    for (int s = 0; s < num_splits; ++s) {
+        const float ms = part_ml[(base + s) * 2];
+        if (ms != -CUDART_INF_F) L += exp2f(ms - M) * part_ml[(base + s) * 2 + 1];
+    }
+    const int tok = cu_q[seq];
+    for (int col = threadIdx.x; col < D; col += blockDim.x) {
+        float O = 0.f;
+        for (int s = 0; s < num_splits; ++s) {
+            const float ms = part_ml[(base + s) * 2];
+            if (ms != -CUDART_INF_F) O += exp2f(ms - M) * part_o[(base + s) * D + col];
+        }
+        out[(size_t)tok * out_stride + (size_t)head * D + col] = __float2bfloat16_rn(O / L);
+    }
+}
+
+constexpr size_t TILED_SMEM = (size_t)(BM + 4 * BN) * KSTR * sizeof(bf16);
+constexpr size_t DECODE_KV_SMEM = (size_t)(4 * BN) * KSTR * sizeof(bf16);
+constexpr size_t DECODE_JOIN_SMEM = (size_t)(4 * 16 * D + 2 * 4 * 16) * sizeof(float);
+constexpr size_t DECODE_SMEM = (size_t)16 * KSTR * sizeof(bf16) +
+                               (DECODE_KV_SMEM > DECODE_JOIN_SMEM ? DECODE_KV_SMEM : DECODE_JOIN_SMEM);
+
+}  // namespace ff
+
+using namespace ff;
+
+FF_EXPORT int ff_attn_head_dim() { return D; }
+FF_EXPORT int ff_attn_block_m() { return BM; }
+
+// total_tiles = sum over sequences of ceil(q_len * G / BM)
+FF_EXPORT int ff_attn_tiled(const void* q, int q_stride, const void* cache, const int* block_table,
+                            int max_blocks, const int* cu_q, const int* ctx_lens, int n_seqs,
+                            int total_tiles, void* out, int out_stride, int nq, int nkv, int block_size,
+                            int num_blocks, float scale, int window, cudaStream_t stream) {
+    if (n_seqs <= 0 || total_tiles <= 0) return 0;
+    if (nkv <= 0 || nq % nkv) return FF_ERR_BAD_ARG;
+    static bool attr_set = false;
+    if (!attr_set) {
+        cudaError_t e = cudaFuncSetAttribute(attn_tiled_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                             (int)TILED_SMEM);
+        if (e != cudaSuccess) return (int)e;
+        attr_set = true;
+    }
+    dim3 grid(total_tiles, nkv);
+    attn_tiled_kernel<<<grid, NTHREADS, TILED_SMEM, stream>>>(
+        (const bf16*)q, q_stride, (const bf16*)cache, block_table, max_blocks, cu_q, ctx_lens, n_seqs,
+        (bf16*)out, out_stride, nq, nkv, block_size, num_blocks, scale * LOG2E, window);
+    FF_LAUNCH_CHECK();
+    return 0;
+}
+
+// Every sequence has exactly one token.  part_o: float [n_seqs*nq*num_splits*D],
+// part_ml: float [n_seqs*nq*num_splits*2] (unused when num_splits == 1).
+FF_EXPORT int ff_attn_decode(const void* q, int q_stride, const void* cache, const int* block_table,
+                             int max_blocks, const int* cu_q, const int* ctx_lens, int n_seqs, void* out,
+                             int out_stride, float* part_o, float* part_ml, int nq, int nkv,
+                             int block_size, int num_blocks, float scale, int window, int num_splits,
+                             cudaStream_t stream) {
+    if (n_seqs <= 0) return 0;
+    if (nkv <= 0 || nq % nkv || num_splits < 1) return FF_ERR_BAD_ARG;
+    if (nq / nkv > 16) return FF_ERR_UNSUPPORTED;
+    static bool attr_set = false;
+    if (!attr_set) {
+        cudaError_t e = cudaFuncSetAttribute(attn_decode_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                             (int)DECODE_SMEM);
+        if (e != cudaSuccess) return (int)e;
+        attr_set = true;
+    }
+    dim3 grid(n_seqs, nkv, num_splits);
+    attn_decode_kernel<<<grid, NTHREADS, DECODE_SMEM, stream>>>(
+        (const bf16*)q, q_stride, (const bf16*)cache, block_table, max_blocks, cu_q, ctx_lens, (bf16*)out,
+        out_stride, part_o, part_ml, nq, nkv, block_size, num_blocks, scale * LOG2E, window, num_splits);
+    FF_LAUNCH_CHECK();
+    if (num_splits > 1) {
+        dim3 cgrid(n_seqs, nq);
+        attn_combine_kernel<<<cgrid, D >= 128 ? 128 : 64, 0, stream>>>(part_o, part_ml, cu_q, (bf16*)out,
+                                                                     out_stride, nq, num_splits);
+        FF_LAUNCH_CHECK();
+    }
+    return 0;
+}

@@ -36,7 +36,7 @@ class KernelBuildError(RuntimeError):
     pass
 
 
-_loaded: Dict[str, ctypes.CDLL] = {}
+_loaded: Dict[tuple, ctypes.CDLL] = {}
 _lock = threading.Lock()
 
 
@@ -51,23 +51,32 @@ def find_nvcc() -> str:
                            "other implementation")
 
 
+_build_dir: Optional[str] = None
+_build_dir_lock = threading.Lock()
+
+
 def build_dir() -> str:
-    cands = []
-    if os.environ.get("FIREFLY_B200_BUILD_DIR"):
-        cands.append(os.environ["FIREFLY_B200_BUILD_DIR"])
-    cands.append(os.path.join(CSRC, "_build"))
-    cands.append(os.path.join(tempfile.gettempdir(), f"firefly_b200-build-{os.getuid()}"))
-    for d in cands:
-        try:
-            os.makedirs(d, exist_ok=True)
-            probe = os.path.join(d, f".w{os.getpid()}")
-            with open(probe, "w"):
-                pass
-            os.unlink(probe)
-            return d
-        except OSError:
-            continue
-    raise KernelBuildError(f"no writable build folder among {cands}")
+    """The folder objects are built into (chosen once per process)."""
+    global _build_dir
+    with _build_dir_lock:
+        if _build_dir is not None:
+            return _build_dir
+        cands = []
+        if os.environ.get("FIREFLY_B200_BUILD_DIR"):
+            cands.append(os.environ["FIREFLY_B200_BUILD_DIR"])
+        cands.append(os.path.join(CSRC, "_build"))
+        cands.append(os.path.join(tempfile.gettempdir(), f"firefly_b200-build-{os.getuid()}"))
+        for d in cands:
+            try:
+                os.makedirs(d, exist_ok=True)
+                fd, probe = tempfile.mkstemp(prefix=".probe", dir=d)
+                os.close(fd)
+                os.unlink(probe)
+                _build_dir = d
+                return d
+            except OSError:
+                continue
+        raise KernelBuildError(f"no writable build folder among {cands}")
 
 
 def _hash(paths: Iterable[str], flags: Sequence[str]) -> str:
@@ -145,16 +154,19 @@ def compile_module(source: str, defines: Optional[Mapping[str, object]] = None, 
 
 
 def load_module(source: str, defines: Optional[Mapping[str, object]] = None) -> ctypes.CDLL:
-    out, _ = library_path(source, defines)
+    key = (source, tuple(sorted((defines or {}).items())))
+    lib = _loaded.get(key)
+    if lib is not None:
+        return lib
     with _lock:
-        lib = _loaded.get(out)
+        lib = _loaded.get(key)
         if lib is None:
             path = compile_module(source, defines)
             try:
                 lib = ctypes.CDLL(path)
             except OSError as e:
                 raise KernelBuildError(f"cannot load {path}: {e}") from e
-            _loaded[out] = lib
+            _loaded[key] = lib
     return lib
 
 

@@ -75,9 +75,14 @@ def _lib(name: str) -> ctypes.CDLL:
     return load_module(src, defs)
 
 
-def build_all(extra=()) -> None:
-    """Compile every module (used by the build check; needs no GPU)."""
-    mods = list(_MODULES.values()) + list(extra)
+DEFAULT_HEAD_DIMS = (128,)
+
+
+def build_all(head_dims=DEFAULT_HEAD_DIMS) -> None:
+    """Compile every module (used by the build check; needs no GPU).  The
+    tensor-core attention is compiled per head size; others are built when a
+    model with that head size is first run."""
+    mods = list(_MODULES.values()) + [("attention_mma.cu", {"FF_HEAD_DIM": int(d)}) for d in head_dims]
     compile_many(mods)
 
 
@@ -233,8 +238,69 @@ def set_exact_matmul() -> None:
         pass
 
 
+_ATTN_FORCE_SIMT = False      # tests flip this to compare the two kernels
+_SM_TARGET_CTAS = 592         # 148 SMs x 4: how many blocks a decode launch should reach
+
+
+def _attn_lib(d: int) -> ctypes.CDLL:
+    return load_module("attention_mma.cu", {"FF_HEAD_DIM": d})
+
+
+def mma_attention_supported(dtype: torch.dtype, d: int) -> bool:
+    return dtype == torch.bfloat16 and d % 16 == 0 and 16 <= d <= 256
+
+
+def attn_tiled(q, q_stride, pages, table, cu_q, ctx_lens, n_seqs, total_tiles, out, nq, nkv, d, scale,
+               window) -> None:
+    """Tensor-core attention for any mix of sequences (bfloat16)."""
+    _need_cuda(pages, table, cu_q, ctx_lens, out)
+    num_blocks, _, _, block_size, _ = pages.shape
+    _check(_attn_lib(d).ff_attn_tiled(
+        _p(q), c_int(q_stride), _p(pages), _p(table), c_int(table.shape[1]), _p(cu_q), _p(ctx_lens),
+        c_int(n_seqs), c_int(total_tiles), _p(out), c_int(out.shape[1]), c_int(nq), c_int(nkv),
+        c_int(block_size), c_int(num_blocks), c_float(scale), c_int(window), _stream()), "attn_tiled")
+
+
+def attn_decode(q, q_stride, pages, table, cu_q, ctx_lens, n_seqs, out, part_o, part_ml, nq, nkv, d,
+                scale, window, num_splits) -> None:
+    """Split-KV tensor-core attention when every sequence has one token (bfloat16)."""
+    _need_cuda(pages, table, cu_q, ctx_lens, out, part_o, part_ml)
+    num_blocks, _, _, block_size, _ = pages.shape
+    _check(_attn_lib(d).ff_attn_decode(
+        _p(q), c_int(q_stride), _p(pages), _p(table), c_int(table.shape[1]), _p(cu_q), _p(ctx_lens),
+        c_int(n_seqs), _p(out), c_int(out.shape[1]), _p(part_o), _p(part_ml), c_int(nq), c_int(nkv),
+        c_int(block_size), c_int(num_blocks), c_float(scale), c_int(window), c_int(num_splits),
+        _stream()), "attn_decode")
+    global LAUNCHES
+    if num_splits > 1:
+        LAUNCHES += 1     # the kernel that joins the splits
+
+
+def decode_splits(n_seqs: int, nkv: int, max_kv_len: int) -> int:
+    tiles = max(1, -(-max_kv_len // 64))
+    want = -(-_SM_TARGET_CTAS // max(1, n_seqs * nkv))
+    return max(1, min(want, tiles, 64))
+
+
 def paged_attention(q: torch.Tensor, q_stride: int, pages: torch.Tensor, table: torch.Tensor, ctx,
                     out: torch.Tensor, nq: int, nkv: int, d: int, scale: float, window: int) -> None:
-    """Attention of a step's tokens over the paged cache; picks the kernel."""
-    paged_attention_simt(q, q_stride, pages, table, ctx.token_seq, ctx.positions, out, nq, nkv, d,
-                         scale, window, ctx.status)
+    """Attention of a step's tokens over the paged cache; picks the kernel: the
+    tensor-core kernels for bfloat16 and head sizes in steps of 16, the plain
+    kernel for 32-bit and every other head size up to 256."""
+    if _ATTN_FORCE_SIMT or not mma_attention_supported(q.dtype, d):
+        paged_attention_simt(q, q_stride, pages, table, ctx.token_seq, ctx.positions, out, nq, nkv, d,
+                             scale, window, ctx.status)
+        return
+    G = nq // nkv
+    if ctx.pure_decode and G <= 16:
+        n = ctx.num_seqs
+        splits = decode_splits(n, nkv, ctx.max_kv_len)
+        part_o = ctx.workspace.get("attn.part_o", (n * nq * splits * d,), torch.float32)
+        part_ml = ctx.workspace.get("attn.part_ml", (n * nq * splits * 2,), torch.float32)
+        attn_decode(q, q_stride, pages, table, ctx.cu_q, ctx.ctx_lens, n, out, part_o, part_ml, nq, nkv, d,
+                    scale, window, splits)
+    else:
+        bm = 64
+        tiles = sum(-(-(ql * G) // bm) for ql in ctx.q_lens)
+        attn_tiled(q, q_stride, pages, table, ctx.cu_q, ctx.ctx_lens, ctx.num_seqs, tiles, out, nq, nkv, d,
+                   scale, window)

@@ -1,0 +1,259 @@
+"""Each kernel alone against a plain 32-bit reference, at sizes other than the
+engine's: head sizes in steps of 16, odd widths and vocabularies, groups of 1-8,
+contexts that cross page edges, windows, pages in shuffled order."""
+import math
+
+import numpy as np
+import pytest
+import torch
+
+import plain_qwen3 as P
+
+pytestmark = pytest.mark.gpu
+
+
+def K():
+    from firefly_b200.ops import kernels
+    return kernels
+
+
+def dev(t):
+    return t.to("cuda")
+
+
+@pytest.mark.parametrize("H,V,tdt", [(72, 333, torch.float32), (4096, 1000, torch.bfloat16), (100, 50, torch.bfloat16)])
+def test_embedding(H, V, tdt):
+    table = torch.randn(V, H).to(tdt)
+    ids = torch.randint(0, V, (37,), dtype=torch.int32)
+    out = torch.empty(37, H, device="cuda")
+    status = torch.zeros(1, dtype=torch.int32, device="cuda")
+    K().embedding(dev(ids), dev(table), out, status)
+    assert torch.equal(out.cpu(), P.embedding(ids, table).float()) and int(status) == 0
+    bad = ids.clone()
+    bad[5] = V
+    K().embedding(dev(bad), dev(table), out, status)
+    assert int(status) == 1                                     # reported, and the table was not overrun
+
+
+@pytest.mark.parametrize("H", [64, 72, 1000, 4096, 5120 + 8, 60000])
+@pytest.mark.parametrize("adt", [torch.float32, torch.bfloat16])
+def test_add_rms_norm(H, adt):
+    rows = 11
+    res = torch.randn(rows, H) * 3
+    delta = (torch.randn(rows, H)).to(adt)
+    w = 1 + 0.1 * torch.randn(H)
+    eps = 1e-5
+    want_res = res.double() + delta.double()
+    want = P.rms_norm(want_res, w.double(), eps)
+    r = dev(res.clone())
+    out = torch.empty(rows, H, dtype=adt, device="cuda")
+    K().add_rms_norm(r, dev(delta), dev(w), eps, out)
+    tol = 1e-5 if adt == torch.float32 else 1e-2
+    assert torch.allclose(r.cpu().double(), want_res, atol=1e-6, rtol=1e-6)     # residual updated in 32-bit
+    assert torch.allclose(out.cpu().double(), want, atol=tol, rtol=tol)
+    # no delta; and selected rows only (the residual stays)
+    r2 = dev(res.clone())
+    K().add_rms_norm(r2, None, dev(w), eps, out)
+    assert torch.allclose(out.cpu().double(), P.rms_norm(res.double(), w.double(), eps), atol=tol, rtol=tol)
+    idx = torch.tensor([7, 0, 3], dtype=torch.int32)
+    out3 = torch.empty(3, H, dtype=adt, device="cuda")
+    r3 = dev(res.clone())
+    K().add_rms_norm(r3, dev(delta), dev(w), eps, out3, dev(idx))
+    assert torch.equal(r3.cpu(), res)
+    assert torch.allclose(out3.cpu().double(), want[idx.long()], atol=tol, rtol=tol)
+
+
+@pytest.mark.parametrize("I", [160, 200, 12288])
+@pytest.mark.parametrize("adt", [torch.float32, torch.bfloat16])
+def test_silu_mul(I, adt):
+    gu = (torch.randn(9, 2 * I) * 3).to(adt)
+    out = torch.empty(9, I, dtype=adt, device="cuda")
+    K().silu_mul(dev(gu), out)
+    want = P.silu_mul(gu[:, :I].double(), gu[:, I:].double())
+    tol = 1e-6 if adt == torch.float32 else 1e-2
+    assert torch.allclose(out.cpu().double(), want, atol=tol, rtol=tol)
+
+
+def _paged(k, v, block, n_extra=3, seed=0):
+    """Scatter whole-sequence k, v [T, nkv, d] into shuffled pages.  Returns
+    (pages [blocks,2,nkv,block,d], table row)."""
+    T, nkv, d = k.shape
+    n_pages = -(-T // block)
+    total = n_pages + n_extra + 1
+    order = np.random.RandomState(seed).permutation(np.arange(1, total))[:n_pages]
+    pages = torch.randn(total, 2, nkv, block, d, dtype=k.dtype) * 7.0      # stale data everywhere else
+    for t in range(T):
+        pg = order[t // block]
+        pages[pg, 0, :, t % block, :] = k[t]
+        pages[pg, 1, :, t % block, :] = v[t]
+    return pages, [int(x) for x in order]
+
+
+@pytest.mark.parametrize("d,nq,nkv,block,rot", [(16, 4, 2, 16, 16), (48, 3, 1, 8, 32), (128, 8, 2, 16, 128),
+                                                (256, 2, 2, 32, 256), (72, 2, 1, 4, 72)])
+@pytest.mark.parametrize("adt", [torch.float32, torch.bfloat16])
+def test_qk_norm_rope_store(d, nq, nkv, block, rot, adt):
+    torch.manual_seed(d)
+    T, theta, eps = 21, 12345.0, 1e-5
+    ctx_len = 13                                   # tokens already cached: the write starts mid-page
+    width = (nq + 2 * nkv) * d
+    qkv = torch.randn(T, width).to(adt)
+    qw, kw = 1 + 0.1 * torch.randn(d), 1 + 0.1 * torch.randn(d)
+    positions = torch.arange(ctx_len, ctx_len + T, dtype=torch.int32)
+    n_pages = -(-(ctx_len + T) // block)
+    table = torch.full((2, n_pages + 2), -1, dtype=torch.int32)
+    table[1, :n_pages] = torch.tensor(np.random.RandomState(1).permutation(np.arange(1, n_pages + 4))[:n_pages])
+    pages = torch.zeros(n_pages + 4, 2, nkv, block, d, dtype=adt)
+    half = rot // 2
+    freq = torch.pow(torch.tensor(theta, dtype=torch.float64), -2.0 * torch.arange(half, dtype=torch.float64) / rot)
+    ang = torch.arange(64, dtype=torch.float64)[:, None] * freq[None]
+    cs = torch.stack([torch.cos(ang), torch.sin(ang)], -1).float()
+    g_qkv, g_pages = dev(qkv.clone()), dev(pages)
+    status = torch.zeros(1, dtype=torch.int32, device="cuda")
+    K().qk_norm_rope_store(g_qkv, nq, nkv, d, dev(qw), dev(kw), eps, dev(cs), rot, dev(positions),
+                           dev(torch.ones(T, dtype=torch.int32)), dev(table), g_pages, status)
+    assert int(status) == 0
+    x = qkv.double()
+    q = x[:, :nq * d].view(T, nq, d)
+    k = x[:, nq * d:(nq + nkv) * d].view(T, nkv, d)
+    v = x[:, (nq + nkv) * d:].view(T, nkv, d)
+
+    def rot_part(t):
+        y = t.clone()
+        y[..., :rot] = P.rope(t[..., :rot], positions, theta)
+        return y
+    q_want = rot_part(P.rms_norm(q, qw.double(), eps))
+    k_want = rot_part(P.rms_norm(k, kw.double(), eps))
+    tol = 2e-5 if adt == torch.float32 else 2e-2
+    got_q = g_qkv.cpu().double()[:, :nq * d].view(T, nq, d)
+    assert torch.allclose(got_q, q_want, atol=tol, rtol=tol)
+    assert torch.equal(g_qkv.cpu()[:, nq * d:], qkv[:, nq * d:])           # k, v columns untouched
+    gp = g_pages.cpu().double()
+    for t in range(T):
+        p = ctx_len + t
+        pg = int(table[1, p // block])
+        assert torch.allclose(gp[pg, 0, :, p % block], k_want[t], atol=tol, rtol=tol)
+        assert torch.allclose(gp[pg, 1, :, p % block], v[t], atol=0, rtol=0)
+    written = {(int(table[1, (ctx_len + t) // block]), (ctx_len + t) % block) for t in range(T)}
+    for pg in range(pages.shape[0]):
+        for o in range(block):
+            if (pg, o) not in written:
+                assert float(gp[pg, :, :, o].abs().max()) == 0.0         # nothing else was written
+
+
+def _attention_case(d, nq, nkv, block, seqs, window, adt, seed=0, spike=True):
+    """seqs: list of (ctx_len, q_len).  Builds whole-sequence q,k,v, pages them and
+    returns everything the kernels need plus the plain result for the new tokens."""
+    g = torch.Generator().manual_seed(seed)
+    G = nq // nkv
+    tables, qs, wants, cu, ctxs, token_seq, positions = [], [], [], [0], [], [], []
+    page_list = []
+    base = 1
+    for si, (ctx_len, q_len) in enumerate(seqs):
+        T = ctx_len + q_len
+        q = torch.randn(T, nq, d, generator=g)
+        k = torch.randn(T, nkv, d, generator=g)
+        v = torch.randn(T, nkv, d, generator=g)
+        if spike and T > 3:
+            # one far key stands out for the last query: a lost or misplaced key shows
+            k[1] = k[1] * 0.1 + 3.0 * q[T - 1, ::G] / math.sqrt(d) * 4
+        q, k, v = q.to(adt), k.to(adt), v.to(adt)
+        want = P.attention(q.double(), k.double(), v.double(), window=window)[ctx_len:]
+        pages, order = _paged(k, v, block, seed=seed + si)
+        page_list.append(pages[1:])
+        tables.append([o - 1 + base for o in order])
+        base += pages.shape[0] - 1
+        qs.append(q[ctx_len:])
+        wants.append(want)
+        cu.append(cu[-1] + q_len)
+        ctxs.append(ctx_len)
+        token_seq += [si] * q_len
+        positions += list(range(ctx_len, T))
+    all_pages = torch.cat([torch.zeros(1, *page_list[0].shape[1:], dtype=adt)] + page_list, 0)
+    mb = max(len(t) for t in tables) + 1
+    table = torch.full((len(seqs), mb), -1, dtype=torch.int32)
+    for i, t in enumerate(tables):
+        table[i, :len(t)] = torch.tensor(t, dtype=torch.int32)
+    return dict(q=torch.cat(qs, 0).reshape(-1, nq * d).contiguous(), pages=all_pages, table=table,
+                cu_q=torch.tensor(cu, dtype=torch.int32), ctx_lens=torch.tensor(ctxs, dtype=torch.int32),
+                token_seq=torch.tensor(token_seq, dtype=torch.int32),
+                positions=torch.tensor(positions, dtype=torch.int32),
+                want=torch.cat(wants, 0).reshape(-1, nq * d), q_lens=[s[1] for s in seqs])
+
+
+ATT_SHAPES = [(16, 4, 2, 16), (32, 6, 2, 8), (48, 3, 1, 32), (64, 8, 1, 16), (128, 8, 2, 16), (80, 5, 5, 4),
+              (256, 4, 2, 64)]
+MIXED = [(0, 1), (0, 2), (5, 17), (63, 1), (64, 1), (65, 3), (130, 70), (0, 129), (300, 1)]
+
+
+@pytest.mark.parametrize("d,nq,nkv,block", ATT_SHAPES)
+@pytest.mark.parametrize("window", [None, 37])
+@pytest.mark.parametrize("adt", [torch.float32, torch.bfloat16])
+def test_attention_simt(d, nq, nkv, block, window, adt):
+    c = _attention_case(d, nq, nkv, block, MIXED, window, adt)
+    out = torch.empty(c["q"].shape, dtype=adt, device="cuda")
+    status = torch.zeros(1, dtype=torch.int32, device="cuda")
+    K().paged_attention_simt(dev(c["q"]), nq * d, dev(c["pages"]), dev(c["table"]), dev(c["token_seq"]),
+                             dev(c["positions"]), out, nq, nkv, d, 1 / math.sqrt(d), window or 0, status)
+    assert int(status) == 0
+    tol = 2e-5 if adt == torch.float32 else 2e-2
+    err = (out.cpu().double() - c["want"]).abs().max() / c["want"].abs().max()
+    assert float(err) < tol
+
+
+@pytest.mark.parametrize("d,nq,nkv,block", ATT_SHAPES)
+@pytest.mark.parametrize("window", [None, 37, 200])
+def test_attention_tiled_tensor_core(d, nq, nkv, block, window):
+    c = _attention_case(d, nq, nkv, block, MIXED, window, torch.bfloat16)
+    G = nq // nkv
+    out = torch.zeros(c["q"].shape, dtype=torch.bfloat16, device="cuda")
+    tiles = sum(-(-(ql * G) // 64) for ql in c["q_lens"])
+    K().attn_tiled(dev(c["q"]), nq * d, dev(c["pages"]), dev(c["table"]), dev(c["cu_q"]), dev(c["ctx_lens"]),
+                   len(MIXED), tiles, out, nq, nkv, d, 1 / math.sqrt(d), window or 0)
+    torch.cuda.synchronize()
+    err = (out.cpu().double() - c["want"]).abs().max() / c["want"].abs().max()
+    assert float(err) < 2e-2, float(err)
+
+
+@pytest.mark.parametrize("d,nq,nkv,block", ATT_SHAPES)
+@pytest.mark.parametrize("window", [None, 100])
+@pytest.mark.parametrize("splits", [1, 2, 5])
+def test_attention_decode_tensor_core(d, nq, nkv, block, window, splits):
+    seqs = [(0, 1), (1, 1), (63, 1), (64, 1), (200, 1), (517, 1), (15, 1)]
+    c = _attention_case(d, nq, nkv, block, seqs, window, torch.bfloat16, seed=3)
+    n = len(seqs)
+    out = torch.zeros(c["q"].shape, dtype=torch.bfloat16, device="cuda")
+    part_o = torch.full((n * nq * splits * d,), float("nan"), device="cuda")
+    part_ml = torch.full((n * nq * splits * 2,), float("nan"), device="cuda")
+    K().attn_decode(dev(c["q"]), nq * d, dev(c["pages"]), dev(c["table"]), dev(c["cu_q"]), dev(c["ctx_lens"]),
+                    n, out, part_o, part_ml, nq, nkv, d, 1 / math.sqrt(d), window or 0, splits)
+    torch.cuda.synchronize()
+    err = (out.cpu().double() - c["want"]).abs().max() / c["want"].abs().max()
+    assert float(err) < 2e-2, float(err)
+
+
+def test_attention_q_inside_wider_buffer():
+    """q read in place from a [T, (nq+2nkv)*d] projection output."""
+    d, nq, nkv, block = 64, 4, 2, 16
+    c = _attention_case(d, nq, nkv, block, [(10, 20), (40, 1)], None, torch.bfloat16)
+    T = c["q"].shape[0]
+    width = (nq + 2 * nkv) * d
+    buf = torch.randn(T, width).to(torch.bfloat16)
+    buf[:, :nq * d] = c["q"]
+    out = torch.zeros(T, nq * d, dtype=torch.bfloat16, device="cuda")
+    K().attn_tiled(dev(buf), width, dev(c["pages"]), dev(c["table"]), dev(c["cu_q"]), dev(c["ctx_lens"]), 2,
+                   2 + 1, out, nq, nkv, d, 1 / math.sqrt(d), 0)
+    err = (out.cpu().double() - c["want"]).abs().max() / c["want"].abs().max()
+    assert float(err) < 2e-2
+
+
+def test_kernels_refuse_cpu_tensors_and_bad_sizes():
+    k = K()
+    with pytest.raises(k.KernelError, match="CUDA device only"):
+        k.silu_mul(torch.zeros(2, 8), torch.zeros(2, 4))
+    q = torch.zeros(1, 300, device="cuda")
+    pages = torch.zeros(2, 2, 1, 16, 300, device="cuda")
+    z = torch.zeros(1, dtype=torch.int32, device="cuda")
+    with pytest.raises(k.KernelError, match="not supported"):
+        k.paged_attention_simt(q, 300, pages, torch.zeros(1, 2, dtype=torch.int32, device="cuda"), z, z,
+                               torch.zeros(1, 300, device="cuda"), 1, 1, 300, 1.0, 0, z)
