@@ -129,6 +129,8 @@ def main() -> int:
     ap.add_argument("--context", type=int, default=4096)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--no-points", action="store_true", help="skip the batch-1 and batch-64 points")
+    ap.add_argument("--no-prefill", action="store_true", help="skip the prefill measurement")
+    ap.add_argument("--no-decode", action="store_true", help="prefill measurement only (for profiling)")
     ap.add_argument("--dtype", default="bfloat16", choices=["bfloat16", "float32"])
     args = ap.parse_args()
     if args.impl == "reference":
@@ -289,11 +291,14 @@ def main() -> int:
                 "frac": flops / (ms / 1e3) / (pk["bf16_tflops_sustained" if False else "bf16_tflops"] * 1e12),
                 "tflops": flops / (ms / 1e3) / 1e12}
 
+    if args.no_decode:
+        print(json.dumps({"prefill": prefill_point(), "config": {"layers": L}}))
+        return 0
     clocks = ClockSampler()
     clocks.start()
     main_res = decode_point(args.batch, K_steps, with_e2e=True)
     clock_info = clocks.stop()
-    prefill = prefill_point()
+    prefill = None if args.no_prefill else prefill_point()
     points = {}
     if not args.no_points:
         for B in (1, 64):

@@ -42,10 +42,12 @@ class DecodeGraphs:
     def _bucket_for(self, n: int) -> _Bucket:
         size = next(b for b in self.sizes if b >= n)
         if size not in self.buckets:
-            # capture from the largest bucket down, so scratch buffers never grow afterwards
-            for s in reversed(self.sizes):
-                if s >= size and s not in self.buckets:
-                    self.buckets[s] = self._capture(s)
+            if not self.workspace.frozen:
+                # one eager run at the largest size gives every scratch buffer its final
+                # extent, so no captured address ever moves
+                self._prepare(self.sizes[-1], capture=False)
+                self.workspace.frozen = True
+            self.buckets[size] = self._prepare(size, capture=True)
         return self.buckets[size]
 
     def _fill(self, b: _Bucket, entries: Sequence[StepEntry]) -> None:
@@ -83,7 +85,7 @@ class DecodeGraphs:
                 h[row: row + len(table)] = table
                 h[row + len(table): row + mb] = -1
 
-    def _capture(self, size: int) -> _Bucket:
+    def _prepare(self, size: int, capture: bool) -> _Bucket:
         r = self.runner
         b = _Bucket()
         b.size = size
@@ -98,22 +100,21 @@ class DecodeGraphs:
         ctx.workspace = self.workspace
         ctx.max_kv_len = r.max_model_len      # launch shapes must not depend on the requests
         ctx.captured = True
-        self.workspace.frozen = False
         side = torch.cuda.Stream(device=r.device)
         side.wait_stream(torch.cuda.current_stream())
         with torch.cuda.stream(side):
-            for _ in range(2):                # warm-up: library handles, lazy module loads
-                logits = r.model.forward(ctx)
-                K.sample(logits, b.tokens)
+            logits = r.model.forward(ctx)     # warm-up: library handles, lazy module loads
+            K.sample(logits, b.tokens)
         torch.cuda.current_stream().wait_stream(side)
         torch.cuda.synchronize(r.device)
+        if not capture:
+            return b
         b.graph = torch.cuda.CUDAGraph()
         before = K.LAUNCHES
         with torch.cuda.graph(b.graph):
             b.logits = r.model.forward(ctx)
             K.sample(b.logits, b.tokens)
         b.launches = K.LAUNCHES - before      # own kernels in one replay
-        self.workspace.frozen = True
         return b
 
     def run(self, entries: Sequence[StepEntry], want_tokens: bool = True

@@ -295,8 +295,10 @@ def paged_attention(q: torch.Tensor, q_stride: int, pages: torch.Tensor, table: 
     if ctx.pure_decode and G <= 16:
         n = ctx.num_seqs
         splits = decode_splits(n, nkv, ctx.max_kv_len)
-        part_o = ctx.workspace.get("attn.part_o", (n * nq * splits * d,), torch.float32)
-        part_ml = ctx.workspace.get("attn.part_ml", (n * nq * splits * 2,), torch.float32)
+        # n*nq*splits < G*target + n*nq for every n: the largest batch needs the most
+        cap = G * _SM_TARGET_CTAS + n * nq
+        part_o = ctx.workspace.get("attn.part_o", (cap * d,), torch.float32)
+        part_ml = ctx.workspace.get("attn.part_ml", (cap * 2,), torch.float32)
         attn_decode(q, q_stride, pages, table, ctx.cu_q, ctx.ctx_lens, n, out, part_o, part_ml, nq, nkv, d,
                     scale, window, splits)
     else:
