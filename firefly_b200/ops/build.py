@@ -141,6 +141,14 @@ def compile_module(source: str, defines: Optional[Mapping[str, object]] = None, 
                 raise KernelBuildError(f"nvcc failed for {source} (exit {proc.returncode}):\n"
                                        f"{' '.join(cmd)}\n{log}")
             os.replace(tmp, out)
+            # objects of the same module built from older sources are of no use any more
+            stem = os.path.basename(out).rsplit("-", 1)[0]
+            for f in os.listdir(os.path.dirname(out)):
+                if f.endswith(".so") and f.rsplit("-", 1)[0] == stem and f != os.path.basename(out):
+                    try:
+                        os.unlink(os.path.join(os.path.dirname(out), f))
+                    except OSError:
+                        pass
             if verbose:
                 print(f"[firefly_b200] built {os.path.basename(out)} in {time.time() - t0:.1f} s",
                       file=sys.stderr, flush=True)
