@@ -46,17 +46,23 @@ def build_parser() -> argparse.ArgumentParser:
 class ReplaySession:
     """A model, its cache and its step function, driven one trace step at a time."""
 
-    def __init__(self, model_dir: str, *, dtype: str = "bfloat16", max_tokens: int, block_size: int = 16,
-                 max_requests: int = 16, device: str = "cuda:0"):
+    def __init__(self, model_dir: Optional[str] = None, *, dtype: str = "bfloat16", max_tokens: int,
+                 block_size: int = 16, max_requests: int = 16, device: str = "cuda:0", model=None):
+        """``model_dir``: a model folder; or ``model``: an already bound DecoderModel."""
         if block_size <= 0 or PAGE_ROUNDING % block_size:
             raise ValueError(f"block size must divide {PAGE_ROUNDING}")
-        self.model, self.config = load_model(model_dir, dtype=dtype, device=device)
+        if model is None:
+            self.model, self.config = load_model(model_dir, dtype=dtype, device=device)
+        else:
+            self.model, self.config = model, None
         self.max_tokens = max_tokens
         num_blocks = -(-max_tokens // block_size)
         self.cache = CacheManager(self.model.cache_slot_specs(), block_size=block_size,
                                   num_blocks=num_blocks, max_requests=max_requests)
         self.cache.allocate_storage(self.model.rt.dtype, self.model.rt.device)
         max_len = min(self.model.spec.max_positions, num_blocks * block_size)
+        if self.cache.groups and all(g.spec.window is not None for g in self.cache.groups):
+            max_len = self.model.spec.max_positions     # windows give pages back: length is not bounded by the pool
         self.runner = ModelRunner(self.model, self.cache, max_model_len=max_len)
         self.live: Dict[str, RequestCache] = {}
 

@@ -1,0 +1,260 @@
+"""The parts alone, and the generality of their assembly: windows, a cache read by
+another layer, a layer that runs twice, and a toy mixer with state of its own that
+is registered, built and stepped from this file without a change to the package."""
+import dataclasses
+import math
+
+import numpy as np
+import pytest
+import torch
+
+import plain_qwen3 as P
+import replay_util as U
+
+pytestmark = pytest.mark.gpu
+
+
+def _runtime(dtype):
+    from firefly_b200.parts import Runtime
+    return Runtime(torch.device("cuda:0"), dtype)
+
+
+def _bound_model(cfg, weights, dtype, spec_edit=None):
+    from firefly_b200.models import DecoderModel, config_from_dict, spec_for
+    from firefly_b200.ops import kernels as K
+    K.set_exact_matmul()
+    spec = spec_for(config_from_dict(cfg))
+    if spec_edit is not None:
+        spec = spec_edit(spec)
+    model = DecoderModel(spec, _runtime(dtype))
+    model.bind({k: v.to("cuda").to(dtype if v.dim() > 1 else torch.float32) for k, v in weights.items()})
+    return model
+
+
+def _session(model, max_tokens, block):
+    from firefly_b200.replay import ReplaySession
+    return ReplaySession(model=model, max_tokens=max_tokens, block_size=block)
+
+
+def _context(model, seqs, block=8):
+    """A StepContext for sequences given as (tokens already cached, new tokens)."""
+    from firefly_b200.cache import CacheManager
+    from firefly_b200.engine.runner import ModelRunner, StepEntry
+    cache = CacheManager(model.cache_slot_specs(), block_size=block, num_blocks=64, max_requests=8)
+    cache.allocate_storage(model.rt.dtype, model.rt.device)
+    runner = ModelRunner(model, cache, max_model_len=256)
+    entries = []
+    for i, (ctx_len, toks) in enumerate(seqs):
+        rc = cache.admit(i)
+        assert cache.grow(rc, ctx_len + len(toks))
+        rc.num_tokens = ctx_len
+        entries.append(StepEntry(rc, toks, [len(toks) - 1]))
+    return runner.build_context(entries), runner
+
+
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+def test_each_part_alone(dtype):
+    cfg = P.TINY_C                    # hidden 72, 3 q heads / 1 kv head, head 48, intermediate 200, vocab 333
+    w = P.random_weights(cfg, 4, dtype=dtype, scale=0.08)
+    wd = {k: v.double() for k, v in w.items()}
+    model = _bound_model(cfg, w, dtype)
+    ctx, runner = _context(model, [(0, [5, 9, 200, 7, 1, 300, 17]), (0, [3, 4])])
+    T, H = 9, cfg["hidden_size"]
+    tol = 1e-5 if dtype == torch.float32 else 2e-2
+    g = torch.Generator().manual_seed(0)
+
+    def close(got, want):
+        want = want.double()
+        return float((got.cpu().double() - want).abs().max()) <= tol * max(1.0, float(want.abs().max()))
+
+    # embedding
+    h = model.embedding.forward(ctx)
+    ids = torch.tensor([5, 9, 200, 7, 1, 300, 17, 3, 4])
+    assert h.dtype == torch.float32 and torch.equal(h.cpu(), P.embedding(ids, w["model.embed_tokens.weight"]).float())
+    # norm (with a pending delta)
+    blk = model.blocks[0]
+    res = torch.randn(T, H, generator=g)
+    delta = torch.randn(T, H, generator=g).to(dtype)
+    r = res.cuda()
+    x = blk.norms[0].forward(r, delta.cuda(), ctx)
+    assert close(r, res.double() + delta.double())
+    assert close(x, P.rms_norm(res.double() + delta.double(), wd["model.layers.0.input_layernorm.weight"], cfg["rms_norm_eps"]))
+    # position encoding: the table holds cos and sin of pos * theta^(-2i/d)
+    table, rot = blk.position.rotary_table()
+    assert rot == cfg["head_dim"] and table.shape == (cfg["max_position_embeddings"], rot // 2, 2)
+    pos, i = 301, 5
+    ang = pos * cfg["rope_theta"] ** (-2.0 * i / rot)
+    assert abs(float(table[pos, i, 0]) - math.cos(ang)) < 1e-6 and abs(float(table[pos, i, 1]) - math.sin(ang)) < 1e-6
+    # mixer: whole sequences from position 0, so the plain block sees the same keys
+    xin = (torch.randn(T, H, generator=g)).to(dtype)
+    got = blk.mixer.forward(xin.cuda(), ctx, 0, True)
+    want = torch.cat([P.attention_block(xin[a:b].double(), wd, "model.layers.0.self_attn", cfg,
+                                        torch.arange(b - a))[0] for a, b in ((0, 7), (7, 9))])
+    assert close(got, want)
+    # feed-forward
+    got = blk.feed_forward.forward(xin.cuda(), ctx)
+    want = P.swiglu_mlp(xin.double(), wd["model.layers.0.mlp.gate_proj.weight"], wd["model.layers.0.mlp.up_proj.weight"],
+                        wd["model.layers.0.mlp.down_proj.weight"])
+    assert close(got, want)
+    # head: 32-bit logits
+    rows = xin[:3].cuda()
+    got = model.head.forward(rows, ctx)
+    assert got.dtype == torch.float32 and close(got, xin[:3].double() @ wd["lm_head.weight"].T)
+    runner.check_status()
+
+
+def _edit_windows_and_schedule(windows, schedule):
+    from firefly_b200.config import ScheduleEntry
+
+    def edit(spec):
+        layers = []
+        for ls, win in zip(spec.layers, windows):
+            layers.append(dataclasses.replace(ls, mixer=ls.mixer.with_params(window=win)))
+        sched = tuple(ScheduleEntry(l, cache=c, write_cache=wr) for l, c, wr in schedule) if schedule \
+            else spec.schedule
+        return dataclasses.replace(spec, layers=tuple(layers), schedule=sched)
+    return edit
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+@pytest.mark.parametrize("case", ["windows", "shared_cache", "layer_twice"])
+def test_assembly_is_data(dtype, case):
+    cfg = P.TINY_B
+    tdt = torch.float32 if dtype == "float32" else torch.bfloat16
+    w = P.random_weights(cfg, 6, dtype=tdt, scale=0.05)
+    windows = [None, None, None]
+    schedule = None
+    if case == "windows":
+        windows = [None, 21, 5]                    # three groups of pages: all keys, 21 keys, 5 keys
+    elif case == "shared_cache":
+        schedule = [(0, 0, True), (1, 1, True), (2, 1, False)]
+    else:
+        schedule = [(0, 0, True), (1, 1, True), (1, 2, True), (2, 3, True)]
+    model = _bound_model(cfg, w, tdt, _edit_windows_and_schedule(windows, schedule))
+    reqs = U.make_requests(cfg["vocab_size"], [90, 33, 140, 7, 61], 3)
+    plain = {rid: P.forward(cfg, w, toks, windows=windows, schedule=schedule).numpy() for rid, toks in reqs.items()}
+    for steps in (U.trace_whole(reqs), U.trace_mixed(reqs, seed=2, max_live=3)):
+        sess = _session(model, U.peak_tokens(steps), 8)
+        if case == "windows":
+            assert len(sess.cache.groups) == 3
+        got = U.run_trace(sess, steps)
+        U.compare(got, plain, U.TOL[dtype], f"{case}/{dtype}")
+        sess.cache.check()
+        assert not sess.cache.live
+
+
+def test_window_pages_are_given_back_while_the_request_lives():
+    cfg = P.TINY_A
+    w = P.random_weights(cfg, 8, scale=0.05)
+    model = _bound_model(cfg, w, torch.float32, _edit_windows_and_schedule([10, 10], None))
+    toks = U.make_requests(cfg["vocab_size"], [128], 1)["r0"]
+    plain = P.forward(cfg, w, toks, windows=[10, 10]).numpy()
+    sess = _session(model, 64, 8)                 # 8 pages of 8 for a sequence of 128: only a window fits
+    got = U.Collected()
+    p = 0
+    for k, n in enumerate([9, 1, 1, 17, 2, 1, 30, 1, 1, 1, 40, 24]):
+        arr = sess.run_step({"step": k, "entries": [{"id": "w", "tokens": toks[p:p + n], "want": list(range(n))}]})
+        for i in range(n):
+            got.add("r0", p + i, arr[i])
+        p += n
+        held = sess.cache.groups[0].allocator.num_held
+        assert held <= 10 // 8 + 2 + (n + 7) // 8
+    assert p == 128
+    U.compare(got, {"r0": plain}, U.TOL["float32"], "window, pages reused by the same request")
+
+
+# ---------------------------------------------------------------- a toy mixer --
+class ToyDecayMixer:
+    """y_t = s_t W_out, s_t = decay * s_{t-1} + x_t W_in: state of fixed size per
+    request, kept in the request's state slot between steps.  Written with torch
+    operations; it stands for any mixer a user might add."""
+
+    def __init__(self, spec, rt, position=None):
+        from firefly_b200.parts.base import Part
+        self._part = Part(spec, rt)
+        self.hidden = spec.params["hidden_size"]
+        self.state = spec.params["state_size"]
+        self.decay = spec.params["decay"]
+        self.prefix = spec.prefix
+
+    def weight_specs(self):
+        from firefly_b200.weights import WeightSpec
+        return [WeightSpec(f"{self.prefix}.in.weight", (self.state, self.hidden)),
+                WeightSpec(f"{self.prefix}.out.weight", (self.hidden, self.state))]
+
+    def bind(self, tensors):
+        self.w_in = tensors[f"{self.prefix}.in.weight"].float()
+        self.w_out = tensors[f"{self.prefix}.out.weight"].float()
+
+    def cache_spec(self):
+        from firefly_b200.cache import StateSpec
+        return StateSpec((self.state,), torch.float32)
+
+    def forward(self, x, ctx, slot, write_cache):
+        st = ctx.state(slot)                                   # [1 + max_requests, state]
+        u = x.float() @ self.w_in.T
+        out = torch.empty(x.shape[0], self.hidden, device=x.device)
+        start = 0
+        for i, n in enumerate(ctx.q_lens):
+            sl = ctx.state_slots[i].long()
+            s = st[sl] * (1 - ctx.seq_fresh[i]).float()        # a fresh request starts from zero
+            for t in range(start, start + n):
+                s = self.decay * s + u[t]
+                out[t] = s @ self.w_out.T
+            st[sl] = s
+            start += n
+        return out.to(ctx.dtype)
+
+
+def _toy_plain(cfg, w, ids, decay):
+    """Whole sequence, float64: attention layer 0, then the toy mixer as layer 1's mixer."""
+    wd = {k: v.double() for k, v in w.items()}
+    T = len(ids)
+    pos = torch.arange(T)
+    h = P.embedding(torch.tensor(ids), wd["model.embed_tokens.weight"])
+    for layer in range(2):
+        p = f"model.layers.{layer}"
+        x = P.rms_norm(h, wd[f"{p}.input_layernorm.weight"], cfg["rms_norm_eps"])
+        if layer == 0:
+            a, _ = P.attention_block(x, wd, f"{p}.self_attn", cfg, pos)
+        else:
+            s = torch.zeros(wd["toy.in.weight"].shape[0], dtype=torch.float64)
+            rows = []
+            for t in range(T):
+                s = decay * s + wd["toy.in.weight"] @ x[t]
+                rows.append(wd["toy.out.weight"] @ s)
+            a = torch.stack(rows)
+        h = h + a
+        x = P.rms_norm(h, wd[f"{p}.post_attention_layernorm.weight"], cfg["rms_norm_eps"])
+        h = h + P.swiglu_mlp(x, wd[f"{p}.mlp.gate_proj.weight"], wd[f"{p}.mlp.up_proj.weight"], wd[f"{p}.mlp.down_proj.weight"])
+    x = P.rms_norm(h, wd["model.norm.weight"], cfg["rms_norm_eps"])
+    return (x @ wd["model.embed_tokens.weight"].T).numpy()
+
+
+def test_toy_mixer_with_state_is_registered_built_and_stepped():
+    from firefly_b200.config import PartSpec
+    from firefly_b200.models import DecoderModel, config_from_dict, spec_for
+    from firefly_b200.parts import register_part
+    register_part("mixer", "toy_decay", ToyDecayMixer, replace=True)
+    cfg = P.TINY_A
+    decay = 0.9
+    spec = spec_for(config_from_dict(cfg))
+    toy = PartSpec("toy_decay", dict(hidden_size=cfg["hidden_size"], state_size=24, decay=decay), prefix="toy")
+    layers = (spec.layers[0], dataclasses.replace(spec.layers[1], mixer=toy, position=None))
+    spec = dataclasses.replace(spec, layers=layers)
+    model = DecoderModel(spec, _runtime(torch.float32))
+    names = {ws.name for ws in model.weight_specs()}
+    assert "toy.in.weight" in names and "model.layers.1.self_attn.q_proj.weight" not in names
+    w = P.random_weights(cfg, 2, scale=0.05)
+    g = torch.Generator().manual_seed(5)
+    w["toy.in.weight"] = torch.randn(24, cfg["hidden_size"], generator=g) * 0.1
+    w["toy.out.weight"] = torch.randn(cfg["hidden_size"], 24, generator=g) * 0.1
+    model.bind({k: v.cuda() for k, v in w.items() if k in names})
+    reqs = U.make_requests(cfg["vocab_size"], [50, 3, 77, 20, 31], 9)
+    plain = {rid: _toy_plain(cfg, w, toks, decay) for rid, toks in reqs.items()}
+    for steps in (U.trace_whole(reqs), U.trace_tail_decode(reqs, tail=8), U.trace_mixed(reqs, seed=4, max_live=3)):
+        sess = _session(model, U.peak_tokens(steps), 16)
+        assert len(sess.cache.groups) == 1 and list(sess.cache.state_specs) == [1]
+        got = U.run_trace(sess, steps)
+        U.compare(got, plain, U.TOL["float32"], "toy mixer")
+        sess.cache.check()
