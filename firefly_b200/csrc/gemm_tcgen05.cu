@@ -1,0 +1,432 @@
+// out[t, n] = sum_k x[t, k] * W[n, k]   (y = x W^T, W as stored in checkpoints)
+// on the fifth-generation tensor cores: tcgen05.mma with the accumulator in tensor
+// memory, operands brought into shared memory by TMA, one elected thread issuing
+// the MMAs, and an epilogue that reads the accumulator back with tcgen05.ld.
+//
+// The weight tile is the 128-row "M" operand of the MMA and the tokens are its "N"
+// dimension (16 to 256), so a decode step with a handful of tokens still fills the
+// tensor-core shape and the kernel's time is the time to stream the weights.  For
+// matrices with few row tiles the K range is split over several blocks; each writes
+// its partial tile to scratch memory, and the block that arrives last at the tile's
+// counter adds the partials in a fixed order and runs the epilogue, so the result
+// does not depend on which block was last.  Epilogues: store bfloat16, store
+// float32, add into a float32 residual, or SiLU(gate)*up for a weight whose rows
+// interleave gate and up in groups of 16.
+//
+// The reference runs these products through a library template with half-precision
+// accumulation (src/kernels/linear.cu:15-104), followed by separate launches for the
+// activation (src/kernels/activation.cu) and the residual add (src/kernels/add.cu).
+//
+// Every wait on an mbarrier is bounded: after about a second the kernel records an
+// error code, stops issuing work, lets its copies land, frees its tensor memory
+// and returns.
+#include "common.cuh"
+
+#include <cuda.h>
+#include <cudaTypedefs.h>
+
+#include <mutex>
+#include <unordered_map>
+
+namespace ff {
+
+constexpr int BN = 128;          // weight rows per tile (MMA M)
+constexpr int BK = 64;           // k per stage: 128 bytes of bfloat16, one swizzle span
+constexpr int UMMA_K = 16;
+constexpr int GEMM_THREADS = 192;
+constexpr unsigned long long WAIT_LIMIT_CYCLES = 2000000000ull;   // about a second
+
+enum Epilogue { EPI_BF16 = 0, EPI_F32 = 1, EPI_RESIDUAL_ADD = 2, EPI_SWIGLU = 3 };
+
+template <int TOK> struct TileCfg {
+    static constexpr int STAGES = TOK <= 32 ? 5 : 4;
+    static constexpr int A_BYTES = BN * BK * 2;
+    static constexpr int B_BYTES = TOK * BK * 2;
+    static constexpr int STAGE_BYTES = A_BYTES + B_BYTES;
+    static constexpr int TMEM_COLS = TOK < 32 ? 32 : TOK;
+    static constexpr size_t SMEM = (size_t)STAGES * STAGE_BYTES + 1024 /* alignment slack */ + 256 /* barriers */;
+};
+
+// ---------------------------------------------------------------- PTX helpers --
+__device__ __forceinline__ uint32_t smem_addr(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }
+
+__device__ __forceinline__ void mbar_init(uint32_t bar, uint32_t count) {
+    asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(bar), "r"(count));
+}
+__device__ __forceinline__ void mbar_expect_tx(uint32_t bar, uint32_t bytes) {
+    asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(bar), "r"(bytes) : "memory");
+}
+__device__ __forceinline__ bool mbar_try_wait(uint32_t bar, uint32_t parity) {
+    uint32_t ok;
+    asm volatile("{\n\t.reg .pred P1;\n\tmbarrier.try_wait.parity.shared::cta.b64 P1, [%1], %2;\n\t"
+                 "selp.b32 %0, 1, 0, P1;\n\t}" : "=r"(ok) : "r"(bar), "r"(parity) : "memory");
+    return ok != 0;
+}
+// Bounded wait.  false: gave up (code recorded in *status, *abort set).
+__device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, int* status, volatile int* abort_flag,
+                                          int code) {
+    const unsigned long long start = clock64();
+    uint32_t spins = 0;
+    while (!mbar_try_wait(bar, parity)) {
+        if (((++spins) & 1023u) == 0) {
+            if (*abort_flag) return false;
+            if (clock64() - start > WAIT_LIMIT_CYCLES) {
+                atomicExch(status, code);
+                *abort_flag = 1;
+                return false;
+            }
+        }
+    }
+    return true;
+}
+__device__ __forceinline__ void tma_load_2d(uint32_t dst, const CUtensorMap* map, int x, int y, uint32_t bar) {
+    asm volatile("cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4}], [%2];"
+                 ::"r"(dst), "l"(map), "r"(bar), "r"(x), "r"(y) : "memory");
+}
+__device__ __forceinline__ void tc_fence_before() { asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory"); }
+__device__ __forceinline__ void tc_fence_after() { asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory"); }
+__device__ __forceinline__ void tc_commit(uint32_t bar) {
+    asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(bar) : "memory");
+}
+__device__ __forceinline__ void tc_mma_bf16(uint32_t tmem_d, uint64_t desc_a, uint64_t desc_b, uint32_t idesc,
+                                            uint32_t accumulate) {
+    asm volatile("{\n\t.reg .pred p;\n\tsetp.ne.b32 p, %4, 0;\n\t"
+                 "tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n\t}"
+                 ::"r"(tmem_d), "l"(desc_a), "l"(desc_b), "r"(idesc), "r"(accumulate) : "memory");
+}
+// 16 consecutive accumulator columns of this warp's 32 lanes
+__device__ __forceinline__ void tc_ld16(uint32_t taddr, float (&v)[16]) {
+    uint32_t r[16];
+    asm volatile("tcgen05.ld.sync.aligned.32x32b.x16.b32 {%0,%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15}, [%16];"
+                 : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]),
+                   "=r"(r[8]), "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15])
+                 : "r"(taddr));
+    asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+#pragma unroll
+    for (int i = 0; i < 16; ++i) v[i] = __uint_as_float(r[i]);
+}
+
+// Shared-memory operand descriptor: K-major tile, rows of 128 bytes, 128-byte swizzle;
+// groups of 8 rows are 1024 bytes apart.
+__device__ __forceinline__ uint64_t smem_desc_sw128(uint32_t addr) {
+    uint64_t d = 0;
+    d |= (uint64_t)((addr & 0x3FFFFu) >> 4);          // start address
+    d |= (uint64_t)1 << 16;                            // leading byte offset (unused for swizzled K-major): 1
+    d |= (uint64_t)(1024 >> 4) << 32;                  // stride byte offset between 8-row groups
+    d |= (uint64_t)1 << 46;                            // descriptor version of this architecture
+    d |= (uint64_t)2 << 61;                            // 128-byte swizzle
+    return d;
+}
+// Instruction descriptor: bfloat16 x bfloat16 -> float32, both operands K-major, M = 128, N = TOK
+__device__ __forceinline__ uint32_t instr_desc(int tok) {
+    return (1u << 4) | (1u << 7) | (1u << 10) | ((uint32_t)(tok >> 3) << 17) | ((uint32_t)(BN >> 4) << 24);
+}
+
+struct GemmArgs {
+    void* out;
+    int ldo;              // elements between rows (tokens) of out
+    int T, N, K;
+    int epilogue;
+    int splits;           // number of K ranges (grid.z)
+    int kb_per_split;     // 64-wide k blocks per range
+    float* partials;      // [splits][token tiles][row tiles][TOK][BN] when splits > 1
+    int* counters;        // [token tiles * row tiles], zero between launches
+    int* status;
+};
+
+template <int TOK>
+__global__ void __launch_bounds__(GEMM_THREADS)
+gemm_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant__ CUtensorMap map_x,
+               const GemmArgs a) {
+    using Cfg = TileCfg<TOK>;
+    extern __shared__ unsigned char smem_raw[];
+    // tiles need 1024-byte alignment for the 128-byte swizzle
+    unsigned char* tiles = reinterpret_cast<unsigned char*>(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
+    uint64_t* bars = reinterpret_cast<uint64_t*>(tiles + (size_t)Cfg::STAGES * Cfg::STAGE_BYTES);
+    // bars[0..S) full, bars[S..2S) empty, bars[2S] accumulator ready
+    __shared__ uint32_t s_tmem_base;
+    __shared__ int s_abort, s_is_last;
+
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int n_tiles = gridDim.x, t_tiles = gridDim.y;
+    const int n0 = blockIdx.x * BN, t0 = blockIdx.y * TOK;
+    const int num_kb = (a.K + BK - 1) / BK;
+    const int kb0 = blockIdx.z * a.kb_per_split;
+    const int kb1 = min(num_kb, kb0 + a.kb_per_split);
+    const int n_iters = max(0, kb1 - kb0);
+
+    if (threadIdx.x == 0) {
+        s_abort = 0;
+        s_is_last = 0;
+        for (int i = 0; i < 2 * Cfg::STAGES + 1; ++i) mbar_init(smem_addr(&bars[i]), 1);
+        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    }
+    if (warp == 1) {   // tensor memory for the accumulator: TOK columns of 128 lanes
+        asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;"
+                     ::"r"(smem_addr(&s_tmem_base)), "r"((uint32_t)Cfg::TMEM_COLS) : "memory");
+        asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+    }
+    tc_fence_before();
+    __syncthreads();
+    tc_fence_after();
+    const uint32_t tmem_base = s_tmem_base;
+    volatile int* abort_flag = &s_abort;
+
+    if (warp == 0 && lane == 0) {
+        // ------------------------------------------------ producer: TMA loads --
+        int issued = 0;
+        for (int it = 0; it < n_iters; ++it) {
+            const int s = it % Cfg::STAGES;
+            const uint32_t ph = (it / Cfg::STAGES) & 1;
+            if (!mbar_wait(smem_addr(&bars[Cfg::STAGES + s]), ph ^ 1, a.status, abort_flag, 101)) break;
+            const uint32_t full = smem_addr(&bars[s]);
+            mbar_expect_tx(full, Cfg::STAGE_BYTES);
+            unsigned char* st = tiles + (size_t)s * Cfg::STAGE_BYTES;
+            tma_load_2d(smem_addr(st), &map_w, (kb0 + it) * BK, n0, full);
+            tma_load_2d(smem_addr(st + Cfg::A_BYTES), &map_x, (kb0 + it) * BK, t0, full);
+            issued = it + 1;
+        }
+        if (*abort_flag) {
+            // let the copies that are still in flight land before the block's memory goes away
+            for (int it = max(0, issued - Cfg::STAGES); it < issued; ++it) {
+                const unsigned long long start = clock64();
+                while (!mbar_try_wait(smem_addr(&bars[it % Cfg::STAGES]), (it / Cfg::STAGES) & 1))
+                    if (clock64() - start > WAIT_LIMIT_CYCLES) break;
+            }
+        }
+    } else if (warp == 1 && lane == 0) {
+        // ------------------------------------------------ MMA issuer ----------
+        const uint32_t idesc = instr_desc(TOK);
+        bool ok = true;
+        for (int it = 0; it < n_iters && ok; ++it) {
+            const int s = it % Cfg::STAGES;
+            const uint32_t ph = (it / Cfg::STAGES) & 1;
+            ok = mbar_wait(smem_addr(&bars[s]), ph, a.status, abort_flag, 102);
+            if (!ok) break;
+            tc_fence_after();
+            const uint32_t sa = smem_addr(tiles + (size_t)s * Cfg::STAGE_BYTES);
+            const uint32_t sb = sa + Cfg::A_BYTES;
+#pragma unroll
+            for (int k = 0; k < BK / UMMA_K; ++k) {
+                const uint64_t da = smem_desc_sw128(sa + k * UMMA_K * 2);
+                const uint64_t db = smem_desc_sw128(sb + k * UMMA_K * 2);
+                tc_mma_bf16(tmem_base, da, db, idesc, (it > 0 || k > 0) ? 1u : 0u);
+            }
+            tc_commit(smem_addr(&bars[Cfg::STAGES + s]));      // stage free when these MMAs have read it
+        }
+        tc_commit(smem_addr(&bars[2 * Cfg::STAGES]));          // accumulator complete
+    } else if (warp >= 2) {
+        // ------------------------------------------------ epilogue ------------
+        const int quad = warp & 3;                              // this warp's 32 lanes of tensor memory
+        const int row = quad * 32 + lane;                       // weight row within the tile
+        const int n = n0 + row;
+        const int et = threadIdx.x - 64;                        // 0..127 among the epilogue threads
+        bool ok = true;
+        if (n_iters > 0) ok = mbar_wait(smem_addr(&bars[2 * Cfg::STAGES]), 0, a.status, abort_flag, 103);
+        ok = __all_sync(0xffffffffu, ok);                       // the tensor-memory loads below are warp-wide
+        tc_fence_after();
+        const size_t tile_id = (size_t)blockIdx.y * n_tiles + blockIdx.x;
+        bool do_final = a.splits == 1;
+        if (a.splits > 1) {
+            // this block's partial tile -> scratch, laid out [token][row] so a warp writes 128 bytes
+            float* mine = a.partials + ((size_t)blockIdx.z * t_tiles * n_tiles + tile_id) * (size_t)(TOK * BN);
+#pragma unroll 1
+            for (int c0 = 0; c0 < TOK; c0 += 16) {
+                float v[16];
+                if (n_iters > 0 && ok) tc_ld16(tmem_base + ((uint32_t)(quad * 32) << 16) + c0, v);
+                else {
+#pragma unroll
+                    for (int i = 0; i < 16; ++i) v[i] = 0.f;
+                }
+#pragma unroll
+                for (int i = 0; i < 16; ++i) mine[(size_t)(c0 + i) * BN + row] = v[i];
+            }
+            __threadfence();
+            asm volatile("bar.sync 1, 128;" ::: "memory");
+            if (et == 0) {
+                const int old = atomicAdd(&a.counters[tile_id], 1);
+                s_is_last = (old == a.splits - 1) ? 1 : 0;
+                if (old == a.splits - 1) a.counters[tile_id] = 0;      // ready for the next launch
+            }
+            asm volatile("bar.sync 1, 128;" ::: "memory");
+            do_final = s_is_last != 0;
+            if (do_final) __threadfence();
+        }
+        if (do_final && !*abort_flag) {
+#pragma unroll 1
+            for (int c0 = 0; c0 < TOK; c0 += 16) {
+                float v[16];
+                if (a.splits == 1) {
+                    if (n_iters > 0 && ok) tc_ld16(tmem_base + ((uint32_t)(quad * 32) << 16) + c0, v);
+                    else {
+#pragma unroll
+                        for (int i = 0; i < 16; ++i) v[i] = 0.f;
+                    }
+                } else {
+#pragma unroll
+                    for (int i = 0; i < 16; ++i) v[i] = 0.f;
+                    for (int z = 0; z < a.splits; ++z) {               // fixed order: the sum is reproducible
+                        const float* p = a.partials + ((size_t)z * t_tiles * n_tiles + tile_id) * (size_t)(TOK * BN);
+#pragma unroll
+                        for (int i = 0; i < 16; ++i) v[i] += __ldcg(p + (size_t)(c0 + i) * BN + row);
+                    }
+                }
+                if (a.epilogue == EPI_SWIGLU) {
+                    // rows come in groups of 32: 16 gate rows, then the 16 up rows of the same columns
+#pragma unroll
+                    for (int i = 0; i < 16; ++i) {
+                        const float other = __shfl_xor_sync(0xffffffffu, v[i], 16);
+                        const int t = t0 + c0 + i;
+                        const int col = (n0 + quad * 32) / 2 + lane;
+                        if (lane < 16 && t < a.T && col < a.N / 2) {
+                            const float g = v[i];
+                            reinterpret_cast<bf16*>(a.out)[(size_t)t * a.ldo + col] =
+                                __float2bfloat16_rn(g / (1.0f + expf(-g)) * other);
+                        }
+                    }
+                } else if (n < a.N) {
+#pragma unroll
+                    for (int i = 0; i < 16; ++i) {
+                        const int t = t0 + c0 + i;
+                        if (t >= a.T) continue;
+                        const size_t o = (size_t)t * a.ldo + n;
+                        if (a.epilogue == EPI_BF16) reinterpret_cast<bf16*>(a.out)[o] = __float2bfloat16_rn(v[i]);
+                        else if (a.epilogue == EPI_F32) reinterpret_cast<float*>(a.out)[o] = v[i];
+                        else reinterpret_cast<float*>(a.out)[o] += v[i];
+                    }
+                }
+            }
+        }
+    }
+    tc_fence_before();
+    __syncthreads();
+    if (warp == 1) {
+        __syncwarp();
+        tc_fence_after();
+        asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"((uint32_t)Cfg::TMEM_COLS) : "memory");
+    }
+}
+
+// ------------------------------------------------------------------ host side --
+typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
+                                  const cuuint64_t*, const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave,
+                                  CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+
+static EncodeTiledFn encode_fn() {
+    static EncodeTiledFn fn = nullptr;
+    static std::once_flag once;
+    std::call_once(once, [] {
+        void* p = nullptr;
+        cudaDriverEntryPointQueryResult q;
+        if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &p, cudaEnableDefault, &q) == cudaSuccess &&
+            q == cudaDriverEntryPointSuccess)
+            fn = reinterpret_cast<EncodeTiledFn>(p);
+    });
+    return fn;
+}
+
+struct MapKey {
+    const void* ptr; int rows, cols, box_rows;
+    bool operator==(const MapKey& o) const { return ptr == o.ptr && rows == o.rows && cols == o.cols && box_rows == o.box_rows; }
+};
+struct MapKeyHash {
+    size_t operator()(const MapKey& k) const {
+        return std::hash<const void*>()(k.ptr) ^ ((size_t)k.rows * 1000003u) ^ ((size_t)k.cols * 7919u) ^ (size_t)k.box_rows;
+    }
+};
+
+// Tensor map of a row-major bfloat16 matrix [rows, cols]: boxes of box_rows x 64, 128-byte swizzle,
+// zeros outside the matrix.
+static int make_map(const void* ptr, int rows, int cols, int box_rows, CUtensorMap* out) {
+    static std::mutex mu;
+    static std::unordered_map<MapKey, CUtensorMap, MapKeyHash> cache;
+    std::lock_guard<std::mutex> lock(mu);
+    const MapKey key{ptr, rows, cols, box_rows};
+    auto it = cache.find(key);
+    if (it != cache.end()) { *out = it->second; return 0; }
+    EncodeTiledFn fn = encode_fn();
+    if (!fn) return FF_ERR_UNSUPPORTED;
+    cuuint64_t dims[2] = {(cuuint64_t)cols, (cuuint64_t)rows};
+    cuuint64_t strides[1] = {(cuuint64_t)cols * 2};
+    cuuint32_t box[2] = {(cuuint32_t)BK, (cuuint32_t)box_rows};
+    cuuint32_t estr[2] = {1, 1};
+    CUresult r = fn(out, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, const_cast<void*>(ptr), dims, strides, box, estr,
+                    CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                    CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+    if (r != CUDA_SUCCESS) return FF_ERR_BAD_ARG;
+    if (cache.size() > 8192) cache.clear();
+    cache.emplace(key, *out);
+    return 0;
+}
+
+template <int TOK>
+static int launch(const CUtensorMap& mw, const CUtensorMap& mx, const GemmArgs& a, int n_tiles, int t_tiles,
+                  cudaStream_t stream) {
+    using Cfg = TileCfg<TOK>;
+    static bool attr_set = false;
+    if (!attr_set) {
+        cudaError_t e = cudaFuncSetAttribute(gemm_tc_kernel<TOK>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)Cfg::SMEM);
+        if (e != cudaSuccess) return (int)e;
+        attr_set = true;
+    }
+    dim3 grid(n_tiles, t_tiles, a.splits);
+    gemm_tc_kernel<TOK><<<grid, GEMM_THREADS, Cfg::SMEM, stream>>>(mw, mx, a);
+    FF_LAUNCH_CHECK();
+    return 0;
+}
+
+}  // namespace ff
+
+using namespace ff;
+
+// How many floats of scratch and how many counters a call needs (0 floats when splits == 1).
+FF_EXPORT int ff_gemm_tc_plan(int T, int N, int K, int want_splits, int* tok_out, int* splits_out,
+                              long long* partial_floats, int* n_counters) {
+    int tok = 16;
+    while (tok < T && tok < 256) tok <<= 1;
+    const int n_tiles = (N + BN - 1) / BN, t_tiles = (T + tok - 1) / tok;
+    const int num_kb = (K + BK - 1) / BK;
+    int splits = want_splits < 1 ? 1 : want_splits;
+    if (splits > num_kb) splits = num_kb;
+    const int per = (num_kb + splits - 1) / splits;
+    splits = (num_kb + per - 1) / per;                   // no empty K range
+    *tok_out = tok;
+    *splits_out = splits;
+    *partial_floats = splits > 1 ? (long long)splits * n_tiles * t_tiles * tok * BN : 0;
+    *n_counters = n_tiles * t_tiles;
+    return 0;
+}
+
+// x: bfloat16 [T, K] contiguous; w: bfloat16 [N, K] contiguous; K a multiple of 8.
+// epilogue: 0 bf16 out [T, ldo], 1 f32 out, 2 f32 out += , 3 swiglu (bf16 out [T, ldo], N/2 columns).
+FF_EXPORT int ff_gemm_tc(const void* x, const void* w, void* out, int ldo, int T, int N, int K, int epilogue,
+                         int want_splits, float* partials, long long partial_floats, int* counters,
+                         int n_counters, int* status, cudaStream_t stream) {
+    if (T <= 0 || N <= 0) return 0;
+    if (K <= 0 || (K % 8) || epilogue < 0 || epilogue > 3) return FF_ERR_BAD_ARG;
+    if (epilogue == EPI_SWIGLU && (N % 32)) return FF_ERR_UNSUPPORTED;
+    if (((uintptr_t)x & 15) || ((uintptr_t)w & 15)) return FF_ERR_BAD_ARG;
+    int tok, splits, need_counters;
+    long long need_floats;
+    ff_gemm_tc_plan(T, N, K, want_splits, &tok, &splits, &need_floats, &need_counters);
+    if (splits > 1 && (need_floats > partial_floats || need_counters > n_counters || !partials || !counters))
+        return FF_ERR_BAD_ARG;
+    const int n_tiles = (N + BN - 1) / BN, t_tiles = (T + tok - 1) / tok;
+    const int num_kb = (K + BK - 1) / BK;
+    CUtensorMap mw, mx;
+    int rc = make_map(w, N, K, BN, &mw);
+    if (rc) return rc;
+    rc = make_map(x, T, K, tok, &mx);
+    if (rc) return rc;
+    GemmArgs a;
+    a.out = out; a.ldo = ldo; a.T = T; a.N = N; a.K = K; a.epilogue = epilogue; a.splits = splits;
+    a.kb_per_split = (num_kb + splits - 1) / splits;
+    a.partials = partials; a.counters = counters; a.status = status;
+    switch (tok) {
+        case 16: return launch<16>(mw, mx, a, n_tiles, t_tiles, stream);
+        case 32: return launch<32>(mw, mx, a, n_tiles, t_tiles, stream);
+        case 64: return launch<64>(mw, mx, a, n_tiles, t_tiles, stream);
+        case 128: return launch<128>(mw, mx, a, n_tiles, t_tiles, stream);
+        default: return launch<256>(mw, mx, a, n_tiles, t_tiles, stream);
+    }
+}

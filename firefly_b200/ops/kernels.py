@@ -67,6 +67,7 @@ _MODULES = {
     "qk_rope_store": ("qk_rope_store.cu", None),
     "attention_simt": ("attention_simt.cu", None),
     "sampling": ("sampling.cu", None),
+    "gemm_tcgen05": ("gemm_tcgen05.cu", None),
 }
 
 
@@ -223,6 +224,51 @@ def linear(x: torch.Tensor, weight: torch.Tensor, out: torch.Tensor) -> None:
         torch.mm(x, weight.t(), out_dtype=torch.float32, out=out)
     else:
         raise KernelError(f"linear: cannot write {out.dtype} from {x.dtype}")
+
+
+EPI_BF16, EPI_F32, EPI_RESIDUAL_ADD, EPI_SWIGLU = 0, 1, 2, 3
+
+
+def gemm_tc_plan(T: int, N: int, K: int, want_splits: int):
+    """(tokens per tile, K ranges, floats of scratch, counters) the tensor-core product would use."""
+    tok, splits, cnt = c_int(), c_int(), c_int()
+    floats = c_longlong()
+    _lib("gemm_tcgen05").ff_gemm_tc_plan(c_int(T), c_int(N), c_int(K), c_int(want_splits), ctypes.byref(tok),
+                                       ctypes.byref(splits), ctypes.byref(floats), ctypes.byref(cnt))
+    return tok.value, splits.value, floats.value, cnt.value
+
+
+def gemm_tc(x: torch.Tensor, weight: torch.Tensor, out: torch.Tensor, epilogue: int, want_splits: int,
+            partials: Optional[torch.Tensor], counters: Optional[torch.Tensor], status: torch.Tensor) -> None:
+    """out (op)= x @ weight^T on tcgen05 tensor cores; bfloat16 operands, 32-bit accumulation.
+
+    epilogue: EPI_BF16 store bfloat16, EPI_F32 store float32, EPI_RESIDUAL_ADD add into a float32
+    ``out``, EPI_SWIGLU store silu(gate)*up as bfloat16 [T, N/2] for a weight whose rows interleave
+    gate and up in groups of 16.  ``partials`` (float32) and ``counters`` (int32, zero) are scratch
+    for the split over K; see ``gemm_tc_plan``."""
+    _need_cuda(x, weight, out, partials, counters, status)
+    assert x.dtype == torch.bfloat16 and weight.dtype == torch.bfloat16
+    T, Kd = x.shape
+    N = weight.shape[0]
+    assert weight.shape[1] == Kd
+    if epilogue == EPI_BF16 or epilogue == EPI_SWIGLU:
+        assert out.dtype == torch.bfloat16
+    else:
+        assert out.dtype == torch.float32
+    assert out.shape[0] == T and out.shape[1] == (N // 2 if epilogue == EPI_SWIGLU else N)
+    _check(_lib("gemm_tcgen05").ff_gemm_tc(
+        _p(x), _p(weight), _p(out), c_int(out.stride(0)), c_int(T), c_int(N), c_int(Kd), c_int(epilogue),
+        c_int(want_splits), _p(partials), c_longlong(partials.numel() if partials is not None else 0),
+        _p(counters), c_int(counters.numel() if counters is not None else 0), _p(status), _stream()),
+        "gemm_tc")
+
+
+def interleave_gate_up(gate: torch.Tensor, up: torch.Tensor) -> torch.Tensor:
+    """Stack gate and up rows in groups of 16: rows [32g, 32g+16) are gate rows [16g, 16g+16),
+    rows [32g+16, 32g+32) the up rows of the same columns.  Needs I % 16 == 0."""
+    I, H = gate.shape
+    assert I % 16 == 0 and up.shape == gate.shape
+    return torch.stack([gate.view(I // 16, 16, H), up.view(I // 16, 16, H)], dim=1).reshape(2 * I, H).contiguous()
 
 
 def set_exact_matmul() -> None:

@@ -1,0 +1,88 @@
+"""The tcgen05 matrix product alone against a 32-bit reference: token counts from 1
+to several tiles, widths and depths that are no multiple of the tile, splits over
+K, and each epilogue."""
+import pytest
+import torch
+
+pytestmark = pytest.mark.gpu
+
+
+def K():
+    from firefly_b200.ops import kernels
+    return kernels
+
+
+def _run(T, N, Kd, splits, epilogue, seed=0):
+    k = K()
+    g = torch.Generator().manual_seed(seed)
+    x = (torch.randn(T, Kd, generator=g)).to(torch.bfloat16)
+    w = (torch.randn(N, Kd, generator=g) / Kd ** 0.5).to(torch.bfloat16)
+    ref = x.double() @ w.double().T
+    tok, s, floats, cnt = k.gemm_tc_plan(T, N, Kd, splits)
+    partials = torch.full((max(floats, 1),), float("nan"), device="cuda")
+    counters = torch.zeros(cnt, dtype=torch.int32, device="cuda")
+    status = torch.zeros(1, dtype=torch.int32, device="cuda")
+    xd, wd = x.cuda(), w.cuda()
+    if epilogue == k.EPI_BF16:
+        out = torch.zeros(T, N, dtype=torch.bfloat16, device="cuda")
+        want = ref
+    elif epilogue == k.EPI_F32:
+        out = torch.zeros(T, N, dtype=torch.float32, device="cuda")
+        want = ref
+    elif epilogue == k.EPI_RESIDUAL_ADD:
+        base = torch.randn(T, N, generator=g)
+        out = base.cuda()
+        want = base.double() + ref
+    else:
+        I = N // 2
+        gate, up = w[:I], w[I:]
+        wd = k.interleave_gate_up(gate.cuda(), up.cuda())
+        out = torch.zeros(T, I, dtype=torch.bfloat16, device="cuda")
+        gv, uv = x.double() @ gate.double().T, x.double() @ up.double().T
+        want = gv / (1 + torch.exp(-gv)) * uv
+    for rep in range(2):                      # twice: the counters must have been left at zero
+        if epilogue == k.EPI_RESIDUAL_ADD and rep:
+            out.copy_(base)
+        k.gemm_tc(xd, wd, out, epilogue, splits, partials, counters, status)
+        torch.cuda.synchronize()
+        assert int(status) == 0
+        assert int(counters.abs().sum()) == 0
+        tol = 2e-2 if out.dtype == torch.bfloat16 else 2e-3
+        err = float((out.cpu().double() - want).abs().max()) / (float(want.abs().max()) + 1e-9)
+        assert err < tol, (T, N, Kd, splits, epilogue, s, tok, err)
+
+
+@pytest.mark.parametrize("T", [1, 8, 16, 17, 64, 100, 256, 300])
+@pytest.mark.parametrize("N,Kd", [(128, 64), (384, 512), (200, 1000), (4096, 4096)])
+def test_store_bf16(T, N, Kd):
+    _run(T, N, Kd, 1, K().EPI_BF16)
+
+
+@pytest.mark.parametrize("T", [1, 8, 33])
+@pytest.mark.parametrize("splits", [2, 3, 8, 100])
+@pytest.mark.parametrize("N,Kd", [(256, 1024), (72, 200), (1024, 12288)])
+def test_split_k(T, splits, N, Kd):
+    _run(T, N, Kd, splits, K().EPI_F32)
+
+
+@pytest.mark.parametrize("T", [3, 64, 130])
+@pytest.mark.parametrize("splits", [1, 4])
+def test_residual_add(T, splits):
+    _run(T, 4096 + 64, 1536, splits, K().EPI_RESIDUAL_ADD)
+
+
+@pytest.mark.parametrize("T", [1, 8, 70])
+@pytest.mark.parametrize("splits", [1, 3])
+@pytest.mark.parametrize("I", [160, 2048, 12288])
+def test_swiglu(T, splits, I):
+    _run(T, 2 * I, 512, splits, K().EPI_SWIGLU)
+
+
+def test_refuses_what_it_cannot_do():
+    k = K()
+    x = torch.zeros(4, 20, dtype=torch.bfloat16, device="cuda")
+    w = torch.zeros(16, 20, dtype=torch.bfloat16, device="cuda")
+    out = torch.zeros(4, 16, dtype=torch.bfloat16, device="cuda")
+    st = torch.zeros(1, dtype=torch.int32, device="cuda")
+    with pytest.raises(k.KernelError, match="bad argument"):
+        k.gemm_tc(x, w, out, k.EPI_BF16, 1, None, None, st)      # K not a multiple of 8
