@@ -60,28 +60,41 @@ __device__ __forceinline__ uint32_t pack_bf16(float lo, float hi) {
     return *reinterpret_cast<uint32_t*>(&v);
 }
 
-// Copy keys [key0, key0+BN) of one kv head into smem tiles (K and V), zero-filling
-// keys outside [kv_lo, kv_hi) and keys whose page is missing.
-__device__ __forceinline__ void load_kv_tile(bf16* Ks, bf16* Vs, const bf16* __restrict__ cache,
-                                             const int* __restrict__ bt, int max_blocks, int num_blocks,
-                                             int nkv, int kh, int block_size, int key0, int kv_lo, int kv_hi) {
-    for (int c = threadIdx.x; c < BN * CHUNKS; c += NTHREADS) {
-        const int row = c / CHUNKS, ch = c % CHUNKS;
-        const int key = key0 + row;
-        bool ok = key >= kv_lo && key < kv_hi;
-        const bf16* ksrc = cache;
-        const bf16* vsrc = cache;
-        if (ok) {
+static_assert(NTHREADS >= BN, "one thread looks up each key row of a tile");
+static_assert((BN * CHUNKS) % NTHREADS == 0, "the copy loop has no tail");
+
+// Where each key row of the tile that starts at key0 lies in the cache, as an element offset
+// of its K row (the V row is v_off further), or -1 when the key is outside [kv_lo, kv_hi) or
+// its page is missing.  Thread r < BN looks up row r: one block-table read per row and tile.
+__device__ __forceinline__ void kv_row_offsets(long long* row_off, const int* __restrict__ bt, int max_blocks,
+                                               int num_blocks, int nkv, int kh, int block_size, int key0,
+                                               int kv_lo, int kv_hi) {
+    if (threadIdx.x < BN) {
+        const int key = key0 + threadIdx.x;
+        long long off = -1;
+        if (key >= kv_lo && key < kv_hi) {
             const int pi = key / block_size;
             const int page = pi < max_blocks ? bt[pi] : -1;
-            ok = page >= 0 && page < num_blocks;
-            if (ok) {
-                ksrc = cache + ((((size_t)page * 2) * nkv + kh) * block_size + key % block_size) * D + ch * 8;
-                vsrc = ksrc + (size_t)nkv * block_size * D;
-            }
+            if (page >= 0 && page < num_blocks)
+                off = ((((long long)page * 2) * nkv + kh) * block_size + (key - pi * block_size)) * D;
         }
-        cp_async16(Ks + row * KSTR + ch * 8, ksrc, ok);
-        cp_async16(Vs + row * KSTR + ch * 8, vsrc, ok);
+        row_off[threadIdx.x] = off;
+    }
+}
+
+// Copy a tile's K and V rows into shared memory, 16 bytes a thread, neighbouring threads on
+// neighbouring pieces of a row; rows that are not there become zeros.
+__device__ __forceinline__ void load_kv_tile(bf16* Ks, bf16* Vs, const bf16* __restrict__ cache,
+                                             const long long* row_off, size_t v_off) {
+#pragma unroll
+    for (int i = 0; i < BN * CHUNKS / NTHREADS; ++i) {
+        const int idx = i * NTHREADS + threadIdx.x;
+        const int row = idx / CHUNKS, ch = idx % CHUNKS;
+        const long long off = row_off[row];
+        const bool ok = off >= 0;
+        const bf16* src = cache + (ok ? off : 0) + ch * 8;
+        cp_async16(Ks + row * KSTR + ch * 8, src, ok);
+        cp_async16(Vs + row * KSTR + ch * 8, src + v_off, ok);
     }
 }
 
@@ -201,6 +214,7 @@ attn_tiled_kernel(const bf16* __restrict__ q, int q_stride, const bf16* __restri
                   const int* __restrict__ block_table, int max_blocks, const int* __restrict__ cu_q,
                   const int* __restrict__ ctx_lens, int n_seqs, bf16* __restrict__ out, int out_stride,
                   int nq, int nkv, int block_size, int num_blocks, float scale_log2, int window) {
+    pdl_prologue();
     extern __shared__ __align__(16) unsigned char smem_raw[];
     bf16* Qs = reinterpret_cast<bf16*>(smem_raw);                 // [BM][KSTR]
     bf16* Ks = Qs + BM * KSTR;                                    // [2][BN][KSTR]
@@ -258,7 +272,13 @@ attn_tiled_kernel(const bf16* __restrict__ q, int q_stride, const bf16* __restri
     const int kv_lo = window > 0 ? max(0, ctx + first_tok - window + 1) : 0;
     const int t_begin = kv_lo / BN, t_end = (kv_hi + BN - 1) / BN;
 
-    load_kv_tile(Ks, Vs, cache, bt, max_blocks, num_blocks, nkv, kh, block_size, t_begin * BN, kv_lo, kv_hi);
+    const size_t v_off = (size_t)nkv * block_size * D;
+    __shared__ long long s_row_off[2][BN];
+    kv_row_offsets(s_row_off[0], bt, max_blocks, num_blocks, nkv, kh, block_size, t_begin * BN, kv_lo, kv_hi);
+    if (t_begin + 1 < t_end)
+        kv_row_offsets(s_row_off[1], bt, max_blocks, num_blocks, nkv, kh, block_size, (t_begin + 1) * BN, kv_lo, kv_hi);
+    __syncthreads();
+    load_kv_tile(Ks, Vs, cache, s_row_off[0], v_off);
     cp_async_commit();
 
     // this thread's two rows
@@ -283,14 +303,16 @@ attn_tiled_kernel(const bf16* __restrict__ q, int q_stride, const bf16* __restri
     for (int t = t_begin; t < t_end; ++t) {
         const int buf = (t - t_begin) & 1;
         if (t + 1 < t_end) {
-            load_kv_tile(Ks + (buf ^ 1) * BN * KSTR, Vs + (buf ^ 1) * BN * KSTR, cache, bt, max_blocks,
-                         num_blocks, nkv, kh, block_size, (t + 1) * BN, kv_lo, kv_hi);
+            load_kv_tile(Ks + (buf ^ 1) * BN * KSTR, Vs + (buf ^ 1) * BN * KSTR, cache, s_row_off[buf ^ 1], v_off);
             cp_async_commit();
             cp_async_wait<1>();
         } else {
             cp_async_wait<0>();
         }
         __syncthreads();
+        // the offsets of tile t are used up: look up those of tile t+2 (read after the next barrier)
+        if (t + 2 < t_end)
+            kv_row_offsets(s_row_off[buf], bt, max_blocks, num_blocks, nkv, kh, block_size, (t + 2) * BN, kv_lo, kv_hi);
         const int key0 = t * BN;
         if (warp_active && key0 <= warp_last_pos && key0 + BN > warp_lo) {   // warp-uniform
             const bool need_mask = key0 + BN > warp_first_pos + 1 || key0 < full_lo || key0 < kv_lo;
@@ -326,6 +348,7 @@ attn_decode_kernel(const bf16* __restrict__ q, int q_stride, const bf16* __restr
                    const int* __restrict__ ctx_lens, bf16* __restrict__ out, int out_stride,
                    float* __restrict__ part_o, float* __restrict__ part_ml, int nq, int nkv,
                    int block_size, int num_blocks, float scale_log2, int window, int num_splits) {
+    pdl_prologue();
     extern __shared__ __align__(16) unsigned char smem_raw[];
     bf16* Qs = reinterpret_cast<bf16*>(smem_raw);                 // [16][KSTR]
     bf16* Ks = Qs + 16 * KSTR;                                    // [2][BN][KSTR]
@@ -348,8 +371,14 @@ attn_decode_kernel(const bf16* __restrict__ q, int q_stride, const bf16* __restr
         const bf16* src = ok ? q + (size_t)tok * q_stride + (size_t)(kh * G + r) * D + ch * 8 : q;
         cp_async16(Qs + r * KSTR + ch * 8, src, ok);
     }
+    const size_t v_off = (size_t)nkv * block_size * D;
+    __shared__ long long s_row_off[2][BN];
     if (t_begin < t_end)
-        load_kv_tile(Ks, Vs, cache, bt, max_blocks, num_blocks, nkv, kh, block_size, t_begin * BN, kv_lo, kv_hi);
+        kv_row_offsets(s_row_off[0], bt, max_blocks, num_blocks, nkv, kh, block_size, t_begin * BN, kv_lo, kv_hi);
+    if (t_begin + 1 < t_end)
+        kv_row_offsets(s_row_off[1], bt, max_blocks, num_blocks, nkv, kh, block_size, (t_begin + 1) * BN, kv_lo, kv_hi);
+    __syncthreads();
+    if (t_begin < t_end) load_kv_tile(Ks, Vs, cache, s_row_off[0], v_off);
     cp_async_commit();
 
     int lo[2] = {kv_lo, kv_lo}, hi[2] = {kv_hi, kv_hi};
@@ -358,14 +387,15 @@ attn_decode_kernel(const bf16* __restrict__ q, int q_stride, const bf16* __restr
     for (int t = t_begin; t < t_end; ++t) {
         const int buf = (t - t_begin) & 1;
         if (t + 1 < t_end) {
-            load_kv_tile(Ks + (buf ^ 1) * BN * KSTR, Vs + (buf ^ 1) * BN * KSTR, cache, bt, max_blocks,
-                         num_blocks, nkv, kh, block_size, (t + 1) * BN, kv_lo, kv_hi);
+            load_kv_tile(Ks + (buf ^ 1) * BN * KSTR, Vs + (buf ^ 1) * BN * KSTR, cache, s_row_off[buf ^ 1], v_off);
             cp_async_commit();
             cp_async_wait<1>();
         } else {
             cp_async_wait<0>();
         }
         __syncthreads();
+        if (t + 2 < t_end)
+            kv_row_offsets(s_row_off[buf], bt, max_blocks, num_blocks, nkv, kh, block_size, (t + 2) * BN, kv_lo, kv_hi);
         const int key0 = t * BN + warp * 16;
         if (key0 < kv_hi && key0 + 16 > kv_lo) {
             const bool need_mask = key0 + 16 > kv_hi || key0 < kv_lo;
@@ -421,6 +451,7 @@ attn_decode_kernel(const bf16* __restrict__ q, int q_stride, const bf16* __restr
 __global__ void attn_combine_kernel(const float* __restrict__ part_o, const float* __restrict__ part_ml,
                                     const int* __restrict__ cu_q, bf16* __restrict__ out, int out_stride,
                                     int nq, int num_splits) {
+    pdl_prologue();
     const int seq = blockIdx.x, head = blockIdx.y;
     const size_t base = ((size_t)seq * nq + head) * num_splits;
     float M = -CUDART_INF_F;
@@ -469,7 +500,7 @@ FF_EXPORT int ff_attn_tiled(const void* q, int q_stride, const void* cache, cons
         attr_set = true;
     }
     dim3 grid(total_tiles, nkv);
-    attn_tiled_kernel<<<grid, NTHREADS, TILED_SMEM, stream>>>(
+    FF_LAUNCH((attn_tiled_kernel), grid, NTHREADS, TILED_SMEM, stream, 
         (const bf16*)q, q_stride, (const bf16*)cache, block_table, max_blocks, cu_q, ctx_lens, n_seqs,
         (bf16*)out, out_stride, nq, nkv, block_size, num_blocks, scale * LOG2E, window);
     FF_LAUNCH_CHECK();
@@ -494,13 +525,13 @@ FF_EXPORT int ff_attn_decode(const void* q, int q_stride, const void* cache, con
         attr_set = true;
     }
     dim3 grid(n_seqs, nkv, num_splits);
-    attn_decode_kernel<<<grid, NTHREADS, DECODE_SMEM, stream>>>(
+    FF_LAUNCH((attn_decode_kernel), grid, NTHREADS, DECODE_SMEM, stream, 
         (const bf16*)q, q_stride, (const bf16*)cache, block_table, max_blocks, cu_q, ctx_lens, (bf16*)out,
         out_stride, part_o, part_ml, nq, nkv, block_size, num_blocks, scale * LOG2E, window, num_splits);
     FF_LAUNCH_CHECK();
     if (num_splits > 1) {
         dim3 cgrid(n_seqs, nq);
-        attn_combine_kernel<<<cgrid, D >= 128 ? 128 : 64, 0, stream>>>(part_o, part_ml, cu_q, (bf16*)out,
+        FF_LAUNCH((attn_combine_kernel), cgrid, D >= 128 ? 128 : 64, 0, stream, part_o, part_ml, cu_q, (bf16*)out,
                                                                      out_stride, nq, num_splits);
         FF_LAUNCH_CHECK();
     }

@@ -28,6 +28,7 @@ __global__ void paged_attention_simt_kernel(
     const int* __restrict__ block_table, int max_blocks, const int* __restrict__ token_seq,
     const int* __restrict__ positions, T* __restrict__ out, int out_stride, int nq, int nkv, int d,
     int block_size, int num_blocks, float scale, int window, int* __restrict__ status) {
+    pdl_prologue();
     __shared__ float s_m[ATT_WARPS], s_l[ATT_WARPS];
     __shared__ float s_acc[ATT_WARPS][ATT_MAX_D];
     const int t = blockIdx.x, h = blockIdx.y;
@@ -112,11 +113,11 @@ FF_EXPORT int ff_paged_attention_simt(const void* q, int dtype, int q_stride, co
     if (nkv <= 0 || nq % nkv) return FF_ERR_BAD_ARG;
     dim3 grid(T, nq);
     if (dtype == 0)
-        paged_attention_simt_kernel<float><<<grid, ATT_WARPS * 32, 0, stream>>>(
+        FF_LAUNCH((paged_attention_simt_kernel<float>), grid, ATT_WARPS * 32, 0, stream, 
             (const float*)q, q_stride, (const float*)cache, block_table, max_blocks, token_seq,
             positions, (float*)out, out_stride, nq, nkv, d, block_size, num_blocks, scale, window, status);
     else if (dtype == 1)
-        paged_attention_simt_kernel<bf16><<<grid, ATT_WARPS * 32, 0, stream>>>(
+        FF_LAUNCH((paged_attention_simt_kernel<bf16>), grid, ATT_WARPS * 32, 0, stream, 
             (const bf16*)q, q_stride, (const bf16*)cache, block_table, max_blocks, token_seq,
             positions, (bf16*)out, out_stride, nq, nkv, d, block_size, num_blocks, scale, window, status);
     else

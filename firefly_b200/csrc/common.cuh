@@ -17,7 +17,42 @@
         if (_e != cudaSuccess) return (int)_e;    \
     } while (0)
 
+// Programmatic dependent launch.  When switched on (ff_set_pdl(1), per library) every kernel
+// is launched with the programmatic-stream-serialization attribute: it may begin while the
+// kernel before it in the stream is still running.  Each kernel therefore first lets its own
+// dependents start (griddepcontrol.launch_dependents) and then waits for its predecessors to
+// finish and their writes to be visible (griddepcontrol.wait) before it touches any memory
+// they produce.  In a launch without the attribute both instructions do nothing.
+static int g_ff_pdl = 0;
+FF_EXPORT void ff_set_pdl(int on) { g_ff_pdl = on; }
+
 namespace ff {
+
+template <typename... KArgs, typename... Args>
+static inline int launch_kernel(void (*kernel)(KArgs...), dim3 grid, dim3 block, size_t smem,
+                                cudaStream_t stream, Args... args) {
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = grid;
+    cfg.blockDim = block;
+    cfg.dynamicSmemBytes = smem;
+    cfg.stream = stream;
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[0].val.programmaticStreamSerializationAllowed = 1;
+    cfg.attrs = attr;
+    cfg.numAttrs = g_ff_pdl ? 1 : 0;
+    return (int)cudaLaunchKernelEx(&cfg, kernel, static_cast<KArgs>(args)...);
+}
+
+#define FF_LAUNCH(kernel, grid, block, smem, stream, ...)                                              \
+    do {                                                                                               \
+        int _rc = ff::launch_kernel(kernel, dim3(grid), dim3(block), (size_t)(smem), stream, __VA_ARGS__); \
+        if (_rc) return _rc;                                                                           \
+    } while (0)
+
+__device__ __forceinline__ void pdl_prologue() {
+    asm volatile("griddepcontrol.launch_dependents;\n\tgriddepcontrol.wait;" ::: "memory");
+}
 
 using bf16 = __nv_bfloat16;
 

@@ -13,6 +13,7 @@ namespace ff {
 template <typename TT>
 __global__ void embedding_kernel(const int* __restrict__ ids, const TT* __restrict__ table,
                                  float* __restrict__ out, int H, int V, int* __restrict__ status) {
+    pdl_prologue();
     const int t = blockIdx.x;
     int id = ids[t];
     if (id < 0 || id >= V) {  // never read outside the table; report it
@@ -32,6 +33,7 @@ __global__ void add_rms_norm_kernel(float* __restrict__ residual, const TD* __re
                                     const int* __restrict__ row_idx, const float* __restrict__ w,
                                     float eps, TO* __restrict__ out, int H, int write_residual,
                                     int use_smem) {
+    pdl_prologue();
     extern __shared__ float row[];
     __shared__ float scratch[32];
     const int r = blockIdx.x;
@@ -58,20 +60,28 @@ __global__ void add_rms_norm_kernel(float* __restrict__ residual, const TD* __re
 }
 
 // ------------------------------------------------------------------ SwiGLU --
-// out[t,i] = silu(gu[t,i]) * gu[t,I+i]
+// out[t,i] = silu(g) * u with g = gu[t,i], u = gu[t,I+i]; or, when the columns of gu
+// interleave gate and up in groups of 16 (the layout the fused product uses for its
+// weight), g = gu[t, 32*(i/16) + i%16], u = gu[t, 32*(i/16) + 16 + i%16].
 template <typename T>
-__global__ void silu_mul_kernel(const T* __restrict__ gu, T* __restrict__ out, int I, size_t total) {
+__global__ void silu_mul_kernel(const T* __restrict__ gu, T* __restrict__ out, int I, size_t total,
+                                int interleaved) {
+    pdl_prologue();
     size_t idx = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
     if (idx >= total) return;
     size_t t = idx / I;
     int i = (int)(idx - t * I);
-    float g = to_float(gu[t * 2 * I + i]);
-    float u = to_float(gu[t * 2 * I + I + i]);
+    const T* row = gu + t * 2 * I;
+    const int gi = interleaved ? 32 * (i / 16) + (i % 16) : i;
+    const int ui = interleaved ? gi + 16 : I + i;
+    float g = to_float(row[gi]);
+    float u = to_float(row[ui]);
     out[idx] = from_float<T>(g / (1.0f + expf(-g)) * u);
 }
 
 template <typename TI, typename TO>
 __global__ void cast_kernel(const TI* __restrict__ in, TO* __restrict__ out, size_t n) {
+    pdl_prologue();
     size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
     if (i < n) out[i] = from_float<TO>(to_float(in[i]));
 }
@@ -79,6 +89,7 @@ __global__ void cast_kernel(const TI* __restrict__ in, TO* __restrict__ out, siz
 // out[r,:] += delta[r,:]   (32-bit residual, delta of either type)
 template <typename TD>
 __global__ void add_kernel(float* __restrict__ res, const TD* __restrict__ delta, size_t n) {
+    pdl_prologue();
     size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
     if (i < n) res[i] += to_float(delta[i]);
 }
@@ -101,9 +112,9 @@ FF_EXPORT int ff_embedding(const int* ids, const void* table, int table_dtype, f
     if (T <= 0) return 0;
     int threads = H >= 1024 ? 256 : (H >= 256 ? 128 : 64);
     if (table_dtype == 0)
-        embedding_kernel<float><<<T, threads, 0, stream>>>(ids, (const float*)table, out, H, V, status);
+        FF_LAUNCH((embedding_kernel<float>), T, threads, 0, stream, ids, (const float*)table, out, H, V, status);
     else if (table_dtype == 1)
-        embedding_kernel<bf16><<<T, threads, 0, stream>>>(ids, (const bf16*)table, out, H, V, status);
+        FF_LAUNCH((embedding_kernel<bf16>), T, threads, 0, stream, ids, (const bf16*)table, out, H, V, status);
     else
         return FF_ERR_BAD_ARG;
     FF_LAUNCH_CHECK();
@@ -122,7 +133,7 @@ static int launch_add_rms_norm(float* residual, const void* delta, const int* ro
         cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
         if (e != cudaSuccess) return (int)e;
     }
-    kern<<<rows, norm_threads(H), smem, stream>>>(residual, (const TD*)delta, row_idx, w, eps, (TO*)out,
+    FF_LAUNCH((kern), rows, norm_threads(H), smem, stream, residual, (const TD*)delta, row_idx, w, eps, (TO*)out,
                                                   H, write_residual, use_smem);
     FF_LAUNCH_CHECK();
     return 0;
@@ -145,12 +156,14 @@ FF_EXPORT int ff_add_rms_norm(float* residual, const void* delta, int delta_dtyp
     return FF_ERR_BAD_ARG;
 }
 
-FF_EXPORT int ff_silu_mul(const void* gate_up, void* out, int dtype, int T, int I, cudaStream_t stream) {
+FF_EXPORT int ff_silu_mul(const void* gate_up, void* out, int dtype, int T, int I, int interleaved,
+                          cudaStream_t stream) {
+    if (interleaved && (I % 16)) return FF_ERR_BAD_ARG;
     size_t total = (size_t)T * I;
     if (total == 0) return 0;
     unsigned blocks = (unsigned)((total + 255) / 256);
-    if (dtype == 0) silu_mul_kernel<float><<<blocks, 256, 0, stream>>>((const float*)gate_up, (float*)out, I, total);
-    else if (dtype == 1) silu_mul_kernel<bf16><<<blocks, 256, 0, stream>>>((const bf16*)gate_up, (bf16*)out, I, total);
+    if (dtype == 0) FF_LAUNCH((silu_mul_kernel<float>), blocks, 256, 0, stream, (const float*)gate_up, (float*)out, I, total, interleaved);
+    else if (dtype == 1) FF_LAUNCH((silu_mul_kernel<bf16>), blocks, 256, 0, stream, (const bf16*)gate_up, (bf16*)out, I, total, interleaved);
     else return FF_ERR_BAD_ARG;
     FF_LAUNCH_CHECK();
     return 0;
@@ -159,10 +172,10 @@ FF_EXPORT int ff_silu_mul(const void* gate_up, void* out, int dtype, int T, int 
 FF_EXPORT int ff_cast(const void* in, int in_dtype, void* out, int out_dtype, size_t n, cudaStream_t stream) {
     if (n == 0) return 0;
     unsigned blocks = (unsigned)((n + 255) / 256);
-    if (in_dtype == 0 && out_dtype == 1) cast_kernel<float, bf16><<<blocks, 256, 0, stream>>>((const float*)in, (bf16*)out, n);
-    else if (in_dtype == 1 && out_dtype == 0) cast_kernel<bf16, float><<<blocks, 256, 0, stream>>>((const bf16*)in, (float*)out, n);
-    else if (in_dtype == 0 && out_dtype == 0) cast_kernel<float, float><<<blocks, 256, 0, stream>>>((const float*)in, (float*)out, n);
-    else if (in_dtype == 1 && out_dtype == 1) cast_kernel<bf16, bf16><<<blocks, 256, 0, stream>>>((const bf16*)in, (bf16*)out, n);
+    if (in_dtype == 0 && out_dtype == 1) FF_LAUNCH((cast_kernel<float, bf16>), blocks, 256, 0, stream, (const float*)in, (bf16*)out, n);
+    else if (in_dtype == 1 && out_dtype == 0) FF_LAUNCH((cast_kernel<bf16, float>), blocks, 256, 0, stream, (const bf16*)in, (float*)out, n);
+    else if (in_dtype == 0 && out_dtype == 0) FF_LAUNCH((cast_kernel<float, float>), blocks, 256, 0, stream, (const float*)in, (float*)out, n);
+    else if (in_dtype == 1 && out_dtype == 1) FF_LAUNCH((cast_kernel<bf16, bf16>), blocks, 256, 0, stream, (const bf16*)in, (bf16*)out, n);
     else return FF_ERR_BAD_ARG;
     FF_LAUNCH_CHECK();
     return 0;
@@ -171,8 +184,8 @@ FF_EXPORT int ff_cast(const void* in, int in_dtype, void* out, int out_dtype, si
 FF_EXPORT int ff_residual_add(float* residual, const void* delta, int delta_dtype, size_t n, cudaStream_t stream) {
     if (n == 0) return 0;
     unsigned blocks = (unsigned)((n + 255) / 256);
-    if (delta_dtype == 0) add_kernel<float><<<blocks, 256, 0, stream>>>(residual, (const float*)delta, n);
-    else if (delta_dtype == 1) add_kernel<bf16><<<blocks, 256, 0, stream>>>(residual, (const bf16*)delta, n);
+    if (delta_dtype == 0) FF_LAUNCH((add_kernel<float>), blocks, 256, 0, stream, residual, (const float*)delta, n);
+    else if (delta_dtype == 1) FF_LAUNCH((add_kernel<bf16>), blocks, 256, 0, stream, residual, (const bf16*)delta, n);
     else return FF_ERR_BAD_ARG;
     FF_LAUNCH_CHECK();
     return 0;

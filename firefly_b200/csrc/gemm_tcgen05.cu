@@ -6,10 +6,11 @@
 // The weight tile is the 128-row "M" operand of the MMA and the tokens are its "N"
 // dimension (16 to 256), so a decode step with a handful of tokens still fills the
 // tensor-core shape and the kernel's time is the time to stream the weights.  For
-// matrices with few row tiles the K range is split over several blocks; each writes
-// its partial tile to scratch memory, and the block that arrives last at the tile's
-// counter adds the partials in a fixed order and runs the epilogue, so the result
-// does not depend on which block was last.  Epilogues: store bfloat16, store
+// matrices with few row tiles the K range is split over the blocks of a thread-block
+// cluster (up to 8): each keeps its partial tile in its own shared memory, and after
+// a cluster barrier every block adds the partials of a slice of the tokens, in a
+// fixed order, reading its peers' shared memory, and runs the epilogue on that
+// slice.  No global scratch memory is involved.  Epilogues: store bfloat16, store
 // float32, add into a float32 residual, or SiLU(gate)*up for a weight whose rows
 // interleave gate and up in groups of 16.
 //
@@ -34,17 +35,27 @@ constexpr int BN = 128;          // weight rows per tile (MMA M)
 constexpr int BK = 64;           // k per stage: 128 bytes of bfloat16, one swizzle span
 constexpr int UMMA_K = 16;
 constexpr int GEMM_THREADS = 192;
+constexpr int NUM_SMS = 148;
 constexpr unsigned long long WAIT_LIMIT_CYCLES = 2000000000ull;   // about a second
 
 enum Epilogue { EPI_BF16 = 0, EPI_F32 = 1, EPI_RESIDUAL_ADD = 2, EPI_SWIGLU = 3 };
 
+constexpr int MAX_STAGES = 12;
+constexpr size_t SMEM_BUDGET = 200 * 1024;   // of the 227 KB a block may have
+
 template <int TOK> struct TileCfg {
-    static constexpr int STAGES = TOK <= 32 ? 5 : 4;
     static constexpr int A_BYTES = BN * BK * 2;
     static constexpr int B_BYTES = TOK * BK * 2;
     static constexpr int STAGE_BYTES = A_BYTES + B_BYTES;
     static constexpr int TMEM_COLS = TOK < 32 ? 32 : TOK;
-    static constexpr size_t SMEM = (size_t)STAGES * STAGE_BYTES + 1024 /* alignment slack */ + 256 /* barriers */;
+    // pipeline depth: all the shared memory of an SM when one block per SM covers the grid
+    // (more weight tiles in flight, and more of them requested before the kernel in front has
+    // finished), half of it when two blocks share an SM
+    static constexpr int DEEP = (SMEM_BUDGET / STAGE_BYTES) > MAX_STAGES ? MAX_STAGES : (int)(SMEM_BUDGET / STAGE_BYTES);
+    static constexpr int SHALLOW = (SMEM_BUDGET / 2 / STAGE_BYTES) < 2 ? 2 : (int)(SMEM_BUDGET / 2 / STAGE_BYTES);
+    static constexpr size_t smem(int stages) {
+        return (size_t)stages * STAGE_BYTES + 1024 /* alignment slack */ + 256 /* barriers */;
+    }
 };
 
 // ---------------------------------------------------------------- PTX helpers --
@@ -106,6 +117,24 @@ __device__ __forceinline__ void tc_ld16(uint32_t taddr, float (&v)[16]) {
     for (int i = 0; i < 16; ++i) v[i] = __uint_as_float(r[i]);
 }
 
+// Programmatic dependent launch: let the next kernel in the stream begin its prologue, and wait
+// for the previous kernel's results.  Both do nothing in a launch without the attribute.
+__device__ __forceinline__ void grid_launch_dependents() { asm volatile("griddepcontrol.launch_dependents;" ::: "memory"); }
+__device__ __forceinline__ void grid_dependency_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
+
+__device__ __forceinline__ void cluster_sync_all() {
+    __syncwarp();
+    asm volatile("barrier.cluster.arrive.release.aligned;\n\tbarrier.cluster.wait.acquire.aligned;" ::: "memory");
+}
+// float at `addr` (a shared-memory address of this block) in the block of rank `rank` of the cluster
+__device__ __forceinline__ float ld_peer_smem(uint32_t addr, uint32_t rank) {
+    uint32_t peer;
+    float v;
+    asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(peer) : "r"(addr), "r"(rank));
+    asm volatile("ld.shared::cluster.f32 %0, [%1];" : "=f"(v) : "r"(peer) : "memory");
+    return v;
+}
+
 // Shared-memory operand descriptor: K-major tile, rows of 128 bytes, 128-byte swizzle;
 // groups of 8 rows are 1024 bytes apart.
 __device__ __forceinline__ uint64_t smem_desc_sw128(uint32_t addr) {
@@ -127,10 +156,9 @@ struct GemmArgs {
     int ldo;              // elements between rows (tokens) of out
     int T, N, K;
     int epilogue;
-    int splits;           // number of K ranges (grid.z)
+    int splits;           // number of K ranges = blocks per cluster (grid.z)
     int kb_per_split;     // 64-wide k blocks per range
-    float* partials;      // [splits][token tiles][row tiles][TOK][BN] when splits > 1
-    int* counters;        // [token tiles * row tiles], zero between launches
+    int stages;           // depth of the load pipeline
     int* status;
 };
 
@@ -139,16 +167,16 @@ __global__ void __launch_bounds__(GEMM_THREADS)
 gemm_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant__ CUtensorMap map_x,
                const GemmArgs a) {
     using Cfg = TileCfg<TOK>;
+    const int STAGES = a.stages;
     extern __shared__ unsigned char smem_raw[];
     // tiles need 1024-byte alignment for the 128-byte swizzle
     unsigned char* tiles = reinterpret_cast<unsigned char*>(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
-    uint64_t* bars = reinterpret_cast<uint64_t*>(tiles + (size_t)Cfg::STAGES * Cfg::STAGE_BYTES);
+    uint64_t* bars = reinterpret_cast<uint64_t*>(tiles + (size_t)STAGES * Cfg::STAGE_BYTES);
     // bars[0..S) full, bars[S..2S) empty, bars[2S] accumulator ready
     __shared__ uint32_t s_tmem_base;
-    __shared__ int s_abort, s_is_last;
+    __shared__ int s_abort;
 
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-    const int n_tiles = gridDim.x, t_tiles = gridDim.y;
     const int n0 = blockIdx.x * BN, t0 = blockIdx.y * TOK;
     const int num_kb = (a.K + BK - 1) / BK;
     const int kb0 = blockIdx.z * a.kb_per_split;
@@ -157,8 +185,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant_
 
     if (threadIdx.x == 0) {
         s_abort = 0;
-        s_is_last = 0;
-        for (int i = 0; i < 2 * Cfg::STAGES + 1; ++i) mbar_init(smem_addr(&bars[i]), 1);
+        for (int i = 0; i < 2 * STAGES + 1; ++i) mbar_init(smem_addr(&bars[i]), 1);
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     }
     if (warp == 1) {   // tensor memory for the accumulator: TOK columns of 128 lanes
@@ -171,14 +198,29 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant_
     tc_fence_after();
     const uint32_t tmem_base = s_tmem_base;
     volatile int* abort_flag = &s_abort;
+    grid_launch_dependents();
 
     if (warp == 0 && lane == 0) {
         // ------------------------------------------------ producer: TMA loads --
+        // The weights do not depend on the kernel before this one: the first stages' weight
+        // tiles are requested at once; the activations only after that kernel has finished.
         int issued = 0;
-        for (int it = 0; it < n_iters; ++it) {
-            const int s = it % Cfg::STAGES;
-            const uint32_t ph = (it / Cfg::STAGES) & 1;
-            if (!mbar_wait(smem_addr(&bars[Cfg::STAGES + s]), ph ^ 1, a.status, abort_flag, 101)) break;
+        const int pre = min(n_iters, STAGES);
+        for (int it = 0; it < pre; ++it) {
+            const uint32_t full = smem_addr(&bars[it]);
+            mbar_expect_tx(full, Cfg::STAGE_BYTES);
+            tma_load_2d(smem_addr(tiles + (size_t)it * Cfg::STAGE_BYTES), &map_w, (kb0 + it) * BK, n0, full);
+        }
+        grid_dependency_wait();
+        for (int it = 0; it < pre; ++it) {
+            tma_load_2d(smem_addr(tiles + (size_t)it * Cfg::STAGE_BYTES + Cfg::A_BYTES), &map_x, (kb0 + it) * BK, t0,
+                        smem_addr(&bars[it]));
+            issued = it + 1;
+        }
+        for (int it = pre; it < n_iters; ++it) {
+            const int s = it % STAGES;
+            const uint32_t ph = (it / STAGES) & 1;
+            if (!mbar_wait(smem_addr(&bars[STAGES + s]), ph ^ 1, a.status, abort_flag, 101)) break;
             const uint32_t full = smem_addr(&bars[s]);
             mbar_expect_tx(full, Cfg::STAGE_BYTES);
             unsigned char* st = tiles + (size_t)s * Cfg::STAGE_BYTES;
@@ -188,9 +230,9 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant_
         }
         if (*abort_flag) {
             // let the copies that are still in flight land before the block's memory goes away
-            for (int it = max(0, issued - Cfg::STAGES); it < issued; ++it) {
+            for (int it = max(0, issued - STAGES); it < issued; ++it) {
                 const unsigned long long start = clock64();
-                while (!mbar_try_wait(smem_addr(&bars[it % Cfg::STAGES]), (it / Cfg::STAGES) & 1))
+                while (!mbar_try_wait(smem_addr(&bars[it % STAGES]), (it / STAGES) & 1))
                     if (clock64() - start > WAIT_LIMIT_CYCLES) break;
             }
         }
@@ -199,8 +241,8 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant_
         const uint32_t idesc = instr_desc(TOK);
         bool ok = true;
         for (int it = 0; it < n_iters && ok; ++it) {
-            const int s = it % Cfg::STAGES;
-            const uint32_t ph = (it / Cfg::STAGES) & 1;
+            const int s = it % STAGES;
+            const uint32_t ph = (it / STAGES) & 1;
             ok = mbar_wait(smem_addr(&bars[s]), ph, a.status, abort_flag, 102);
             if (!ok) break;
             tc_fence_after();
@@ -212,24 +254,22 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant_
                 const uint64_t db = smem_desc_sw128(sb + k * UMMA_K * 2);
                 tc_mma_bf16(tmem_base, da, db, idesc, (it > 0 || k > 0) ? 1u : 0u);
             }
-            tc_commit(smem_addr(&bars[Cfg::STAGES + s]));      // stage free when these MMAs have read it
+            tc_commit(smem_addr(&bars[STAGES + s]));      // stage free when these MMAs have read it
         }
-        tc_commit(smem_addr(&bars[2 * Cfg::STAGES]));          // accumulator complete
+        tc_commit(smem_addr(&bars[2 * STAGES]));          // accumulator complete
     } else if (warp >= 2) {
         // ------------------------------------------------ epilogue ------------
         const int quad = warp & 3;                              // this warp's 32 lanes of tensor memory
         const int row = quad * 32 + lane;                       // weight row within the tile
         const int n = n0 + row;
-        const int et = threadIdx.x - 64;                        // 0..127 among the epilogue threads
         bool ok = true;
-        if (n_iters > 0) ok = mbar_wait(smem_addr(&bars[2 * Cfg::STAGES]), 0, a.status, abort_flag, 103);
+        if (n_iters > 0) ok = mbar_wait(smem_addr(&bars[2 * STAGES]), 0, a.status, abort_flag, 103);
         ok = __all_sync(0xffffffffu, ok);                       // the tensor-memory loads below are warp-wide
         tc_fence_after();
-        const size_t tile_id = (size_t)blockIdx.y * n_tiles + blockIdx.x;
-        bool do_final = a.splits == 1;
         if (a.splits > 1) {
-            // this block's partial tile -> scratch, laid out [token][row] so a warp writes 128 bytes
-            float* mine = a.partials + ((size_t)blockIdx.z * t_tiles * n_tiles + tile_id) * (size_t)(TOK * BN);
+            // this block's partial tile -> its own shared memory (the pipeline's stages are
+            // free now), laid out [token][row]
+            float* mine = reinterpret_cast<float*>(tiles);
 #pragma unroll 1
             for (int c0 = 0; c0 < TOK; c0 += 16) {
                 float v[16];
@@ -239,65 +279,73 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant_
                     for (int i = 0; i < 16; ++i) v[i] = 0.f;
                 }
 #pragma unroll
-                for (int i = 0; i < 16; ++i) mine[(size_t)(c0 + i) * BN + row] = v[i];
+                for (int i = 0; i < 16; ++i) mine[(c0 + i) * BN + row] = v[i];
             }
-            __threadfence();
-            asm volatile("bar.sync 1, 128;" ::: "memory");
-            if (et == 0) {
-                const int old = atomicAdd(&a.counters[tile_id], 1);
-                s_is_last = (old == a.splits - 1) ? 1 : 0;
-                if (old == a.splits - 1) a.counters[tile_id] = 0;      // ready for the next launch
-            }
-            asm volatile("bar.sync 1, 128;" ::: "memory");
-            do_final = s_is_last != 0;
-            if (do_final) __threadfence();
         }
-        if (do_final && !*abort_flag) {
+    }
+    if (a.splits > 1) cluster_sync_all();          // every block's partial tile is in place
+    if (warp >= 2) {
+        const int quad = warp & 3;
+        const int row = quad * 32 + lane;
+        const int n = n0 + row;
+        bool ok = !*abort_flag;
+        ok = __all_sync(0xffffffffu, ok);
+        grid_dependency_wait();                    // the output may still be in use by the kernel before
+        // tokens of the tile this block finishes: all of them without a split, else a slice
+        int c_begin = 0, c_end = TOK;
+        if (a.splits > 1) {
+            const int per = (TOK + a.splits - 1) / a.splits;
+            c_begin = min(TOK, (int)blockIdx.z * per);
+            c_end = min(TOK, c_begin + per);
+        }
+        const uint32_t mine_addr = smem_addr(tiles);
 #pragma unroll 1
-            for (int c0 = 0; c0 < TOK; c0 += 16) {
-                float v[16];
-                if (a.splits == 1) {
-                    if (n_iters > 0 && ok) tc_ld16(tmem_base + ((uint32_t)(quad * 32) << 16) + c0, v);
-                    else {
-#pragma unroll
-                        for (int i = 0; i < 16; ++i) v[i] = 0.f;
-                    }
-                } else {
+        for (int c0 = c_begin; c0 < c_end; c0 += 16) {
+            float v[16];
+            const int cn = min(16, c_end - c0);
+            if (a.splits == 1) {
+                if (n_iters > 0 && ok) tc_ld16(tmem_base + ((uint32_t)(quad * 32) << 16) + c0, v);
+                else {
 #pragma unroll
                     for (int i = 0; i < 16; ++i) v[i] = 0.f;
-                    for (int z = 0; z < a.splits; ++z) {               // fixed order: the sum is reproducible
-                        const float* p = a.partials + ((size_t)z * t_tiles * n_tiles + tile_id) * (size_t)(TOK * BN);
+                }
+            } else {
 #pragma unroll
-                        for (int i = 0; i < 16; ++i) v[i] += __ldcg(p + (size_t)(c0 + i) * BN + row);
+                for (int i = 0; i < 16; ++i) v[i] = 0.f;
+                for (int z = 0; z < a.splits; ++z) {               // fixed order: the sum is reproducible
+#pragma unroll
+                    for (int i = 0; i < 16; ++i)
+                        if (i < cn) v[i] += ld_peer_smem(mine_addr + (uint32_t)((c0 + i) * BN + row) * 4u, (uint32_t)z);
+                }
+            }
+            if (!ok) continue;
+            if (a.epilogue == EPI_SWIGLU) {
+                // rows come in groups of 32: 16 gate rows, then the 16 up rows of the same columns
+#pragma unroll
+                for (int i = 0; i < 16; ++i) {
+                    const float other = __shfl_xor_sync(0xffffffffu, v[i], 16);
+                    const int t = t0 + c0 + i;
+                    const int col = (n0 + quad * 32) / 2 + lane;
+                    if (i < cn && lane < 16 && t < a.T && col < a.N / 2) {
+                        const float g = v[i];
+                        reinterpret_cast<bf16*>(a.out)[(size_t)t * a.ldo + col] =
+                            __float2bfloat16_rn(g / (1.0f + expf(-g)) * other);
                     }
                 }
-                if (a.epilogue == EPI_SWIGLU) {
-                    // rows come in groups of 32: 16 gate rows, then the 16 up rows of the same columns
+            } else if (n < a.N) {
 #pragma unroll
-                    for (int i = 0; i < 16; ++i) {
-                        const float other = __shfl_xor_sync(0xffffffffu, v[i], 16);
-                        const int t = t0 + c0 + i;
-                        const int col = (n0 + quad * 32) / 2 + lane;
-                        if (lane < 16 && t < a.T && col < a.N / 2) {
-                            const float g = v[i];
-                            reinterpret_cast<bf16*>(a.out)[(size_t)t * a.ldo + col] =
-                                __float2bfloat16_rn(g / (1.0f + expf(-g)) * other);
-                        }
-                    }
-                } else if (n < a.N) {
-#pragma unroll
-                    for (int i = 0; i < 16; ++i) {
-                        const int t = t0 + c0 + i;
-                        if (t >= a.T) continue;
-                        const size_t o = (size_t)t * a.ldo + n;
-                        if (a.epilogue == EPI_BF16) reinterpret_cast<bf16*>(a.out)[o] = __float2bfloat16_rn(v[i]);
-                        else if (a.epilogue == EPI_F32) reinterpret_cast<float*>(a.out)[o] = v[i];
-                        else reinterpret_cast<float*>(a.out)[o] += v[i];
-                    }
+                for (int i = 0; i < 16; ++i) {
+                    const int t = t0 + c0 + i;
+                    if (i >= cn || t >= a.T) continue;
+                    const size_t o = (size_t)t * a.ldo + n;
+                    if (a.epilogue == EPI_BF16) reinterpret_cast<bf16*>(a.out)[o] = __float2bfloat16_rn(v[i]);
+                    else if (a.epilogue == EPI_F32) reinterpret_cast<float*>(a.out)[o] = v[i];
+                    else reinterpret_cast<float*>(a.out)[o] += v[i];
                 }
             }
         }
     }
+    if (a.splits > 1) cluster_sync_all();          // peers may still be reading this block's tile
     tc_fence_before();
     __syncthreads();
     if (warp == 1) {
@@ -360,18 +408,45 @@ static int make_map(const void* ptr, int rows, int cols, int box_rows, CUtensorM
 }
 
 template <int TOK>
-static int launch(const CUtensorMap& mw, const CUtensorMap& mx, const GemmArgs& a, int n_tiles, int t_tiles,
-                  cudaStream_t stream) {
+static int launch(const CUtensorMap& mw, const CUtensorMap& mx, const GemmArgs& a_in, int n_tiles, int t_tiles,
+                  int pdl, cudaStream_t stream) {
     using Cfg = TileCfg<TOK>;
     static bool attr_set = false;
     if (!attr_set) {
-        cudaError_t e = cudaFuncSetAttribute(gemm_tc_kernel<TOK>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)Cfg::SMEM);
+        cudaError_t e = cudaFuncSetAttribute(gemm_tc_kernel<TOK>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                             (int)Cfg::smem(Cfg::DEEP));
         if (e != cudaSuccess) return (int)e;
         attr_set = true;
     }
-    dim3 grid(n_tiles, t_tiles, a.splits);
-    gemm_tc_kernel<TOK><<<grid, GEMM_THREADS, Cfg::SMEM, stream>>>(mw, mx, a);
-    FF_LAUNCH_CHECK();
+    GemmArgs a = a_in;
+    const long long blocks = (long long)n_tiles * t_tiles * a.splits;
+    // half an SM's shared memory per block: the next product's blocks can move in beside this one's and
+    // request their first weight tiles while this one is still running
+    (void)blocks;
+    a.stages = Cfg::SHALLOW;
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = dim3(n_tiles, t_tiles, a.splits);
+    cfg.blockDim = dim3(GEMM_THREADS);
+    cfg.dynamicSmemBytes = Cfg::smem(a.stages);
+    cfg.stream = stream;
+    cudaLaunchAttribute attrs[2];
+    int na = 0;
+    if (a.splits > 1) {                         // the K ranges of a tile form one cluster
+        attrs[na].id = cudaLaunchAttributeClusterDimension;
+        attrs[na].val.clusterDim.x = 1;
+        attrs[na].val.clusterDim.y = 1;
+        attrs[na].val.clusterDim.z = a.splits;
+        ++na;
+    }
+    if (pdl || g_ff_pdl) {
+        attrs[na].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+        attrs[na].val.programmaticStreamSerializationAllowed = 1;
+        ++na;
+    }
+    cfg.attrs = attrs;
+    cfg.numAttrs = na;
+    cudaError_t e = cudaLaunchKernelEx(&cfg, gemm_tc_kernel<TOK>, mw, mx, a);
+    if (e != cudaSuccess) return (int)e;
     return 0;
 }
 
@@ -379,38 +454,34 @@ static int launch(const CUtensorMap& mw, const CUtensorMap& mx, const GemmArgs& 
 
 using namespace ff;
 
-// How many floats of scratch and how many counters a call needs (0 floats when splits == 1).
-FF_EXPORT int ff_gemm_tc_plan(int T, int N, int K, int want_splits, int* tok_out, int* splits_out,
-                              long long* partial_floats, int* n_counters) {
+// Tokens per tile and K ranges (= blocks per cluster, at most 8) a call would use.
+FF_EXPORT int ff_gemm_tc_plan(int T, int N, int K, int want_splits, int* tok_out, int* splits_out) {
     int tok = 16;
     while (tok < T && tok < 256) tok <<= 1;
-    const int n_tiles = (N + BN - 1) / BN, t_tiles = (T + tok - 1) / tok;
     const int num_kb = (K + BK - 1) / BK;
     int splits = want_splits < 1 ? 1 : want_splits;
+    if (splits > 8) splits = 8;
+    if (tok > 64) splits = 1;                            // large token tiles have enough blocks without
     if (splits > num_kb) splits = num_kb;
     const int per = (num_kb + splits - 1) / splits;
     splits = (num_kb + per - 1) / per;                   // no empty K range
     *tok_out = tok;
     *splits_out = splits;
-    *partial_floats = splits > 1 ? (long long)splits * n_tiles * t_tiles * tok * BN : 0;
-    *n_counters = n_tiles * t_tiles;
     return 0;
 }
 
 // x: bfloat16 [T, K] contiguous; w: bfloat16 [N, K] contiguous; K a multiple of 8.
 // epilogue: 0 bf16 out [T, ldo], 1 f32 out, 2 f32 out += , 3 swiglu (bf16 out [T, ldo], N/2 columns).
+// pdl: launch with programmatic stream serialization (the kernel before must tolerate an early start
+// of this one, which only prefetches weights before it waits).
 FF_EXPORT int ff_gemm_tc(const void* x, const void* w, void* out, int ldo, int T, int N, int K, int epilogue,
-                         int want_splits, float* partials, long long partial_floats, int* counters,
-                         int n_counters, int* status, cudaStream_t stream) {
+                         int want_splits, int pdl, int* status, cudaStream_t stream) {
     if (T <= 0 || N <= 0) return 0;
     if (K <= 0 || (K % 8) || epilogue < 0 || epilogue > 3) return FF_ERR_BAD_ARG;
     if (epilogue == EPI_SWIGLU && (N % 32)) return FF_ERR_UNSUPPORTED;
     if (((uintptr_t)x & 15) || ((uintptr_t)w & 15)) return FF_ERR_BAD_ARG;
-    int tok, splits, need_counters;
-    long long need_floats;
-    ff_gemm_tc_plan(T, N, K, want_splits, &tok, &splits, &need_floats, &need_counters);
-    if (splits > 1 && (need_floats > partial_floats || need_counters > n_counters || !partials || !counters))
-        return FF_ERR_BAD_ARG;
+    int tok, splits;
+    ff_gemm_tc_plan(T, N, K, want_splits, &tok, &splits);
     const int n_tiles = (N + BN - 1) / BN, t_tiles = (T + tok - 1) / tok;
     const int num_kb = (K + BK - 1) / BK;
     CUtensorMap mw, mx;
@@ -421,12 +492,12 @@ FF_EXPORT int ff_gemm_tc(const void* x, const void* w, void* out, int ldo, int T
     GemmArgs a;
     a.out = out; a.ldo = ldo; a.T = T; a.N = N; a.K = K; a.epilogue = epilogue; a.splits = splits;
     a.kb_per_split = (num_kb + splits - 1) / splits;
-    a.partials = partials; a.counters = counters; a.status = status;
+    a.status = status;
     switch (tok) {
-        case 16: return launch<16>(mw, mx, a, n_tiles, t_tiles, stream);
-        case 32: return launch<32>(mw, mx, a, n_tiles, t_tiles, stream);
-        case 64: return launch<64>(mw, mx, a, n_tiles, t_tiles, stream);
-        case 128: return launch<128>(mw, mx, a, n_tiles, t_tiles, stream);
-        default: return launch<256>(mw, mx, a, n_tiles, t_tiles, stream);
+        case 16: return launch<16>(mw, mx, a, n_tiles, t_tiles, pdl, stream);
+        case 32: return launch<32>(mw, mx, a, n_tiles, t_tiles, pdl, stream);
+        case 64: return launch<64>(mw, mx, a, n_tiles, t_tiles, pdl, stream);
+        case 128: return launch<128>(mw, mx, a, n_tiles, t_tiles, pdl, stream);
+        default: return launch<256>(mw, mx, a, n_tiles, t_tiles, pdl, stream);
     }
 }

@@ -24,6 +24,7 @@ __global__ void qk_norm_rope_store_kernel(
     const int* __restrict__ positions, const int* __restrict__ token_seq,
     const int* __restrict__ block_table, int max_blocks, int block_size, int num_blocks,
     T* __restrict__ cache, int* __restrict__ status) {
+    pdl_prologue();
     __shared__ float bufs[QKR_WARPS][QKR_MAX_D];
     const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
     const int heads = nq + 2 * nkv;
@@ -97,12 +98,12 @@ FF_EXPORT int ff_qk_norm_rope_store(void* qkv, int dtype, int row_width, int T, 
     const long long items = (long long)T * (nq + 2 * nkv);
     const unsigned blocks = (unsigned)((items + QKR_WARPS - 1) / QKR_WARPS);
     if (dtype == 0)
-        qk_norm_rope_store_kernel<float><<<blocks, QKR_WARPS * 32, 0, stream>>>(
+        FF_LAUNCH((qk_norm_rope_store_kernel<float>), blocks, QKR_WARPS * 32, 0, stream, 
             (float*)qkv, row_width, T, nq, nkv, d, q_norm_w, k_norm_w, eps, cos_sin, rotary_dim,
             max_positions, positions, token_seq, block_table, max_blocks, block_size, num_blocks,
             (float*)cache, status);
     else if (dtype == 1)
-        qk_norm_rope_store_kernel<bf16><<<blocks, QKR_WARPS * 32, 0, stream>>>(
+        FF_LAUNCH((qk_norm_rope_store_kernel<bf16>), blocks, QKR_WARPS * 32, 0, stream, 
             (bf16*)qkv, row_width, T, nq, nkv, d, q_norm_w, k_norm_w, eps, cos_sin, rotary_dim,
             max_positions, positions, token_seq, block_table, max_blocks, block_size, num_blocks,
             (bf16*)cache, status);

@@ -38,6 +38,23 @@ class Workspace:
             self._bufs[key] = buf
         return buf[:n].view(*shape)
 
+    def get_zeroed(self, tag: str, numel: int, dtype: torch.dtype) -> torch.Tensor:
+        """A buffer that is zero when first handed out (and after it grows); users
+        must leave it zero (counters that a kernel resets itself)."""
+        key = (tag, dtype)
+        buf = self._bufs.get(key)
+        if buf is None or buf.numel() < numel:
+            if self.frozen:
+                raise RuntimeError(f"workspace buffer '{tag}' would have to grow while a captured graph uses it")
+            buf = torch.zeros(max(numel, 1), dtype=dtype, device=self.device)
+            self._bufs[key] = buf
+        return buf[:numel]
+
+    def zero(self, tag: str, dtype: torch.dtype) -> None:
+        buf = self._bufs.get((tag, dtype))
+        if buf is not None:
+            buf.zero_()
+
     def reserve(self, tag: str, numel: int, dtype: torch.dtype) -> None:
         self.get(tag, (numel,), dtype)
 

@@ -43,7 +43,10 @@ class StepError(RuntimeError):
 _STATUS = {1: "a token id outside the vocabulary reached the embedding kernel",
            2: "a token's cache page is missing from its block table (write)",
            3: "a position beyond the rotary table",
-           4: "a key's cache page is missing from a block table (read)"}
+           4: "a key's cache page is missing from a block table (read)",
+           101: "matrix product: the loader's wait for a free stage ran out",
+           102: "matrix product: the wait for a loaded stage ran out",
+           103: "matrix product: the wait for the accumulator ran out"}
 
 
 class MetaLayout:

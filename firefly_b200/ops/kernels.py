@@ -71,9 +71,26 @@ _MODULES = {
 }
 
 
+USE_PDL = True      # programmatic dependent launch: a kernel's prologue overlaps its predecessor's tail
+_pdl_state = {}     # id(library) -> flag it was last given
+
+
+def _configured(lib: ctypes.CDLL) -> ctypes.CDLL:
+    if _pdl_state.get(id(lib)) != USE_PDL:
+        lib.ff_set_pdl(c_int(1 if USE_PDL else 0))
+        _pdl_state[id(lib)] = USE_PDL
+    return lib
+
+
+def set_pdl(on: bool) -> None:
+    """Switch programmatic dependent launch on or off for all kernels of this package."""
+    global USE_PDL
+    USE_PDL = bool(on)
+
+
 def _lib(name: str) -> ctypes.CDLL:
     src, defs = _MODULES[name]
-    return load_module(src, defs)
+    return _configured(load_module(src, defs))
 
 
 DEFAULT_HEAD_DIMS = (128,)
@@ -131,13 +148,14 @@ def residual_add(residual: torch.Tensor, delta: torch.Tensor) -> None:
                                               c_size_t(residual.numel()), _stream()), "residual_add")
 
 
-def silu_mul(gate_up: torch.Tensor, out: torch.Tensor) -> None:
-    """out[t,i] = silu(gate_up[t,i]) * gate_up[t,I+i]."""
+def silu_mul(gate_up: torch.Tensor, out: torch.Tensor, interleaved: bool = False) -> None:
+    """out[t,i] = silu(gate) * up, gate = gate_up[t,i], up = gate_up[t,I+i]; with
+    ``interleaved`` the columns hold gate and up in alternating groups of 16."""
     _need_cuda(gate_up, out)
     T, I = out.shape
     assert gate_up.shape == (T, 2 * I) and gate_up.dtype == out.dtype
     _check(_lib("elementwise").ff_silu_mul(_p(gate_up), _p(out), c_int(_dt(out)), c_int(T), c_int(I),
-                                          _stream()), "silu_mul")
+                                          c_int(1 if interleaved else 0), _stream()), "silu_mul")
 
 
 def cast(src: torch.Tensor, out: torch.Tensor) -> None:
@@ -193,20 +211,37 @@ def paged_attention_simt(q: torch.Tensor, q_stride: int, cache: torch.Tensor, bl
         _stream()), "paged_attention_simt")
 
 
+_sample_scratch = {}
+
+
 def sample(logits: torch.Tensor, out: torch.Tensor, temperature: Optional[torch.Tensor] = None,
            seeds: Optional[torch.Tensor] = None, counters: Optional[torch.Tensor] = None) -> None:
     """out[r] = arg-max of logits[r] (lowest index on ties), or, where
     temperature[r] > 0, a draw from softmax(logits[r] / temperature[r]) with the
     random numbers of (seeds[r], counters[r])."""
+    global LAUNCHES
     _need_cuda(logits, out, temperature, seeds, counters)
     assert logits.dtype == torch.float32 and out.dtype == torch.int32 and logits.dim() == 2
     rows, V = logits.shape
     if temperature is not None:
         assert temperature.dtype == torch.float32 and seeds.dtype == torch.int64 \
             and counters.dtype == torch.int64
+    # a row is split over several blocks so that few rows still fill the GPU
+    chunks = max(1, min(64, _SM_TARGET_CTAS // 2 // max(rows, 1), V // 2048))
+    pv = pi = None
+    if chunks > 1:
+        key = logits.device
+        buf = _sample_scratch.get(key)
+        if buf is None or buf[0].numel() < rows * chunks:
+            n = max(rows * chunks, 4096)
+            buf = (torch.empty(n, dtype=torch.float32, device=key), torch.empty(n, dtype=torch.int32, device=key))
+            _sample_scratch[key] = buf
+        pv, pi = buf
     _check(_lib("sampling").ff_sample(_p(logits), c_int(rows), c_int(V), c_size_t(logits.stride(0)),
-                                     _p(temperature), _p(seeds), _p(counters), _p(out), _stream()),
-           "sample")
+                                     _p(temperature), _p(seeds), _p(counters), _p(out), c_int(chunks),
+                                     _p(pv), _p(pi), _stream()), "sample")
+    if chunks > 1:
+        LAUNCHES += 1
 
 
 # --------------------------------------------------------------------------- #
@@ -227,26 +262,25 @@ def linear(x: torch.Tensor, weight: torch.Tensor, out: torch.Tensor) -> None:
 
 
 EPI_BF16, EPI_F32, EPI_RESIDUAL_ADD, EPI_SWIGLU = 0, 1, 2, 3
+USE_TCGEN05_GEMM = True    # tests flip this to compare with the library route
 
 
 def gemm_tc_plan(T: int, N: int, K: int, want_splits: int):
-    """(tokens per tile, K ranges, floats of scratch, counters) the tensor-core product would use."""
-    tok, splits, cnt = c_int(), c_int(), c_int()
-    floats = c_longlong()
+    """(tokens per tile, K ranges) the tensor-core product would use."""
+    tok, splits = c_int(), c_int()
     _lib("gemm_tcgen05").ff_gemm_tc_plan(c_int(T), c_int(N), c_int(K), c_int(want_splits), ctypes.byref(tok),
-                                       ctypes.byref(splits), ctypes.byref(floats), ctypes.byref(cnt))
-    return tok.value, splits.value, floats.value, cnt.value
+                                       ctypes.byref(splits))
+    return tok.value, splits.value
 
 
 def gemm_tc(x: torch.Tensor, weight: torch.Tensor, out: torch.Tensor, epilogue: int, want_splits: int,
-            partials: Optional[torch.Tensor], counters: Optional[torch.Tensor], status: torch.Tensor) -> None:
+            status: torch.Tensor) -> None:
     """out (op)= x @ weight^T on tcgen05 tensor cores; bfloat16 operands, 32-bit accumulation.
 
     epilogue: EPI_BF16 store bfloat16, EPI_F32 store float32, EPI_RESIDUAL_ADD add into a float32
     ``out``, EPI_SWIGLU store silu(gate)*up as bfloat16 [T, N/2] for a weight whose rows interleave
-    gate and up in groups of 16.  ``partials`` (float32) and ``counters`` (int32, zero) are scratch
-    for the split over K; see ``gemm_tc_plan``."""
-    _need_cuda(x, weight, out, partials, counters, status)
+    gate and up in groups of 16.  ``want_splits`` K ranges (at most 8) share a thread-block cluster."""
+    _need_cuda(x, weight, out, status)
     assert x.dtype == torch.bfloat16 and weight.dtype == torch.bfloat16
     T, Kd = x.shape
     N = weight.shape[0]
@@ -258,9 +292,7 @@ def gemm_tc(x: torch.Tensor, weight: torch.Tensor, out: torch.Tensor, epilogue: 
     assert out.shape[0] == T and out.shape[1] == (N // 2 if epilogue == EPI_SWIGLU else N)
     _check(_lib("gemm_tcgen05").ff_gemm_tc(
         _p(x), _p(weight), _p(out), c_int(out.stride(0)), c_int(T), c_int(N), c_int(Kd), c_int(epilogue),
-        c_int(want_splits), _p(partials), c_longlong(partials.numel() if partials is not None else 0),
-        _p(counters), c_int(counters.numel() if counters is not None else 0), _p(status), _stream()),
-        "gemm_tc")
+        c_int(want_splits), c_int(1 if USE_PDL else 0), _p(status), _stream()), "gemm_tc")
 
 
 def interleave_gate_up(gate: torch.Tensor, up: torch.Tensor) -> torch.Tensor:
@@ -285,11 +317,12 @@ def set_exact_matmul() -> None:
 
 
 _ATTN_FORCE_SIMT = False      # tests flip this to compare the two kernels
-_SM_TARGET_CTAS = 592         # 148 SMs x 4: how many blocks a decode launch should reach
+_SM_TARGET_CTAS = 592         # 148 SMs x 4: scratch of the decode attention is sized for this many blocks
+_SM_COUNT = 148
 
 
 def _attn_lib(d: int) -> ctypes.CDLL:
-    return load_module("attention_mma.cu", {"FF_HEAD_DIM": d})
+    return _configured(load_module("attention_mma.cu", {"FF_HEAD_DIM": d}))
 
 
 def mma_attention_supported(dtype: torch.dtype, d: int) -> bool:
@@ -323,8 +356,10 @@ def attn_decode(q, q_stride, pages, table, cu_q, ctx_lens, n_seqs, out, part_o, 
 
 
 def decode_splits(n_seqs: int, nkv: int, max_kv_len: int) -> int:
+    """Ranges of keys per (sequence, kv head): about 8 tiles of 64 keys a block, and at
+    least one block per SM when the batch is small."""
     tiles = max(1, -(-max_kv_len // 64))
-    want = -(-_SM_TARGET_CTAS // max(1, n_seqs * nkv))
+    want = max(-(-tiles // 8), -(-_SM_COUNT // max(1, n_seqs * nkv)))
     return max(1, min(want, tiles, 64))
 
 
@@ -342,7 +377,7 @@ def paged_attention(q: torch.Tensor, q_stride: int, pages: torch.Tensor, table: 
         n = ctx.num_seqs
         splits = decode_splits(n, nkv, ctx.max_kv_len)
         # n*nq*splits < G*target + n*nq for every n: the largest batch needs the most
-        cap = G * _SM_TARGET_CTAS + n * nq
+        cap = max(n * nq * splits, G * _SM_TARGET_CTAS + n * nq)
         part_o = ctx.workspace.get("attn.part_o", (cap * d,), torch.float32)
         part_ml = ctx.workspace.get("attn.part_ml", (cap * 2,), torch.float32)
         attn_decode(q, q_stride, pages, table, ctx.cu_q, ctx.ctx_lens, n, out, part_o, part_ml, nq, nkv, d,

@@ -29,7 +29,7 @@ from ..cache.spec import PagedKVSpec
 from ..ops import kernels as K
 from ..weights.loader import WeightSpec
 from .base import Part, register_part
-from .linear import apply_linear
+from .linear import apply_linear, linear_into_residual
 
 
 class GQAttention(Part):
@@ -86,7 +86,7 @@ class GQAttention(Part):
                 self.k_norm_w = self._vector32(tensors[self.name("k_norm.weight")])
 
     # -- run ------------------------------------------------------------------
-    def forward(self, x: torch.Tensor, ctx, slot: int, write_cache: bool) -> torch.Tensor:
+    def forward(self, x: torch.Tensor, ctx, slot: int, write_cache: bool, accumulate_into=None):
         T = x.shape[0]
         ws = ctx.workspace
         if write_cache and not self.has_kv:
@@ -95,7 +95,7 @@ class GQAttention(Part):
         width = (self.nq + 2 * nkv_w) * self.d
         w = self.w_qkv if (write_cache or not self.has_kv) else self.w_qkv[: self.nq * self.d]
         qkv = ws.get("attn.qkv", (T, width), ctx.dtype)
-        apply_linear(x, w, qkv, ws, "attn.qkv")
+        apply_linear(x, w, qkv, ctx, "attn.qkv")
         pages, table = ctx.kv(slot)
         rot = self.position.rotary_table() if self.position is not None else None
         cos_sin, rotary_dim = rot if rot is not None else (None, 0)
@@ -105,9 +105,7 @@ class GQAttention(Part):
                              pages if write_cache else None, ctx.status)
         att = ws.get("attn.out", (T, self.nq * self.d), ctx.dtype)
         self._attend(qkv, width, pages, table, ctx, att)
-        out = ws.get("attn.proj", (T, self.hidden), ctx.dtype)
-        apply_linear(att, self.w_o, out, ws, "attn.proj")
-        return out
+        return linear_into_residual(att, self.w_o, accumulate_into, ctx, "attn.proj")
 
     def _attend(self, qkv, width, pages, table, ctx, att) -> None:
         window = 0 if self.window is None else int(self.window)

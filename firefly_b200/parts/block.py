@@ -8,6 +8,7 @@ each sum is done once, in 32-bit, without a pass of its own.
 """
 from __future__ import annotations
 
+import inspect
 from typing import List, Mapping, Optional, Tuple
 
 import torch
@@ -31,6 +32,10 @@ class Block:
             raise ValueError(f"arrangement '{layer_spec.arrangement}' needs {self.n_norms} norms, "
                              f"got {len(layer_spec.norms)}")
         self.norms = [build_part("norm", n, rt) for n in layer_spec.norms]
+        # a part whose forward takes ``accumulate_into`` may add its output into the 32-bit
+        # residual itself (and return None); others return a delta
+        self._mixer_fuses = "accumulate_into" in inspect.signature(self.mixer.forward).parameters
+        self._ffn_fuses = "accumulate_into" in inspect.signature(self.feed_forward.forward).parameters
 
     def parts(self) -> List[Part]:
         out = [self.mixer, self.feed_forward, *self.norms]
@@ -53,9 +58,15 @@ class PreNormBlock(Block):
     def forward(self, residual: torch.Tensor, pending: Optional[torch.Tensor], ctx, slot: int,
                 write_cache: bool) -> Tuple[torch.Tensor, Optional[torch.Tensor]]:
         x = self.norms[0].forward(residual, pending, ctx)
-        a = self.mixer.forward(x, ctx, slot, write_cache)
+        if self._mixer_fuses:
+            a = self.mixer.forward(x, ctx, slot, write_cache, accumulate_into=residual)
+        else:
+            a = self.mixer.forward(x, ctx, slot, write_cache)
         x = self.norms[1].forward(residual, a, ctx)
-        f = self.feed_forward.forward(x, ctx)
+        if self._ffn_fuses:
+            f = self.feed_forward.forward(x, ctx, accumulate_into=residual)
+        else:
+            f = self.feed_forward.forward(x, ctx)
         return residual, f
 
 

@@ -61,7 +61,7 @@ class LMHead(Part):
     def forward(self, x_rows: torch.Tensor, ctx) -> torch.Tensor:
         out = ctx.workspace.get("logits", (x_rows.shape[0], self.vocab), torch.float32)
         if x_rows.shape[0]:
-            apply_linear(x_rows, self.weight, out, ctx.workspace, "logits")
+            apply_linear(x_rows, self.weight, out, ctx, "logits")
         return out
 
 

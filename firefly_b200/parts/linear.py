@@ -1,18 +1,53 @@
-"""A matrix product y = x W^T with the weight as stored ([out, in], row-major).
+"""Matrix products y = x W^T with the weight as stored ([out, in], row-major), and
+the fused forms the layers use.
 
-The product runs in the weight's type: bfloat16 operands with 32-bit
-accumulation, or true 32-bit.  When a 32-bit weight meets 16-bit activations
-(a tensor stored in 32-bit inside a bfloat16 engine) the activations are widened
-and the result narrowed again, so the weight is never rounded.
+Two routes.  For few tokens (decode steps, short portions) bfloat16 products run
+on this package's own tcgen05 kernel, whose epilogue can add into the 32-bit
+residual or apply SiLU(gate)*up, so those steps need no further launch.  Larger
+token counts, 32-bit weights and shapes the kernel does not take go to the
+library routine (cuBLAS), followed by the separate kernels.  The product runs in
+the weight's type: bfloat16 operands with 32-bit accumulation, or true 32-bit;
+when a 32-bit weight meets 16-bit activations (a tensor stored in 32-bit inside a
+bfloat16 engine) the activations are widened and the result narrowed again, so the
+weight is never rounded.
 """
 from __future__ import annotations
+
+from typing import Optional
 
 import torch
 
 from ..ops import kernels as K
 
+TC_MAX_TOKENS = 64        # up to here the tcgen05 kernel is at least as fast as the library
+_SM_COUNT = 148
 
-def apply_linear(x: torch.Tensor, weight: torch.Tensor, out: torch.Tensor, ws, tag: str) -> torch.Tensor:
+
+def tc_usable(x: torch.Tensor, weight: torch.Tensor) -> bool:
+    return (K.USE_TCGEN05_GEMM and x.dtype == torch.bfloat16 and weight.dtype == torch.bfloat16
+            and x.shape[0] <= TC_MAX_TOKENS and weight.shape[1] % 8 == 0)
+
+
+def _splits(N: int, Kd: int) -> int:
+    """K ranges (blocks of a cluster) so that about one block per SM streams the weight; the
+    other half of each SM's shared memory is left for the blocks of the product that follows,
+    which request their first weight tiles while this one still runs."""
+    tiles = -(-N // 128)
+    kb = -(-Kd // 64)
+    return max(1, min(_SM_COUNT // tiles, 8, kb // 4))
+
+
+def _tc(x, weight, out, epilogue, ctx) -> None:
+    N, Kd = weight.shape
+    K.gemm_tc(x, weight, out, epilogue, _splits(N, Kd), ctx.status)
+
+
+def apply_linear(x: torch.Tensor, weight: torch.Tensor, out: torch.Tensor, ctx, tag: str) -> torch.Tensor:
+    """out = x W^T (out in the activation type, or float32)."""
+    ws = ctx.workspace
+    if tc_usable(x, weight):
+        _tc(x, weight, out, K.EPI_F32 if out.dtype == torch.float32 else K.EPI_BF16, ctx)
+        return out
     if x.dtype == weight.dtype:
         K.linear(x, weight, out)
         return out
@@ -29,3 +64,30 @@ def apply_linear(x: torch.Tensor, weight: torch.Tensor, out: torch.Tensor, ws, t
     if weight.dtype == torch.bfloat16 and x.dtype == torch.float32:
         raise K.KernelError("a 32-bit engine holds 32-bit matrices only")
     raise K.KernelError(f"linear: no product for {x.dtype} x {weight.dtype}")
+
+
+def linear_into_residual(x: torch.Tensor, weight: torch.Tensor, residual: Optional[torch.Tensor], ctx,
+                         tag: str) -> Optional[torch.Tensor]:
+    """The product as a delta for the residual stream.  When it can be fused it is
+    added into ``residual`` (float32) in the product's epilogue and None is
+    returned; else the delta is returned for the next norm to add."""
+    if residual is not None and tc_usable(x, weight):
+        _tc(x, weight, residual, K.EPI_RESIDUAL_ADD, ctx)
+        return None
+    out = ctx.workspace.get(tag, (x.shape[0], weight.shape[0]), ctx.dtype)
+    return apply_linear(x, weight, out, ctx, tag)
+
+
+def linear_swiglu(x: torch.Tensor, w_gate_up: torch.Tensor, inter: int, interleaved: bool, ctx) -> torch.Tensor:
+    """silu(x Wg^T) * (x Wu^T) for the stacked weight [2I, H] (``interleaved``: gate
+    and up rows alternate in groups of 16)."""
+    ws = ctx.workspace
+    T = x.shape[0]
+    act = ws.get("mlp.act", (T, inter), ctx.dtype)
+    if interleaved and tc_usable(x, w_gate_up):
+        _tc(x, w_gate_up, act, K.EPI_SWIGLU, ctx)
+        return act
+    gu = ws.get("mlp.gate_up", (T, 2 * inter), ctx.dtype)
+    apply_linear(x, w_gate_up, gu, ctx, "mlp.gate_up")
+    K.silu_mul(gu, act, interleaved)
+    return act

@@ -14,7 +14,7 @@ import torch
 from ..ops import kernels as K
 from ..weights.loader import WeightSpec
 from .base import Part, register_part
-from .linear import apply_linear
+from .linear import linear_into_residual, linear_swiglu
 
 
 class SwiGLUMLP(Part):
@@ -23,6 +23,7 @@ class SwiGLUMLP(Part):
         self.hidden = int(self.p("hidden_size"))
         self.inter = int(self.p("intermediate_size"))
         self.w_gate_up = self.w_down = None
+        self.interleaved = False
 
     def weight_specs(self) -> List[WeightSpec]:
         return [WeightSpec(self.name("gate_proj.weight"), (self.inter, self.hidden)),
@@ -34,19 +35,17 @@ class SwiGLUMLP(Part):
         u = self._matrix(tensors[self.name("up_proj.weight")])
         if g.dtype != u.dtype:
             g, u = g.to(torch.float32), u.to(torch.float32)
-        self.w_gate_up = torch.cat([g, u], dim=0).contiguous()
+        # bfloat16: rows of gate and up alternate in groups of 16, the layout the fused
+        # product's epilogue pairs up; else gate rows first, then up rows
+        self.interleaved = g.dtype == torch.bfloat16 and self.inter % 16 == 0
+        self.w_gate_up = K.interleave_gate_up(g, u) if self.interleaved else torch.cat([g, u], dim=0).contiguous()
         self.w_down = self._matrix(tensors[self.name("down_proj.weight")])
 
-    def forward(self, x: torch.Tensor, ctx) -> torch.Tensor:
-        T = x.shape[0]
-        ws = ctx.workspace
-        gu = ws.get("mlp.gate_up", (T, 2 * self.inter), ctx.dtype)
-        apply_linear(x, self.w_gate_up, gu, ws, "mlp.gate_up")
-        act = ws.get("mlp.act", (T, self.inter), ctx.dtype)
-        K.silu_mul(gu, act)
-        out = ws.get("mlp.down", (T, self.hidden), ctx.dtype)
-        apply_linear(act, self.w_down, out, ws, "mlp.down")
-        return out
+    def forward(self, x: torch.Tensor, ctx, accumulate_into=None):
+        """Returns the delta [T, hidden], or None when it was added into
+        ``accumulate_into`` (the 32-bit residual) by the last product's epilogue."""
+        act = linear_swiglu(x, self.w_gate_up, self.inter, self.interleaved, ctx)
+        return linear_into_residual(act, self.w_down, accumulate_into, ctx, "mlp.down")
 
 
 register_part("feed_forward", "swiglu_mlp", SwiGLUMLP)

@@ -18,9 +18,7 @@ def _run(T, N, Kd, splits, epilogue, seed=0):
     x = (torch.randn(T, Kd, generator=g)).to(torch.bfloat16)
     w = (torch.randn(N, Kd, generator=g) / Kd ** 0.5).to(torch.bfloat16)
     ref = x.double() @ w.double().T
-    tok, s, floats, cnt = k.gemm_tc_plan(T, N, Kd, splits)
-    partials = torch.full((max(floats, 1),), float("nan"), device="cuda")
-    counters = torch.zeros(cnt, dtype=torch.int32, device="cuda")
+    tok, s = k.gemm_tc_plan(T, N, Kd, splits)
     status = torch.zeros(1, dtype=torch.int32, device="cuda")
     xd, wd = x.cuda(), w.cuda()
     if epilogue == k.EPI_BF16:
@@ -40,13 +38,12 @@ def _run(T, N, Kd, splits, epilogue, seed=0):
         out = torch.zeros(T, I, dtype=torch.bfloat16, device="cuda")
         gv, uv = x.double() @ gate.double().T, x.double() @ up.double().T
         want = gv / (1 + torch.exp(-gv)) * uv
-    for rep in range(2):                      # twice: the counters must have been left at zero
+    for rep in range(2):
         if epilogue == k.EPI_RESIDUAL_ADD and rep:
             out.copy_(base)
-        k.gemm_tc(xd, wd, out, epilogue, splits, partials, counters, status)
+        k.gemm_tc(xd, wd, out, epilogue, splits, status)
         torch.cuda.synchronize()
         assert int(status) == 0
-        assert int(counters.abs().sum()) == 0
         tol = 2e-2 if out.dtype == torch.bfloat16 else 2e-3
         err = float((out.cpu().double() - want).abs().max()) / (float(want.abs().max()) + 1e-9)
         assert err < tol, (T, N, Kd, splits, epilogue, s, tok, err)
@@ -59,7 +56,7 @@ def test_store_bf16(T, N, Kd):
 
 
 @pytest.mark.parametrize("T", [1, 8, 33])
-@pytest.mark.parametrize("splits", [2, 3, 8, 100])
+@pytest.mark.parametrize("splits", [2, 3, 4, 5, 6, 7, 8, 100])
 @pytest.mark.parametrize("N,Kd", [(256, 1024), (72, 200), (1024, 12288)])
 def test_split_k(T, splits, N, Kd):
     _run(T, N, Kd, splits, K().EPI_F32)
@@ -85,4 +82,4 @@ def test_refuses_what_it_cannot_do():
     out = torch.zeros(4, 16, dtype=torch.bfloat16, device="cuda")
     st = torch.zeros(1, dtype=torch.int32, device="cuda")
     with pytest.raises(k.KernelError, match="bad argument"):
-        k.gemm_tc(x, w, out, k.EPI_BF16, 1, None, None, st)      # K not a multiple of 8
+        k.gemm_tc(x, w, out, k.EPI_BF16, 1, st)      # K not a multiple of 8
