@@ -28,20 +28,38 @@ FF_EXPORT void ff_set_pdl(int on) { g_ff_pdl = on; }
 
 namespace ff {
 
+// cluster_z > 1: blocks (x, y, z0..z0+cluster_z) form one thread-block cluster.
 template <typename... KArgs, typename... Args>
-static inline int launch_kernel(void (*kernel)(KArgs...), dim3 grid, dim3 block, size_t smem,
-                                cudaStream_t stream, Args... args) {
+static inline int launch_kernel_cluster(void (*kernel)(KArgs...), dim3 grid, dim3 block, size_t smem,
+                                        cudaStream_t stream, int cluster_z, Args... args) {
     cudaLaunchConfig_t cfg = {};
     cfg.gridDim = grid;
     cfg.blockDim = block;
     cfg.dynamicSmemBytes = smem;
     cfg.stream = stream;
-    cudaLaunchAttribute attr[1];
-    attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
-    attr[0].val.programmaticStreamSerializationAllowed = 1;
+    cudaLaunchAttribute attr[2];
+    int na = 0;
+    if (g_ff_pdl) {
+        attr[na].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+        attr[na].val.programmaticStreamSerializationAllowed = 1;
+        ++na;
+    }
+    if (cluster_z > 1) {
+        attr[na].id = cudaLaunchAttributeClusterDimension;
+        attr[na].val.clusterDim.x = 1;
+        attr[na].val.clusterDim.y = 1;
+        attr[na].val.clusterDim.z = (unsigned)cluster_z;
+        ++na;
+    }
     cfg.attrs = attr;
-    cfg.numAttrs = g_ff_pdl ? 1 : 0;
+    cfg.numAttrs = na;
     return (int)cudaLaunchKernelEx(&cfg, kernel, static_cast<KArgs>(args)...);
+}
+
+template <typename... KArgs, typename... Args>
+static inline int launch_kernel(void (*kernel)(KArgs...), dim3 grid, dim3 block, size_t smem,
+                                cudaStream_t stream, Args... args) {
+    return launch_kernel_cluster(kernel, grid, block, smem, stream, 1, args...);
 }
 
 #define FF_LAUNCH(kernel, grid, block, smem, stream, ...)                                              \
@@ -52,6 +70,20 @@ static inline int launch_kernel(void (*kernel)(KArgs...), dim3 grid, dim3 block,
 
 __device__ __forceinline__ void pdl_prologue() {
     asm volatile("griddepcontrol.launch_dependents;\n\tgriddepcontrol.wait;" ::: "memory");
+}
+
+// Barrier over all threads of all blocks of the cluster (release/acquire).
+__device__ __forceinline__ void cluster_sync_all() {
+    __syncwarp();
+    asm volatile("barrier.cluster.arrive.release.aligned;\n\tbarrier.cluster.wait.acquire.aligned;" ::: "memory");
+}
+// float at shared-memory address `addr` (as seen by this block) in the block of rank `rank` of the cluster
+__device__ __forceinline__ float ld_peer_smem(uint32_t addr, uint32_t rank) {
+    uint32_t peer;
+    float v;
+    asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(peer) : "r"(addr), "r"(rank));
+    asm volatile("ld.shared::cluster.f32 %0, [%1];" : "=f"(v) : "r"(peer) : "memory");
+    return v;
 }
 
 using bf16 = __nv_bfloat16;

@@ -28,34 +28,78 @@ __global__ void embedding_kernel(const int* __restrict__ ids, const TT* __restri
 // ------------------------------------------------------ residual add + norm --
 // residual[src,:] (+= delta[src,:]);  out[r,:] = v * rsqrt(mean(v^2)+eps) * w
 // src = row_idx ? row_idx[r] : r.  With row_idx the residual is not written back.
-template <typename TD, typename TO>
+// four consecutive elements of either type
+__device__ __forceinline__ float4 load4(const float* p) { return *reinterpret_cast<const float4*>(p); }
+__device__ __forceinline__ float4 load4(const bf16* p) {
+    const uint2 raw = *reinterpret_cast<const uint2*>(p);
+    const __nv_bfloat162 a = *reinterpret_cast<const __nv_bfloat162*>(&raw.x);
+    const __nv_bfloat162 b = *reinterpret_cast<const __nv_bfloat162*>(&raw.y);
+    return make_float4(__low2float(a), __high2float(a), __low2float(b), __high2float(b));
+}
+__device__ __forceinline__ void store4(float* p, float4 v) { *reinterpret_cast<float4*>(p) = v; }
+__device__ __forceinline__ void store4(bf16* p, float4 v) {
+    __nv_bfloat162 a = __floats2bfloat162_rn(v.x, v.y), b = __floats2bfloat162_rn(v.z, v.w);
+    uint2 raw;
+    raw.x = *reinterpret_cast<uint32_t*>(&a);
+    raw.y = *reinterpret_cast<uint32_t*>(&b);
+    *reinterpret_cast<uint2*>(p) = raw;
+}
+
+// VEC = 4: four elements a thread and step (needs H % 4 == 0); VEC = 1: any H.
+template <typename TD, typename TO, int VEC>
 __global__ void add_rms_norm_kernel(float* __restrict__ residual, const TD* __restrict__ delta,
                                     const int* __restrict__ row_idx, const float* __restrict__ w,
                                     float eps, TO* __restrict__ out, int H, int write_residual,
                                     int use_smem) {
     pdl_prologue();
-    extern __shared__ float row[];
+    extern __shared__ __align__(16) float row[];
     __shared__ float scratch[32];
     const int r = blockIdx.x;
     const int src = row_idx ? row_idx[r] : r;
     float* res = residual + (size_t)src * H;
     const TD* dl = delta ? delta + (size_t)src * H : nullptr;
     float ss = 0.f;
-    for (int i = threadIdx.x; i < H; i += blockDim.x) {
-        float v = res[i];
-        if (dl) v += to_float(dl[i]);
-        if (use_smem) row[i] = v;
-        if (dl && write_residual) res[i] = v;
-        ss += v * v;
+    if (VEC == 4) {
+        for (int i = threadIdx.x * 4; i < H; i += blockDim.x * 4) {
+            float4 v = load4(res + i);
+            if (dl) {
+                const float4 d = load4(dl + i);
+                v.x += d.x; v.y += d.y; v.z += d.z; v.w += d.w;
+                if (write_residual) store4(res + i, v);
+            }
+            if (use_smem) store4(row + i, v);
+            ss += v.x * v.x + v.y * v.y + v.z * v.z + v.w * v.w;
+        }
+    } else {
+        for (int i = threadIdx.x; i < H; i += blockDim.x) {
+            float v = res[i];
+            if (dl) v += to_float(dl[i]);
+            if (use_smem) row[i] = v;
+            if (dl && write_residual) res[i] = v;
+            ss += v * v;
+        }
     }
     ss = block_sum(ss, scratch);
     const float inv = 1.0f / sqrtf(ss / (float)H + eps);
     TO* o = out + (size_t)r * H;
-    for (int i = threadIdx.x; i < H; i += blockDim.x) {
-        float v;
-        if (use_smem) v = row[i];
-        else { v = res[i]; if (dl && !write_residual) v += to_float(dl[i]); }
-        o[i] = from_float<TO>(v * inv * w[i]);
+    if (VEC == 4) {
+        for (int i = threadIdx.x * 4; i < H; i += blockDim.x * 4) {
+            float4 v;
+            if (use_smem) v = load4(row + i);
+            else {
+                v = load4(res + i);
+                if (dl && !write_residual) { const float4 d = load4(dl + i); v.x += d.x; v.y += d.y; v.z += d.z; v.w += d.w; }
+            }
+            const float4 ww = load4(w + i);
+            store4(o + i, make_float4(v.x * inv * ww.x, v.y * inv * ww.y, v.z * inv * ww.z, v.w * inv * ww.w));
+        }
+    } else {
+        for (int i = threadIdx.x; i < H; i += blockDim.x) {
+            float v;
+            if (use_smem) v = row[i];
+            else { v = res[i]; if (dl && !write_residual) v += to_float(dl[i]); }
+            o[i] = from_float<TO>(v * inv * w[i]);
+        }
     }
 }
 
@@ -79,6 +123,24 @@ __global__ void silu_mul_kernel(const T* __restrict__ gu, T* __restrict__ out, i
     out[idx] = from_float<T>(g / (1.0f + expf(-g)) * u);
 }
 
+// Four outputs a thread (needs I % 4 == 0, and I % 16 == 0 when interleaved).
+template <typename T>
+__global__ void silu_mul_vec_kernel(const T* __restrict__ gu, T* __restrict__ out, int I, size_t total4,
+                                    int interleaved) {
+    pdl_prologue();
+    size_t idx = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
+    if (idx >= total4) return;
+    const int per_row = I / 4;
+    size_t t = idx / per_row;
+    int i = (int)(idx - t * per_row) * 4;
+    const T* row = gu + t * 2 * I;
+    const int gi = interleaved ? 32 * (i / 16) + (i % 16) : i;
+    const int ui = interleaved ? gi + 16 : I + i;
+    const float4 g = load4(row + gi), u = load4(row + ui);
+    store4(out + t * I + i, make_float4(g.x / (1.0f + expf(-g.x)) * u.x, g.y / (1.0f + expf(-g.y)) * u.y,
+                                        g.z / (1.0f + expf(-g.z)) * u.z, g.w / (1.0f + expf(-g.w)) * u.w));
+}
+
 template <typename TI, typename TO>
 __global__ void cast_kernel(const TI* __restrict__ in, TO* __restrict__ out, size_t n) {
     pdl_prologue();
@@ -95,7 +157,7 @@ __global__ void add_kernel(float* __restrict__ res, const TD* __restrict__ delta
 }
 
 static inline int norm_threads(int H) {
-    int t = (H + 3) / 4;
+    int t = (H + 7) / 8;
     t = ((t + 31) / 32) * 32;
     if (t < 32) t = 32;
     if (t > 1024) t = 1024;
@@ -128,7 +190,8 @@ static int launch_add_rms_norm(float* residual, const void* delta, const int* ro
     size_t smem = (size_t)H * sizeof(float);
     int use_smem = smem <= 200 * 1024;
     if (!use_smem) smem = 0;
-    auto kern = add_rms_norm_kernel<TD, TO>;
+    const bool vec = (H % 4) == 0;
+    auto kern = vec ? add_rms_norm_kernel<TD, TO, 4> : add_rms_norm_kernel<TD, TO, 1>;
     if (smem > 48 * 1024) {
         cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
         if (e != cudaSuccess) return (int)e;
@@ -161,10 +224,17 @@ FF_EXPORT int ff_silu_mul(const void* gate_up, void* out, int dtype, int T, int 
     if (interleaved && (I % 16)) return FF_ERR_BAD_ARG;
     size_t total = (size_t)T * I;
     if (total == 0) return 0;
+    if (dtype != 0 && dtype != 1) return FF_ERR_BAD_ARG;
+    if (I % 4 == 0) {
+        const size_t total4 = total / 4;
+        unsigned blocks = (unsigned)((total4 + 255) / 256);
+        if (dtype == 0) FF_LAUNCH((silu_mul_vec_kernel<float>), blocks, 256, 0, stream, (const float*)gate_up, (float*)out, I, total4, interleaved);
+        else FF_LAUNCH((silu_mul_vec_kernel<bf16>), blocks, 256, 0, stream, (const bf16*)gate_up, (bf16*)out, I, total4, interleaved);
+        return 0;
+    }
     unsigned blocks = (unsigned)((total + 255) / 256);
     if (dtype == 0) FF_LAUNCH((silu_mul_kernel<float>), blocks, 256, 0, stream, (const float*)gate_up, (float*)out, I, total, interleaved);
-    else if (dtype == 1) FF_LAUNCH((silu_mul_kernel<bf16>), blocks, 256, 0, stream, (const bf16*)gate_up, (bf16*)out, I, total, interleaved);
-    else return FF_ERR_BAD_ARG;
+    else FF_LAUNCH((silu_mul_kernel<bf16>), blocks, 256, 0, stream, (const bf16*)gate_up, (bf16*)out, I, total, interleaved);
     FF_LAUNCH_CHECK();
     return 0;
 }

@@ -122,19 +122,6 @@ __device__ __forceinline__ void tc_ld16(uint32_t taddr, float (&v)[16]) {
 __device__ __forceinline__ void grid_launch_dependents() { asm volatile("griddepcontrol.launch_dependents;" ::: "memory"); }
 __device__ __forceinline__ void grid_dependency_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
 
-__device__ __forceinline__ void cluster_sync_all() {
-    __syncwarp();
-    asm volatile("barrier.cluster.arrive.release.aligned;\n\tbarrier.cluster.wait.acquire.aligned;" ::: "memory");
-}
-// float at `addr` (a shared-memory address of this block) in the block of rank `rank` of the cluster
-__device__ __forceinline__ float ld_peer_smem(uint32_t addr, uint32_t rank) {
-    uint32_t peer;
-    float v;
-    asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(peer) : "r"(addr), "r"(rank));
-    asm volatile("ld.shared::cluster.f32 %0, [%1];" : "=f"(v) : "r"(peer) : "memory");
-    return v;
-}
-
 // Shared-memory operand descriptor: K-major tile, rows of 128 bytes, 128-byte swizzle;
 // groups of 8 rows are 1024 bytes apart.
 __device__ __forceinline__ uint64_t smem_desc_sw128(uint32_t addr) {
