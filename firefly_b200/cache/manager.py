@@ -56,6 +56,7 @@ class RequestCache:
     first_live: List[int] = field(default_factory=list)     # per group: first page index still held
     state_slot: int = -1
     fresh: bool = True                    # no step has run yet (state must start at zero)
+    serial: int = 0                       # unique per admission (an id() may be reused, this is not)
 
 
 class CacheManager:
@@ -91,6 +92,7 @@ class CacheManager:
         # state slots: index 0 is scratch (padded lanes), requests get 1..max_requests
         self._free_state = list(range(max_requests, 0, -1))
         self.live: Dict[object, RequestCache] = {}
+        self._serial = 0
 
     # ---- sizes ----------------------------------------------------------------
     def bytes_per_block(self, dtype: torch.dtype) -> int:
@@ -117,8 +119,9 @@ class CacheManager:
             raise PageError(f"request {request_id!r} is already live")
         if not self._free_state:
             raise OutOfPages(f"no free request slot (max_requests={self.max_requests})")
+        self._serial += 1
         rc = RequestCache(request_id, 0, [[] for _ in self.groups], [0 for _ in self.groups],
-                          self._free_state.pop())
+                          self._free_state.pop(), True, self._serial)
         self.live[request_id] = rc
         return rc
 

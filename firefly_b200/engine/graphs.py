@@ -24,7 +24,8 @@ from .runner import MetaLayout, ModelRunner, StepEntry
 
 
 class _Bucket:
-    __slots__ = ("size", "layout", "meta_host", "meta_dev", "graph", "logits", "tokens", "h_tokens", "launches")
+    __slots__ = ("size", "layout", "meta_host", "meta_dev", "graph", "logits", "tokens", "h_tokens", "launches",
+                 "lanes")
 
 
 class DecodeGraphs:
@@ -51,39 +52,66 @@ class DecodeGraphs:
         return self.buckets[size]
 
     def _fill(self, b: _Bucket, entries: Sequence[StepEntry]) -> None:
+        """Write the step's metadata into the bucket's pinned buffer.  A lane that holds the same
+        request as in the step before only gets what changed: its token, position and any new
+        page; block-table rows are rewritten only for lanes whose request changed."""
         r, lay = self.runner, b.layout
         h = b.meta_host.numpy()
         n = len(entries)
         mb = r.max_blocks_per_seq
-        # padding lanes first (whole arrays), then the live lanes
-        h[lay.token_ids: lay.token_ids + b.size] = 0
-        h[lay.positions: lay.positions + b.size] = 0
-        h[lay.token_seq: lay.token_seq + b.size] = np.arange(b.size)
-        h[lay.cu_q: lay.cu_q + b.size + 1] = np.arange(b.size + 1)
-        h[lay.ctx_lens: lay.ctx_lens + b.size] = 0
-        h[lay.state_slots: lay.state_slots + b.size] = 0
-        h[lay.seq_fresh: lay.seq_fresh + b.size] = 0
-        h[lay.logits_rows: lay.logits_rows + b.size] = np.arange(b.size)
-        for off in lay.tables:
-            tab = h[off: off + b.size * mb].reshape(b.size, mb)
-            tab[n:, 0] = SCRATCH_PAGE
-            tab[n:, 1:] = -1
+        if b.lanes is None:
+            # constant parts, and every lane as padding: a dummy token at position 0 in the scratch page
+            h[lay.token_ids: lay.token_ids + b.size] = 0
+            h[lay.positions: lay.positions + b.size] = 0
+            h[lay.token_seq: lay.token_seq + b.size] = np.arange(b.size)
+            h[lay.cu_q: lay.cu_q + b.size + 1] = np.arange(b.size + 1)
+            h[lay.ctx_lens: lay.ctx_lens + b.size] = 0
+            h[lay.state_slots: lay.state_slots + b.size] = 0
+            h[lay.seq_fresh: lay.seq_fresh + b.size] = 0
+            h[lay.logits_rows: lay.logits_rows + b.size] = np.arange(b.size)
+            for off in lay.tables:
+                tab = h[off: off + b.size * mb].reshape(b.size, mb)
+                tab[:, 0] = SCRATCH_PAGE
+                tab[:, 1:] = -1
+            b.lanes = [None] * b.size
+        for i in range(n, b.size):                 # lanes that fell out of use become padding again
+            if b.lanes[i] is not None:
+                h[lay.token_ids + i] = 0
+                h[lay.positions + i] = 0
+                h[lay.ctx_lens + i] = 0
+                h[lay.state_slots + i] = 0
+                h[lay.seq_fresh + i] = 0
+                for off in lay.tables:
+                    h[off + i * mb] = SCRATCH_PAGE
+                    h[off + i * mb + 1: off + (i + 1) * mb] = -1
+                b.lanes[i] = None
         for i, e in enumerate(entries):
-            cl = e.cache.num_tokens
+            rc = e.cache
+            cl = rc.num_tokens
             tok = int(e.tokens[0])
             if not (0 <= tok < r.vocab_size):
                 raise ValueError(f"token id {tok} outside the vocabulary")
             if cl + 1 > r.max_model_len:
-                raise ValueError(f"request {e.cache.request_id!r} exceeds max_model_len")
+                raise ValueError(f"request {rc.request_id!r} exceeds max_model_len")
             h[lay.token_ids + i] = tok
             h[lay.positions + i] = cl
             h[lay.ctx_lens + i] = cl
-            h[lay.state_slots + i] = e.cache.state_slot
-            h[lay.seq_fresh + i] = 1 if e.cache.fresh else 0
-            for g, table in enumerate(e.cache.tables):
+            h[lay.seq_fresh + i] = 1 if rc.fresh else 0
+            old = b.lanes[i]
+            same = old is not None and old[0] == rc.serial
+            if not same:
+                h[lay.state_slots + i] = rc.state_slot
+            lens = []
+            for g, table in enumerate(rc.tables):
                 row = lay.tables[g] + i * mb
-                h[row: row + len(table)] = table
-                h[row + len(table): row + mb] = -1
+                if same and old[2][g] == rc.first_live[g] and old[1][g] <= len(table):
+                    if old[1][g] < len(table):
+                        h[row + old[1][g]: row + len(table)] = table[old[1][g]:]
+                else:
+                    h[row: row + len(table)] = table
+                    h[row + len(table): row + mb] = -1
+                lens.append(len(table))
+            b.lanes[i] = (rc.serial, lens, list(rc.first_live))
 
     def _prepare(self, size: int, capture: bool) -> _Bucket:
         r = self.runner
@@ -94,6 +122,7 @@ class DecodeGraphs:
         b.meta_dev = torch.zeros(b.layout.size, dtype=torch.int32, device=r.device)
         b.tokens = torch.zeros(size, dtype=torch.int32, device=r.device)
         b.h_tokens = torch.zeros(size, dtype=torch.int32).pin_memory()
+        b.lanes = None
         self._fill(b, [])
         b.meta_dev.copy_(b.meta_host)
         ctx = r.context_from_layout(b.layout, b.meta_dev, [1] * size, [0] * size)

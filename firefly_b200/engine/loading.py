@@ -37,13 +37,33 @@ def require_cuda(device) -> torch.device:
     return dev
 
 
+def load_config_with_file_hints(model_dir: str) -> ModelConfig:
+    """The typed configuration of a model folder.  A config.json that says nothing about
+    ``tie_word_embeddings`` is read as tied when the weight file holds no ``lm_head.weight``
+    (checkpoints with a shared head usually store the matrix once)."""
+    from ..config.base import read_config_json
+    from ..models.registry import config_from_dict
+    from ..weights.safetensors_io import open_model_files
+    raw = read_config_json(model_dir)
+    if "tie_word_embeddings" not in raw:
+        files = open_model_files(model_dir)
+        try:
+            names = {n for f in files for n in f.entries}
+        finally:
+            for f in files:
+                f.close()
+        if "lm_head.weight" not in names and "model.embed_tokens.weight" in names:
+            raw = dict(raw, tie_word_embeddings=True)
+    return config_from_dict(raw)
+
+
 def load_model(model_dir: str, *, dtype="bfloat16", device="cuda:0") -> Tuple[DecoderModel, ModelConfig]:
     """Read ``config.json``, pick the model by its architecture name, bind the
     tensors of ``model.safetensors`` by name."""
     dt = parse_dtype(dtype)
     dev = require_cuda(device)
     K.set_exact_matmul()
-    config = load_config(model_dir)
+    config = load_config_with_file_hints(model_dir)
     model = DecoderModel(spec_for(config), Runtime(dev, dt))
     tensors = load_weights(model_dir, model.weight_specs(), dtype=dt, device=dev)
     model.bind(tensors)

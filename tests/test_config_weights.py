@@ -170,6 +170,19 @@ def test_load_weights_dtype_policy(tmp_path):
     assert storage_dtype(torch.float16, torch.bfloat16) == torch.bfloat16
 
 
+def test_tied_head_is_inferred_when_the_key_is_absent(tmp_path):
+    from firefly_b200.engine.loading import load_config_with_file_hints
+    raw = {k: v for k, v in P.TINY_A.items() if k != "tie_word_embeddings"}
+    w = P.random_weights(P.TINY_A, 0)                      # no lm_head.weight
+    d = _folder(tmp_path, raw, w, "tied")
+    assert load_config_with_file_hints(d).tie_word_embeddings is True
+    w["lm_head.weight"] = torch.zeros(256, 64)
+    d2 = _folder(tmp_path, raw, w, "untied")
+    assert load_config_with_file_hints(d2).tie_word_embeddings is False
+    d3 = _folder(tmp_path, dict(raw, tie_word_embeddings=False), P.random_weights(P.TINY_A, 0), "says_untied")
+    assert load_config_with_file_hints(d3).tie_word_embeddings is False      # what config.json says stands
+
+
 def test_missing_files(tmp_path):
     with pytest.raises(ConfigError, match="config.json"):
         load_config(str(tmp_path))
