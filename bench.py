@@ -30,12 +30,22 @@ if ROOT not in sys.path:
 FALLBACK_PEAKS = {"hbm_gbs": 6650.0, "bf16_tflops": 1590.0, "bf16_tflops_sustained": 1400.0}
 
 
-def load_shape():
-    """Layer sizes of BASELINE.json's configs[2] (Qwen3-8B-shaped), as config.json keys."""
-    return dict(architectures=["Qwen3ForCausalLM"], hidden_size=4096, intermediate_size=12288,
-                num_hidden_layers=36, num_attention_heads=32, num_key_value_heads=8, head_dim=128,
-                vocab_size=151936, max_position_embeddings=4096, rms_norm_eps=1e-6, rope_theta=1e6,
-                tie_word_embeddings=False)
+SHAPES = {   # BASELINE.json configs[2] (the metric), configs[3] and configs[4]
+    "8b": dict(hidden_size=4096, intermediate_size=12288, num_hidden_layers=36, num_attention_heads=32,
+               num_key_value_heads=8, tie_word_embeddings=False),
+    "0.6b": dict(hidden_size=1024, intermediate_size=3072, num_hidden_layers=28, num_attention_heads=16,
+                 num_key_value_heads=8, tie_word_embeddings=True),
+    "32b": dict(hidden_size=5120, intermediate_size=25600, num_hidden_layers=64, num_attention_heads=64,
+                num_key_value_heads=8, tie_word_embeddings=False),
+}
+
+
+def load_shape(name: str = "8b"):
+    """Layer sizes of a BASELINE.json shape (default configs[2], Qwen3-8B-shaped), as config.json keys."""
+    base = dict(architectures=["Qwen3ForCausalLM"], head_dim=128, vocab_size=151936,
+                max_position_embeddings=4096, rms_norm_eps=1e-6, rope_theta=1e6)
+    base.update(SHAPES[name])
+    return base
 
 
 def peaks():
@@ -132,6 +142,7 @@ def main() -> int:
     ap.add_argument("--no-prefill", action="store_true", help="skip the prefill measurement")
     ap.add_argument("--no-decode", action="store_true", help="prefill measurement only (for profiling)")
     ap.add_argument("--dtype", default="bfloat16", choices=["bfloat16", "float32"])
+    ap.add_argument("--shape", default="8b", choices=sorted(SHAPES), help="model shape (default: the metric's 8b)")
     args = ap.parse_args()
     if args.impl == "reference":
         return reference_arm()
@@ -150,7 +161,7 @@ def main() -> int:
     from firefly_b200.ops import kernels as K
     from firefly_b200.sampling import SamplingParams
 
-    shape = load_shape()
+    shape = load_shape(args.shape)
     full_layers = shape["num_hidden_layers"]
     if args.layers:
         shape["num_hidden_layers"] = args.layers
@@ -309,12 +320,12 @@ def main() -> int:
     step_bytes = weight_bytes + args.batch * main_res["ctx_mean"] * kv_bytes_per_token
     achieved = step_bytes / (main_res["ms_per_step"] / 1e3) / 1e9
     out = {
-        "metric": "decode tok/s at batch 8 (Qwen3-8B-shaped bf16, 2048-token prompts)",
+        "metric": f"decode tok/s at batch {args.batch} (Qwen3-{args.shape.upper()}-shaped {args.dtype}, {P}-token prompts)",
         "value": main_res["tok_s"], "unit": "tok/s", "n_gpus": 1, "steps": K_steps, "warmup": W,
         "ms_per_step": main_res["ms_per_step"], "higher_is_better": True, "scaling": "weak",
         "vs_baseline": None, "dtype": "bf16" if args.dtype == "bfloat16" else "fp32", "data": "synthetic",
         "impl": "ours",
-        "config": {"model": "Qwen3-8B-shaped random weights", "global_batch": args.batch, "seq_len": args.context,
+        "config": {"model": f"Qwen3-{args.shape.upper()}-shaped random weights", "global_batch": args.batch, "seq_len": args.context,
                    "parallelism": "single GPU", "layers": L, "layers_of_config": full_layers, "hidden": H,
                    "q_heads": nq, "kv_heads": nkv, "head_dim": d, "intermediate": I, "vocab": V,
                    "prompt_len": P, "new_tokens": need_new, "kv_block": 16, "cuda_graphs": True,
