@@ -12,7 +12,11 @@
 // fixed order, reading its peers' shared memory, and runs the epilogue on that
 // slice.  No global scratch memory is involved.  Epilogues: store bfloat16, store
 // float32, add into a float32 residual, or SiLU(gate)*up for a weight whose rows
-// interleave gate and up in groups of 16.
+// interleave gate and up in groups of 16.  Two optional extras fold an RMSNorm between
+// two products into them: the residual-adding product also writes bfloat16(residual*w)
+// for the norm that follows and each row tile's sum of squares per token; the product
+// that consumes those activations multiplies its accumulator by 1/rms of the token,
+// summed from those partial sums in tile order.
 //
 // The reference runs these products through a library template with half-precision
 // accumulation (src/kernels/linear.cu:15-104), followed by separate launches for the
@@ -147,6 +151,17 @@ struct GemmArgs {
     int kb_per_split;     // 64-wide k blocks per range
     int stages;           // depth of the load pipeline
     int* status;
+    // RMSNorm folded in, producing side (EPI_RESIDUAL_ADD only; null: off): after out += acc,
+    // xw_out[t, n] = bfloat16(out[t, n] * xw_w[n]) and ssq_out[row tile][t] = sum over the tile's columns of out^2
+    bf16* xw_out;
+    const float* xw_w;
+    float* ssq_out;
+    // RMSNorm folded in, consuming side (null: off): the accumulator of token t is multiplied by
+    // rsqrt(sum_p ssq_in[p][t] / norm_dim + norm_eps), p < ssq_parts
+    const float* ssq_in;
+    int ssq_parts;
+    int norm_dim;
+    float norm_eps;
 };
 
 template <int TOK>
@@ -162,6 +177,8 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant_
     // bars[0..S) full, bars[S..2S) empty, bars[2S] accumulator ready
     __shared__ uint32_t s_tmem_base;
     __shared__ int s_abort;
+    __shared__ float s_inv[256];          // 1/rms per token of the tile (norm folded in, consuming side)
+    __shared__ float s_red[4][16];        // per-warp sums of squares (producing side)
 
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int n0 = blockIdx.x * BN, t0 = blockIdx.y * TOK;
@@ -250,6 +267,21 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant_
         const int row = quad * 32 + lane;                       // weight row within the tile
         const int n = n0 + row;
         bool ok = true;
+        if (a.ssq_in) {
+            // 1/rms of the tile's tokens from the per-tile sums of squares the product in front left:
+            // done while the main loop runs (these warps have nothing else to do until it ends)
+            grid_dependency_wait();
+            const int et = threadIdx.x - 64;
+            for (int c = et; c < TOK; c += 128) {
+                const int t = t0 + c;
+                float ss = 0.f;
+                if (t < a.T) {
+#pragma unroll 8
+                    for (int p = 0; p < a.ssq_parts; ++p) ss += __ldcg(a.ssq_in + (size_t)p * a.T + t);   // fixed order
+                }
+                s_inv[c] = 1.0f / sqrtf(ss / (float)a.norm_dim + a.norm_eps);
+            }
+        }
         if (n_iters > 0) ok = mbar_wait(smem_addr(&bars[2 * STAGES]), 0, a.status, abort_flag, 103);
         ok = __all_sync(0xffffffffu, ok);                       // the tensor-memory loads below are warp-wide
         tc_fence_after();
@@ -275,8 +307,8 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant_
         const int quad = warp & 3;
         const int row = quad * 32 + lane;
         const int n = n0 + row;
-        bool ok = !*abort_flag;
-        ok = __all_sync(0xffffffffu, ok);
+        asm volatile("bar.sync 1, 128;" ::: "memory");   // all four warps see the same abort flag below
+        const bool ok = !*abort_flag;
         grid_dependency_wait();                    // the output may still be in use by the kernel before
         // tokens of the tile this block finishes: all of them without a split, else a slice
         int c_begin = 0, c_end = TOK;
@@ -306,6 +338,10 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant_
                 }
             }
             if (!ok) continue;
+            if (a.ssq_in) {
+#pragma unroll
+                for (int i = 0; i < 16; ++i) v[i] *= s_inv[min(c0 + i, TOK - 1)];
+            }
             if (a.epilogue == EPI_SWIGLU) {
                 // rows come in groups of 32: 16 gate rows, then the 16 up rows of the same columns
 #pragma unroll
@@ -319,6 +355,32 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant_
                             __float2bfloat16_rn(g / (1.0f + expf(-g)) * other);
                     }
                 }
+            } else if (a.epilogue == EPI_RESIDUAL_ADD && a.xw_out) {
+                // out += acc; and for the norm that follows: bfloat16(out * w) and this tile's sums of squares
+                const float wn = n < a.N ? __ldg(a.xw_w + n) : 0.f;
+                float sq[16];
+#pragma unroll
+                for (int i = 0; i < 16; ++i) {
+                    const int t = t0 + c0 + i;
+                    sq[i] = 0.f;
+                    if (i >= cn || t >= a.T || n >= a.N) continue;
+                    const size_t o = (size_t)t * a.ldo + n;
+                    const float r = reinterpret_cast<float*>(a.out)[o] + v[i];
+                    reinterpret_cast<float*>(a.out)[o] = r;
+                    a.xw_out[(size_t)t * a.N + n] = __float2bfloat16_rn(r * wn);
+                    sq[i] = r * r;
+                }
+#pragma unroll
+                for (int i = 0; i < 16; ++i) {
+                    const float w_sum = warp_sum(sq[i]);
+                    if (lane == 0) s_red[quad][i] = w_sum;
+                }
+                asm volatile("bar.sync 1, 128;" ::: "memory");
+                const int et = threadIdx.x - 64;
+                if (et < cn && t0 + c0 + et < a.T)
+                    a.ssq_out[(size_t)blockIdx.x * a.T + t0 + c0 + et] =
+                        s_red[0][et] + s_red[1][et] + s_red[2][et] + s_red[3][et];
+                asm volatile("bar.sync 1, 128;" ::: "memory");
             } else if (n < a.N) {
 #pragma unroll
                 for (int i = 0; i < 16; ++i) {
@@ -461,8 +523,14 @@ FF_EXPORT int ff_gemm_tc_plan(int T, int N, int K, int want_splits, int* tok_out
 // epilogue: 0 bf16 out [T, ldo], 1 f32 out, 2 f32 out += , 3 swiglu (bf16 out [T, ldo], N/2 columns).
 // pdl: launch with programmatic stream serialization (the kernel before must tolerate an early start
 // of this one, which only prefetches weights before it waits).
+// Norm folded in (all optional, see GemmArgs): xw_out/xw_w/ssq_out with EPI_RESIDUAL_ADD
+// (ssq_out holds ceil(N/128) * T floats); ssq_in/ssq_parts/norm_dim/norm_eps on the consuming side.
 FF_EXPORT int ff_gemm_tc(const void* x, const void* w, void* out, int ldo, int T, int N, int K, int epilogue,
-                         int want_splits, int pdl, int* status, cudaStream_t stream) {
+                         int want_splits, int pdl, void* xw_out, const float* xw_w, float* ssq_out,
+                         const float* ssq_in, int ssq_parts, int norm_dim, float norm_eps, int* status,
+                         cudaStream_t stream) {
+    if (xw_out && (epilogue != EPI_RESIDUAL_ADD || !xw_w || !ssq_out)) return FF_ERR_BAD_ARG;
+    if (ssq_in && (ssq_parts <= 0 || norm_dim <= 0)) return FF_ERR_BAD_ARG;
     if (T <= 0 || N <= 0) return 0;
     if (K <= 0 || (K % 8) || epilogue < 0 || epilogue > 3) return FF_ERR_BAD_ARG;
     if (epilogue == EPI_SWIGLU && (N % 32)) return FF_ERR_UNSUPPORTED;
@@ -480,6 +548,8 @@ FF_EXPORT int ff_gemm_tc(const void* x, const void* w, void* out, int ldo, int T
     a.out = out; a.ldo = ldo; a.T = T; a.N = N; a.K = K; a.epilogue = epilogue; a.splits = splits;
     a.kb_per_split = (num_kb + splits - 1) / splits;
     a.status = status;
+    a.xw_out = (bf16*)xw_out; a.xw_w = xw_w; a.ssq_out = ssq_out;
+    a.ssq_in = ssq_in; a.ssq_parts = ssq_parts; a.norm_dim = norm_dim; a.norm_eps = norm_eps;
     switch (tok) {
         case 16: return launch<16>(mw, mx, a, n_tiles, t_tiles, pdl, stream);
         case 32: return launch<32>(mw, mx, a, n_tiles, t_tiles, pdl, stream);

@@ -26,6 +26,8 @@ class DecoderModel:
         self.final_norm = build_part("norm", spec.final_norm, rt)
         self.head = build_part("head", spec.head, rt)
         self.schedule = spec.resolved_schedule()
+        import inspect
+        self._forward_params = [set(inspect.signature(b.forward).parameters) for b in self.blocks]
         self.bound = False
 
     # -- weights ------------------------------------------------------------------
@@ -75,8 +77,16 @@ class DecoderModel:
         if self.embedding_position is not None:
             self.embedding_position.apply_to_embedding(residual, ctx)
         pending: Optional[torch.Tensor] = None
-        for layer, slot, write in self.schedule:
-            residual, pending = self.blocks[layer].forward(residual, pending, ctx, slot, write)
+        runs = self.schedule
+        for i, (layer, slot, write) in enumerate(runs):
+            block = self.blocks[layer]
+            # the norm that follows this run, for a last product that can fold it in
+            nxt = self.blocks[runs[i + 1][0]] if i + 1 < len(runs) else None
+            next_norm = nxt.first_norm() if nxt is not None and hasattr(nxt, "first_norm") else None
+            if "next_norm" in self._forward_params[layer]:
+                residual, pending = block.forward(residual, pending, ctx, slot, write, next_norm=next_norm)
+            else:
+                residual, pending = block.forward(residual, pending, ctx, slot, write)
         x = self.final_norm.forward(residual, pending, ctx, tag="final_normed", row_idx=ctx.logits_rows)
         return self.head.forward(x, ctx)
 

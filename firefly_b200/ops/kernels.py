@@ -263,6 +263,7 @@ def linear(x: torch.Tensor, weight: torch.Tensor, out: torch.Tensor) -> None:
 
 EPI_BF16, EPI_F32, EPI_RESIDUAL_ADD, EPI_SWIGLU = 0, 1, 2, 3
 USE_TCGEN05_GEMM = True    # tests flip this to compare with the library route
+FOLD_NORM = True           # fold the RMSNorm between two tcgen05 products into their epilogues
 
 
 def gemm_tc_plan(T: int, N: int, K: int, want_splits: int):
@@ -274,12 +275,17 @@ def gemm_tc_plan(T: int, N: int, K: int, want_splits: int):
 
 
 def gemm_tc(x: torch.Tensor, weight: torch.Tensor, out: torch.Tensor, epilogue: int, want_splits: int,
-            status: torch.Tensor) -> None:
+            status: torch.Tensor, *, norm_out: Optional[tuple] = None, norm_in: Optional[tuple] = None) -> None:
     """out (op)= x @ weight^T on tcgen05 tensor cores; bfloat16 operands, 32-bit accumulation.
 
     epilogue: EPI_BF16 store bfloat16, EPI_F32 store float32, EPI_RESIDUAL_ADD add into a float32
     ``out``, EPI_SWIGLU store silu(gate)*up as bfloat16 [T, N/2] for a weight whose rows interleave
-    gate and up in groups of 16.  ``want_splits`` K ranges (at most 8) share a thread-block cluster."""
+    gate and up in groups of 16.  ``want_splits`` K ranges (at most 8) share a thread-block cluster.
+
+    An RMSNorm between two products can be folded into them.  Producing side (EPI_RESIDUAL_ADD):
+    ``norm_out`` = (xw bfloat16 [T, N], norm weight float32 [N], ssq float32 [ceil(N/128), T]) receives
+    bfloat16(out * w) and each row tile's sum of squares per token.  Consuming side: ``norm_in`` =
+    (ssq [parts, T], norm_dim, eps) scales token t's result by rsqrt(sum_p ssq[p, t] / norm_dim + eps)."""
     _need_cuda(x, weight, out, status)
     assert x.dtype == torch.bfloat16 and weight.dtype == torch.bfloat16
     T, Kd = x.shape
@@ -290,9 +296,24 @@ def gemm_tc(x: torch.Tensor, weight: torch.Tensor, out: torch.Tensor, epilogue: 
     else:
         assert out.dtype == torch.float32
     assert out.shape[0] == T and out.shape[1] == (N // 2 if epilogue == EPI_SWIGLU else N)
+    xw = xw_w = ssq_out = ssq_in = None
+    parts = dim = 0
+    eps = 0.0
+    if norm_out is not None:
+        xw, xw_w, ssq_out = norm_out
+        _need_cuda(xw, xw_w, ssq_out)
+        assert epilogue == EPI_RESIDUAL_ADD and xw.dtype == torch.bfloat16 and xw.shape == (T, N)
+        assert xw_w.dtype == torch.float32 and xw_w.numel() == N
+        assert ssq_out.dtype == torch.float32 and ssq_out.numel() >= -(-N // 128) * T
+    if norm_in is not None:
+        ssq_in, dim, eps = norm_in
+        _need_cuda(ssq_in)
+        assert ssq_in.dtype == torch.float32 and ssq_in.dim() == 2 and ssq_in.shape[1] == T
+        parts = ssq_in.shape[0]
     _check(_lib("gemm_tcgen05").ff_gemm_tc(
         _p(x), _p(weight), _p(out), c_int(out.stride(0)), c_int(T), c_int(N), c_int(Kd), c_int(epilogue),
-        c_int(want_splits), c_int(1 if USE_PDL else 0), _p(status), _stream()), "gemm_tc")
+        c_int(want_splits), c_int(1 if USE_PDL else 0), _p(xw), _p(xw_w), _p(ssq_out), _p(ssq_in),
+        c_int(parts), c_int(dim), c_float(eps), _p(status), _stream()), "gemm_tc")
 
 
 def interleave_gate_up(gate: torch.Tensor, up: torch.Tensor) -> torch.Tensor:

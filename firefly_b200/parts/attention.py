@@ -33,6 +33,8 @@ from .linear import apply_linear, linear_into_residual
 
 
 class GQAttention(Part):
+    accepts_folded_norm = True       # its first operation is a product that can finish a folded norm
+
     def __init__(self, spec, rt, position=None):
         super().__init__(spec, rt)
         self.hidden = int(self.p("hidden_size"))
@@ -86,7 +88,7 @@ class GQAttention(Part):
                 self.k_norm_w = self._vector32(tensors[self.name("k_norm.weight")])
 
     # -- run ------------------------------------------------------------------
-    def forward(self, x: torch.Tensor, ctx, slot: int, write_cache: bool, accumulate_into=None):
+    def forward(self, x, ctx, slot: int, write_cache: bool, accumulate_into=None, then_norm=None):
         T = x.shape[0]
         ws = ctx.workspace
         if write_cache and not self.has_kv:
@@ -105,7 +107,7 @@ class GQAttention(Part):
                              pages if write_cache else None, ctx.status)
         att = ws.get("attn.out", (T, self.nq * self.d), ctx.dtype)
         self._attend(qkv, width, pages, table, ctx, att)
-        return linear_into_residual(att, self.w_o, accumulate_into, ctx, "attn.proj")
+        return linear_into_residual(att, self.w_o, accumulate_into, ctx, "attn.proj", then_norm)
 
     def _attend(self, qkv, width, pages, table, ctx, att) -> None:
         window = 0 if self.window is None else int(self.window)

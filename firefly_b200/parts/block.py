@@ -36,6 +36,15 @@ class Block:
         # residual itself (and return None); others return a delta
         self._mixer_fuses = "accumulate_into" in inspect.signature(self.mixer.forward).parameters
         self._ffn_fuses = "accumulate_into" in inspect.signature(self.feed_forward.forward).parameters
+        # ... and, told which norm follows (``then_norm``), may fold that norm into its last product
+        self._mixer_folds = "then_norm" in inspect.signature(self.mixer.forward).parameters
+        self._ffn_folds = "then_norm" in inspect.signature(self.feed_forward.forward).parameters
+        # a part that declares ``accepts_folded_norm`` may be handed a FoldedNorm as its input
+        self._mixer_defers = bool(getattr(self.mixer, "accepts_folded_norm", False))
+        self._ffn_defers = bool(getattr(self.feed_forward, "accepts_folded_norm", False))
+        for k, nrm in enumerate(self.norms):
+            if hasattr(nrm, "fold_tag"):
+                nrm.fold_tag = f"fold.{k}"
 
     def parts(self) -> List[Part]:
         out = [self.mixer, self.feed_forward, *self.norms]
@@ -55,18 +64,25 @@ class Block:
 
 
 class PreNormBlock(Block):
-    def forward(self, residual: torch.Tensor, pending: Optional[torch.Tensor], ctx, slot: int,
-                write_cache: bool) -> Tuple[torch.Tensor, Optional[torch.Tensor]]:
-        x = self.norms[0].forward(residual, pending, ctx)
+    def first_norm(self):
+        """The norm a block in front of this one may fold into its last product."""
+        return self.norms[0]
+
+    def forward(self, residual: torch.Tensor, pending, ctx, slot: int, write_cache: bool, next_norm=None):
+        x = self.norms[0].forward(residual, pending, ctx, may_defer=self._mixer_defers)
+        kw = {}
         if self._mixer_fuses:
-            a = self.mixer.forward(x, ctx, slot, write_cache, accumulate_into=residual)
-        else:
-            a = self.mixer.forward(x, ctx, slot, write_cache)
-        x = self.norms[1].forward(residual, a, ctx)
+            kw["accumulate_into"] = residual
+            if self._mixer_folds:
+                kw["then_norm"] = self.norms[1]
+        a = self.mixer.forward(x, ctx, slot, write_cache, **kw)
+        x = self.norms[1].forward(residual, a, ctx, may_defer=self._ffn_defers)
+        kw = {}
         if self._ffn_fuses:
-            f = self.feed_forward.forward(x, ctx, accumulate_into=residual)
-        else:
-            f = self.feed_forward.forward(x, ctx)
+            kw["accumulate_into"] = residual
+            if self._ffn_folds:
+                kw["then_norm"] = next_norm
+        f = self.feed_forward.forward(x, ctx, **kw)
         return residual, f
 
 

@@ -37,14 +37,28 @@ def _splits(N: int, Kd: int) -> int:
     return max(1, min(_SM_COUNT // tiles, 8, kb // 4))
 
 
-def _tc(x, weight, out, epilogue, ctx) -> None:
+def _resolve(x, weight):
+    """A folded norm stays folded only if the product that consumes it can finish it."""
+    from .norm import FoldedNorm
+    if isinstance(x, FoldedNorm) and not tc_usable(x, weight):
+        return x.materialize()
+    return x
+
+
+def _tc(x, weight, out, epilogue, ctx, norm_out=None) -> None:
+    from .norm import FoldedNorm
     N, Kd = weight.shape
-    K.gemm_tc(x, weight, out, epilogue, _splits(N, Kd), ctx.status)
+    if isinstance(x, FoldedNorm):
+        K.gemm_tc(x.xw, weight, out, epilogue, _splits(N, Kd), ctx.status, norm_out=norm_out,
+                  norm_in=(x.ssq, x.norm.size, x.norm.eps))
+    else:
+        K.gemm_tc(x, weight, out, epilogue, _splits(N, Kd), ctx.status, norm_out=norm_out)
 
 
 def apply_linear(x: torch.Tensor, weight: torch.Tensor, out: torch.Tensor, ctx, tag: str) -> torch.Tensor:
     """out = x W^T (out in the activation type, or float32)."""
     ws = ctx.workspace
+    x = _resolve(x, weight)
     if tc_usable(x, weight):
         _tc(x, weight, out, K.EPI_F32 if out.dtype == torch.float32 else K.EPI_BF16, ctx)
         return out
@@ -67,11 +81,20 @@ def apply_linear(x: torch.Tensor, weight: torch.Tensor, out: torch.Tensor, ctx, 
 
 
 def linear_into_residual(x: torch.Tensor, weight: torch.Tensor, residual: Optional[torch.Tensor], ctx,
-                         tag: str) -> Optional[torch.Tensor]:
+                         tag: str, then_norm=None):
     """The product as a delta for the residual stream.  When it can be fused it is
-    added into ``residual`` (float32) in the product's epilogue and None is
-    returned; else the delta is returned for the next norm to add."""
+    added into ``residual`` (float32) in the product's epilogue; then None is
+    returned, or, when the norm that follows is given as ``then_norm`` and can be
+    folded, a FoldedNorm that the norm's consumer finishes.  Else the delta is
+    returned for the next norm to add."""
+    x = _resolve(x, weight)
     if residual is not None and tc_usable(x, weight):
+        if then_norm is not None and K.FOLD_NORM and getattr(then_norm, "size", None) == weight.shape[0] \
+                and hasattr(then_norm, "fold_buffers"):
+            from .norm import FoldedNorm
+            xw, nw, ssq = then_norm.fold_buffers(x.shape[0], ctx)
+            _tc(x, weight, residual, K.EPI_RESIDUAL_ADD, ctx, norm_out=(xw, nw, ssq))
+            return FoldedNorm(then_norm, residual, xw, ssq, ctx)
         _tc(x, weight, residual, K.EPI_RESIDUAL_ADD, ctx)
         return None
     out = ctx.workspace.get(tag, (x.shape[0], weight.shape[0]), ctx.dtype)
@@ -82,6 +105,9 @@ def linear_swiglu(x: torch.Tensor, w_gate_up: torch.Tensor, inter: int, interlea
     """silu(x Wg^T) * (x Wu^T) for the stacked weight [2I, H] (``interleaved``: gate
     and up rows alternate in groups of 16)."""
     ws = ctx.workspace
+    x = _resolve(x, w_gate_up)
+    if not interleaved and not isinstance(x, torch.Tensor):
+        x = x.materialize()
     T = x.shape[0]
     act = ws.get("mlp.act", (T, inter), ctx.dtype)
     if interleaved and tc_usable(x, w_gate_up):

@@ -18,6 +18,8 @@ from .linear import linear_into_residual, linear_swiglu
 
 
 class SwiGLUMLP(Part):
+    accepts_folded_norm = True       # its first operation is a product that can finish a folded norm
+
     def __init__(self, spec, rt):
         super().__init__(spec, rt)
         self.hidden = int(self.p("hidden_size"))
@@ -41,11 +43,12 @@ class SwiGLUMLP(Part):
         self.w_gate_up = K.interleave_gate_up(g, u) if self.interleaved else torch.cat([g, u], dim=0).contiguous()
         self.w_down = self._matrix(tensors[self.name("down_proj.weight")])
 
-    def forward(self, x: torch.Tensor, ctx, accumulate_into=None):
-        """Returns the delta [T, hidden], or None when it was added into
-        ``accumulate_into`` (the 32-bit residual) by the last product's epilogue."""
+    def forward(self, x, ctx, accumulate_into=None, then_norm=None):
+        """Returns the delta [T, hidden]; or None when it was added into ``accumulate_into`` (the
+        32-bit residual) by the last product's epilogue; or a FoldedNorm when that epilogue also
+        prepared the norm that follows (``then_norm``)."""
         act = linear_swiglu(x, self.w_gate_up, self.inter, self.interleaved, ctx)
-        return linear_into_residual(act, self.w_down, accumulate_into, ctx, "mlp.down")
+        return linear_into_residual(act, self.w_down, accumulate_into, ctx, "mlp.down", then_norm)
 
 
 register_part("feed_forward", "swiglu_mlp", SwiGLUMLP)

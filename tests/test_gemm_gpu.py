@@ -75,6 +75,38 @@ def test_swiglu(T, splits, I):
     _run(T, 2 * I, 512, splits, K().EPI_SWIGLU)
 
 
+@pytest.mark.parametrize("T", [1, 8, 20, 64])
+@pytest.mark.parametrize("splits", [1, 4])
+def test_rms_norm_folded_into_two_products(T, splits):
+    """Product A adds into the residual and leaves bfloat16(residual*w) and per-tile sums of
+    squares; product B consumes them: together they equal add, RMSNorm, product."""
+    k = K()
+    g = torch.Generator().manual_seed(T * 10 + splits)
+    H, Ka, Nb, eps = 328, 512, 384, 1e-5                 # a width that is no multiple of 128
+    res0 = torch.randn(T, H, generator=g) * 2
+    xa = torch.randn(T, Ka, generator=g).to(torch.bfloat16)
+    wa = (torch.randn(H, Ka, generator=g) / Ka ** 0.5).to(torch.bfloat16)
+    nw = 1 + 0.1 * torch.randn(H, generator=g)
+    wb = (torch.randn(Nb, H, generator=g) / H ** 0.5).to(torch.bfloat16)
+    status = torch.zeros(1, dtype=torch.int32, device="cuda")
+    res = res0.cuda()
+    xw = torch.zeros(T, H, dtype=torch.bfloat16, device="cuda")
+    parts = -(-H // 128)
+    ssq = torch.full((parts, T), float("nan"), device="cuda")
+    k.gemm_tc(xa.cuda(), wa.cuda(), res, k.EPI_RESIDUAL_ADD, splits, status, norm_out=(xw, nw.cuda(), ssq))
+    outb = torch.zeros(T, Nb, dtype=torch.float32, device="cuda")
+    k.gemm_tc(xw, wb.cuda(), outb, k.EPI_F32, splits, status, norm_in=(ssq, H, eps))
+    torch.cuda.synchronize()
+    assert int(status) == 0
+    res_want = res0.double() + xa.double() @ wa.double().T
+    assert float((res.cpu().double() - res_want).abs().max()) < 2e-2
+    assert torch.allclose(ssq.sum(0).cpu().double(), (res.cpu().double() ** 2).sum(-1), rtol=1e-4)
+    xn = res_want * torch.rsqrt((res_want ** 2).mean(-1, keepdim=True) + eps) * nw.double()
+    want = xn @ wb.double().T
+    err = float((outb.cpu().double() - want).abs().max()) / float(want.abs().max())
+    assert err < 2e-2, err
+
+
 def test_refuses_what_it_cannot_do():
     k = K()
     x = torch.zeros(4, 20, dtype=torch.bfloat16, device="cuda")
