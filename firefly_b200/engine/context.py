@@ -84,6 +84,7 @@ class StepContext:
     cache: object                      # CacheManager
     dtype: torch.dtype                 # activation type of this engine
     pure_decode: bool = False
+    num_decode_seqs: int = 0           # the first this-many sequences have exactly one token
     captured: bool = False             # being captured into a CUDA graph: launch shapes must be static
 
     def kv(self, slot: int) -> Tuple[torch.Tensor, torch.Tensor]:

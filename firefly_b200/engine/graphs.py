@@ -129,6 +129,7 @@ class DecodeGraphs:
         ctx.workspace = self.workspace
         ctx.max_kv_len = r.max_model_len      # launch shapes must not depend on the requests
         ctx.captured = True
+        ctx.num_decode_seqs = size
         side = torch.cuda.Stream(device=r.device)
         side.wait_stream(torch.cuda.current_stream())
         with torch.cuda.stream(side):

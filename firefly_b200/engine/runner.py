@@ -103,19 +103,28 @@ class ModelRunner:
 
     def build_context(self, entries: Sequence[StepEntry], *, meta_host: Optional[torch.Tensor] = None,
                       meta_dev: Optional[torch.Tensor] = None, upload: bool = True) -> StepContext:
+        # sequences that decode one token come first in the step's arrays (in their given order), the
+        # others after them: the attention kernels for the two kinds then each see one contiguous range
         n = len(entries)
+        given = list(entries)
+        order = sorted(range(n), key=lambda i: 0 if len(given[i].tokens) == 1 else 1)
+        entries = [given[i] for i in order]
         q_lens = [len(e.tokens) for e in entries]
         T = sum(q_lens)
         ctx_lens = [e.cache.num_tokens for e in entries]
-        wants: List[int] = []
-        start = 0
+        starts = {}
+        pos = 0
         for e, ql in zip(entries, q_lens):
+            starts[id(e)] = pos
+            pos += ql
+        wants: List[int] = []          # in the order the caller gave the entries
+        for e in given:
+            ql = len(e.tokens)
             for w in e.want:
                 if not (0 <= w < ql):
                     raise StepError(f"request {e.cache.request_id!r}: wanted place {w} is outside its "
                                     f"{ql} tokens of this step")
-                wants.append(start + w)
-            start += ql
+                wants.append(starts[id(e)] + w)
         lay = MetaLayout(T, n, len(wants), len(self.cache.groups), self.max_blocks_per_seq)
         if meta_host is None:
             self._ensure_meta(lay.size)
@@ -171,7 +180,7 @@ class ModelRunner:
             max_q_len=max(q_lens, default=0),
             max_kv_len=max((c + q for c, q in zip(ctx_lens, q_lens)), default=0),
             workspace=self.workspace, status=self.status, cache=self.cache, dtype=self.dtype,
-            pure_decode=all(q == 1 for q in q_lens))
+            pure_decode=all(q == 1 for q in q_lens), num_decode_seqs=sum(1 for q in q_lens if q == 1))
 
     # ------------------------------------------------------------------------------
     def step(self, entries: Sequence[StepEntry]) -> torch.Tensor:

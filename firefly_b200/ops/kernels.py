@@ -394,17 +394,19 @@ def paged_attention(q: torch.Tensor, q_stride: int, pages: torch.Tensor, table: 
                              scale, window, ctx.status)
         return
     G = nq // nkv
-    if ctx.pure_decode and G <= 16:
-        n = ctx.num_seqs
-        splits = decode_splits(n, nkv, ctx.max_kv_len)
+    n = ctx.num_seqs
+    n_dec = ctx.num_decode_seqs if G <= 16 else 0      # these come first in the step's arrays
+    if n_dec:
+        # one-token sequences: split-KV kernel
+        splits = decode_splits(n_dec, nkv, ctx.max_kv_len)
         # n*nq*splits < G*target + n*nq for every n: the largest batch needs the most
-        cap = max(n * nq * splits, G * _SM_TARGET_CTAS + n * nq)
+        cap = max(n_dec * nq * splits, G * _SM_TARGET_CTAS + n_dec * nq)
         part_o = ctx.workspace.get("attn.part_o", (cap * d,), torch.float32)
         part_ml = ctx.workspace.get("attn.part_ml", (cap * 2,), torch.float32)
-        attn_decode(q, q_stride, pages, table, ctx.cu_q, ctx.ctx_lens, n, out, part_o, part_ml, nq, nkv, d,
+        attn_decode(q, q_stride, pages, table, ctx.cu_q, ctx.ctx_lens, n_dec, out, part_o, part_ml, nq, nkv, d,
                     scale, window, splits)
-    else:
-        bm = 64
-        tiles = sum(-(-(ql * G) // bm) for ql in ctx.q_lens)
-        attn_tiled(q, q_stride, pages, table, ctx.cu_q, ctx.ctx_lens, ctx.num_seqs, tiles, out, nq, nkv, d,
-                   scale, window)
+    if n_dec < n:
+        # portions of prompts: tiled kernel over the remaining sequences (token offsets in cu_q are absolute)
+        tiles = sum(-(-(ql * G) // 64) for ql in ctx.q_lens[n_dec:])
+        attn_tiled(q, q_stride, pages, table[n_dec:], ctx.cu_q[n_dec:], ctx.ctx_lens[n_dec:], n - n_dec, tiles,
+                   out, nq, nkv, d, scale, window)
