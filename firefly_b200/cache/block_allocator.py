@@ -1,6 +1,8 @@
 """Free list of cache pages.
 
-Same contract as the reference's ``BlockAllocator`` (include/firefly/scheduler.h:13-35,
+The list itself is native code (``csrc/host/block_pool.cc``, built with the host
+C++ compiler at first use); this class is its Python face.  Same contract as the
+reference's ``BlockAllocator`` (include/firefly/scheduler.h:13-35,
 src/scheduler.cc:13-54): ``allocate(n)`` is all-or-nothing, ``free`` gives pages
 back, and the list is last-in-first-out, so a page that was just given back is
 the next one handed out.  Added: every page is tracked, so freeing a page twice,
@@ -10,11 +12,32 @@ for padded lanes of a captured graph).
 """
 from __future__ import annotations
 
+import ctypes
 from typing import Iterable, List, Optional
 
 
 class PageError(RuntimeError):
     pass
+
+
+_lib = None
+
+
+def _native():
+    global _lib
+    if _lib is None:
+        from ..ops.build import load_host_module
+        lib = load_host_module("host/block_pool.cc")
+        lib.ffh_pool_create.restype = ctypes.c_void_p
+        lib.ffh_pool_create.argtypes = [ctypes.c_int, ctypes.c_int]
+        lib.ffh_pool_destroy.argtypes = [ctypes.c_void_p]
+        lib.ffh_pool_num_free.argtypes = [ctypes.c_void_p]
+        lib.ffh_pool_allocate.argtypes = [ctypes.c_void_p, ctypes.c_int, ctypes.POINTER(ctypes.c_int)]
+        lib.ffh_pool_free.argtypes = [ctypes.c_void_p, ctypes.POINTER(ctypes.c_int), ctypes.c_int,
+                                      ctypes.POINTER(ctypes.c_int)]
+        lib.ffh_pool_check.argtypes = [ctypes.c_void_p, ctypes.POINTER(ctypes.c_int)]
+        _lib = lib
+    return _lib
 
 
 class BlockAllocator:
@@ -23,51 +46,59 @@ class BlockAllocator:
             raise ValueError("num_blocks must be >= 0")
         self.num_blocks = num_blocks
         self.first_id = first_id
-        # LIFO: the lowest ids are handed out first from a fresh pool
-        self._free: List[int] = list(range(first_id + num_blocks - 1, first_id - 1, -1))
-        self._held = [False] * num_blocks
+        self._lib = _native()
+        self._h = self._lib.ffh_pool_create(num_blocks, first_id)
+        if not self._h:
+            raise MemoryError("could not create the page pool")
+
+    def __del__(self):
+        h, self._h = getattr(self, "_h", None), None
+        if h:
+            self._lib.ffh_pool_destroy(h)
 
     @property
     def num_free(self) -> int:
-        return len(self._free)
+        return self._lib.ffh_pool_num_free(self._h)
 
     @property
     def num_held(self) -> int:
-        return self.num_blocks - len(self._free)
+        return self.num_blocks - self.num_free
 
     def can_allocate(self, n: int) -> bool:
-        return n <= len(self._free)
+        return n <= self.num_free
 
     def allocate(self, n: int) -> Optional[List[int]]:
         """``n`` pages, or None (and nothing taken) when fewer are free."""
         if n < 0:
             raise ValueError("cannot allocate a negative number of pages")
-        if n > len(self._free):
+        if n == 0:
+            return []
+        buf = (ctypes.c_int * n)()
+        rc = self._lib.ffh_pool_allocate(self._h, n, buf)
+        if rc == 0:
             return None
-        out = [self._free.pop() for _ in range(n)]
-        for b in out:
-            self._held[b - self.first_id] = True
-        return out
+        return list(buf)
 
     def free(self, blocks: Iterable[int]) -> None:
-        for b in blocks:
-            i = b - self.first_id
-            if not (0 <= i < self.num_blocks):
-                raise PageError(f"page {b} does not belong to this pool "
-                                f"[{self.first_id}, {self.first_id + self.num_blocks})")
-            if not self._held[i]:
-                raise PageError(f"page {b} freed twice (or never allocated)")
-            self._held[i] = False
-            self._free.append(b)
+        ids = list(blocks)
+        if not ids:
+            return
+        arr = (ctypes.c_int * len(ids))(*ids)
+        bad = ctypes.c_int(0)
+        rc = self._lib.ffh_pool_free(self._h, arr, len(ids), ctypes.byref(bad))
+        if rc == 1:
+            raise PageError(f"page {bad.value} does not belong to this pool "
+                            f"[{self.first_id}, {self.first_id + self.num_blocks})")
+        if rc == 2:
+            raise PageError(f"page {bad.value} freed twice (or never allocated)")
 
     def check(self) -> None:
         """Every page is either free or held, exactly once."""
-        seen = set()
-        for b in self._free:
-            if b in seen:
-                raise PageError(f"page {b} is on the free list twice")
-            seen.add(b)
-            if self._held[b - self.first_id]:
-                raise PageError(f"page {b} is both free and held")
-        if len(seen) + sum(self._held) != self.num_blocks:
+        bad = ctypes.c_int(0)
+        rc = self._lib.ffh_pool_check(self._h, ctypes.byref(bad))
+        if rc == 1:
+            raise PageError(f"page {bad.value} is on the free list twice")
+        if rc == 2:
+            raise PageError(f"page {bad.value} is both free and held")
+        if rc == 3:
             raise PageError("a page was lost")

@@ -161,6 +161,61 @@ def compile_module(source: str, defines: Optional[Mapping[str, object]] = None, 
     return out
 
 
+def find_cxx() -> str:
+    for cand in (os.environ.get("CXX"), shutil.which("g++"), shutil.which("c++"), shutil.which("clang++")):
+        if cand and shutil.which(cand):
+            return shutil.which(cand)
+    raise KernelBuildError("no C++ compiler found (looked at $CXX, g++, c++, clang++)")
+
+
+def load_host_module(source: str) -> ctypes.CDLL:
+    """Build (with the host C++ compiler) and load a host-only module of ``csrc/``."""
+    key = ("host", source)
+    lib = _loaded.get(key)
+    if lib is not None:
+        return lib
+    with _lock:
+        lib = _loaded.get(key)
+        if lib is not None:
+            return lib
+        src = os.path.join(CSRC, source)
+        if not os.path.isfile(src):
+            raise KernelBuildError(f"source missing: {src}")
+        flags = ["-O2", "-std=c++17", "-shared", "-fPIC", "-fvisibility=hidden"]
+        tag = _hash([src], flags)
+        stem = os.path.splitext(os.path.basename(source))[0]
+        out = os.path.join(build_dir(), f"ffh_{stem}-{tag}.so")
+        if not os.path.isfile(out):
+            with open(out + ".lock", "w") as lock_fh:
+                fcntl.flock(lock_fh, fcntl.LOCK_EX)
+                try:
+                    if not os.path.isfile(out):
+                        tmp = f"{out}.tmp{os.getpid()}"
+                        cmd = [find_cxx(), *flags, "-o", tmp, src]
+                        proc = subprocess.run(cmd, stdout=subprocess.PIPE, stderr=subprocess.STDOUT, text=True)
+                        if proc.returncode != 0 or not os.path.isfile(tmp):
+                            raise KernelBuildError(f"C++ build failed for {source}:\n{' '.join(cmd)}\n{proc.stdout}")
+                        os.replace(tmp, out)
+                        for f in os.listdir(os.path.dirname(out)):
+                            if f.startswith(f"ffh_{stem}-") and f.endswith(".so") and f != os.path.basename(out):
+                                try:
+                                    os.unlink(os.path.join(os.path.dirname(out), f))
+                                except OSError:
+                                    pass
+                finally:
+                    fcntl.flock(lock_fh, fcntl.LOCK_UN)
+            try:
+                os.unlink(out + ".lock")
+            except OSError:
+                pass
+        try:
+            lib = ctypes.CDLL(out)
+        except OSError as e:
+            raise KernelBuildError(f"cannot load {out}: {e}") from e
+        _loaded[key] = lib
+    return lib
+
+
 def load_module(source: str, defines: Optional[Mapping[str, object]] = None) -> ctypes.CDLL:
     key = (source, tuple(sorted((defines or {}).items())))
     lib = _loaded.get(key)

@@ -22,7 +22,19 @@ def test_allocator_lifo_and_errors():
         a.free([1])
     with pytest.raises(PageError, match="does not belong"):
         a.free([0])
+    got = a.allocate(2)
+    before = a.num_free
+    with pytest.raises(PageError, match="twice"):
+        a.free([got[0], got[1], got[0]])                    # named twice in one call: nothing is freed
+    assert a.num_free == before
+    a.free(got)
     a.check()
+    big = BlockAllocator(100000)
+    ids = big.allocate(100000)
+    assert ids[0] == 0 and ids[-1] == 99999 and big.allocate(1) is None
+    big.free(reversed(ids))
+    assert big.allocate(1) == [0]
+    big.check()
 
 
 def _manager(window=None, num_blocks=12, block=4, two_groups=False, state=False):
