@@ -1,0 +1,509 @@
+// Flash-style attention over the paged cache on the fifth-generation tensor cores, for
+// portions of prompts (and any mix of sequences) in bfloat16.
+//
+// A block owns 128 rows of one kv head (row = token * G + head-in-group, so the heads of a
+// group share every key and value it fetches) and walks the visible keys in tiles of 64:
+//   S = Q K^T      tcgen05.mma, Q and K from shared memory (K brought in by TMA, page by page),
+//                  S (128 x 64, float32) in tensor memory;
+//   softmax        four warps, one thread per row: tcgen05.ld of its row of S, mask, running max
+//                  and sum in 32-bit, P as bfloat16 into shared memory, and - only when a row's
+//                  max moved - a rescale of its row of O in tensor memory;
+//   O += P V       tcgen05.mma, P from shared memory, V (the cache's [key][d] tile as it is, the
+//                  MMA's N-major operand form), O (128 x D, float32) in tensor memory.
+// One thread issues TMA loads two tiles deep, one thread issues the MMAs; two blocks share an
+// SM (at head size 128), so one block's softmax runs under the other's MMAs.
+//
+// It replaces, for head sizes that are multiples of 64 and page sizes that divide 64, the
+// mma.sync kernel of attention_mma.cu (which stays for every other size); the reference's
+// prefill kernel is a WMMA kernel over the portion's own k and v (src/kernels/attention.cu:22-286).
+// Every mbarrier wait is bounded; on time-out the kernel records code 107 in the status word,
+// stops, frees its tensor memory and returns.
+//
+// Compiled once per head size: -DFF_HEAD_DIM=<64, 128, 192 or 256>.
+// Cache layout of a slot: [num_blocks][2 (k,v)][n_kv_heads][block_size][head_dim].
+#include "common.cuh"
+
+#include <cuda.h>
+#include <cudaTypedefs.h>
+#include <math_constants.h>
+
+#include <cstring>
+#include <mutex>
+#include <unordered_map>
+
+#ifndef FF_HEAD_DIM
+#define FF_HEAD_DIM 128
+#endif
+
+namespace ff {
+
+constexpr int D = FF_HEAD_DIM;
+static_assert(D % 64 == 0 && D >= 64 && D <= 256, "head size must be 64, 128, 192 or 256");
+constexpr int BM = 128;                 // rows per block (MMA M)
+constexpr int BN = 64;                  // keys per tile
+constexpr int PANELS = D / 64;          // 64-column (128-byte) panels of a row
+constexpr int KV_STAGES = 2;
+constexpr int ATC_THREADS = 192;        // warps 0-3 softmax, warp 4 loads, warp 5 MMAs
+constexpr int MAX_PAGE_LIST = 1024;     // page ids of a block's tiles kept in shared memory
+constexpr float LOG2E = 1.4426950408889634f;
+constexpr unsigned long long WAIT_LIMIT_CYCLES = 2000000000ull;
+
+constexpr int Q_BYTES = BM * D * 2;
+constexpr int KV_TILE_BYTES = BN * D * 2;            // one K or V tile
+constexpr int P_BYTES = BM * BN * 2;
+constexpr int TMEM_COLS = (BN + D) <= 128 ? 128 : ((BN + D) <= 256 ? 256 : 512);
+// P takes the place of the K tile it was computed from (K is dead once S is complete) when that
+// tile is large enough; this is what lets two blocks share an SM at head size 128
+constexpr bool P_ALIASES_K = KV_TILE_BYTES >= P_BYTES;
+constexpr size_t ATC_SMEM = 1024 + Q_BYTES + KV_STAGES * 2 * KV_TILE_BYTES + (P_ALIASES_K ? 0 : P_BYTES) + 128 +
+                            MAX_PAGE_LIST * 4;
+
+__device__ __forceinline__ uint32_t sa(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }
+__device__ __forceinline__ void mb_init(uint32_t bar, uint32_t count) {
+    asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(bar), "r"(count));
+}
+__device__ __forceinline__ void mb_expect_tx(uint32_t bar, uint32_t bytes) {
+    asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(bar), "r"(bytes) : "memory");
+}
+__device__ __forceinline__ void mb_arrive(uint32_t bar) {
+    asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(bar) : "memory");
+}
+__device__ __forceinline__ bool mb_try(uint32_t bar, uint32_t parity) {
+    uint32_t ok;
+    asm volatile("{\n\t.reg .pred P1;\n\tmbarrier.try_wait.parity.shared::cta.b64 P1, [%1], %2;\n\t"
+                 "selp.b32 %0, 1, 0, P1;\n\t}" : "=r"(ok) : "r"(bar), "r"(parity) : "memory");
+    return ok != 0;
+}
+__device__ __forceinline__ bool mb_wait(uint32_t bar, uint32_t parity, int* status, volatile int* abort_flag) {
+    const unsigned long long start = clock64();
+    uint32_t spins = 0;
+    while (!mb_try(bar, parity)) {
+        if (((++spins) & 1023u) == 0) {
+            if (*abort_flag) return false;
+            if (clock64() - start > WAIT_LIMIT_CYCLES) {
+                atomicExch(status, 107);
+                *abort_flag = 1;
+                return false;
+            }
+        }
+    }
+    return true;
+}
+__device__ __forceinline__ void tma_2d(uint32_t dst, const void* map, int x, int y, uint32_t bar) {
+    asm volatile("cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4}], [%2];"
+                 ::"r"(dst), "l"(map), "r"(bar), "r"(x), "r"(y) : "memory");
+}
+__device__ __forceinline__ void tc_before() { asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory"); }
+__device__ __forceinline__ void tc_after() { asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory"); }
+__device__ __forceinline__ void tc_commit_to(uint32_t bar) {
+    asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(bar) : "memory");
+}
+__device__ __forceinline__ void tc_mma(uint32_t d_tmem, uint64_t da, uint64_t db, uint32_t idesc, uint32_t acc) {
+    asm volatile("{\n\t.reg .pred p;\n\tsetp.ne.b32 p, %4, 0;\n\t"
+                 "tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n\t}"
+                 ::"r"(d_tmem), "l"(da), "l"(db), "r"(idesc), "r"(acc) : "memory");
+}
+__device__ __forceinline__ void tm_ld16(uint32_t taddr, float (&v)[16]) {
+    uint32_t r[16];
+    asm volatile("tcgen05.ld.sync.aligned.32x32b.x16.b32 {%0,%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15}, [%16];"
+                 : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]),
+                   "=r"(r[8]), "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15])
+                 : "r"(taddr));
+    asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+#pragma unroll
+    for (int i = 0; i < 16; ++i) v[i] = __uint_as_float(r[i]);
+}
+__device__ __forceinline__ void tm_st16(uint32_t taddr, const float (&v)[16]) {
+    asm volatile("tcgen05.st.sync.aligned.32x32b.x16.b32 [%0], {%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15,%16};"
+                 ::"r"(taddr), "r"(__float_as_uint(v[0])), "r"(__float_as_uint(v[1])), "r"(__float_as_uint(v[2])),
+                   "r"(__float_as_uint(v[3])), "r"(__float_as_uint(v[4])), "r"(__float_as_uint(v[5])),
+                   "r"(__float_as_uint(v[6])), "r"(__float_as_uint(v[7])), "r"(__float_as_uint(v[8])),
+                   "r"(__float_as_uint(v[9])), "r"(__float_as_uint(v[10])), "r"(__float_as_uint(v[11])),
+                   "r"(__float_as_uint(v[12])), "r"(__float_as_uint(v[13])), "r"(__float_as_uint(v[14])),
+                   "r"(__float_as_uint(v[15])) : "memory");
+}
+
+// Operand descriptors.  Tiles are made of 64-column panels whose 128-byte rows are swizzled in
+// groups of eight (the layout TMA writes with the 128-byte swizzle).
+// K-major (the reduction dimension runs along the 128-byte row): groups of 8 rows 1024 bytes apart.
+__device__ __forceinline__ uint64_t desc_k_major(uint32_t addr) {
+    return (uint64_t)((addr & 0x3FFFFu) >> 4) | ((uint64_t)1 << 16) | ((uint64_t)(1024 >> 4) << 32) |
+           ((uint64_t)1 << 46) | ((uint64_t)2 << 61);
+}
+// N-major (the rows of the tile are the reduction dimension, the 128-byte row runs along N):
+// groups of 8 reduction rows 1024 bytes apart (stride offset), 64-column panels `panel_bytes`
+// apart (leading offset).
+__device__ __forceinline__ uint64_t desc_n_major(uint32_t addr, uint32_t panel_bytes) {
+    return (uint64_t)((addr & 0x3FFFFu) >> 4) | ((uint64_t)((panel_bytes >> 4) & 0x3FFF) << 16) |
+           ((uint64_t)(1024 >> 4) << 32) | ((uint64_t)1 << 46) | ((uint64_t)2 << 61);
+}
+// bfloat16 x bfloat16 -> float32, M = 128, N = n; b_n_major: the B operand is N-major
+__device__ __forceinline__ uint32_t idesc_bf16(int n, bool b_n_major) {
+    return (1u << 4) | (1u << 7) | (1u << 10) | ((b_n_major ? 1u : 0u) << 16) | ((uint32_t)(n >> 3) << 17) |
+           ((uint32_t)(BM >> 4) << 24);
+}
+
+struct alignas(64) TensorMapArg { unsigned char bytes[128]; };   // a CUtensorMap, opaque to device code
+
+__global__ void __launch_bounds__(ATC_THREADS)
+attn_tc_kernel(const __grid_constant__ TensorMapArg kv_map, const bf16* __restrict__ q, int q_stride,
+               const int* __restrict__ block_table, int max_blocks, const int* __restrict__ cu_q,
+               const int* __restrict__ ctx_lens, int n_seqs, bf16* __restrict__ out, int out_stride, int nq,
+               int nkv, int block_size, int num_blocks, float scale_log2, int window, int* __restrict__ status) {
+    asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
+    extern __shared__ unsigned char smem_raw[];
+    unsigned char* base = reinterpret_cast<unsigned char*>(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
+    unsigned char* Qs = base;                                        // [PANELS][128][128 B]
+    unsigned char* KVs = Qs + Q_BYTES;                               // [stage][K|V][PANELS][64][128 B]
+    unsigned char* Ps = KVs + KV_STAGES * 2 * KV_TILE_BYTES;         // [128][128 B] unless it aliases K
+    uint64_t* bars = reinterpret_cast<uint64_t*>(Ps + (P_ALIASES_K ? 0 : P_BYTES));
+    // bars: [0,1] kv_full, [2,3] kv_empty, [4] s_full, [5] p_full, [6] pv_done, [7] q_ready
+    int* s_pages = reinterpret_cast<int*>(bars + 16);
+    __shared__ int s_seq, s_tile, s_abort;
+    __shared__ uint32_t s_tmem;
+    const int G = nq / nkv;
+    const int kh = blockIdx.y;
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    volatile int* abort_flag = &s_abort;
+
+    if (threadIdx.x == 0) {
+        s_abort = 0;
+        mb_init(sa(&bars[0]), 1); mb_init(sa(&bars[1]), 1);
+        mb_init(sa(&bars[2]), 1); mb_init(sa(&bars[3]), 1);
+        mb_init(sa(&bars[4]), 1); mb_init(sa(&bars[5]), 4); mb_init(sa(&bars[6]), 1); mb_init(sa(&bars[7]), 4);
+        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    }
+    if (warp == 5) {
+        asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;"
+                     ::"r"(sa(&s_tmem)), "r"((uint32_t)TMEM_COLS) : "memory");
+        asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+    }
+    asm volatile("griddepcontrol.wait;" ::: "memory");
+    if (warp == 0) {   // which sequence owns row tile blockIdx.x
+        int cum = 0, found_seq = -1, found_tile = 0;
+        for (int s0 = 0; s0 < n_seqs && found_seq < 0; s0 += 32) {
+            const int s = s0 + lane;
+            const int cnt = s < n_seqs ? ((cu_q[s + 1] - cu_q[s]) * G + BM - 1) / BM : 0;
+            int incl = cnt;
+#pragma unroll
+            for (int o = 1; o < 32; o <<= 1) {
+                const int v = __shfl_up_sync(0xffffffffu, incl, o);
+                if (lane >= o) incl += v;
+            }
+            const int total = __shfl_sync(0xffffffffu, incl, 31);
+            const unsigned hit = __ballot_sync(0xffffffffu, cum + incl > (int)blockIdx.x);
+            if (hit) {
+                const int l0 = __ffs(hit) - 1;
+                found_seq = s0 + l0;
+                found_tile = (int)blockIdx.x - (cum + __shfl_sync(0xffffffffu, incl, l0) - __shfl_sync(0xffffffffu, cnt, l0));
+            }
+            cum += total;
+        }
+        if (lane == 0) { s_seq = found_seq; s_tile = found_tile; }
+    }
+    tc_before();
+    __syncthreads();
+    tc_after();
+    const uint32_t tmem = s_tmem;
+    const uint32_t tm_S = tmem;                  // columns [0, 64)
+    const uint32_t tm_O = tmem + BN;             // columns [64, 64 + D)
+    const int seq = s_seq, tile = s_tile;
+
+    int n_tiles = 0, t_begin = 0, tok0 = 0, q_len = 0, ctx = 0, rows = 0, row0 = 0, kv_lo = 0, kv_hi = 0;
+    if (seq >= 0) {
+        tok0 = cu_q[seq]; q_len = cu_q[seq + 1] - tok0; ctx = ctx_lens[seq];
+        rows = q_len * G; row0 = tile * BM;
+        const int first_tok = row0 / G, last_tok = min(q_len - 1, (row0 + BM - 1) / G);
+        kv_hi = ctx + last_tok + 1;
+        kv_lo = window > 0 ? max(0, ctx + first_tok - window + 1) : 0;
+        t_begin = kv_lo / BN;
+        n_tiles = (kv_hi + BN - 1) / BN - t_begin;
+    }
+    const int pages_per_tile = BN / block_size;
+    const bool list_fits = n_tiles * pages_per_tile <= MAX_PAGE_LIST;
+    if (!list_fits && threadIdx.x == 0) atomicExch(status, 108);
+    if (seq < 0 || !list_fits) n_tiles = 0;
+
+    if (warp < 4) {
+        // ------------------------------------------------ set-up by the softmax warps --
+        const int r = threadIdx.x;                            // this thread's row of the tile
+        const int rg = row0 + r;
+        const bool valid = rg < rows;
+        const int rgc = min(rg, max(rows - 1, 0));
+        const int token = rgc / G, head = kh * G + rgc % G;
+        // page ids of all tiles
+        const int* bt = block_table + (size_t)max(seq, 0) * max_blocks;
+        const int last_page = (kv_hi - 1) / block_size, first_page = kv_lo / block_size;
+        for (int i = threadIdx.x; i < n_tiles * pages_per_tile; i += 128) {
+            const int pi = t_begin * pages_per_tile + i;
+            int page = (pi >= first_page && pi <= last_page && pi < max_blocks) ? bt[pi] : -1;
+            if (page >= num_blocks) page = -1;
+            s_pages[i] = page;
+        }
+        // zero the K/V stages once: parts no page is loaded into must hold finite numbers
+        for (int i = threadIdx.x; i < KV_STAGES * 2 * KV_TILE_BYTES / 16; i += 128)
+            reinterpret_cast<uint4*>(KVs)[i] = make_uint4(0u, 0u, 0u, 0u);
+        // this row of q -> the swizzled Q tile
+        if (n_tiles > 0) {
+            const bf16* src = q + (size_t)(tok0 + token) * q_stride + (size_t)head * D;
+#pragma unroll
+            for (int ch = 0; ch < D / 8; ++ch) {
+                uint4 v = valid ? *reinterpret_cast<const uint4*>(src + ch * 8) : make_uint4(0u, 0u, 0u, 0u);
+                *reinterpret_cast<uint4*>(Qs + (ch >> 3) * (BM * 128) + r * 128 + (((ch & 7) ^ (r & 7)) << 4)) = v;
+            }
+        }
+        asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+        __syncwarp();
+        if (lane == 0) mb_arrive(sa(&bars[7]));
+
+        // ------------------------------------------------ softmax, one thread per row --
+        const int pos = ctx + token;
+        const int hi = pos + 1;
+        const int lo = window > 0 ? max(0, pos - window + 1) : 0;
+        const int first_pos = ctx + row0 / G;                        // the tile's smallest position
+        const int last_pos = ctx + min(q_len - 1, (row0 + BM - 1) / G);
+        const int full_lo = window > 0 ? max(0, last_pos - window + 1) : 0;
+        const uint32_t lane_base = (uint32_t)((warp * 32) << 16);
+        float m = -CUDART_INF_F, l = 0.f;
+        bool ok = true;
+        for (int j = 0; j < n_tiles && ok; ++j) {
+            ok = mb_wait(sa(&bars[4]), j & 1, status, abort_flag);
+            ok = __all_sync(0xffffffffu, ok);
+            if (!ok) break;
+            tc_after();
+            const int key0 = (t_begin + j) * BN;
+            const bool need_mask = key0 + BN > first_pos + 1 || key0 < full_lo;
+            float s[BN];
+#pragma unroll
+            for (int c = 0; c < BN / 16; ++c) {
+                float v[16];
+                tm_ld16(tm_S + lane_base + c * 16, v);
+#pragma unroll
+                for (int i = 0; i < 16; ++i) s[c * 16 + i] = v[i];
+            }
+            float mx = -CUDART_INF_F;
+#pragma unroll
+            for (int i = 0; i < BN; ++i) {
+                float v = s[i] * scale_log2;
+                if (need_mask) {
+                    const int key = key0 + i;
+                    if (key < lo || key >= hi) v = -CUDART_INF_F;
+                }
+                s[i] = v;
+                mx = fmaxf(mx, v);
+            }
+            const float m_new = fmaxf(m, mx);
+            const float msafe = m_new == -CUDART_INF_F ? 0.f : m_new;
+            const float corr = exp2f(m - msafe);
+            m = m_new;
+            float sum = 0.f;
+            uint32_t packed[BN / 2];
+#pragma unroll
+            for (int i = 0; i < BN; i += 2) {
+                const float p0 = exp2f(s[i] - msafe), p1 = exp2f(s[i + 1] - msafe);
+                sum += p0 + p1;
+                __nv_bfloat162 pp = __floats2bfloat162_rn(p0, p1);
+                packed[i / 2] = *reinterpret_cast<uint32_t*>(&pp);
+            }
+            l = l * corr + sum;
+            // O of the tiles so far is complete, and P's buffer is free, once the last P V is done
+            if (j > 0) {
+                ok = mb_wait(sa(&bars[6]), (j - 1) & 1, status, abort_flag);
+                ok = __all_sync(0xffffffffu, ok);
+                if (!ok) break;
+                tc_after();
+                if (!__all_sync(0xffffffffu, corr == 1.0f)) {          // some row's max moved: rescale O
+#pragma unroll 1
+                    for (int c = 0; c < D / 16; ++c) {
+                        float v[16];
+                        tm_ld16(tm_O + lane_base + c * 16, v);
+#pragma unroll
+                        for (int i = 0; i < 16; ++i) v[i] *= corr;
+                        tm_st16(tm_O + lane_base + c * 16, v);
+                    }
+                    asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory");
+                }
+            }
+            unsigned char* Pt = P_ALIASES_K ? KVs + (size_t)(j % KV_STAGES) * 2 * KV_TILE_BYTES : Ps;
+#pragma unroll
+            for (int c = 0; c < BN / 8; ++c)
+                *reinterpret_cast<uint4*>(Pt + r * 128 + ((c ^ (r & 7)) << 4)) =
+                    make_uint4(packed[c * 4], packed[c * 4 + 1], packed[c * 4 + 2], packed[c * 4 + 3]);
+            asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+            tc_before();
+            __syncwarp();
+            if (lane == 0) mb_arrive(sa(&bars[5]));
+        }
+        // ------------------------------------------------ epilogue ------------
+        if (n_tiles > 0 && ok) {
+            ok = mb_wait(sa(&bars[6]), (n_tiles - 1) & 1, status, abort_flag);
+            ok = __all_sync(0xffffffffu, ok);
+        }
+        if (n_tiles > 0 && ok) {
+            tc_after();
+            const float inv = 1.0f / l;
+            bf16* dst = out + (size_t)(tok0 + token) * out_stride + (size_t)head * D;
+#pragma unroll 1
+            for (int c = 0; c < D / 16; ++c) {
+                float v[16];
+                tm_ld16(tm_O + lane_base + c * 16, v);
+                if (valid) {
+                    uint32_t w[8];
+#pragma unroll
+                    for (int i = 0; i < 8; ++i) {
+                        __nv_bfloat162 pp = __floats2bfloat162_rn(v[2 * i] * inv, v[2 * i + 1] * inv);
+                        w[i] = *reinterpret_cast<uint32_t*>(&pp);
+                    }
+                    *reinterpret_cast<uint4*>(dst + c * 16) = make_uint4(w[0], w[1], w[2], w[3]);
+                    *reinterpret_cast<uint4*>(dst + c * 16 + 8) = make_uint4(w[4], w[5], w[6], w[7]);
+                }
+            }
+        }
+    } else if (warp == 4 && lane == 0) {
+        // ------------------------------------------------ loads: K and V tiles by TMA --
+        // the stages are zeroed by the softmax warps first (q_ready also says that is done)
+        bool ok = n_tiles == 0 || mb_wait(sa(&bars[7]), 0, status, abort_flag);
+        for (int j = 0; j < n_tiles && ok; ++j) {
+            const int s = j % KV_STAGES;
+            ok = mb_wait(sa(&bars[2 + s]), ((j / KV_STAGES) & 1) ^ 1, status, abort_flag);
+            if (!ok) break;
+            int valid_pages = 0;
+            for (int p = 0; p < pages_per_tile; ++p) valid_pages += s_pages[j * pages_per_tile + p] >= 0;
+            const uint32_t bar = sa(&bars[s]);
+            mb_expect_tx(bar, (uint32_t)(valid_pages * 2 * block_size * D * 2));
+            unsigned char* st = KVs + (size_t)s * 2 * KV_TILE_BYTES;
+            for (int p = 0; p < pages_per_tile; ++p) {
+                const int page = s_pages[j * pages_per_tile + p];
+                if (page < 0) continue;
+#pragma unroll
+                for (int kv = 0; kv < 2; ++kv) {
+                    const int y = ((page * 2 + kv) * nkv + kh) * block_size;
+#pragma unroll
+                    for (int h = 0; h < PANELS; ++h)
+                        tma_2d(sa(st + kv * KV_TILE_BYTES + h * (BN * 128) + p * block_size * 128), &kv_map, h * 64, y, bar);
+                }
+            }
+        }
+    } else if (warp == 5 && lane == 0) {
+        // ------------------------------------------------ MMAs -----------------
+        const uint32_t idesc_qk = idesc_bf16(BN, false);
+        const uint32_t idesc_pv = idesc_bf16(D, true);
+        bool ok = n_tiles == 0 || mb_wait(sa(&bars[7]), 0, status, abort_flag);
+        tc_after();
+        for (int j = 0; j < n_tiles && ok; ++j) {
+            const int s = j % KV_STAGES;
+            ok = mb_wait(sa(&bars[s]), (j / KV_STAGES) & 1, status, abort_flag);
+            if (!ok) break;
+            tc_after();
+            const uint32_t ks = sa(KVs + (size_t)s * 2 * KV_TILE_BYTES);
+            const uint32_t vs = ks + KV_TILE_BYTES;
+            // S = Q K^T over D in steps of 16
+#pragma unroll
+            for (int k = 0; k < D / 16; ++k) {
+                const uint64_t da = desc_k_major(sa(Qs) + (k >> 2) * (BM * 128) + (k & 3) * 32);
+                const uint64_t db = desc_k_major(ks + (k >> 2) * (BN * 128) + (k & 3) * 32);
+                tc_mma(tm_S, da, db, idesc_qk, k > 0 ? 1u : 0u);
+            }
+            tc_commit_to(sa(&bars[4]));
+            // O += P V over the 64 keys in steps of 16, once the softmax warps have written P
+            ok = mb_wait(sa(&bars[5]), j & 1, status, abort_flag);
+            if (!ok) break;
+            tc_after();
+#pragma unroll
+            for (int k = 0; k < BN / 16; ++k) {
+                const uint64_t da = desc_k_major((P_ALIASES_K ? ks : sa(Ps)) + k * 32);
+                const uint64_t db = desc_n_major(vs + k * 16 * 128, BN * 128);
+                tc_mma(tm_O, da, db, idesc_pv, (j > 0 || k > 0) ? 1u : 0u);
+            }
+            tc_commit_to(sa(&bars[6]));
+            tc_commit_to(sa(&bars[2 + s]));
+        }
+    }
+    tc_before();
+    __syncthreads();
+    if (warp == 5) {
+        __syncwarp();
+        tc_after();
+        asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem), "r"((uint32_t)TMEM_COLS) : "memory");
+    }
+}
+
+// ------------------------------------------------------------------ host side --
+typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
+                                  const cuuint64_t*, const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave,
+                                  CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+
+static EncodeTiledFn encode_fn() {
+    static EncodeTiledFn fn = nullptr;
+    static std::once_flag once;
+    std::call_once(once, [] {
+        void* p = nullptr;
+        cudaDriverEntryPointQueryResult qr;
+        if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &p, cudaEnableDefault, &qr) == cudaSuccess &&
+            qr == cudaDriverEntryPointSuccess)
+            fn = reinterpret_cast<EncodeTiledFn>(p);
+    });
+    return fn;
+}
+
+// Tensor map of a cache slot seen as [rows, D] bfloat16: boxes of block_size rows x 64 columns, 128-byte swizzle.
+static int cache_map(const void* cache, long long rows, int block_size, CUtensorMap* out) {
+    struct Key { const void* p; long long rows; int bs; };
+    static std::mutex mu;
+    static std::unordered_map<const void*, std::pair<Key, CUtensorMap>> cache_maps;
+    std::lock_guard<std::mutex> lock(mu);
+    auto it = cache_maps.find(cache);
+    if (it != cache_maps.end() && it->second.first.rows == rows && it->second.first.bs == block_size) {
+        *out = it->second.second;
+        return 0;
+    }
+    EncodeTiledFn fn = encode_fn();
+    if (!fn) return FF_ERR_UNSUPPORTED;
+    cuuint64_t dims[2] = {(cuuint64_t)D, (cuuint64_t)rows};
+    cuuint64_t strides[1] = {(cuuint64_t)D * 2};
+    cuuint32_t box[2] = {64u, (cuuint32_t)block_size};
+    cuuint32_t estr[2] = {1, 1};
+    CUresult r = fn(out, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, const_cast<void*>(cache), dims, strides, box, estr,
+                    CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                    CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+    if (r != CUDA_SUCCESS) return FF_ERR_BAD_ARG;
+    if (cache_maps.size() > 4096) cache_maps.clear();
+    cache_maps[cache] = {Key{cache, rows, block_size}, *out};
+    return 0;
+}
+
+}  // namespace ff
+
+using namespace ff;
+
+FF_EXPORT int ff_attn_tc_block_m() { return BM; }
+
+// total_tiles = sum over sequences of ceil(q_len * G / 128).  Needs a block size that divides 64
+// (8, 16, 32 or 64), a 128-byte aligned cache and q rows aligned to 16 bytes.
+FF_EXPORT int ff_attn_tc(const void* q, int q_stride, const void* cache, const int* block_table, int max_blocks,
+                         const int* cu_q, const int* ctx_lens, int n_seqs, int total_tiles, void* out,
+                         int out_stride, int nq, int nkv, int block_size, int num_blocks, float scale, int window,
+                         int* status, cudaStream_t stream) {
+    if (n_seqs <= 0 || total_tiles <= 0) return 0;
+    if (nkv <= 0 || nq % nkv) return FF_ERR_BAD_ARG;
+    if (block_size < 8 || BN % block_size) return FF_ERR_UNSUPPORTED;
+    if (((uintptr_t)cache & 127) || ((uintptr_t)q & 15) || (q_stride % 8) || ((uintptr_t)out & 15) || (out_stride % 8))
+        return FF_ERR_UNSUPPORTED;
+    const long long rows = (long long)num_blocks * 2 * nkv * block_size;
+    if (rows >= (1ll << 31)) return FF_ERR_UNSUPPORTED;
+    static bool attr_set = false;
+    if (!attr_set) {
+        cudaError_t e = cudaFuncSetAttribute(attn_tc_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)ATC_SMEM);
+        if (e != cudaSuccess) return (int)e;
+        attr_set = true;
+    }
+    CUtensorMap map;
+    int rc = cache_map(cache, rows, block_size, &map);
+    if (rc) return rc;
+    TensorMapArg arg;
+    std::memcpy(arg.bytes, &map, sizeof(map));
+    FF_LAUNCH((attn_tc_kernel), dim3(total_tiles, nkv), ATC_THREADS, ATC_SMEM, stream, arg, (const bf16*)q, q_stride,
+              block_table, max_blocks, cu_q, ctx_lens, n_seqs, (bf16*)out, out_stride, nq, nkv, block_size, num_blocks,
+              scale * LOG2E, window, status);
+    return 0;
+}

@@ -46,7 +46,9 @@ _STATUS = {1: "a token id outside the vocabulary reached the embedding kernel",
            4: "a key's cache page is missing from a block table (read)",
            101: "matrix product: the loader's wait for a free stage ran out",
            102: "matrix product: the wait for a loaded stage ran out",
-           103: "matrix product: the wait for the accumulator ran out"}
+           103: "matrix product: the wait for the accumulator ran out",
+           107: "attention (tcgen05): a bounded wait ran out",
+           108: "attention (tcgen05): a sequence's page list does not fit the kernel's shared memory"}
 
 
 class MetaLayout:

@@ -100,7 +100,8 @@ def build_all(head_dims=DEFAULT_HEAD_DIMS) -> None:
     """Compile every module (used by the build check; needs no GPU).  The
     tensor-core attention is compiled per head size; others are built when a
     model with that head size is first run."""
-    mods = list(_MODULES.values()) + [("attention_mma.cu", {"FF_HEAD_DIM": int(d)}) for d in head_dims]
+    mods = list(_MODULES.values()) + [("attention_mma.cu", {"FF_HEAD_DIM": int(d)}) for d in head_dims] + \
+        [("attention_tc.cu", {"FF_HEAD_DIM": int(d)}) for d in head_dims if int(d) % 64 == 0]
     compile_many(mods)
 
 
@@ -376,6 +377,31 @@ def attn_decode(q, q_stride, pages, table, cu_q, ctx_lens, n_seqs, out, part_o, 
         LAUNCHES += 1     # the kernel that joins the splits
 
 
+USE_TC_ATTENTION = True     # tcgen05 attention for prompt portions where the sizes allow
+
+
+def _attn_tc_lib(d: int) -> ctypes.CDLL:
+    return _configured(load_module("attention_tc.cu", {"FF_HEAD_DIM": d}))
+
+
+def tc_attention_supported(dtype: torch.dtype, d: int, block_size: int, max_kv_len: int) -> bool:
+    """The tcgen05 attention kernel takes head sizes 64..256 in steps of 64, pages of 8..64 tokens
+    that divide 64, and contexts whose page list fits its shared memory."""
+    return (dtype == torch.bfloat16 and d % 64 == 0 and 64 <= d <= 256 and block_size in (8, 16, 32, 64)
+            and -(-max_kv_len // 64) * (64 // block_size) <= 1024)
+
+
+def attn_tc(q, q_stride, pages, table, cu_q, ctx_lens, n_seqs, total_tiles, out, nq, nkv, d, scale, window,
+            status) -> None:
+    """tcgen05 flash attention over the paged cache (bfloat16); total_tiles counts row tiles of 128."""
+    _need_cuda(pages, table, cu_q, ctx_lens, out, status)
+    num_blocks, _, _, block_size, _ = pages.shape
+    _check(_attn_tc_lib(d).ff_attn_tc(
+        _p(q), c_int(q_stride), _p(pages), _p(table), c_int(table.shape[1]), _p(cu_q), _p(ctx_lens),
+        c_int(n_seqs), c_int(total_tiles), _p(out), c_int(out.shape[1]), c_int(nq), c_int(nkv),
+        c_int(block_size), c_int(num_blocks), c_float(scale), c_int(window), _p(status), _stream()), "attn_tc")
+
+
 def decode_splits(n_seqs: int, nkv: int, max_kv_len: int) -> int:
     """Ranges of keys per (sequence, kv head): about 8 tiles of 64 keys a block, and at
     least one block per SM when the batch is small."""
@@ -407,6 +433,11 @@ def paged_attention(q: torch.Tensor, q_stride: int, pages: torch.Tensor, table: 
                     scale, window, splits)
     if n_dec < n:
         # portions of prompts: tiled kernel over the remaining sequences (token offsets in cu_q are absolute)
-        tiles = sum(-(-(ql * G) // 64) for ql in ctx.q_lens[n_dec:])
-        attn_tiled(q, q_stride, pages, table[n_dec:], ctx.cu_q[n_dec:], ctx.ctx_lens[n_dec:], n - n_dec, tiles,
-                   out, nq, nkv, d, scale, window)
+        if USE_TC_ATTENTION and tc_attention_supported(q.dtype, d, pages.shape[3], ctx.max_kv_len):
+            tiles = sum(-(-(ql * G) // 128) for ql in ctx.q_lens[n_dec:])
+            attn_tc(q, q_stride, pages, table[n_dec:], ctx.cu_q[n_dec:], ctx.ctx_lens[n_dec:], n - n_dec, tiles,
+                    out, nq, nkv, d, scale, window, ctx.status)
+        else:
+            tiles = sum(-(-(ql * G) // 64) for ql in ctx.q_lens[n_dec:])
+            attn_tiled(q, q_stride, pages, table[n_dec:], ctx.cu_q[n_dec:], ctx.ctx_lens[n_dec:], n - n_dec,
+                       tiles, out, nq, nkv, d, scale, window)

@@ -215,6 +215,27 @@ def test_attention_tiled_tensor_core(d, nq, nkv, block, window):
     assert float(err) < 2e-2, float(err)
 
 
+TC_SHAPES = [(64, 8, 1, 16), (128, 8, 2, 16), (256, 4, 2, 64), (128, 32, 8, 16), (64, 6, 2, 8), (128, 4, 4, 32),
+             (192, 5, 1, 16)]
+
+
+@pytest.mark.parametrize("d,nq,nkv,block", TC_SHAPES)
+@pytest.mark.parametrize("window", [None, 37, 200])
+def test_attention_tcgen05(d, nq, nkv, block, window):
+    seqs = MIXED + [(700, 300), (0, 1000)]
+    c = _attention_case(d, nq, nkv, block, seqs, window, torch.bfloat16, seed=5)
+    G = nq // nkv
+    out = torch.zeros(c["q"].shape, dtype=torch.bfloat16, device="cuda")
+    status = torch.zeros(1, dtype=torch.int32, device="cuda")
+    tiles = sum(-(-(ql * G) // 128) for ql in c["q_lens"])
+    K().attn_tc(dev(c["q"]), nq * d, dev(c["pages"]), dev(c["table"]), dev(c["cu_q"]), dev(c["ctx_lens"]),
+                len(seqs), tiles, out, nq, nkv, d, 1 / math.sqrt(d), window or 0, status)
+    torch.cuda.synchronize()
+    assert int(status) == 0
+    err = (out.cpu().double() - c["want"]).abs().max() / c["want"].abs().max()
+    assert float(err) < 2e-2, float(err)
+
+
 @pytest.mark.parametrize("d,nq,nkv,block", ATT_SHAPES)
 @pytest.mark.parametrize("window", [None, 100])
 @pytest.mark.parametrize("splits", [1, 2, 5])
