@@ -78,6 +78,7 @@ __device__ __forceinline__ bool mb_wait(uint32_t bar, uint32_t parity, int* stat
     const unsigned long long start = clock64();
     uint32_t spins = 0;
     while (!mb_try(bar, parity)) {
+        __nanosleep(32);                     // leave the issue slots to the warps that have work
         if (((++spins) & 1023u) == 0) {
             if (*abort_flag) return false;
             if (clock64() - start > WAIT_LIMIT_CYCLES) {
@@ -112,6 +113,33 @@ __device__ __forceinline__ void tm_ld16(uint32_t taddr, float (&v)[16]) {
     asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
 #pragma unroll
     for (int i = 0; i < 16; ++i) v[i] = __uint_as_float(r[i]);
+}
+// 32 consecutive accumulator columns of this warp's 32 lanes (no wait: call tm_ld_wait() before use)
+__device__ __forceinline__ void tm_ld32_nowait(uint32_t taddr, float* v) {
+    uint32_t* r = reinterpret_cast<uint32_t*>(v);
+    asm volatile("tcgen05.ld.sync.aligned.32x32b.x32.b32 "
+                 "{%0,%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15,"
+                 "%16,%17,%18,%19,%20,%21,%22,%23,%24,%25,%26,%27,%28,%29,%30,%31}, [%32];"
+                 : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]),
+                   "=r"(r[8]), "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15]),
+                   "=r"(r[16]), "=r"(r[17]), "=r"(r[18]), "=r"(r[19]), "=r"(r[20]), "=r"(r[21]), "=r"(r[22]), "=r"(r[23]),
+                   "=r"(r[24]), "=r"(r[25]), "=r"(r[26]), "=r"(r[27]), "=r"(r[28]), "=r"(r[29]), "=r"(r[30]), "=r"(r[31])
+                 : "r"(taddr));
+}
+__device__ __forceinline__ void tm_ld_wait() { asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory"); }
+
+__device__ __forceinline__ float fast_exp2(float x) {   // 2^x; -inf -> 0
+    float y;
+    asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
+    return y;
+}
+// 2^x for two values at once on the special-function unit, result rounded to bfloat16 (the form P
+// is stored in): half as many special-function operations as two 32-bit exponentials
+__device__ __forceinline__ uint32_t exp2_bf16x2(float x0, float x1) {
+    uint32_t packed, y;
+    asm("cvt.rn.bf16x2.f32 %0, %1, %2;" : "=r"(packed) : "f"(x1), "f"(x0));   // low half = x0
+    asm("ex2.approx.ftz.bf16x2 %0, %1;" : "=r"(y) : "r"(packed));
+    return y;
 }
 __device__ __forceinline__ void tm_st16(uint32_t taddr, const float (&v)[16]) {
     asm volatile("tcgen05.st.sync.aligned.32x32b.x16.b32 [%0], {%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15,%16};"
@@ -179,7 +207,10 @@ attn_tc_kernel(const __grid_constant__ TensorMapArg kv_map, const bf16* __restri
         asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
     }
     asm volatile("griddepcontrol.wait;" ::: "memory");
-    if (warp == 0) {   // which sequence owns row tile blockIdx.x
+    // Row tiles are handed out last first: in a prompt the late tiles see the most keys, and the
+    // long blocks should not be the ones that start last.
+    const int vtile = (int)gridDim.x - 1 - (int)blockIdx.x;
+    if (warp == 0) {   // which sequence owns row tile vtile
         int cum = 0, found_seq = -1, found_tile = 0;
         for (int s0 = 0; s0 < n_seqs && found_seq < 0; s0 += 32) {
             const int s = s0 + lane;
@@ -191,11 +222,11 @@ attn_tc_kernel(const __grid_constant__ TensorMapArg kv_map, const bf16* __restri
                 if (lane >= o) incl += v;
             }
             const int total = __shfl_sync(0xffffffffu, incl, 31);
-            const unsigned hit = __ballot_sync(0xffffffffu, cum + incl > (int)blockIdx.x);
+            const unsigned hit = __ballot_sync(0xffffffffu, cum + incl > vtile);
             if (hit) {
                 const int l0 = __ffs(hit) - 1;
                 found_seq = s0 + l0;
-                found_tile = (int)blockIdx.x - (cum + __shfl_sync(0xffffffffu, incl, l0) - __shfl_sync(0xffffffffu, cnt, l0));
+                found_tile = vtile - (cum + __shfl_sync(0xffffffffu, incl, l0) - __shfl_sync(0xffffffffu, cnt, l0));
             }
             cum += total;
         }
@@ -274,52 +305,59 @@ attn_tc_kernel(const __grid_constant__ TensorMapArg kv_map, const bf16* __restri
             const int key0 = (t_begin + j) * BN;
             const bool need_mask = key0 + BN > first_pos + 1 || key0 < full_lo;
             float s[BN];
-#pragma unroll
-            for (int c = 0; c < BN / 16; ++c) {
-                float v[16];
-                tm_ld16(tm_S + lane_base + c * 16, v);
-#pragma unroll
-                for (int i = 0; i < 16; ++i) s[c * 16 + i] = v[i];
-            }
-            float mx = -CUDART_INF_F;
+            tm_ld32_nowait(tm_S + lane_base, s);
+            tm_ld32_nowait(tm_S + lane_base + 32, s + 32);
+            tm_ld_wait();
+            // (mask and) row max of the raw scores, four independent chains; the scale (> 0) is applied later
+            float mx4[4] = {-CUDART_INF_F, -CUDART_INF_F, -CUDART_INF_F, -CUDART_INF_F};
 #pragma unroll
             for (int i = 0; i < BN; ++i) {
-                float v = s[i] * scale_log2;
                 if (need_mask) {
                     const int key = key0 + i;
-                    if (key < lo || key >= hi) v = -CUDART_INF_F;
+                    if (key < lo || key >= hi) s[i] = -CUDART_INF_F;
                 }
-                s[i] = v;
-                mx = fmaxf(mx, v);
+                mx4[i & 3] = fmaxf(mx4[i & 3], s[i]);
             }
-            const float m_new = fmaxf(m, mx);
-            const float msafe = m_new == -CUDART_INF_F ? 0.f : m_new;
-            const float corr = exp2f(m - msafe);
-            m = m_new;
-            float sum = 0.f;
+            const float mx = fmaxf(fmaxf(mx4[0], mx4[1]), fmaxf(mx4[2], mx4[3])) * scale_log2;
+            // The reference max `m` follows the true row max lazily: it moves (and O is rescaled) only
+            // when the true max has grown by more than 2^8 since, which keeps p <= 256 and makes the
+            // rescale rare after the first tiles.
+            float corr = 1.0f;
+            if (mx > m + 8.0f || m == -CUDART_INF_F) {
+                const float m_new = fmaxf(m, mx);
+                const float msafe_new = m_new == -CUDART_INF_F ? 0.f : m_new;
+                corr = fast_exp2(m - msafe_new);               // m = -inf: 0
+                m = m_new;
+            }
+            const float neg_m = m == -CUDART_INF_F ? 0.f : -m;
+            // p = 2^(s*scale - m), two at a time in bfloat16; the row sum adds the rounded values, the
+            // same numbers the P V product sees
+            float sum4[4] = {0.f, 0.f, 0.f, 0.f};
             uint32_t packed[BN / 2];
 #pragma unroll
             for (int i = 0; i < BN; i += 2) {
-                const float p0 = exp2f(s[i] - msafe), p1 = exp2f(s[i + 1] - msafe);
-                sum += p0 + p1;
-                __nv_bfloat162 pp = __floats2bfloat162_rn(p0, p1);
-                packed[i / 2] = *reinterpret_cast<uint32_t*>(&pp);
+                const uint32_t pp = exp2_bf16x2(fmaf(s[i], scale_log2, neg_m), fmaf(s[i + 1], scale_log2, neg_m));
+                packed[i / 2] = pp;
+                sum4[(i >> 1) & 3] += __uint_as_float(pp << 16) + __uint_as_float(pp & 0xffff0000u);
             }
-            l = l * corr + sum;
+            l = l * corr + ((sum4[0] + sum4[1]) + (sum4[2] + sum4[3]));
             // O of the tiles so far is complete, and P's buffer is free, once the last P V is done
             if (j > 0) {
                 ok = mb_wait(sa(&bars[6]), (j - 1) & 1, status, abort_flag);
                 ok = __all_sync(0xffffffffu, ok);
                 if (!ok) break;
                 tc_after();
-                if (!__all_sync(0xffffffffu, corr == 1.0f)) {          // some row's max moved: rescale O
+                if (!__all_sync(0xffffffffu, corr == 1.0f)) {          // some row's reference max moved: rescale O
 #pragma unroll 1
-                    for (int c = 0; c < D / 16; ++c) {
-                        float v[16];
-                        tm_ld16(tm_O + lane_base + c * 16, v);
+                    for (int c = 0; c < D / 32; ++c) {
+                        float v[32];
+                        tm_ld32_nowait(tm_O + lane_base + c * 32, v);
+                        tm_ld_wait();
+                        float lo16[16], hi16[16];
 #pragma unroll
-                        for (int i = 0; i < 16; ++i) v[i] *= corr;
-                        tm_st16(tm_O + lane_base + c * 16, v);
+                        for (int i = 0; i < 16; ++i) { lo16[i] = v[i] * corr; hi16[i] = v[16 + i] * corr; }
+                        tm_st16(tm_O + lane_base + c * 32, lo16);
+                        tm_st16(tm_O + lane_base + c * 32 + 16, hi16);
                     }
                     asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory");
                 }

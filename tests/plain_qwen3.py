@@ -178,6 +178,13 @@ TINY_C = dict(architectures=["Qwen3ForCausalLM"], hidden_size=72, intermediate_s
               tie_word_embeddings=False)
 
 
+# head size 64: the size class of the tcgen05 attention kernel, with a group of 4
+TINY_D = dict(architectures=["Qwen3ForCausalLM"], hidden_size=128, intermediate_size=272,
+              num_hidden_layers=2, num_attention_heads=4, num_key_value_heads=1, head_dim=64,
+              vocab_size=500, max_position_embeddings=1024, rms_norm_eps=1e-6, rope_theta=10000.0,
+              tie_word_embeddings=True)
+
+
 def expected_tensor_shapes(cfg: Mapping) -> Dict[str, Tuple[int, ...]]:
     """Tensor names and shapes of a checkpoint (src/model/qwen_model.cu:58-92)."""
     H, I, V = cfg["hidden_size"], cfg["intermediate_size"], cfg["vocab_size"]

@@ -18,7 +18,8 @@ pytestmark = pytest.mark.gpu
 
 CONFIGS = {"A": (P.TINY_A, 0, 16, [40, 100, 1, 77, 128, 33]),
            "B": (P.TINY_B, 1, 8, [70, 3, 200, 45, 256, 129, 17]),
-           "C": (P.TINY_C, 2, 32, [150, 64, 65, 300, 2, 97])}
+           "C": (P.TINY_C, 2, 32, [150, 64, 65, 300, 2, 97]),
+           "D": (P.TINY_D, 3, 16, [300, 129, 640, 70, 1000])}
 
 
 @pytest.fixture(scope="module")
