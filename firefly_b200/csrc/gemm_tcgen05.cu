@@ -83,6 +83,7 @@ __device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, int* st
     const unsigned long long start = clock64();
     uint32_t spins = 0;
     while (!mbar_try_wait(bar, parity)) {
+        __nanosleep(20);                     // waiting warps should not burn issue slots and power
         if (((++spins) & 1023u) == 0) {
             if (*abort_flag) return false;
             if (clock64() - start > WAIT_LIMIT_CYCLES) {
