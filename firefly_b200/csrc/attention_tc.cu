@@ -308,16 +308,18 @@ attn_tc_kernel(const __grid_constant__ TensorMapArg kv_map, const bf16* __restri
             tm_ld32_nowait(tm_S + lane_base, s);
             tm_ld32_nowait(tm_S + lane_base + 32, s + 32);
             tm_ld_wait();
-            // (mask and) row max of the raw scores, four independent chains; the scale (> 0) is applied later
-            float mx4[4] = {-CUDART_INF_F, -CUDART_INF_F, -CUDART_INF_F, -CUDART_INF_F};
+            // mask (only tiles that touch the diagonal or a window's edge), then the row max of the raw
+            // scores with four independent chains; the scale (> 0) is applied later
+            if (need_mask) {
 #pragma unroll
-            for (int i = 0; i < BN; ++i) {
-                if (need_mask) {
+                for (int i = 0; i < BN; ++i) {
                     const int key = key0 + i;
                     if (key < lo || key >= hi) s[i] = -CUDART_INF_F;
                 }
-                mx4[i & 3] = fmaxf(mx4[i & 3], s[i]);
             }
+            float mx4[4] = {s[0], s[1], s[2], s[3]};
+#pragma unroll
+            for (int i = 4; i < BN; ++i) mx4[i & 3] = fmaxf(mx4[i & 3], s[i]);
             const float mx = fmaxf(fmaxf(mx4[0], mx4[1]), fmaxf(mx4[2], mx4[3])) * scale_log2;
             // The reference max `m` follows the true row max lazily: it moves (and O is rescaled) only
             // when the true max has grown by more than 2^8 since, which keeps p <= 256 and makes the
@@ -330,17 +332,6 @@ attn_tc_kernel(const __grid_constant__ TensorMapArg kv_map, const bf16* __restri
                 m = m_new;
             }
             const float neg_m = m == -CUDART_INF_F ? 0.f : -m;
-            // p = 2^(s*scale - m), two at a time in bfloat16; the row sum adds the rounded values, the
-            // same numbers the P V product sees
-            float sum4[4] = {0.f, 0.f, 0.f, 0.f};
-            uint32_t packed[BN / 2];
-#pragma unroll
-            for (int i = 0; i < BN; i += 2) {
-                const uint32_t pp = exp2_bf16x2(fmaf(s[i], scale_log2, neg_m), fmaf(s[i + 1], scale_log2, neg_m));
-                packed[i / 2] = pp;
-                sum4[(i >> 1) & 3] += __uint_as_float(pp << 16) + __uint_as_float(pp & 0xffff0000u);
-            }
-            l = l * corr + ((sum4[0] + sum4[1]) + (sum4[2] + sum4[3]));
             // O of the tiles so far is complete, and P's buffer is free, once the last P V is done
             if (j > 0) {
                 ok = mb_wait(sa(&bars[6]), (j - 1) & 1, status, abort_flag);
@@ -362,11 +353,22 @@ attn_tc_kernel(const __grid_constant__ TensorMapArg kv_map, const bf16* __restri
                     asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory");
                 }
             }
+            // p = 2^(s*scale - m), two at a time in bfloat16, written to P's tile eight at a time; the
+            // row sum adds the rounded values, the same numbers the P V product sees
             unsigned char* Pt = P_ALIASES_K ? KVs + (size_t)(j % KV_STAGES) * 2 * KV_TILE_BYTES : Ps;
+            float sum4[4] = {0.f, 0.f, 0.f, 0.f};
 #pragma unroll
-            for (int c = 0; c < BN / 8; ++c)
-                *reinterpret_cast<uint4*>(Pt + r * 128 + ((c ^ (r & 7)) << 4)) =
-                    make_uint4(packed[c * 4], packed[c * 4 + 1], packed[c * 4 + 2], packed[c * 4 + 3]);
+            for (int c = 0; c < BN / 8; ++c) {
+                uint32_t w[4];
+#pragma unroll
+                for (int e = 0; e < 4; ++e) {
+                    const int i = c * 8 + e * 2;
+                    w[e] = exp2_bf16x2(fmaf(s[i], scale_log2, neg_m), fmaf(s[i + 1], scale_log2, neg_m));
+                    sum4[e] += __uint_as_float(w[e] << 16) + __uint_as_float(w[e] & 0xffff0000u);
+                }
+                *reinterpret_cast<uint4*>(Pt + r * 128 + ((c ^ (r & 7)) << 4)) = make_uint4(w[0], w[1], w[2], w[3]);
+            }
+            l = l * corr + ((sum4[0] + sum4[1]) + (sum4[2] + sum4[3]));
             asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
             tc_before();
             __syncwarp();
