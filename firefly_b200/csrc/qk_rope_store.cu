@@ -80,6 +80,92 @@ __global__ void qk_norm_rope_store_kernel(
     }
 }
 
+// The same for bfloat16 with a head of 64*C elements that is rotated whole: a lane keeps C
+// consecutive elements of the first half and the C they pair with in the second half in registers,
+// so every access of the warp is one full line and nothing goes through shared memory.
+template <int C>
+__global__ void qk_norm_rope_store_vec_kernel(
+    bf16* __restrict__ qkv, int row_width, int T_tokens, int nq, int nkv,
+    const float* __restrict__ q_norm_w, const float* __restrict__ k_norm_w, float eps,
+    const float* __restrict__ cos_sin, int max_positions,
+    const int* __restrict__ positions, const int* __restrict__ token_seq,
+    const int* __restrict__ block_table, int max_blocks, int block_size, int num_blocks,
+    bf16* __restrict__ cache, int* __restrict__ status) {
+    pdl_prologue();
+    constexpr int HALF = 32 * C, d = 64 * C;
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+    const int heads = nq + 2 * nkv;
+    const long long item = (long long)blockIdx.x * QKR_WARPS + warp;
+    if (item >= (long long)T_tokens * heads) return;
+    const int t = (int)(item / heads), hh = (int)(item % heads);
+    bf16* src = qkv + (size_t)t * row_width + (size_t)hh * d;
+    const int kind = hh < nq ? 0 : (hh < nq + nkv ? 1 : 2);  // q, k, v
+    const int pos = positions[t];
+    const int e0 = lane * C;                                  // this lane's first element of each half
+
+    float lo[C], hi[C];
+    {
+        __align__(8) bf16 a[C], b[C];
+        if (C == 2) {
+            *reinterpret_cast<uint32_t*>(a) = *reinterpret_cast<const uint32_t*>(src + e0);
+            *reinterpret_cast<uint32_t*>(b) = *reinterpret_cast<const uint32_t*>(src + HALF + e0);
+        } else {
+            *reinterpret_cast<uint2*>(a) = *reinterpret_cast<const uint2*>(src + e0);
+            *reinterpret_cast<uint2*>(b) = *reinterpret_cast<const uint2*>(src + HALF + e0);
+        }
+#pragma unroll
+        for (int j = 0; j < C; ++j) { lo[j] = __bfloat162float(a[j]); hi[j] = __bfloat162float(b[j]); }
+    }
+    const float* nw = kind == 0 ? q_norm_w : (kind == 1 ? k_norm_w : nullptr);
+    if (nw) {
+        float ss = 0.f;
+#pragma unroll
+        for (int j = 0; j < C; ++j) ss += lo[j] * lo[j] + hi[j] * hi[j];
+        ss = warp_sum(ss);
+        const float inv = 1.0f / sqrtf(ss / (float)d + eps);
+#pragma unroll
+        for (int j = 0; j < C; ++j) {
+            lo[j] = lo[j] * inv * nw[e0 + j];
+            hi[j] = hi[j] * inv * nw[HALF + e0 + j];
+        }
+    }
+    bf16* dst = src;
+    if (kind != 0) {
+        const int seq = token_seq[t];
+        const int page = block_table[(size_t)seq * max_blocks + pos / block_size];
+        if (page < 0 || page >= num_blocks) {
+            if (lane == 0) atomicExch(status, 2);
+            return;
+        }
+        const int kh = kind == 1 ? hh - nq : hh - nq - nkv;
+        dst = cache + ((((size_t)page * 2 + (kind == 2)) * nkv + kh) * block_size + pos % block_size) * d;
+    }
+    if (kind != 2 && cos_sin) {
+        if (pos < 0 || pos >= max_positions) {
+            if (lane == 0) atomicExch(status, 3);
+            return;
+        }
+        const float* cs = cos_sin + (size_t)pos * d + 2 * e0;  // [half][2]
+#pragma unroll
+        for (int j = 0; j < C; ++j) {
+            const float c = cs[2 * j], s = cs[2 * j + 1];
+            const float a = lo[j], b = hi[j];
+            lo[j] = a * c - b * s;
+            hi[j] = b * c + a * s;
+        }
+    }
+    __align__(8) bf16 a[C], b[C];
+#pragma unroll
+    for (int j = 0; j < C; ++j) { a[j] = __float2bfloat16_rn(lo[j]); b[j] = __float2bfloat16_rn(hi[j]); }
+    if (C == 2) {
+        *reinterpret_cast<uint32_t*>(dst + e0) = *reinterpret_cast<const uint32_t*>(a);
+        *reinterpret_cast<uint32_t*>(dst + HALF + e0) = *reinterpret_cast<const uint32_t*>(b);
+    } else {
+        *reinterpret_cast<uint2*>(dst + e0) = *reinterpret_cast<const uint2*>(a);
+        *reinterpret_cast<uint2*>(dst + HALF + e0) = *reinterpret_cast<const uint2*>(b);
+    }
+}
+
 }  // namespace ff
 
 using namespace ff;
@@ -97,6 +183,20 @@ FF_EXPORT int ff_qk_norm_rope_store(void* qkv, int dtype, int row_width, int T, 
     if (row_width < (nq + 2 * nkv) * d) return FF_ERR_BAD_ARG;
     const long long items = (long long)T * (nq + 2 * nkv);
     const unsigned blocks = (unsigned)((items + QKR_WARPS - 1) / QKR_WARPS);
+    // whole-head rotation of a 128- or 256-wide bfloat16 head with aligned rows: the register form
+    if (dtype == 1 && (d == 128 || d == 256) && (!cos_sin || rotary_dim == d) && row_width % 4 == 0 &&
+        ((uintptr_t)qkv & 7) == 0 && ((uintptr_t)cache & 7) == 0) {
+        if (d == 128)
+            FF_LAUNCH((qk_norm_rope_store_vec_kernel<2>), blocks, QKR_WARPS * 32, 0, stream, (bf16*)qkv, row_width, T,
+                      nq, nkv, q_norm_w, k_norm_w, eps, cos_sin, max_positions, positions, token_seq, block_table,
+                      max_blocks, block_size, num_blocks, (bf16*)cache, status);
+        else
+            FF_LAUNCH((qk_norm_rope_store_vec_kernel<4>), blocks, QKR_WARPS * 32, 0, stream, (bf16*)qkv, row_width, T,
+                      nq, nkv, q_norm_w, k_norm_w, eps, cos_sin, max_positions, positions, token_seq, block_table,
+                      max_blocks, block_size, num_blocks, (bf16*)cache, status);
+        FF_LAUNCH_CHECK();
+        return 0;
+    }
     if (dtype == 0)
         FF_LAUNCH((qk_norm_rope_store_kernel<float>), blocks, QKR_WARPS * 32, 0, stream, 
             (float*)qkv, row_width, T, nq, nkv, d, q_norm_w, k_norm_w, eps, cos_sin, rotary_dim,

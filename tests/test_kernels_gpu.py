@@ -74,6 +74,19 @@ def test_silu_mul(I, adt):
     assert torch.allclose(out.cpu().double(), want, atol=tol, rtol=tol)
 
 
+@pytest.mark.parametrize("I", [48, 160, 12288])
+@pytest.mark.parametrize("adt", [torch.float32, torch.bfloat16])
+def test_silu_mul_interleaved(I, adt):
+    """Gate and up columns alternating in groups of 16, the layout the fused product's weight has."""
+    gate, up = (torch.randn(7, I) * 3).to(adt), (torch.randn(7, I) * 3).to(adt)
+    gu = torch.stack([gate.view(7, I // 16, 16), up.view(7, I // 16, 16)], dim=2).reshape(7, 2 * I).contiguous()
+    out = torch.empty(7, I, dtype=adt, device="cuda")
+    K().silu_mul(dev(gu), out, True)
+    want = P.silu_mul(gate.double(), up.double())
+    tol = 1e-6 if adt == torch.float32 else 1e-2
+    assert torch.allclose(out.cpu().double(), want, atol=tol, rtol=tol)
+
+
 def _paged(k, v, block, n_extra=3, seed=0):
     """Scatter whole-sequence k, v [T, nkv, d] into shuffled pages.  Returns
     (pages [blocks,2,nkv,block,d], table row)."""
