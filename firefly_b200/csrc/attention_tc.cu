@@ -5,13 +5,15 @@
 // group share every key and value it fetches) and walks the visible keys in tiles of 64:
 //   S = Q K^T      tcgen05.mma, Q and K from shared memory (K brought in by TMA, page by page),
 //                  S (128 x 64, float32) in tensor memory;
+//                  S (128 x 64, float32) in tensor memory, two buffers, so that the product for
+//                  the next tile runs while the softmax works on this one;
 //   softmax        four warps, one thread per row: tcgen05.ld of its row of S, mask, running max
-//                  and sum in 32-bit, P as bfloat16 into shared memory, and - only when a row's
-//                  max moved - a rescale of its row of O in tensor memory;
-//   O += P V       tcgen05.mma, P from shared memory, V (the cache's [key][d] tile as it is, the
+//                  and sum in 32-bit, P as bfloat16 written back over S in tensor memory
+//                  (tcgen05.st), and - only when a row's max moved far - a rescale of its row of O;
+//   O += P V       tcgen05.mma, P from tensor memory, V (the cache's [key][d] tile as it is, the
 //                  MMA's N-major operand form), O (128 x D, float32) in tensor memory.
-// One thread issues TMA loads two tiles deep, one thread issues the MMAs; two blocks share an
-// SM (at head size 128), so one block's softmax runs under the other's MMAs.
+// One thread issues TMA loads (K and V have two stages each, freed separately), one thread
+// issues the MMAs; two blocks share an SM (at head size 128).
 //
 // It replaces, for head sizes that are multiples of 64 and page sizes that divide 64, the
 // mma.sync kernel of attention_mma.cu (which stays for every other size); the reference's
@@ -50,13 +52,15 @@ constexpr unsigned long long WAIT_LIMIT_CYCLES = 2000000000ull;
 
 constexpr int Q_BYTES = BM * D * 2;
 constexpr int KV_TILE_BYTES = BN * D * 2;            // one K or V tile
-constexpr int P_BYTES = BM * BN * 2;
-constexpr int TMEM_COLS = (BN + D) <= 128 ? 128 : ((BN + D) <= 256 ? 256 : 512);
-// P takes the place of the K tile it was computed from (K is dead once S is complete) when that
-// tile is large enough; this is what lets two blocks share an SM at head size 128
-constexpr bool P_ALIASES_K = KV_TILE_BYTES >= P_BYTES;
-constexpr size_t ATC_SMEM = 1024 + Q_BYTES + KV_STAGES * 2 * KV_TILE_BYTES + (P_ALIASES_K ? 0 : P_BYTES) + 128 +
-                            MAX_PAGE_LIST * 4;
+// tensor memory: S in two buffers of BN columns (P, as bfloat16 pairs, takes the first BN/2
+// columns of the S it was computed from), then O
+constexpr int TMEM_COLS = (2 * BN + D) <= 256 ? 256 : 512;
+constexpr size_t ATC_SMEM = 1024 + Q_BYTES + KV_STAGES * 2 * KV_TILE_BYTES + 128 + MAX_PAGE_LIST * 4;
+// barriers
+enum { B_K_FULL = 0, B_V_FULL = 2, B_K_EMPTY = 4, B_V_EMPTY = 6, B_S_FULL = 8, B_P_FULL = 10, B_PV_DONE = 12,
+       B_Q_READY = 13, B_COUNT = 14 };
+// S and P have a barrier per buffer: a softmax warp may be a whole tile ahead of another, and its
+// arrival for the next tile must not count for this one
 
 __device__ __forceinline__ uint32_t sa(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }
 __device__ __forceinline__ void mb_init(uint32_t bar, uint32_t count) {
@@ -103,6 +107,12 @@ __device__ __forceinline__ void tc_mma(uint32_t d_tmem, uint64_t da, uint64_t db
     asm volatile("{\n\t.reg .pred p;\n\tsetp.ne.b32 p, %4, 0;\n\t"
                  "tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n\t}"
                  ::"r"(d_tmem), "l"(da), "l"(db), "r"(idesc), "r"(acc) : "memory");
+}
+// the same with the A operand (128 x 16 bfloat16, two to a 32-bit cell, 8 columns) in tensor memory
+__device__ __forceinline__ void tc_mma_a_tmem(uint32_t d_tmem, uint32_t a_tmem, uint64_t db, uint32_t idesc, uint32_t acc) {
+    asm volatile("{\n\t.reg .pred p;\n\tsetp.ne.b32 p, %4, 0;\n\t"
+                 "tcgen05.mma.cta_group::1.kind::f16 [%0], [%1], %2, %3, p;\n\t}"
+                 ::"r"(d_tmem), "r"(a_tmem), "l"(db), "r"(idesc), "r"(acc) : "memory");
 }
 __device__ __forceinline__ void tm_ld16(uint32_t taddr, float (&v)[16]) {
     uint32_t r[16];
@@ -151,6 +161,12 @@ __device__ __forceinline__ void tm_st16(uint32_t taddr, const float (&v)[16]) {
                    "r"(__float_as_uint(v[15])) : "memory");
 }
 
+__device__ __forceinline__ void tm_st16u(uint32_t taddr, const uint32_t* v) {
+    asm volatile("tcgen05.st.sync.aligned.32x32b.x16.b32 [%0], {%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15,%16};"
+                 ::"r"(taddr), "r"(v[0]), "r"(v[1]), "r"(v[2]), "r"(v[3]), "r"(v[4]), "r"(v[5]), "r"(v[6]), "r"(v[7]),
+                   "r"(v[8]), "r"(v[9]), "r"(v[10]), "r"(v[11]), "r"(v[12]), "r"(v[13]), "r"(v[14]), "r"(v[15]) : "memory");
+}
+
 // Operand descriptors.  Tiles are made of 64-column panels whose 128-byte rows are swizzled in
 // groups of eight (the layout TMA writes with the 128-byte swizzle).
 // K-major (the reduction dimension runs along the 128-byte row): groups of 8 rows 1024 bytes apart.
@@ -182,10 +198,9 @@ attn_tc_kernel(const __grid_constant__ TensorMapArg kv_map, const bf16* __restri
     extern __shared__ unsigned char smem_raw[];
     unsigned char* base = reinterpret_cast<unsigned char*>(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
     unsigned char* Qs = base;                                        // [PANELS][128][128 B]
-    unsigned char* KVs = Qs + Q_BYTES;                               // [stage][K|V][PANELS][64][128 B]
-    unsigned char* Ps = KVs + KV_STAGES * 2 * KV_TILE_BYTES;         // [128][128 B] unless it aliases K
-    uint64_t* bars = reinterpret_cast<uint64_t*>(Ps + (P_ALIASES_K ? 0 : P_BYTES));
-    // bars: [0,1] kv_full, [2,3] kv_empty, [4] s_full, [5] p_full, [6] pv_done, [7] q_ready
+    unsigned char* Ks = Qs + Q_BYTES;                                // [stage][PANELS][64][128 B]
+    unsigned char* Vs = Ks + KV_STAGES * KV_TILE_BYTES;              // [stage][PANELS][64][128 B]
+    uint64_t* bars = reinterpret_cast<uint64_t*>(Vs + KV_STAGES * KV_TILE_BYTES);
     int* s_pages = reinterpret_cast<int*>(bars + 16);
     __shared__ int s_seq, s_tile, s_abort;
     __shared__ uint32_t s_tmem;
@@ -196,9 +211,7 @@ attn_tc_kernel(const __grid_constant__ TensorMapArg kv_map, const bf16* __restri
 
     if (threadIdx.x == 0) {
         s_abort = 0;
-        mb_init(sa(&bars[0]), 1); mb_init(sa(&bars[1]), 1);
-        mb_init(sa(&bars[2]), 1); mb_init(sa(&bars[3]), 1);
-        mb_init(sa(&bars[4]), 1); mb_init(sa(&bars[5]), 4); mb_init(sa(&bars[6]), 1); mb_init(sa(&bars[7]), 4);
+        for (int i = 0; i < B_COUNT; ++i) mb_init(sa(&bars[i]), (i == B_P_FULL || i == B_P_FULL + 1 || i == B_Q_READY) ? 4 : 1);
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     }
     if (warp == 5) {
@@ -236,8 +249,8 @@ attn_tc_kernel(const __grid_constant__ TensorMapArg kv_map, const bf16* __restri
     __syncthreads();
     tc_after();
     const uint32_t tmem = s_tmem;
-    const uint32_t tm_S = tmem;                  // columns [0, 64)
-    const uint32_t tm_O = tmem + BN;             // columns [64, 64 + D)
+    const uint32_t tm_S = tmem;                  // two buffers: columns [0, 64) and [64, 128)
+    const uint32_t tm_O = tmem + 2 * BN;         // columns [128, 128 + D)
     const int seq = s_seq, tile = s_tile;
 
     int n_tiles = 0, t_begin = 0, tok0 = 0, q_len = 0, ctx = 0, rows = 0, row0 = 0, kv_lo = 0, kv_hi = 0;
@@ -273,7 +286,7 @@ attn_tc_kernel(const __grid_constant__ TensorMapArg kv_map, const bf16* __restri
         }
         // zero the K/V stages once: parts no page is loaded into must hold finite numbers
         for (int i = threadIdx.x; i < KV_STAGES * 2 * KV_TILE_BYTES / 16; i += 128)
-            reinterpret_cast<uint4*>(KVs)[i] = make_uint4(0u, 0u, 0u, 0u);
+            reinterpret_cast<uint4*>(Ks)[i] = make_uint4(0u, 0u, 0u, 0u);
         // this row of q -> the swizzled Q tile
         if (n_tiles > 0) {
             const bf16* src = q + (size_t)(tok0 + token) * q_stride + (size_t)head * D;
@@ -285,7 +298,7 @@ attn_tc_kernel(const __grid_constant__ TensorMapArg kv_map, const bf16* __restri
         }
         asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
         __syncwarp();
-        if (lane == 0) mb_arrive(sa(&bars[7]));
+        if (lane == 0) mb_arrive(sa(&bars[B_Q_READY]));
 
         // ------------------------------------------------ softmax, one thread per row --
         const int pos = ctx + token;
@@ -298,15 +311,16 @@ attn_tc_kernel(const __grid_constant__ TensorMapArg kv_map, const bf16* __restri
         float m = -CUDART_INF_F, l = 0.f;
         bool ok = true;
         for (int j = 0; j < n_tiles && ok; ++j) {
-            ok = mb_wait(sa(&bars[4]), j & 1, status, abort_flag);
+            ok = mb_wait(sa(&bars[B_S_FULL + (j & 1)]), (j >> 1) & 1, status, abort_flag);
             ok = __all_sync(0xffffffffu, ok);
             if (!ok) break;
             tc_after();
+            const uint32_t tm_Sj = tm_S + (uint32_t)((j & 1) * BN) + lane_base;
             const int key0 = (t_begin + j) * BN;
             const bool need_mask = key0 + BN > first_pos + 1 || key0 < full_lo;
             float s[BN];
-            tm_ld32_nowait(tm_S + lane_base, s);
-            tm_ld32_nowait(tm_S + lane_base + 32, s + 32);
+            tm_ld32_nowait(tm_Sj, s);
+            tm_ld32_nowait(tm_Sj + 32, s + 32);
             tm_ld_wait();
             // mask (only tiles that touch the diagonal or a window's edge), then the row max of the raw
             // scores with four independent chains; the scale (> 0) is applied later
@@ -332,9 +346,20 @@ attn_tc_kernel(const __grid_constant__ TensorMapArg kv_map, const bf16* __restri
                 m = m_new;
             }
             const float neg_m = m == -CUDART_INF_F ? 0.f : -m;
-            // O of the tiles so far is complete, and P's buffer is free, once the last P V is done
+            // p = 2^(s*scale - m), two at a time in bfloat16; the row sum adds the rounded values, the
+            // same numbers the P V product sees
+            uint32_t w[BN / 2];
+            float sum4[4] = {0.f, 0.f, 0.f, 0.f};
+#pragma unroll
+            for (int e = 0; e < BN / 2; ++e) {
+                w[e] = exp2_bf16x2(fmaf(s[2 * e], scale_log2, neg_m), fmaf(s[2 * e + 1], scale_log2, neg_m));
+                sum4[e & 3] += __uint_as_float(w[e] << 16) + __uint_as_float(w[e] & 0xffff0000u);
+            }
+            // Tensor memory is written only between products: the last P V must be complete before P
+            // of this tile is stored (stores issued while it was still running gave wrong sums, although
+            // they go to other columns), and before O is rescaled.  It was issued a whole tile ago.
             if (j > 0) {
-                ok = mb_wait(sa(&bars[6]), (j - 1) & 1, status, abort_flag);
+                ok = mb_wait(sa(&bars[B_PV_DONE]), (j - 1) & 1, status, abort_flag);
                 ok = __all_sync(0xffffffffu, ok);
                 if (!ok) break;
                 tc_after();
@@ -350,33 +375,20 @@ attn_tc_kernel(const __grid_constant__ TensorMapArg kv_map, const bf16* __restri
                         tm_st16(tm_O + lane_base + c * 32, lo16);
                         tm_st16(tm_O + lane_base + c * 32 + 16, hi16);
                     }
-                    asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory");
                 }
             }
-            // p = 2^(s*scale - m), two at a time in bfloat16, written to P's tile eight at a time; the
-            // row sum adds the rounded values, the same numbers the P V product sees
-            unsigned char* Pt = P_ALIASES_K ? KVs + (size_t)(j % KV_STAGES) * 2 * KV_TILE_BYTES : Ps;
-            float sum4[4] = {0.f, 0.f, 0.f, 0.f};
-#pragma unroll
-            for (int c = 0; c < BN / 8; ++c) {
-                uint32_t w[4];
-#pragma unroll
-                for (int e = 0; e < 4; ++e) {
-                    const int i = c * 8 + e * 2;
-                    w[e] = exp2_bf16x2(fmaf(s[i], scale_log2, neg_m), fmaf(s[i + 1], scale_log2, neg_m));
-                    sum4[e] += __uint_as_float(w[e] << 16) + __uint_as_float(w[e] & 0xffff0000u);
-                }
-                *reinterpret_cast<uint4*>(Pt + r * 128 + ((c ^ (r & 7)) << 4)) = make_uint4(w[0], w[1], w[2], w[3]);
-            }
+            // P over the first half of this S buffer (the row's scores are in registers by now)
+            tm_st16u(tm_Sj, w);
+            tm_st16u(tm_Sj + 16, w + 16);
             l = l * corr + ((sum4[0] + sum4[1]) + (sum4[2] + sum4[3]));
-            asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+            asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory");
             tc_before();
             __syncwarp();
-            if (lane == 0) mb_arrive(sa(&bars[5]));
+            if (lane == 0) mb_arrive(sa(&bars[B_P_FULL + (j & 1)]));
         }
         // ------------------------------------------------ epilogue ------------
         if (n_tiles > 0 && ok) {
-            ok = mb_wait(sa(&bars[6]), (n_tiles - 1) & 1, status, abort_flag);
+            ok = mb_wait(sa(&bars[B_PV_DONE]), (n_tiles - 1) & 1, status, abort_flag);
             ok = __all_sync(0xffffffffu, ok);
         }
         if (n_tiles > 0 && ok) {
@@ -399,64 +411,80 @@ attn_tc_kernel(const __grid_constant__ TensorMapArg kv_map, const bf16* __restri
                 }
             }
         }
-    } else if (warp == 4 && lane == 0) {
+    } else if (warp == 4) {
         // ------------------------------------------------ loads: K and V tiles by TMA --
-        // the stages are zeroed by the softmax warps first (q_ready also says that is done)
-        bool ok = n_tiles == 0 || mb_wait(sa(&bars[7]), 0, status, abort_flag);
-        for (int j = 0; j < n_tiles && ok; ++j) {
+        // The whole warp: a tile is pages_per_tile x PANELS boxes (at most 32), one per lane, since a
+        // single thread needs well over a hundred cycles for each copy it starts.
+        // The stages are zeroed by the softmax warps first (q_ready also says that is done).
+        // Order K0, K1, V0, K2, V1, ...: the order in which the MMAs need them and free their stages.
+        bool ok = n_tiles == 0 || mb_wait(sa(&bars[B_Q_READY]), 0, status, abort_flag);
+        ok = __all_sync(0xffffffffu, ok);
+        const int p = lane / PANELS, h = lane % PANELS;                  // this lane's page and panel of a tile
+        auto load_tile = [&](int j, int kv) -> bool {
             const int s = j % KV_STAGES;
-            ok = mb_wait(sa(&bars[2 + s]), ((j / KV_STAGES) & 1) ^ 1, status, abort_flag);
-            if (!ok) break;
-            int valid_pages = 0;
-            for (int p = 0; p < pages_per_tile; ++p) valid_pages += s_pages[j * pages_per_tile + p] >= 0;
-            const uint32_t bar = sa(&bars[s]);
-            mb_expect_tx(bar, (uint32_t)(valid_pages * 2 * block_size * D * 2));
-            unsigned char* st = KVs + (size_t)s * 2 * KV_TILE_BYTES;
-            for (int p = 0; p < pages_per_tile; ++p) {
-                const int page = s_pages[j * pages_per_tile + p];
-                if (page < 0) continue;
-#pragma unroll
-                for (int kv = 0; kv < 2; ++kv) {
-                    const int y = ((page * 2 + kv) * nkv + kh) * block_size;
-#pragma unroll
-                    for (int h = 0; h < PANELS; ++h)
-                        tma_2d(sa(st + kv * KV_TILE_BYTES + h * (BN * 128) + p * block_size * 128), &kv_map, h * 64, y, bar);
-                }
+            bool fine = mb_wait(sa(&bars[(kv ? B_V_EMPTY : B_K_EMPTY) + s]), ((j / KV_STAGES) & 1) ^ 1, status, abort_flag);
+            if (!__all_sync(0xffffffffu, fine)) return false;
+            const int page = p < pages_per_tile ? s_pages[j * pages_per_tile + p] : -1;
+            const unsigned boxes = __ballot_sync(0xffffffffu, page >= 0);
+            const uint32_t bar = sa(&bars[(kv ? B_V_FULL : B_K_FULL) + s]);
+            if (lane == 0) mb_expect_tx(bar, (uint32_t)(__popc(boxes) * block_size * 128));
+            __syncwarp();
+            if (page >= 0) {
+                unsigned char* st = (kv ? Vs : Ks) + (size_t)s * KV_TILE_BYTES;
+                const int y = ((page * 2 + kv) * nkv + kh) * block_size;
+                tma_2d(sa(st + h * (BN * 128) + p * block_size * 128), &kv_map, h * 64, y, bar);
             }
+            return true;
+        };
+        if (ok && n_tiles > 0) ok = load_tile(0, 0);
+        for (int j = 0; j < n_tiles && ok; ++j) {
+            if (j + 1 < n_tiles) ok = load_tile(j + 1, 0);
+            if (ok) ok = load_tile(j, 1);
         }
     } else if (warp == 5 && lane == 0) {
         // ------------------------------------------------ MMAs -----------------
         const uint32_t idesc_qk = idesc_bf16(BN, false);
         const uint32_t idesc_pv = idesc_bf16(D, true);
-        bool ok = n_tiles == 0 || mb_wait(sa(&bars[7]), 0, status, abort_flag);
+        bool ok = n_tiles == 0 || mb_wait(sa(&bars[B_Q_READY]), 0, status, abort_flag);
         tc_after();
-        for (int j = 0; j < n_tiles && ok; ++j) {
+        // S(j) = Q K(j)^T over D in steps of 16, into S buffer j & 1
+        auto issue_qk = [&](int j) -> bool {
             const int s = j % KV_STAGES;
-            ok = mb_wait(sa(&bars[s]), (j / KV_STAGES) & 1, status, abort_flag);
-            if (!ok) break;
+            if (!mb_wait(sa(&bars[B_K_FULL + s]), (j / KV_STAGES) & 1, status, abort_flag)) return false;
             tc_after();
-            const uint32_t ks = sa(KVs + (size_t)s * 2 * KV_TILE_BYTES);
-            const uint32_t vs = ks + KV_TILE_BYTES;
-            // S = Q K^T over D in steps of 16
+            const uint32_t ks = sa(Ks + (size_t)s * KV_TILE_BYTES);
 #pragma unroll
             for (int k = 0; k < D / 16; ++k) {
                 const uint64_t da = desc_k_major(sa(Qs) + (k >> 2) * (BM * 128) + (k & 3) * 32);
                 const uint64_t db = desc_k_major(ks + (k >> 2) * (BN * 128) + (k & 3) * 32);
-                tc_mma(tm_S, da, db, idesc_qk, k > 0 ? 1u : 0u);
+                tc_mma(tm_S + (uint32_t)((j & 1) * BN), da, db, idesc_qk, k > 0 ? 1u : 0u);
             }
-            tc_commit_to(sa(&bars[4]));
+            tc_commit_to(sa(&bars[B_S_FULL + (j & 1)]));
+            tc_commit_to(sa(&bars[B_K_EMPTY + s]));
+            return true;
+        };
+        if (ok && n_tiles > 0) ok = issue_qk(0);
+        for (int j = 0; j < n_tiles && ok; ++j) {
+            // the next tile's scores first: they are computed while the softmax warps work on this tile
+            if (j + 1 < n_tiles) {
+                ok = issue_qk(j + 1);
+                if (!ok) break;
+            }
+            const int s = j % KV_STAGES;
             // O += P V over the 64 keys in steps of 16, once the softmax warps have written P
-            ok = mb_wait(sa(&bars[5]), j & 1, status, abort_flag);
+            ok = mb_wait(sa(&bars[B_P_FULL + (j & 1)]), (j >> 1) & 1, status, abort_flag);
+            if (!ok) break;
+            ok = mb_wait(sa(&bars[B_V_FULL + s]), (j / KV_STAGES) & 1, status, abort_flag);
             if (!ok) break;
             tc_after();
+            const uint32_t vs = sa(Vs + (size_t)s * KV_TILE_BYTES);
 #pragma unroll
             for (int k = 0; k < BN / 16; ++k) {
-                const uint64_t da = desc_k_major((P_ALIASES_K ? ks : sa(Ps)) + k * 32);
                 const uint64_t db = desc_n_major(vs + k * 16 * 128, BN * 128);
-                tc_mma(tm_O, da, db, idesc_pv, (j > 0 || k > 0) ? 1u : 0u);
+                tc_mma_a_tmem(tm_O, tm_S + (uint32_t)((j & 1) * BN + k * 8), db, idesc_pv, (j > 0 || k > 0) ? 1u : 0u);
             }
-            tc_commit_to(sa(&bars[6]));
-            tc_commit_to(sa(&bars[2 + s]));
+            tc_commit_to(sa(&bars[B_PV_DONE]));
+            tc_commit_to(sa(&bars[B_V_EMPTY + s]));
         }
     }
     tc_before();
