@@ -58,7 +58,7 @@ constexpr int TMEM_COLS = (2 * BN + D) <= 256 ? 256 : 512;
 constexpr size_t ATC_SMEM = 1024 + Q_BYTES + KV_STAGES * 2 * KV_TILE_BYTES + 128 + MAX_PAGE_LIST * 4;
 // barriers
 enum { B_K_FULL = 0, B_V_FULL = 2, B_K_EMPTY = 4, B_V_EMPTY = 6, B_S_FULL = 8, B_P_FULL = 10, B_PV_DONE = 12,
-       B_Q_READY = 13, B_COUNT = 14 };
+       B_Q_READY = 13, B_PAGES_READY = 14, B_COUNT = 15 };
 // S and P have a barrier per buffer: a softmax warp may be a whole tile ahead of another, and its
 // arrival for the next tile must not count for this one
 
@@ -202,16 +202,16 @@ attn_tc_kernel(const __grid_constant__ TensorMapArg kv_map, const bf16* __restri
     unsigned char* Vs = Ks + KV_STAGES * KV_TILE_BYTES;              // [stage][PANELS][64][128 B]
     uint64_t* bars = reinterpret_cast<uint64_t*>(Vs + KV_STAGES * KV_TILE_BYTES);
     int* s_pages = reinterpret_cast<int*>(bars + 16);
-    __shared__ int s_seq, s_tile, s_abort;
+    __shared__ int s_seq, s_tile, s_abort, s_tok0, s_qlen, s_ctx;
     __shared__ uint32_t s_tmem;
     const int G = nq / nkv;
-    const int kh = blockIdx.y;
+    const int kh = (int)(blockIdx.x % (unsigned)nkv);
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     volatile int* abort_flag = &s_abort;
 
     if (threadIdx.x == 0) {
         s_abort = 0;
-        for (int i = 0; i < B_COUNT; ++i) mb_init(sa(&bars[i]), (i == B_P_FULL || i == B_P_FULL + 1 || i == B_Q_READY) ? 4 : 1);
+        for (int i = 0; i < B_COUNT; ++i) mb_init(sa(&bars[i]), (i == B_P_FULL || i == B_P_FULL + 1 || i >= B_Q_READY) ? 4 : 1);
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     }
     if (warp == 5) {
@@ -220,9 +220,9 @@ attn_tc_kernel(const __grid_constant__ TensorMapArg kv_map, const bf16* __restri
         asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
     }
     asm volatile("griddepcontrol.wait;" ::: "memory");
-    // Row tiles are handed out last first: in a prompt the late tiles see the most keys, and the
-    // long blocks should not be the ones that start last.
-    const int vtile = (int)gridDim.x - 1 - (int)blockIdx.x;
+    // Row tiles are handed out last first, for all kv heads before the next tile: in a prompt the
+    // late tiles see the most keys, and the long blocks should not be the ones that start last.
+    const int vtile = (int)(gridDim.x / (unsigned)nkv) - 1 - (int)(blockIdx.x / (unsigned)nkv);
     if (warp == 0) {   // which sequence owns row tile vtile
         int cum = 0, found_seq = -1, found_tile = 0;
         for (int s0 = 0; s0 < n_seqs && found_seq < 0; s0 += 32) {
@@ -243,7 +243,13 @@ attn_tc_kernel(const __grid_constant__ TensorMapArg kv_map, const bf16* __restri
             }
             cum += total;
         }
-        if (lane == 0) { s_seq = found_seq; s_tile = found_tile; }
+        if (lane == 0) {
+            s_seq = found_seq; s_tile = found_tile;
+            if (found_seq >= 0) {
+                const int a = cu_q[found_seq];
+                s_tok0 = a; s_qlen = cu_q[found_seq + 1] - a; s_ctx = ctx_lens[found_seq];
+            }
+        }
     }
     tc_before();
     __syncthreads();
@@ -255,7 +261,7 @@ attn_tc_kernel(const __grid_constant__ TensorMapArg kv_map, const bf16* __restri
 
     int n_tiles = 0, t_begin = 0, tok0 = 0, q_len = 0, ctx = 0, rows = 0, row0 = 0, kv_lo = 0, kv_hi = 0;
     if (seq >= 0) {
-        tok0 = cu_q[seq]; q_len = cu_q[seq + 1] - tok0; ctx = ctx_lens[seq];
+        tok0 = s_tok0; q_len = s_qlen; ctx = s_ctx;
         rows = q_len * G; row0 = tile * BM;
         const int first_tok = row0 / G, last_tok = min(q_len - 1, (row0 + BM - 1) / G);
         kv_hi = ctx + last_tok + 1;
@@ -275,6 +281,13 @@ attn_tc_kernel(const __grid_constant__ TensorMapArg kv_map, const bf16* __restri
         const bool valid = rg < rows;
         const int rgc = min(rg, max(rows - 1, 0));
         const int token = rgc / G, head = kh * G + rgc % G;
+        // this row of q into registers first: its latency passes under the work on the page list
+        uint4 qv[D / 8];
+        if (n_tiles > 0) {
+            const uint4* src = reinterpret_cast<const uint4*>(q + (size_t)(tok0 + token) * q_stride + (size_t)head * D);
+#pragma unroll
+            for (int ch = 0; ch < D / 8; ++ch) qv[ch] = valid ? __ldg(src + ch) : make_uint4(0u, 0u, 0u, 0u);
+        }
         // page ids of all tiles
         const int* bt = block_table + (size_t)max(seq, 0) * max_blocks;
         const int last_page = (kv_hi - 1) / block_size, first_page = kv_lo / block_size;
@@ -287,14 +300,14 @@ attn_tc_kernel(const __grid_constant__ TensorMapArg kv_map, const bf16* __restri
         // zero the K/V stages once: parts no page is loaded into must hold finite numbers
         for (int i = threadIdx.x; i < KV_STAGES * 2 * KV_TILE_BYTES / 16; i += 128)
             reinterpret_cast<uint4*>(Ks)[i] = make_uint4(0u, 0u, 0u, 0u);
-        // this row of q -> the swizzled Q tile
+        asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+        __syncwarp();
+        if (lane == 0) mb_arrive(sa(&bars[B_PAGES_READY]));               // the loads may start
+        // the row of q -> the swizzled Q tile
         if (n_tiles > 0) {
-            const bf16* src = q + (size_t)(tok0 + token) * q_stride + (size_t)head * D;
 #pragma unroll
-            for (int ch = 0; ch < D / 8; ++ch) {
-                uint4 v = valid ? *reinterpret_cast<const uint4*>(src + ch * 8) : make_uint4(0u, 0u, 0u, 0u);
-                *reinterpret_cast<uint4*>(Qs + (ch >> 3) * (BM * 128) + r * 128 + (((ch & 7) ^ (r & 7)) << 4)) = v;
-            }
+            for (int ch = 0; ch < D / 8; ++ch)
+                *reinterpret_cast<uint4*>(Qs + (ch >> 3) * (BM * 128) + r * 128 + (((ch & 7) ^ (r & 7)) << 4)) = qv[ch];
         }
         asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
         __syncwarp();
@@ -415,9 +428,9 @@ attn_tc_kernel(const __grid_constant__ TensorMapArg kv_map, const bf16* __restri
         // ------------------------------------------------ loads: K and V tiles by TMA --
         // The whole warp: a tile is pages_per_tile x PANELS boxes (at most 32), one per lane, since a
         // single thread needs well over a hundred cycles for each copy it starts.
-        // The stages are zeroed by the softmax warps first (q_ready also says that is done).
+        // The softmax warps write the page list and zero the stages first.
         // Order K0, K1, V0, K2, V1, ...: the order in which the MMAs need them and free their stages.
-        bool ok = n_tiles == 0 || mb_wait(sa(&bars[B_Q_READY]), 0, status, abort_flag);
+        bool ok = n_tiles == 0 || mb_wait(sa(&bars[B_PAGES_READY]), 0, status, abort_flag);
         ok = __all_sync(0xffffffffu, ok);
         const int p = lane / PANELS, h = lane % PANELS;                  // this lane's page and panel of a tile
         auto load_tile = [&](int j, int kv) -> bool {
@@ -570,7 +583,8 @@ FF_EXPORT int ff_attn_tc(const void* q, int q_stride, const void* cache, const i
     if (rc) return rc;
     TensorMapArg arg;
     std::memcpy(arg.bytes, &map, sizeof(map));
-    FF_LAUNCH((attn_tc_kernel), dim3(total_tiles, nkv), ATC_THREADS, ATC_SMEM, stream, arg, (const bf16*)q, q_stride,
+    if ((long long)total_tiles * nkv >= (1ll << 31)) return FF_ERR_UNSUPPORTED;
+    FF_LAUNCH((attn_tc_kernel), dim3((unsigned)(total_tiles * nkv)), ATC_THREADS, ATC_SMEM, stream, arg, (const bf16*)q, q_stride,
               block_table, max_blocks, cu_q, ctx_lens, n_seqs, (bf16*)out, out_stride, nq, nkv, block_size, num_blocks,
               scale * LOG2E, window, status);
     return 0;
