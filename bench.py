@@ -7,9 +7,11 @@ throughput, the decode step's memory roofline and batch-1 / batch-64 points.
 
 One JSON line is printed.  ``value`` is device-timed (CUDA events around K
 decode steps that run back to back from CUDA graphs, the sampled tokens fed to
-the next step on the device); ``e2e`` is the same K steps through the Python
-entry point's engine loop, with token ids going host -> device and sampled
-tokens device -> host every step.  The decode step streams ~15 GB of weights, far
+the next step on the device); ``e2e`` is K steps through the Python entry
+point's engine loop (``Engine.step``: scheduler, the step's metadata host ->
+device from pinned memory, sampled tokens device -> host, every step), half of
+them before and half after the device-timed bracket, because the step time
+drifts upward over the first hundreds of steps at full power.  The decode step streams ~15 GB of weights, far
 more than the 126 MB L2, so no extra flush is needed between timed iterations.
 """
 from __future__ import annotations
@@ -183,7 +185,7 @@ def main() -> int:
     kv_bytes_per_token = L * 2 * nkv * d * es
     P = args.prompt_len
     K_steps, W = args.steps, args.warmup
-    need_new = 1 + W + 2 * K_steps + 2
+    need_new = 1 + W + 2 * K_steps + 6
     if P + need_new > args.context:
         print(f"bench.py: {P} prompt + {need_new} decode tokens exceed the context {args.context}")
         return 2
@@ -251,26 +253,37 @@ def main() -> int:
         b = eng.graphs._bucket_for(n)
         torch.cuda.synchronize()
         t = time.perf_counter()
+        produced = 0
         for _ in range(steps):
             outs = eng.step()
             assert len(outs) == n
+            produced += len(outs)
+        produced += len(eng.drain())                # a step launched ahead belongs to the timed work
         torch.cuda.synchronize()
         dt = time.perf_counter() - t
-        return dt, b.layout.size * 4, n * 4
+        return dt, produced, b.layout.size * 4, n * 4
 
     def decode_point(B, steps, with_e2e):
         eng = make_engine(B)
         reqs = start_requests(eng, B)
         for _ in range(W):
             eng.step()
+        eng.drain()
         assert eng.stats["graph_steps"] >= W, "decode did not run from CUDA graphs"
+        # The step time drifts upward by a few per cent over the first hundreds of steps at full
+        # power, so the end-to-end steps are split: half before the device-timed bracket, half after.
+        e2e_dt = e2e_produced = 0
+        if with_e2e:
+            e2e_dt, e2e_produced, h2d, d2h = e2e_decode(eng, reqs, steps // 2)
         ctx0 = reqs[0].cache.num_tokens
         ms, launches = device_timed_decode(eng, reqs, steps)
         res = {"B": B, "ms_per_step": ms / steps, "tok_s": B * steps / (ms / 1e3), "launches": launches,
                "ctx_mean": ctx0 + steps / 2}
         if with_e2e:
-            dt, h2d, d2h = e2e_decode(eng, reqs, steps)
-            res["e2e"] = {"value": B * steps / dt, "unit": "tok/s", "h2d_bytes_per_step": h2d,
+            dt, produced, h2d, d2h = e2e_decode(eng, reqs, steps - steps // 2)
+            dt, produced = dt + e2e_dt, produced + e2e_produced
+            res["e2e"] = {"value": produced / dt, "unit": "tok/s", "steps": steps,
+                          "steps_launched_ahead": eng.stats["launched_ahead"], "h2d_bytes_per_step": h2d,
                           "d2h_bytes_per_step": d2h}
         eng.runner.check_status()
         del eng
@@ -306,7 +319,8 @@ def main() -> int:
         print(json.dumps({"prefill": prefill_point(), "config": {"layers": L}}))
         return 0
     clocks = ClockSampler()
-    clocks.start()
+    if not os.environ.get("FF_NO_CLOCKS"):
+        clocks.start()
     main_res = decode_point(args.batch, K_steps, with_e2e=True)
     clock_info = clocks.stop()
     prefill = None if args.no_prefill else prefill_point()

@@ -8,6 +8,14 @@ results arrive on a ``ResultQueue`` as (request id, new token ids, is_finished)
 ``max_prefill_chunk_size`` has the reference's meaning and default (256).
 One iteration is ``Engine.step()``: the scheduler picks portions and decode
 tokens, the step function runs them as one batch, the sampler picks next tokens.
+
+Greedy decode steps that run from a CUDA graph are overlapped with the host's work
+(``overlap_decode``): while step n runs, step n+1 for the same requests is put on
+the stream, its input tokens copied on the device from step n's output, and only
+then are step n's tokens read.  The device never waits for the scheduler.  A step
+is launched ahead only when no request of the batch can end by length at step n,
+none waits for admission and every request gets its next page; a request that ends
+at step n by an end-of-sequence token has one more token computed, which is dropped.
 """
 from __future__ import annotations
 
@@ -58,6 +66,14 @@ class ResultQueue:
 
 
 @dataclass
+class _InFlight:
+    """A decode step on the stream whose tokens the host has not read yet."""
+    step: object                            # graphs.LaunchedStep
+    requests: List[GenerationRequest]
+    dropped: List[bool]                     # per lane: the request ended before this step's token
+
+
+@dataclass
 class EngineOptions:
     max_prefill_chunk_size: int = 256       # the reference's --max-prefill-chunk-size
     max_batch_size_limit: int = 64          # most active requests (reference: 64)
@@ -68,6 +84,7 @@ class EngineOptions:
     max_model_len: Optional[int] = None     # None: the model's max positions
     eos_token_ids: Optional[Sequence[int]] = None   # None: config.json's eos_token_id, if any
     use_cuda_graphs: bool = True
+    overlap_decode: bool = True             # launch the next greedy decode step before this one's tokens are read
     graph_batch_sizes: Sequence[int] = (1, 2, 4, 8, 16, 32, 64)   # reference: engine.h:72
 
 
@@ -124,7 +141,9 @@ class Engine:
         self._thread: Optional[threading.Thread] = None
         self._running = False
         self.requests: Dict[str, GenerationRequest] = {}
-        self.stats = {"steps": 0, "graph_steps": 0, "tokens": 0, "preemptions": 0}
+        self.stats = {"steps": 0, "graph_steps": 0, "tokens": 0, "preemptions": 0, "launched_ahead": 0,
+                      "dropped_tokens": 0}
+        self._inflight: Optional[_InFlight] = None
 
     # ---- the reference's interface ----------------------------------------------
     def async_generate(self, id: str, input_ids: Sequence[int], max_tokens: int = 512,
@@ -150,7 +169,7 @@ class Engine:
         torch.cuda.set_device(self.device)
         while self._running:
             self._drain_inbox()
-            if not self.scheduler.has_unfinished_requests():
+            if not self.scheduler.has_unfinished_requests() and self._inflight is None:
                 time.sleep(0.0005)
                 continue
             for out in self.step():
@@ -180,10 +199,71 @@ class Engine:
         self.requests[req.id] = req
 
     def has_unfinished_requests(self) -> bool:
-        return self.scheduler.has_unfinished_requests() or not self._inbox.empty()
+        return (self.scheduler.has_unfinished_requests() or not self._inbox.empty()
+                or self._inflight is not None)
+
+    # ---- decode steps launched ahead ---------------------------------------------------
+    def _can_launch_ahead(self, cur: _InFlight) -> bool:
+        """May the step after ``cur`` go on the stream before ``cur``'s tokens are known?"""
+        sch = self.scheduler
+        if sch.pending_requests or not self._inbox.empty() or any(cur.dropped):
+            return False
+        if len(sch.active_requests) != len(cur.requests) or \
+                any(a is not b for a, b in zip(sch.active_requests, cur.requests)):
+            return False
+        for req in cur.requests:
+            # cur's token makes generated+1 and total+1; the request must go on after it
+            if len(req.generated_tokens) + 1 >= req.max_tokens or req.get_total_len() + 1 >= self.max_model_len:
+                return False
+            if req.sampling.temperature > 0:
+                return False
+        # the next page of every request, all or nothing
+        if not all(self.cache.can_grow(req.cache, req.cache.num_tokens + 1) for req in cur.requests):
+            return False
+        need = [sum(self.cache.pages_needed(req.cache, req.cache.num_tokens + 1)[g] for req in cur.requests)
+                for g in range(len(self.cache.groups))]
+        return all(grp.allocator.num_free >= n for grp, n in zip(self.cache.groups, need))
+
+    def _launch_ahead(self, cur: _InFlight) -> _InFlight:
+        for req in cur.requests:
+            ok = self.cache.grow(req.cache, req.cache.num_tokens + 1)
+            assert ok
+        entries = [StepEntry(req.cache, [0], [0]) for req in cur.requests]     # ids come from cur on the device
+        step = self.graphs.launch(entries, want_tokens=True, tokens_from_last_replay=True)
+        self.stats["graph_steps"] += 1
+        self.stats["launched_ahead"] += 1
+        return _InFlight(step, list(cur.requests), [False] * len(cur.requests))
+
+    def drain(self) -> List[StepOutput]:
+        """Read the tokens of a step that is still on the stream, launching nothing new."""
+        return self._finish_inflight(launch_next=False) if self._inflight is not None else []
+
+    def _finish_inflight(self, launch_next: bool = True) -> List[StepOutput]:
+        """Read the tokens of the step on the stream, after putting the next one there if that
+        is allowed."""
+        cur = self._inflight
+        nxt = self._launch_ahead(cur) if launch_next and self._can_launch_ahead(cur) else None
+        tokens = self.graphs.collect(cur.step)
+        outputs: List[StepOutput] = []
+        self.stats["steps"] += 1
+        for lane, (req, tok) in enumerate(zip(cur.requests, tokens)):
+            if cur.dropped[lane]:
+                self.stats["dropped_tokens"] += 1
+                continue
+            self.stats["tokens"] += 1
+            done = self.scheduler.append_token(req, tok)
+            outputs.append(StepOutput(req.id, [int(tok)], done, req.finish_reason))
+            if done:
+                self.requests.pop(req.id, None)
+                if nxt is not None:
+                    nxt.dropped[lane] = True          # its pages are free again; the stream keeps the order
+        self._inflight = nxt
+        return outputs
 
     def step(self) -> List[StepOutput]:
         """One iteration: returns what each affected request produced."""
+        if self._inflight is not None:
+            return self._finish_inflight()
         batch = self.scheduler.step()
         outputs: List[StepOutput] = []
         for req in batch.failed:
@@ -203,6 +283,11 @@ class Engine:
                 and all(it.num_tokens == 1 for it in batch.items)
                 and self.graphs.supports(len(entries))):
             greedy = all(p.temperature <= 0 for p in params)
+            if greedy and self.options.overlap_decode:
+                self.stats["graph_steps"] += 1
+                self._inflight = _InFlight(self.graphs.launch(entries, want_tokens=True),
+                                           [it.request for it in batch.items], [False] * len(entries))
+                return outputs + self._finish_inflight()
             logits, tokens = self.graphs.run(entries, want_tokens=greedy)
             self.stats["graph_steps"] += 1
         else:
@@ -257,7 +342,7 @@ class LLM:
             self._next_id += 1
             self.engine.add_request(req)
             reqs.append(req)
-        while self.engine.scheduler.has_unfinished_requests():
+        while self.engine.has_unfinished_requests():
             self.engine.step()
         self.engine.runner.check_status()
         for r in reqs:

@@ -24,8 +24,14 @@ from .runner import MetaLayout, ModelRunner, StepEntry
 
 
 class _Bucket:
-    __slots__ = ("size", "layout", "meta_host", "meta_dev", "graph", "logits", "tokens", "h_tokens", "launches",
-                 "lanes")
+    __slots__ = ("size", "layout", "meta_host", "meta_stage", "meta_dev", "graph", "logits", "tokens", "h_tokens",
+                 "events", "launches", "lanes", "turn")
+
+
+class LaunchedStep:
+    """A replay that has been put on the stream: its tokens arrive in ``h_tokens`` once
+    ``event`` has passed."""
+    __slots__ = ("bucket", "n", "h_tokens", "event", "logits")
 
 
 class DecodeGraphs:
@@ -119,9 +125,13 @@ class DecodeGraphs:
         b.size = size
         b.layout = MetaLayout(size, size, size, len(r.cache.groups), r.max_blocks_per_seq)
         b.meta_host = torch.zeros(b.layout.size, dtype=torch.int32).pin_memory()
+        # two of everything the host touches while a replay may still be using the other
+        b.meta_stage = [torch.zeros(b.layout.size, dtype=torch.int32).pin_memory() for _ in range(2)]
         b.meta_dev = torch.zeros(b.layout.size, dtype=torch.int32, device=r.device)
         b.tokens = torch.zeros(size, dtype=torch.int32, device=r.device)
-        b.h_tokens = torch.zeros(size, dtype=torch.int32).pin_memory()
+        b.h_tokens = [torch.zeros(size, dtype=torch.int32).pin_memory() for _ in range(2)]
+        b.events = [torch.cuda.Event() for _ in range(2)]
+        b.turn = 0
         b.lanes = None
         self._fill(b, [])
         b.meta_dev.copy_(b.meta_host)
@@ -147,25 +157,52 @@ class DecodeGraphs:
         b.launches = K.LAUNCHES - before      # own kernels in one replay
         return b
 
+    def launch(self, entries: Sequence[StepEntry], want_tokens: bool = True,
+               tokens_from_last_replay: bool = False) -> LaunchedStep:
+        """Put one decode step for ``entries`` (one token each) on the stream without waiting
+        for it.  With ``tokens_from_last_replay`` the token of lane i is taken, on the device,
+        from what this bucket's previous replay sampled for lane i (the host does not know it
+        yet; the ids in ``entries`` are placeholders).  At most two launched steps of a bucket may
+        be outstanding."""
+        n = len(entries)
+        b = self._bucket_for(n)
+        self._fill(b, entries)
+        k = b.turn
+        b.turn ^= 1
+        stage = b.meta_stage[k]
+        stage.copy_(b.meta_host)
+        b.meta_dev.copy_(stage, non_blocking=True)
+        if tokens_from_last_replay:
+            lay = b.layout
+            b.meta_dev[lay.token_ids: lay.token_ids + n].copy_(b.tokens[:n], non_blocking=True)
+        b.graph.replay()
+        self.replays += 1
+        self.kernel_launches += b.launches
+        step = LaunchedStep()
+        step.bucket, step.n, step.logits = b, n, b.logits[:n]
+        step.h_tokens, step.event = None, None
+        if want_tokens:
+            step.h_tokens = b.h_tokens[k]
+            step.h_tokens[:n].copy_(b.tokens[:n], non_blocking=True)
+            step.event = b.events[k]
+            step.event.record()
+        for e in entries:
+            self.runner.cache.advance(e.cache, 1)
+        self.runner.steps_run += 1
+        return step
+
+    @staticmethod
+    def collect(step: LaunchedStep) -> Optional[List[int]]:
+        """Wait for a launched step; its arg-max tokens (None if they were not asked for)."""
+        if step.event is None:
+            return None
+        step.event.synchronize()
+        return step.h_tokens[:step.n].tolist()
+
     def run(self, entries: Sequence[StepEntry], want_tokens: bool = True
             ) -> Tuple[torch.Tensor, Optional[List[int]]]:
         """One decode step for ``entries`` (one token each).  Returns the logits
         [n, vocab] (valid until the next replay of this bucket) and, when asked,
         the arg-max tokens already copied to the host."""
-        n = len(entries)
-        b = self._bucket_for(n)
-        self._fill(b, entries)
-        b.meta_dev.copy_(b.meta_host, non_blocking=True)
-        b.graph.replay()
-        self.replays += 1
-        self.kernel_launches += b.launches
-        tokens = None
-        if want_tokens:
-            b.h_tokens[:n].copy_(b.tokens[:n], non_blocking=True)
-            torch.cuda.current_stream().synchronize()
-            tokens = b.h_tokens[:n].tolist()
-        for e in entries:
-            r_cache = e.cache
-            self.runner.cache.advance(r_cache, 1)
-        self.runner.steps_run += 1
-        return b.logits[:n], tokens
+        step = self.launch(entries, want_tokens)
+        return step.logits, self.collect(step)

@@ -140,3 +140,69 @@ def test_async_engine_interface(models):
     eng.stop()
     assert toks["x"] == P.greedy_generate(cfg, w, [3, 1, 4, 1, 5, 9, 2, 6, 5, 3, 5], 6)
     assert toks["y"] == P.greedy_generate(cfg, w, [2, 7], 4)
+
+
+def test_decode_steps_launched_ahead_give_the_same_tokens(models):
+    """Greedy decode steps are put on the stream before the step before them has been read.
+    Requests of different lengths end at different steps, some by an end-of-sequence token
+    that the engine learns of one step late: the tokens are those of the plain implementation
+    (cut at the end-of-sequence token), with and without the overlap."""
+    from firefly_b200 import SamplingParams
+    path, cfg, w = models["A"]
+    rng = np.random.RandomState(11)
+    prompts = [list(map(int, rng.randint(0, cfg["vocab_size"], size=n))) for n in (5, 19, 3, 33)]
+    limits = [25, 9, 17, 25]
+    plain = [P.greedy_generate(cfg, w, p, m) for p, m in zip(prompts, limits)]
+    first = {}
+    for i, t in enumerate(plain[0]):
+        first.setdefault(t, i)
+    eos = max(first, key=first.get)                     # request 0 ends by end of sequence, some steps in
+    assert 3 <= first[eos] < limits[0] - 1
+
+    def cut(toks):
+        return toks[:toks.index(eos) + 1] if eos in toks else toks
+    want = [cut(t) for t in plain]
+    assert len(want[0]) < limits[0]
+    results = {}
+    for overlap in (True, False):
+        llm = _llm(path, dtype="float32", num_kv_blocks=64, overlap_decode=overlap, eos_token_ids=[eos])
+        got = llm.generate(prompts, sampling=[SamplingParams(max_tokens=m) for m in limits])
+        assert got == want
+        st = llm.engine.stats
+        if overlap:
+            assert st["launched_ahead"] > 0
+            # alone, request 0 is ahead by one step when its end-of-sequence token is read
+            before = st["dropped_tokens"]
+            assert llm.generate([prompts[0]], max_tokens=limits[0]) == [want[0]]
+            assert llm.engine.stats["dropped_tokens"] == before + 1
+        else:
+            assert st["launched_ahead"] == 0
+        llm.engine.cache.check()
+        assert not llm.engine.cache.live and llm.engine._inflight is None
+        results[overlap] = got
+    assert results[True] == results[False]
+
+
+def test_launch_ahead_stops_for_new_requests_and_scarce_pages(models):
+    """A waiting request, or a batch whose next pages are not all free, is left to the scheduler."""
+    from firefly_b200 import Engine, SamplingParams
+    from firefly_b200.engine import load_model
+    from firefly_b200.engine.engine import EngineOptions
+    from firefly_b200.engine.request import GenerationRequest
+    path, cfg, w = models["B"]
+    model, config = load_model(path, dtype="float32")
+    eng = Engine(model, config, options=EngineOptions(kv_block_size=8, num_kv_blocks=12, max_prefill_chunk_size=16))
+    a, b = [3, 1, 4, 1, 5, 9, 2, 6], [2, 7, 1, 8, 2, 8]
+    ra = GenerationRequest("a", a, SamplingParams(max_tokens=40))
+    eng.add_request(ra)
+    for _ in range(4):
+        eng.step()
+    assert eng.stats["launched_ahead"] > 0
+    rb = GenerationRequest("b", b, SamplingParams(max_tokens=30))
+    eng.add_request(rb)                                 # arrives while a step of "a" is on the stream
+    while eng.has_unfinished_requests():
+        eng.step()
+    assert ra.generated_tokens == P.greedy_generate(cfg, w, a, 40)
+    assert rb.generated_tokens == P.greedy_generate(cfg, w, b, 30)
+    eng.cache.check()
+    assert not eng.cache.live
