@@ -100,19 +100,24 @@ __device__ __forceinline__ void tma_2d(uint32_t dst, const void* map, int x, int
 }
 __device__ __forceinline__ void tc_before() { asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory"); }
 __device__ __forceinline__ void tc_after() { asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory"); }
-__device__ __forceinline__ void tc_commit_to(uint32_t bar) {
-    asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(bar) : "memory");
+__device__ __forceinline__ void tc_commit_to(bool issue, uint32_t bar) {
+    asm volatile("{\n\t.reg .pred q;\n\tsetp.ne.b32 q, %1, 0;\n\t"
+                 "@q tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];\n\t}"
+                 ::"r"(bar), "r"((uint32_t)issue) : "memory");
 }
-__device__ __forceinline__ void tc_mma(uint32_t d_tmem, uint64_t da, uint64_t db, uint32_t idesc, uint32_t acc) {
-    asm volatile("{\n\t.reg .pred p;\n\tsetp.ne.b32 p, %4, 0;\n\t"
-                 "tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n\t}"
-                 ::"r"(d_tmem), "l"(da), "l"(db), "r"(idesc), "r"(acc) : "memory");
+// The MMA warp runs its loop with all lanes (so that descriptors and addresses are warp-uniform values);
+// `issue` is true in the one lane that really issues the instruction.
+__device__ __forceinline__ void tc_mma(bool issue, uint32_t d_tmem, uint64_t da, uint64_t db, uint32_t idesc, uint32_t acc) {
+    asm volatile("{\n\t.reg .pred p, q;\n\tsetp.ne.b32 p, %4, 0;\n\tsetp.ne.b32 q, %5, 0;\n\t"
+                 "@q tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n\t}"
+                 ::"r"(d_tmem), "l"(da), "l"(db), "r"(idesc), "r"(acc), "r"((uint32_t)issue) : "memory");
 }
 // the same with the A operand (128 x 16 bfloat16, two to a 32-bit cell, 8 columns) in tensor memory
-__device__ __forceinline__ void tc_mma_a_tmem(uint32_t d_tmem, uint32_t a_tmem, uint64_t db, uint32_t idesc, uint32_t acc) {
-    asm volatile("{\n\t.reg .pred p;\n\tsetp.ne.b32 p, %4, 0;\n\t"
-                 "tcgen05.mma.cta_group::1.kind::f16 [%0], [%1], %2, %3, p;\n\t}"
-                 ::"r"(d_tmem), "r"(a_tmem), "l"(db), "r"(idesc), "r"(acc) : "memory");
+__device__ __forceinline__ void tc_mma_a_tmem(bool issue, uint32_t d_tmem, uint32_t a_tmem, uint64_t db, uint32_t idesc,
+                                              uint32_t acc) {
+    asm volatile("{\n\t.reg .pred p, q;\n\tsetp.ne.b32 p, %4, 0;\n\tsetp.ne.b32 q, %5, 0;\n\t"
+                 "@q tcgen05.mma.cta_group::1.kind::f16 [%0], [%1], %2, %3, p;\n\t}"
+                 ::"r"(d_tmem), "r"(a_tmem), "l"(db), "r"(idesc), "r"(acc), "r"((uint32_t)issue) : "memory");
 }
 __device__ __forceinline__ void tm_ld16(uint32_t taddr, float (&v)[16]) {
     uint32_t r[16];
@@ -206,7 +211,9 @@ attn_tc_kernel(const __grid_constant__ TensorMapArg kv_map, const bf16* __restri
     __shared__ uint32_t s_tmem;
     const int G = nq / nkv;
     const int kh = (int)(blockIdx.x % (unsigned)nkv);
-    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    // the warp index through a shuffle, so that the compiler knows it to be the same in the whole warp and
+    // keeps the address arithmetic of the single-thread roles in uniform registers
+    const int warp = __shfl_sync(0xffffffffu, (int)(threadIdx.x >> 5), 0), lane = threadIdx.x & 31;
     volatile int* abort_flag = &s_abort;
 
     if (threadIdx.x == 0) {
@@ -454,26 +461,29 @@ attn_tc_kernel(const __grid_constant__ TensorMapArg kv_map, const bf16* __restri
             if (j + 1 < n_tiles) ok = load_tile(j + 1, 0);
             if (ok) ok = load_tile(j, 1);
         }
-    } else if (warp == 5 && lane == 0) {
+    } else if (warp == 5) {
         // ------------------------------------------------ MMAs -----------------
         const uint32_t idesc_qk = idesc_bf16(BN, false);
         const uint32_t idesc_pv = idesc_bf16(D, true);
+        const bool issue = lane == 0;                               // always the same lane: commits follow its MMAs
         bool ok = n_tiles == 0 || mb_wait(sa(&bars[B_Q_READY]), 0, status, abort_flag);
+        ok = __all_sync(0xffffffffu, ok);
         tc_after();
         // S(j) = Q K(j)^T over D in steps of 16, into S buffer j & 1
         auto issue_qk = [&](int j) -> bool {
             const int s = j % KV_STAGES;
-            if (!mb_wait(sa(&bars[B_K_FULL + s]), (j / KV_STAGES) & 1, status, abort_flag)) return false;
+            if (!__all_sync(0xffffffffu, mb_wait(sa(&bars[B_K_FULL + s]), (j / KV_STAGES) & 1, status, abort_flag))) return false;
             tc_after();
             const uint32_t ks = sa(Ks + (size_t)s * KV_TILE_BYTES);
 #pragma unroll
             for (int k = 0; k < D / 16; ++k) {
                 const uint64_t da = desc_k_major(sa(Qs) + (k >> 2) * (BM * 128) + (k & 3) * 32);
                 const uint64_t db = desc_k_major(ks + (k >> 2) * (BN * 128) + (k & 3) * 32);
-                tc_mma(tm_S + (uint32_t)((j & 1) * BN), da, db, idesc_qk, k > 0 ? 1u : 0u);
+                tc_mma(issue, tm_S + (uint32_t)((j & 1) * BN), da, db, idesc_qk, k > 0 ? 1u : 0u);
             }
-            tc_commit_to(sa(&bars[B_S_FULL + (j & 1)]));
-            tc_commit_to(sa(&bars[B_K_EMPTY + s]));
+            tc_commit_to(issue, sa(&bars[B_S_FULL + (j & 1)]));
+            tc_commit_to(issue, sa(&bars[B_K_EMPTY + s]));
+            __syncwarp();
             return true;
         };
         if (ok && n_tiles > 0) ok = issue_qk(0);
@@ -485,19 +495,20 @@ attn_tc_kernel(const __grid_constant__ TensorMapArg kv_map, const bf16* __restri
             }
             const int s = j % KV_STAGES;
             // O += P V over the 64 keys in steps of 16, once the softmax warps have written P
-            ok = mb_wait(sa(&bars[B_P_FULL + (j & 1)]), (j >> 1) & 1, status, abort_flag);
+            ok = __all_sync(0xffffffffu, mb_wait(sa(&bars[B_P_FULL + (j & 1)]), (j >> 1) & 1, status, abort_flag));
             if (!ok) break;
-            ok = mb_wait(sa(&bars[B_V_FULL + s]), (j / KV_STAGES) & 1, status, abort_flag);
+            ok = __all_sync(0xffffffffu, mb_wait(sa(&bars[B_V_FULL + s]), (j / KV_STAGES) & 1, status, abort_flag));
             if (!ok) break;
             tc_after();
             const uint32_t vs = sa(Vs + (size_t)s * KV_TILE_BYTES);
 #pragma unroll
             for (int k = 0; k < BN / 16; ++k) {
                 const uint64_t db = desc_n_major(vs + k * 16 * 128, BN * 128);
-                tc_mma_a_tmem(tm_O, tm_S + (uint32_t)((j & 1) * BN + k * 8), db, idesc_pv, (j > 0 || k > 0) ? 1u : 0u);
+                tc_mma_a_tmem(issue, tm_O, tm_S + (uint32_t)((j & 1) * BN + k * 8), db, idesc_pv, (j > 0 || k > 0) ? 1u : 0u);
             }
-            tc_commit_to(sa(&bars[B_PV_DONE]));
-            tc_commit_to(sa(&bars[B_V_EMPTY + s]));
+            tc_commit_to(issue, sa(&bars[B_PV_DONE]));
+            tc_commit_to(issue, sa(&bars[B_V_EMPTY + s]));
+            __syncwarp();
         }
     }
     tc_before();

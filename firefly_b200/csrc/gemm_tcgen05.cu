@@ -68,8 +68,12 @@ __device__ __forceinline__ uint32_t smem_addr(const void* p) { return (uint32_t)
 __device__ __forceinline__ void mbar_init(uint32_t bar, uint32_t count) {
     asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(bar), "r"(count));
 }
-__device__ __forceinline__ void mbar_expect_tx(uint32_t bar, uint32_t bytes) {
-    asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(bar), "r"(bytes) : "memory");
+// The producer and MMA warps run their loops with all lanes, so that addresses and descriptors are
+// warp-uniform values (kept in uniform registers); `issue` is true in the one lane that acts.
+__device__ __forceinline__ void mbar_expect_tx(bool issue, uint32_t bar, uint32_t bytes) {
+    asm volatile("{\n\t.reg .pred q;\n\tsetp.ne.b32 q, %2, 0;\n\t"
+                 "@q mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;\n\t}"
+                 ::"r"(bar), "r"(bytes), "r"((uint32_t)issue) : "memory");
 }
 __device__ __forceinline__ bool mbar_try_wait(uint32_t bar, uint32_t parity) {
     uint32_t ok;
@@ -95,20 +99,23 @@ __device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, int* st
     }
     return true;
 }
-__device__ __forceinline__ void tma_load_2d(uint32_t dst, const CUtensorMap* map, int x, int y, uint32_t bar) {
-    asm volatile("cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4}], [%2];"
-                 ::"r"(dst), "l"(map), "r"(bar), "r"(x), "r"(y) : "memory");
+__device__ __forceinline__ void tma_load_2d(bool issue, uint32_t dst, const CUtensorMap* map, int x, int y, uint32_t bar) {
+    asm volatile("{\n\t.reg .pred q;\n\tsetp.ne.b32 q, %5, 0;\n\t"
+                 "@q cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4}], [%2];\n\t}"
+                 ::"r"(dst), "l"(map), "r"(bar), "r"(x), "r"(y), "r"((uint32_t)issue) : "memory");
 }
 __device__ __forceinline__ void tc_fence_before() { asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory"); }
 __device__ __forceinline__ void tc_fence_after() { asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory"); }
-__device__ __forceinline__ void tc_commit(uint32_t bar) {
-    asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(bar) : "memory");
+__device__ __forceinline__ void tc_commit(bool issue, uint32_t bar) {
+    asm volatile("{\n\t.reg .pred q;\n\tsetp.ne.b32 q, %1, 0;\n\t"
+                 "@q tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];\n\t}"
+                 ::"r"(bar), "r"((uint32_t)issue) : "memory");
 }
-__device__ __forceinline__ void tc_mma_bf16(uint32_t tmem_d, uint64_t desc_a, uint64_t desc_b, uint32_t idesc,
+__device__ __forceinline__ void tc_mma_bf16(bool issue, uint32_t tmem_d, uint64_t desc_a, uint64_t desc_b, uint32_t idesc,
                                             uint32_t accumulate) {
-    asm volatile("{\n\t.reg .pred p;\n\tsetp.ne.b32 p, %4, 0;\n\t"
-                 "tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n\t}"
-                 ::"r"(tmem_d), "l"(desc_a), "l"(desc_b), "r"(idesc), "r"(accumulate) : "memory");
+    asm volatile("{\n\t.reg .pred p, q;\n\tsetp.ne.b32 p, %4, 0;\n\tsetp.ne.b32 q, %5, 0;\n\t"
+                 "@q tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n\t}"
+                 ::"r"(tmem_d), "l"(desc_a), "l"(desc_b), "r"(idesc), "r"(accumulate), "r"((uint32_t)issue) : "memory");
 }
 // 16 consecutive accumulator columns of this warp's 32 lanes
 __device__ __forceinline__ void tc_ld16(uint32_t taddr, float (&v)[16]) {
@@ -181,7 +188,9 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant_
     __shared__ float s_inv[256];          // 1/rms per token of the tile (norm folded in, consuming side)
     __shared__ float s_red[4][16];        // per-warp sums of squares (producing side)
 
-    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    // the warp index through a shuffle: the compiler then knows it to be the same in the whole warp
+    const int warp = __shfl_sync(0xffffffffu, (int)(threadIdx.x >> 5), 0), lane = threadIdx.x & 31;
+    const bool issue = lane == 0;
     const int n0 = blockIdx.x * BN, t0 = blockIdx.y * TOK;
     const int num_kb = (a.K + BK - 1) / BK;
     const int kb0 = blockIdx.z * a.kb_per_split;
@@ -205,7 +214,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant_
     volatile int* abort_flag = &s_abort;
     grid_launch_dependents();
 
-    if (warp == 0 && lane == 0) {
+    if (warp == 0) {
         // ------------------------------------------------ producer: TMA loads --
         // The weights do not depend on the kernel before this one: the first stages' weight
         // tiles are requested at once; the activations only after that kernel has finished.
@@ -213,24 +222,24 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant_
         const int pre = min(n_iters, STAGES);
         for (int it = 0; it < pre; ++it) {
             const uint32_t full = smem_addr(&bars[it]);
-            mbar_expect_tx(full, Cfg::STAGE_BYTES);
-            tma_load_2d(smem_addr(tiles + (size_t)it * Cfg::STAGE_BYTES), &map_w, (kb0 + it) * BK, n0, full);
+            mbar_expect_tx(issue, full, Cfg::STAGE_BYTES);
+            tma_load_2d(issue, smem_addr(tiles + (size_t)it * Cfg::STAGE_BYTES), &map_w, (kb0 + it) * BK, n0, full);
         }
         grid_dependency_wait();
         for (int it = 0; it < pre; ++it) {
-            tma_load_2d(smem_addr(tiles + (size_t)it * Cfg::STAGE_BYTES + Cfg::A_BYTES), &map_x, (kb0 + it) * BK, t0,
+            tma_load_2d(issue, smem_addr(tiles + (size_t)it * Cfg::STAGE_BYTES + Cfg::A_BYTES), &map_x, (kb0 + it) * BK, t0,
                         smem_addr(&bars[it]));
             issued = it + 1;
         }
         for (int it = pre; it < n_iters; ++it) {
             const int s = it % STAGES;
             const uint32_t ph = (it / STAGES) & 1;
-            if (!mbar_wait(smem_addr(&bars[STAGES + s]), ph ^ 1, a.status, abort_flag, 101)) break;
+            if (!__all_sync(0xffffffffu, mbar_wait(smem_addr(&bars[STAGES + s]), ph ^ 1, a.status, abort_flag, 101))) break;
             const uint32_t full = smem_addr(&bars[s]);
-            mbar_expect_tx(full, Cfg::STAGE_BYTES);
+            mbar_expect_tx(issue, full, Cfg::STAGE_BYTES);
             unsigned char* st = tiles + (size_t)s * Cfg::STAGE_BYTES;
-            tma_load_2d(smem_addr(st), &map_w, (kb0 + it) * BK, n0, full);
-            tma_load_2d(smem_addr(st + Cfg::A_BYTES), &map_x, (kb0 + it) * BK, t0, full);
+            tma_load_2d(issue, smem_addr(st), &map_w, (kb0 + it) * BK, n0, full);
+            tma_load_2d(issue, smem_addr(st + Cfg::A_BYTES), &map_x, (kb0 + it) * BK, t0, full);
             issued = it + 1;
         }
         if (*abort_flag) {
@@ -241,14 +250,14 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant_
                     if (clock64() - start > WAIT_LIMIT_CYCLES) break;
             }
         }
-    } else if (warp == 1 && lane == 0) {
+    } else if (warp == 1) {
         // ------------------------------------------------ MMA issuer ----------
         const uint32_t idesc = instr_desc(TOK);
         bool ok = true;
         for (int it = 0; it < n_iters && ok; ++it) {
             const int s = it % STAGES;
             const uint32_t ph = (it / STAGES) & 1;
-            ok = mbar_wait(smem_addr(&bars[s]), ph, a.status, abort_flag, 102);
+            ok = __all_sync(0xffffffffu, mbar_wait(smem_addr(&bars[s]), ph, a.status, abort_flag, 102));
             if (!ok) break;
             tc_fence_after();
             const uint32_t sa = smem_addr(tiles + (size_t)s * Cfg::STAGE_BYTES);
@@ -257,11 +266,12 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant_
             for (int k = 0; k < BK / UMMA_K; ++k) {
                 const uint64_t da = smem_desc_sw128(sa + k * UMMA_K * 2);
                 const uint64_t db = smem_desc_sw128(sb + k * UMMA_K * 2);
-                tc_mma_bf16(tmem_base, da, db, idesc, (it > 0 || k > 0) ? 1u : 0u);
+                tc_mma_bf16(issue, tmem_base, da, db, idesc, (it > 0 || k > 0) ? 1u : 0u);
             }
-            tc_commit(smem_addr(&bars[STAGES + s]));      // stage free when these MMAs have read it
+            tc_commit(issue, smem_addr(&bars[STAGES + s]));      // stage free when these MMAs have read it
+            __syncwarp();
         }
-        tc_commit(smem_addr(&bars[2 * STAGES]));          // accumulator complete
+        tc_commit(issue, smem_addr(&bars[2 * STAGES]));          // accumulator complete
     } else if (warp >= 2) {
         // ------------------------------------------------ epilogue ------------
         const int quad = warp & 3;                              // this warp's 32 lanes of tensor memory
