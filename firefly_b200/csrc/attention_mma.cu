@@ -447,26 +447,45 @@ attn_decode_kernel(const bf16* __restrict__ q, int q_stride, const bf16* __restr
     }
 }
 
-// out[token of seq, head, :] = sum_s w_s o_s / sum_s w_s l_s,  w_s = 2^(m_s - max m)
+// out[token of seq, head, :] = sum_s w_s o_s / sum_s w_s l_s,  w_s = 2^(m_s - max m).
+// The splits are taken eight at a time, all their loads issued before the first is used (one
+// trip to memory for up to eight splits), with a running maximum over the groups of eight.
 __global__ void attn_combine_kernel(const float* __restrict__ part_o, const float* __restrict__ part_ml,
                                     const int* __restrict__ cu_q, bf16* __restrict__ out, int out_stride,
                                     int nq, int num_splits) {
     pdl_prologue();
     const int seq = blockIdx.x, head = blockIdx.y;
     const size_t base = ((size_t)seq * nq + head) * num_splits;
-    float M = -CUDART_INF_F;
-    for (int s = 0; s < num_splits; ++s) M = fmaxf(M, part_ml[(base + s) * 2]);
-    float L = 0.f;
-    for (int s = 0; s < num_splits; ++s) {
-        const float ms = part_ml[(base + s) * 2];
-        if (ms != -CUDART_INF_F) L += exp2f(ms - M) * part_ml[(base + s) * 2 + 1];
-    }
     const int tok = cu_q[seq];
     for (int col = threadIdx.x; col < D; col += blockDim.x) {
-        float O = 0.f;
-        for (int s = 0; s < num_splits; ++s) {
-            const float ms = part_ml[(base + s) * 2];
-            if (ms != -CUDART_INF_F) O += exp2f(ms - M) * part_o[(base + s) * D + col];
+        float M = -CUDART_INF_F, L = 0.f, O = 0.f;
+        for (int s0 = 0; s0 < num_splits; s0 += 8) {
+            float ms[8], ls[8], os[8];
+#pragma unroll
+            for (int k = 0; k < 8; ++k) {
+                const bool have = s0 + k < num_splits;
+                const size_t p = base + min(s0 + k, num_splits - 1);
+                ms[k] = part_ml[p * 2];
+                ls[k] = part_ml[p * 2 + 1];
+                os[k] = part_o[p * D + col];
+                if (!have) ms[k] = -CUDART_INF_F;
+            }
+            float Mn = M;
+#pragma unroll
+            for (int k = 0; k < 8; ++k) Mn = fmaxf(Mn, ms[k]);
+            if (Mn == -CUDART_INF_F) continue;                     // no key in any split so far
+            const float r = M == -CUDART_INF_F ? 0.f : exp2f(M - Mn);
+            L *= r;
+            O *= r;
+#pragma unroll
+            for (int k = 0; k < 8; ++k) {
+                if (ms[k] != -CUDART_INF_F) {
+                    const float w = exp2f(ms[k] - Mn);
+                    L += w * ls[k];
+                    O += w * os[k];
+                }
+            }
+            M = Mn;
         }
         out[(size_t)tok * out_stride + (size_t)head * D + col] = __float2bfloat16_rn(O / L);
     }
