@@ -348,7 +348,10 @@ attn_decode_kernel(const bf16* __restrict__ q, int q_stride, const bf16* __restr
                    const int* __restrict__ ctx_lens, bf16* __restrict__ out, int out_stride,
                    float* __restrict__ part_o, float* __restrict__ part_ml, int nq, int nkv,
                    int block_size, int num_blocks, float scale_log2, int window, int num_splits) {
-    pdl_prologue();
+    // The kernel in front of this one (per-head norm, rotation, cache write) produces q and the
+    // newest key and value only.  The step's metadata and every older key do not depend on it: they
+    // are fetched before the wait for that kernel, so the first tile is on its way when it ends.
+    asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
     extern __shared__ __align__(16) unsigned char smem_raw[];
     bf16* Qs = reinterpret_cast<bf16*>(smem_raw);                 // [16][KSTR]
     bf16* Ks = Qs + 16 * KSTR;                                    // [2][BN][KSTR]
@@ -365,12 +368,6 @@ attn_decode_kernel(const bf16* __restrict__ q, int q_stride, const bf16* __restr
     const int per = (t1 - t0 + num_splits - 1) / num_splits;
     const int t_begin = t0 + split * per, t_end = min(t1, t_begin + per);
 
-    for (int c = threadIdx.x; c < 16 * CHUNKS; c += NTHREADS) {
-        const int r = c / CHUNKS, ch = c % CHUNKS;
-        const bool ok = r < G;
-        const bf16* src = ok ? q + (size_t)tok * q_stride + (size_t)(kh * G + r) * D + ch * 8 : q;
-        cp_async16(Qs + r * KSTR + ch * 8, src, ok);
-    }
     const size_t v_off = (size_t)nkv * block_size * D;
     __shared__ long long s_row_off[2][BN];
     if (t_begin < t_end)
@@ -378,7 +375,16 @@ attn_decode_kernel(const bf16* __restrict__ q, int q_stride, const bf16* __restr
     if (t_begin + 1 < t_end)
         kv_row_offsets(s_row_off[1], bt, max_blocks, num_blocks, nkv, kh, block_size, (t_begin + 1) * BN, kv_lo, kv_hi);
     __syncthreads();
-    if (t_begin < t_end) load_kv_tile(Ks, Vs, cache, s_row_off[0], v_off);
+    const bool early = t_begin < t_end && (t_begin + 1) * BN <= pos;   // the first tile ends before the newest key
+    if (early) load_kv_tile(Ks, Vs, cache, s_row_off[0], v_off);
+    asm volatile("griddepcontrol.wait;" ::: "memory");
+    for (int c = threadIdx.x; c < 16 * CHUNKS; c += NTHREADS) {
+        const int r = c / CHUNKS, ch = c % CHUNKS;
+        const bool ok = r < G;
+        const bf16* src = ok ? q + (size_t)tok * q_stride + (size_t)(kh * G + r) * D + ch * 8 : q;
+        cp_async16(Qs + r * KSTR + ch * 8, src, ok);
+    }
+    if (!early && t_begin < t_end) load_kv_tile(Ks, Vs, cache, s_row_off[0], v_off);
     cp_async_commit();
 
     int lo[2] = {kv_lo, kv_lo}, hi[2] = {kv_hi, kv_hi};
