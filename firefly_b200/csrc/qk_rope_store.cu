@@ -53,7 +53,7 @@ __global__ void qk_norm_rope_store_kernel(
     T* dst = src;
     if (kind != 0) {
         const int seq = token_seq[t];
-        const int page = block_table[(size_t)seq * max_blocks + pos / block_size];
+        const int page = (pos >= 0 && pos / block_size < max_blocks) ? block_table[(size_t)seq * max_blocks + pos / block_size] : -1;
         if (page < 0 || page >= num_blocks) {
             if (lane == 0) atomicExch(status, 2);
             return;
@@ -91,17 +91,42 @@ __global__ void qk_norm_rope_store_vec_kernel(
     const int* __restrict__ positions, const int* __restrict__ token_seq,
     const int* __restrict__ block_table, int max_blocks, int block_size, int num_blocks,
     bf16* __restrict__ cache, int* __restrict__ status) {
-    pdl_prologue();
+    // Only the projection's output depends on the kernel in front: position, page, norm weights,
+    // cosines and sines are fetched before the wait for it.
+    asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
     constexpr int HALF = 32 * C, d = 64 * C;
     const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
     const int heads = nq + 2 * nkv;
     const long long item = (long long)blockIdx.x * QKR_WARPS + warp;
-    if (item >= (long long)T_tokens * heads) return;
-    const int t = (int)(item / heads), hh = (int)(item % heads);
+    const bool active = item < (long long)T_tokens * heads;
+    const int t = active ? (int)(item / heads) : 0, hh = active ? (int)(item % heads) : 0;
     bf16* src = qkv + (size_t)t * row_width + (size_t)hh * d;
     const int kind = hh < nq ? 0 : (hh < nq + nkv ? 1 : 2);  // q, k, v
     const int pos = positions[t];
     const int e0 = lane * C;                                  // this lane's first element of each half
+    const float* nw = kind == 0 ? q_norm_w : (kind == 1 ? k_norm_w : nullptr);
+    float wl[C], wh[C], cs_c[C], cs_s[C];
+#pragma unroll
+    for (int j = 0; j < C; ++j) {
+        wl[j] = nw ? nw[e0 + j] : 1.f;
+        wh[j] = nw ? nw[HALF + e0 + j] : 1.f;
+    }
+    int page = 0;
+    if (kind != 0) page = (pos >= 0 && pos / block_size < max_blocks) ? block_table[(size_t)token_seq[t] * max_blocks + pos / block_size] : -1;
+    const bool rotate = kind != 2 && cos_sin != nullptr;
+    const bool pos_ok = pos >= 0 && pos < max_positions;
+#pragma unroll
+    for (int j = 0; j < C; ++j) {
+        cs_c[j] = 1.f;
+        cs_s[j] = 0.f;
+        if (rotate && pos_ok) {
+            const float* cs = cos_sin + (size_t)pos * d + 2 * (e0 + j);  // [half][2]
+            cs_c[j] = cs[0];
+            cs_s[j] = cs[1];
+        }
+    }
+    asm volatile("griddepcontrol.wait;" ::: "memory");
+    if (!active) return;
 
     float lo[C], hi[C];
     {
@@ -116,7 +141,6 @@ __global__ void qk_norm_rope_store_vec_kernel(
 #pragma unroll
         for (int j = 0; j < C; ++j) { lo[j] = __bfloat162float(a[j]); hi[j] = __bfloat162float(b[j]); }
     }
-    const float* nw = kind == 0 ? q_norm_w : (kind == 1 ? k_norm_w : nullptr);
     if (nw) {
         float ss = 0.f;
 #pragma unroll
@@ -125,14 +149,12 @@ __global__ void qk_norm_rope_store_vec_kernel(
         const float inv = 1.0f / sqrtf(ss / (float)d + eps);
 #pragma unroll
         for (int j = 0; j < C; ++j) {
-            lo[j] = lo[j] * inv * nw[e0 + j];
-            hi[j] = hi[j] * inv * nw[HALF + e0 + j];
+            lo[j] = lo[j] * inv * wl[j];
+            hi[j] = hi[j] * inv * wh[j];
         }
     }
     bf16* dst = src;
     if (kind != 0) {
-        const int seq = token_seq[t];
-        const int page = block_table[(size_t)seq * max_blocks + pos / block_size];
         if (page < 0 || page >= num_blocks) {
             if (lane == 0) atomicExch(status, 2);
             return;
@@ -140,18 +162,16 @@ __global__ void qk_norm_rope_store_vec_kernel(
         const int kh = kind == 1 ? hh - nq : hh - nq - nkv;
         dst = cache + ((((size_t)page * 2 + (kind == 2)) * nkv + kh) * block_size + pos % block_size) * d;
     }
-    if (kind != 2 && cos_sin) {
-        if (pos < 0 || pos >= max_positions) {
+    if (rotate) {
+        if (!pos_ok) {
             if (lane == 0) atomicExch(status, 3);
             return;
         }
-        const float* cs = cos_sin + (size_t)pos * d + 2 * e0;  // [half][2]
 #pragma unroll
         for (int j = 0; j < C; ++j) {
-            const float c = cs[2 * j], s = cs[2 * j + 1];
             const float a = lo[j], b = hi[j];
-            lo[j] = a * c - b * s;
-            hi[j] = b * c + a * s;
+            lo[j] = a * cs_c[j] - b * cs_s[j];
+            hi[j] = b * cs_c[j] + a * cs_s[j];
         }
     }
     __align__(8) bf16 a[C], b[C];
