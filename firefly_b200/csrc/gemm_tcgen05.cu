@@ -214,6 +214,10 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant_
     volatile int* abort_flag = &s_abort;
     grid_launch_dependents();
 
+    // what the epilogue adds to (the residual's values of this block's first 16 tokens) and the norm
+    // weight of its row, fetched by the epilogue warps while the main loop runs
+    float res_pre[16];
+    float wn_pre = 0.f;
     if (warp == 0) {
         // ------------------------------------------------ producer: TMA loads --
         // The weights do not depend on the kernel before this one: the first stages' weight
@@ -292,6 +296,22 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant_
                 }
                 s_inv[c] = 1.0f / sqrtf(ss / (float)a.norm_dim + a.norm_eps);
             }
+        }
+        if (a.epilogue == EPI_RESIDUAL_ADD) {
+            grid_dependency_wait();                             // the residual may still be in use by the kernel before
+            int c_begin = 0, c_end = TOK;
+            if (a.splits > 1) {
+                const int per = (TOK + a.splits - 1) / a.splits;
+                c_begin = min(TOK, (int)blockIdx.z * per);
+                c_end = min(TOK, c_begin + per);
+            }
+#pragma unroll
+            for (int i = 0; i < 16; ++i) {
+                const int t = t0 + c_begin + i;
+                res_pre[i] = (c_begin + i < c_end && t < a.T && n < a.N)
+                                 ? __ldcg(reinterpret_cast<const float*>(a.out) + (size_t)t * a.ldo + n) : 0.f;
+            }
+            if (a.xw_out && n < a.N) wn_pre = __ldg(a.xw_w + n);
         }
         if (n_iters > 0) ok = mbar_wait(smem_addr(&bars[2 * STAGES]), 0, a.status, abort_flag, 103);
         ok = __all_sync(0xffffffffu, ok);                       // the tensor-memory loads below are warp-wide
@@ -381,7 +401,8 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant_
                 }
             } else if (a.epilogue == EPI_RESIDUAL_ADD && a.xw_out) {
                 // out += acc; and for the norm that follows: bfloat16(out * w) and this tile's sums of squares
-                const float wn = n < a.N ? __ldg(a.xw_w + n) : 0.f;
+                const float wn = wn_pre;
+                const bool first = c0 == c_begin;               // its residual values are in registers already
                 float sq[16];
 #pragma unroll
                 for (int i = 0; i < 16; ++i) {
@@ -389,7 +410,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant_
                     sq[i] = 0.f;
                     if (i >= cn || t >= a.T || n >= a.N) continue;
                     const size_t o = (size_t)t * a.ldo + n;
-                    const float r = reinterpret_cast<float*>(a.out)[o] + v[i];
+                    const float r = (first ? res_pre[i] : reinterpret_cast<float*>(a.out)[o]) + v[i];
                     reinterpret_cast<float*>(a.out)[o] = r;
                     a.xw_out[(size_t)t * a.N + n] = __float2bfloat16_rn(r * wn);
                     sq[i] = r * r;
@@ -413,7 +434,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant_
                     const size_t o = (size_t)t * a.ldo + n;
                     if (a.epilogue == EPI_BF16) reinterpret_cast<bf16*>(a.out)[o] = __float2bfloat16_rn(v[i]);
                     else if (a.epilogue == EPI_F32) reinterpret_cast<float*>(a.out)[o] = v[i];
-                    else reinterpret_cast<float*>(a.out)[o] += v[i];
+                    else reinterpret_cast<float*>(a.out)[o] = (c0 == c_begin ? res_pre[i] : reinterpret_cast<float*>(a.out)[o]) + v[i];
                 }
             }
         }
