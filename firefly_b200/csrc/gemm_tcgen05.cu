@@ -45,7 +45,7 @@ constexpr unsigned long long WAIT_LIMIT_CYCLES = 2000000000ull;   // about a sec
 enum Epilogue { EPI_BF16 = 0, EPI_F32 = 1, EPI_RESIDUAL_ADD = 2, EPI_SWIGLU = 3 };
 
 constexpr int MAX_STAGES = 12;
-constexpr size_t SMEM_BUDGET = 200 * 1024;   // of the 227 KB a block may have
+constexpr size_t SMEM_BUDGET = 220 * 1024;   // of the 227 KB a block may have
 
 template <int TOK> struct TileCfg {
     static constexpr int A_BYTES = BN * BK * 2;
