@@ -16,7 +16,13 @@ import replay_util as U
 
 pytestmark = pytest.mark.gpu
 
+# "S": the weights of the per-head q and k norms are three times as large, so the scores have three
+# times the spread and a row's attention rests on a few keys, near or far: a key that is lost, read
+# from the wrong page or masked by mistake changes the logits far beyond the tolerance.  In 32-bit
+# only: scores that sharp multiply the rounding of bfloat16 activations beyond its tolerance at every
+# position (the tensor-core attention kernels have their own test with one key that stands out).
 CONFIGS = {"A": (P.TINY_A, 0, 16, [40, 100, 1, 77, 128, 33]),
+           "S": (P.TINY_D, 5, 16, [130, 47, 333, 16, 65, 700]),
            "B": (P.TINY_B, 1, 8, [70, 3, 200, 45, 256, 129, 17]),
            "C": (P.TINY_C, 2, 32, [150, 64, 65, 300, 2, 97]),
            "D": (P.TINY_D, 3, 16, [300, 129, 640, 70, 1000])}
@@ -27,7 +33,13 @@ def folders(tmp_path_factory):
     out = {}
     for name, (cfg, seed, block, lengths) in CONFIGS.items():
         for dtype, tdt in (("float32", torch.float32), ("bfloat16", torch.bfloat16)):
+            if name == "S" and dtype != "float32":
+                continue
             w = P.random_weights(cfg, seed, dtype=tdt, scale=0.05)
+            if name == "S":
+                for k in w:
+                    if k.endswith("q_norm.weight") or k.endswith("k_norm.weight"):
+                        w[k] = (w[k].float() * 3.0).to(tdt)
             path = str(tmp_path_factory.mktemp(f"model{name}_{dtype}"))
             U.write_model_dir(path, cfg, w, tdt)
             reqs = U.make_requests(cfg["vocab_size"], lengths, seed + 10)
@@ -41,8 +53,8 @@ def _session(path, dtype, max_tokens, block):
     return ReplaySession(path, dtype=dtype, max_tokens=max_tokens, block_size=block)
 
 
-@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
-@pytest.mark.parametrize("name", list(CONFIGS))
+@pytest.mark.parametrize("name,dtype", [(n, d) for n in CONFIGS for d in ("float32", "bfloat16")
+                                        if n != "S" or d == "float32"])
 @pytest.mark.parametrize("family", ["whole", "tail", "portions", "mixed"])
 def test_replay_family(folders, name, dtype, family):
     path, cfg, block, reqs, plain = folders[(name, dtype)]
