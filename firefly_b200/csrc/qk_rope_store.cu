@@ -11,6 +11,8 @@
 // Cache layout of one slot: [num_blocks][2 (k,v)][n_kv_heads][block_size][head_dim].
 #include "common.cuh"
 
+#include <type_traits>
+
 namespace ff {
 
 constexpr int QKR_WARPS = 4;
@@ -186,6 +188,110 @@ __global__ void qk_norm_rope_store_vec_kernel(
     }
 }
 
+// The same for long portions of prompts: a warp takes HPW consecutive heads of one token, so the
+// token's position, page, cosines and sines are fetched once for all of them and the loads of the
+// HPW heads are in flight together.
+template <int C, int HPW>
+__global__ void qk_norm_rope_store_rows_kernel(
+    bf16* __restrict__ qkv, int row_width, int T_tokens, int nq, int nkv,
+    const float* __restrict__ q_norm_w, const float* __restrict__ k_norm_w, float eps,
+    const float* __restrict__ cos_sin, int max_positions,
+    const int* __restrict__ positions, const int* __restrict__ token_seq,
+    const int* __restrict__ block_table, int max_blocks, int block_size, int num_blocks,
+    bf16* __restrict__ cache, int* __restrict__ status) {
+    asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
+    constexpr int HALF = 32 * C, d = 64 * C;
+    using Vec = typename std::conditional<C == 2, uint32_t, uint2>::type;
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+    const int heads = nq + 2 * nkv;
+    const int chunks = (heads + HPW - 1) / HPW;
+    const long long item = (long long)blockIdx.x * QKR_WARPS + warp;
+    const bool active = item < (long long)T_tokens * chunks;
+    const int t = active ? (int)(item / chunks) : 0, h0 = active ? (int)(item % chunks) * HPW : 0;
+    const int pos = positions[t];
+    const int e0 = lane * C;
+    float wq_l[C], wq_h[C], wk_l[C], wk_h[C], cs_c[C], cs_s[C];
+    const bool pos_ok = pos >= 0 && pos < max_positions;
+#pragma unroll
+    for (int j = 0; j < C; ++j) {
+        wq_l[j] = q_norm_w ? q_norm_w[e0 + j] : 1.f;
+        wq_h[j] = q_norm_w ? q_norm_w[HALF + e0 + j] : 1.f;
+        wk_l[j] = k_norm_w ? k_norm_w[e0 + j] : 1.f;
+        wk_h[j] = k_norm_w ? k_norm_w[HALF + e0 + j] : 1.f;
+        cs_c[j] = 1.f;
+        cs_s[j] = 0.f;
+        if (cos_sin && pos_ok) {
+            const float* cs = cos_sin + (size_t)pos * d + 2 * (e0 + j);  // [half][2]
+            cs_c[j] = cs[0];
+            cs_s[j] = cs[1];
+        }
+    }
+    const bool has_kv = h0 + HPW > nq;
+    int page = 0;
+    if (has_kv) page = (pos >= 0 && pos / block_size < max_blocks) ? block_table[(size_t)token_seq[t] * max_blocks + pos / block_size] : -1;
+    asm volatile("griddepcontrol.wait;" ::: "memory");
+    if (!active) return;
+    if (has_kv && (page < 0 || page >= num_blocks)) {
+        if (lane == 0) atomicExch(status, 2);
+        return;
+    }
+    if (cos_sin && !pos_ok && h0 < nq + nkv) {
+        if (lane == 0) atomicExch(status, 3);
+        return;
+    }
+    bf16* row = qkv + (size_t)t * row_width;
+    Vec a[HPW], b[HPW];
+#pragma unroll
+    for (int u = 0; u < HPW; ++u) {
+        const int hh = min(h0 + u, heads - 1);
+        a[u] = *reinterpret_cast<const Vec*>(row + (size_t)hh * d + e0);
+        b[u] = *reinterpret_cast<const Vec*>(row + (size_t)hh * d + HALF + e0);
+    }
+#pragma unroll
+    for (int u = 0; u < HPW; ++u) {
+        const int hh = h0 + u;
+        if (hh >= heads) break;
+        const int kind = hh < nq ? 0 : (hh < nq + nkv ? 1 : 2);  // q, k, v
+        float lo[C], hi[C];
+        const bf16* pa = reinterpret_cast<const bf16*>(&a[u]);
+        const bf16* pb = reinterpret_cast<const bf16*>(&b[u]);
+#pragma unroll
+        for (int j = 0; j < C; ++j) { lo[j] = __bfloat162float(pa[j]); hi[j] = __bfloat162float(pb[j]); }
+        if ((kind == 0 && q_norm_w) || (kind == 1 && k_norm_w)) {
+            float ss = 0.f;
+#pragma unroll
+            for (int j = 0; j < C; ++j) ss += lo[j] * lo[j] + hi[j] * hi[j];
+            ss = warp_sum(ss);
+            const float inv = 1.0f / sqrtf(ss / (float)d + eps);
+#pragma unroll
+            for (int j = 0; j < C; ++j) {
+                lo[j] = lo[j] * inv * (kind == 0 ? wq_l[j] : wk_l[j]);
+                hi[j] = hi[j] * inv * (kind == 0 ? wq_h[j] : wk_h[j]);
+            }
+        }
+        if (kind != 2 && cos_sin) {
+#pragma unroll
+            for (int j = 0; j < C; ++j) {
+                const float x = lo[j], y = hi[j];
+                lo[j] = x * cs_c[j] - y * cs_s[j];
+                hi[j] = y * cs_c[j] + x * cs_s[j];
+            }
+        }
+        bf16* dst = row + (size_t)hh * d;
+        if (kind != 0) {
+            const int kh = kind == 1 ? hh - nq : hh - nq - nkv;
+            dst = cache + ((((size_t)page * 2 + (kind == 2)) * nkv + kh) * block_size + pos % block_size) * d;
+        }
+        Vec oa, ob;
+        bf16* qa = reinterpret_cast<bf16*>(&oa);
+        bf16* qb = reinterpret_cast<bf16*>(&ob);
+#pragma unroll
+        for (int j = 0; j < C; ++j) { qa[j] = __float2bfloat16_rn(lo[j]); qb[j] = __float2bfloat16_rn(hi[j]); }
+        *reinterpret_cast<Vec*>(dst + e0) = oa;
+        *reinterpret_cast<Vec*>(dst + HALF + e0) = ob;
+    }
+}
+
 }  // namespace ff
 
 using namespace ff;
@@ -206,6 +312,21 @@ FF_EXPORT int ff_qk_norm_rope_store(void* qkv, int dtype, int row_width, int T, 
     // whole-head rotation of a 128- or 256-wide bfloat16 head with aligned rows: the register form
     if (dtype == 1 && (d == 128 || d == 256) && (!cos_sin || rotary_dim == d) && row_width % 4 == 0 &&
         ((uintptr_t)qkv & 7) == 0 && ((uintptr_t)cache & 7) == 0) {
+        if (T >= 256) {   // long portions: a warp per (token, 8 heads)
+            constexpr int HPW = 8;
+            const long long ritems = (long long)T * ((nq + 2 * nkv + HPW - 1) / HPW);
+            const unsigned rblocks = (unsigned)((ritems + QKR_WARPS - 1) / QKR_WARPS);
+            if (d == 128)
+                FF_LAUNCH((qk_norm_rope_store_rows_kernel<2, HPW>), rblocks, QKR_WARPS * 32, 0, stream, (bf16*)qkv,
+                          row_width, T, nq, nkv, q_norm_w, k_norm_w, eps, cos_sin, max_positions, positions, token_seq,
+                          block_table, max_blocks, block_size, num_blocks, (bf16*)cache, status);
+            else
+                FF_LAUNCH((qk_norm_rope_store_rows_kernel<4, HPW>), rblocks, QKR_WARPS * 32, 0, stream, (bf16*)qkv,
+                          row_width, T, nq, nkv, q_norm_w, k_norm_w, eps, cos_sin, max_positions, positions, token_seq,
+                          block_table, max_blocks, block_size, num_blocks, (bf16*)cache, status);
+            FF_LAUNCH_CHECK();
+            return 0;
+        }
         if (d == 128)
             FF_LAUNCH((qk_norm_rope_store_vec_kernel<2>), blocks, QKR_WARPS * 32, 0, stream, (bf16*)qkv, row_width, T,
                       nq, nkv, q_norm_w, k_norm_w, eps, cos_sin, max_positions, positions, token_seq, block_table,

@@ -105,9 +105,10 @@ def _paged(k, v, block, n_extra=3, seed=0):
 @pytest.mark.parametrize("d,nq,nkv,block,rot", [(16, 4, 2, 16, 16), (48, 3, 1, 8, 32), (128, 8, 2, 16, 128),
                                                 (256, 2, 2, 32, 256), (72, 2, 1, 4, 72)])
 @pytest.mark.parametrize("adt", [torch.float32, torch.bfloat16])
-def test_qk_norm_rope_store(d, nq, nkv, block, rot, adt):
+@pytest.mark.parametrize("T", [21, 300])          # 300: the form for long portions (a warp per 8 heads of a token)
+def test_qk_norm_rope_store(d, nq, nkv, block, rot, adt, T):
     torch.manual_seed(d)
-    T, theta, eps = 21, 12345.0, 1e-5
+    theta, eps = 12345.0, 1e-5
     ctx_len = 13                                   # tokens already cached: the write starts mid-page
     width = (nq + 2 * nkv) * d
     qkv = torch.randn(T, width).to(adt)
@@ -119,7 +120,7 @@ def test_qk_norm_rope_store(d, nq, nkv, block, rot, adt):
     pages = torch.zeros(n_pages + 4, 2, nkv, block, d, dtype=adt)
     half = rot // 2
     freq = torch.pow(torch.tensor(theta, dtype=torch.float64), -2.0 * torch.arange(half, dtype=torch.float64) / rot)
-    ang = torch.arange(64, dtype=torch.float64)[:, None] * freq[None]
+    ang = torch.arange(ctx_len + T + 3, dtype=torch.float64)[:, None] * freq[None]
     cs = torch.stack([torch.cos(ang), torch.sin(ang)], -1).float()
     g_qkv, g_pages = dev(qkv.clone()), dev(pages)
     status = torch.zeros(1, dtype=torch.int32, device="cuda")
