@@ -186,8 +186,8 @@ def main() -> int:
     P = args.prompt_len
     K_steps, W = args.steps, args.warmup
     need_new = 1 + W + 2 * K_steps + 6
-    if P + need_new > args.context:
-        print(f"bench.py: {P} prompt + {need_new} decode tokens exceed the context {args.context}")
+    if P + need_new + max(args.batch, 64) > args.context:
+        print(f"bench.py: {P} prompt + {need_new + max(args.batch, 64)} decode tokens exceed the context {args.context}")
         return 2
     gen = torch.Generator().manual_seed(1234)
 
@@ -202,7 +202,7 @@ def main() -> int:
         reqs = []
         for i in range(B):
             ids = torch.randint(0, V, (P,), generator=gen).tolist()
-            r = GenerationRequest(f"b{i}", ids, SamplingParams(max_tokens=max(256, need_new), ignore_eos=True))
+            r = GenerationRequest(f"b{i}", ids, SamplingParams(max_tokens=max(256, need_new + B), ignore_eos=True))   # early requests decode while later prompts come in
             eng.add_request(r)
             reqs.append(r)
         while any(len(r.generated_tokens) == 0 for r in reqs):   # prompts in, first token sampled
