@@ -66,20 +66,23 @@ static_assert((BN * CHUNKS) % NTHREADS == 0, "the copy loop has no tail");
 // Where each key row of the tile that starts at key0 lies in the cache, as an element offset
 // of its K row (the V row is v_off further), or -1 when the key is outside [kv_lo, kv_hi) or
 // its page is missing.  Thread r < BN looks up row r: one block-table read per row and tile.
+__device__ __forceinline__ long long kv_row_offset(const int* __restrict__ bt, int max_blocks, int num_blocks,
+                                                   int nkv, int kh, int block_size, int key, int kv_lo, int kv_hi) {
+    long long off = -1;
+    if (key >= kv_lo && key < kv_hi) {
+        const int pi = key / block_size;
+        const int page = pi < max_blocks ? bt[pi] : -1;
+        if (page >= 0 && page < num_blocks)
+            off = ((((long long)page * 2) * nkv + kh) * block_size + (key - pi * block_size)) * D;
+    }
+    return off;
+}
 __device__ __forceinline__ void kv_row_offsets(long long* row_off, const int* __restrict__ bt, int max_blocks,
                                                int num_blocks, int nkv, int kh, int block_size, int key0,
                                                int kv_lo, int kv_hi) {
-    if (threadIdx.x < BN) {
-        const int key = key0 + threadIdx.x;
-        long long off = -1;
-        if (key >= kv_lo && key < kv_hi) {
-            const int pi = key / block_size;
-            const int page = pi < max_blocks ? bt[pi] : -1;
-            if (page >= 0 && page < num_blocks)
-                off = ((((long long)page * 2) * nkv + kh) * block_size + (key - pi * block_size)) * D;
-        }
-        row_off[threadIdx.x] = off;
-    }
+    if (threadIdx.x < BN)
+        row_off[threadIdx.x] = kv_row_offset(bt, max_blocks, num_blocks, nkv, kh, block_size, key0 + threadIdx.x,
+                                             kv_lo, kv_hi);
 }
 
 // Copy a tile's K and V rows into shared memory, 16 bytes a thread, neighbouring threads on
@@ -400,14 +403,19 @@ attn_decode_kernel(const bf16* __restrict__ q, int q_stride, const bf16* __restr
             cp_async_wait<0>();
         }
         __syncthreads();
-        if (t + 2 < t_end)
-            kv_row_offsets(s_row_off[buf], bt, max_blocks, num_blocks, nkv, kh, block_size, (t + 2) * BN, kv_lo, kv_hi);
+        // the offsets of tile t are used up: look up those of tile t+2.  The page id is asked for now and
+        // written to shared memory after this tile's arithmetic, so its trip to memory costs nothing.
+        const bool look = t + 2 < t_end && threadIdx.x < BN;
+        long long off_next = -1;
+        if (look)
+            off_next = kv_row_offset(bt, max_blocks, num_blocks, nkv, kh, block_size, (t + 2) * BN + threadIdx.x, kv_lo, kv_hi);
         const int key0 = t * BN + warp * 16;
         if (key0 < kv_hi && key0 + 16 > kv_lo) {
             const bool need_mask = key0 + 16 > kv_hi || key0 < kv_lo;
             st.step(Qs, Ks + (buf * BN + warp * 16) * KSTR, Vs + (buf * BN + warp * 16) * KSTR, key0, lo, hi,
                     scale_log2, need_mask);
         }
+        if (look) s_row_off[buf][threadIdx.x] = off_next;
         __syncthreads();
     }
     cp_async_wait<0>();
