@@ -12,8 +12,9 @@
 //                  (tcgen05.st), and - only when a row's max moved far - a rescale of its row of O;
 //   O += P V       tcgen05.mma, P from tensor memory, V (the cache's [key][d] tile as it is, the
 //                  MMA's N-major operand form), O (128 x D, float32) in tensor memory.
-// One thread issues TMA loads (K and V have two stages each, freed separately), one thread
-// issues the MMAs; two blocks share an SM (at head size 128).
+// One warp starts the TMA copies, a page and panel per lane (K and V have two stages each, freed
+// separately); one warp issues the MMAs, converged, with the issuing lane predicated; two blocks
+// share an SM (at head size 128).
 //
 // It replaces, for head sizes that are multiples of 64 and page sizes that divide 64, the
 // mma.sync kernel of attention_mma.cu (which stays for every other size); the reference's

@@ -1,7 +1,7 @@
 // out[t, n] = sum_k x[t, k] * W[n, k]   (y = x W^T, W as stored in checkpoints)
 // on the fifth-generation tensor cores: tcgen05.mma with the accumulator in tensor
-// memory, operands brought into shared memory by TMA, one elected thread issuing
-// the MMAs, and an epilogue that reads the accumulator back with tcgen05.ld.
+// memory, operands brought into shared memory by TMA, one lane of a converged warp
+// issuing the MMAs, and an epilogue that reads the accumulator back with tcgen05.ld.
 //
 // The weight tile is the 128-row "M" operand of the MMA and the tokens are its "N"
 // dimension (16 to 256), so a decode step with a handful of tokens still fills the
@@ -52,9 +52,8 @@ template <int TOK> struct TileCfg {
     static constexpr int B_BYTES = TOK * BK * 2;
     static constexpr int STAGE_BYTES = A_BYTES + B_BYTES;
     static constexpr int TMEM_COLS = TOK < 32 ? 32 : TOK;
-    // pipeline depth: all the shared memory of an SM when one block per SM covers the grid
-    // (more weight tiles in flight, and more of them requested before the kernel in front has
-    // finished), half of it when two blocks share an SM
+    // pipeline depth: half of an SM's shared memory (SHALLOW, what every launch uses: two blocks, of
+    // this product or of this and the next one, share an SM) or all of it (DEEP, measured slower)
     static constexpr int DEEP = (SMEM_BUDGET / STAGE_BYTES) > MAX_STAGES ? MAX_STAGES : (int)(SMEM_BUDGET / STAGE_BYTES);
     static constexpr int SHALLOW = (SMEM_BUDGET / 2 / STAGE_BYTES) < 2 ? 2 : (int)(SMEM_BUDGET / 2 / STAGE_BYTES);
     static constexpr size_t smem(int stages) {
