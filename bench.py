@@ -167,6 +167,7 @@ def main() -> int:
     full_layers = shape["num_hidden_layers"]
     if args.layers:
         shape["num_hidden_layers"] = args.layers
+    shape["max_position_embeddings"] = max(shape["max_position_embeddings"], args.context)
     cfg = config_from_dict(shape)
     dev = torch.device("cuda:0")
     torch.cuda.set_device(dev)
