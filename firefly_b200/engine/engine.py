@@ -175,6 +175,9 @@ class Engine:
             for out in self.step():
                 if self.result_queue is not None:
                     self.result_queue.push(out)
+        for out in self.drain():                     # a step may still be on the stream
+            if self.result_queue is not None:
+                self.result_queue.push(out)
 
     def _drain_inbox(self) -> None:
         while True:
