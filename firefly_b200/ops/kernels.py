@@ -27,7 +27,14 @@ def _p(t: Optional[torch.Tensor]) -> c_void_p:
     return c_void_p(0 if t is None else t.data_ptr())
 
 
+_raw_stream = getattr(torch._C, "_cuda_getCurrentRawStream", None)
+
+
 def _stream() -> c_void_p:
+    """The current stream's handle.  Asked for at every launch: the raw getter costs well under a
+    microsecond where ``torch.cuda.current_stream()`` builds an object each time (15 us)."""
+    if _raw_stream is not None:
+        return c_void_p(_raw_stream(torch.cuda.current_device()))
     return c_void_p(torch.cuda.current_stream().cuda_stream)
 
 
