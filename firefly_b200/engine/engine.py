@@ -24,8 +24,8 @@ import os
 import queue
 import threading
 import time
-from dataclasses import dataclass, field
-from typing import Dict, Iterable, List, Optional, Sequence, Tuple
+from dataclasses import dataclass
+from typing import Dict, List, Optional, Sequence
 
 import torch
 
@@ -34,10 +34,10 @@ from ..config.base import ModelConfig
 from ..models.decoder import DecoderModel
 from ..sampling.params import SamplingParams
 from ..sampling.sampler import Sampler
-from .loading import load_model, parse_dtype, random_model
+from .loading import load_model, random_model
 from .request import GenerationRequest, RequestStatus
 from .runner import ModelRunner, StepEntry
-from .scheduler import Scheduler, SchedulerBatch
+from .scheduler import Scheduler
 
 
 @dataclass

@@ -8,13 +8,12 @@ tensor that is not on a CUDA device, or a kernel that cannot be built, raises.
 from __future__ import annotations
 
 import ctypes
-import os
-from ctypes import c_float, c_int, c_longlong, c_size_t, c_void_p
+from ctypes import c_float, c_int, c_size_t, c_void_p
 from typing import Optional
 
 import torch
 
-from .build import KernelBuildError, compile_many, load_module
+from .build import compile_many, load_module
 
 _DT = {torch.float32: 0, torch.bfloat16: 1}
 
