@@ -373,3 +373,165 @@ def test_toy_routed_feed_forward_and_learned_positions():
         got = U.run_trace(sess, steps)
         # a token whose two best experts are within rounding may be routed differently: not with these weights
         U.compare(got, plain, 2e-4, "toy routed feed-forward and learned positions")
+
+
+# ------------------------------------- a toy norm, arrangement and architecture --
+class ToyMeanAbsNorm:
+    """y = v / (mean |v| + eps) * w after the pending delta has been added into the 32-bit residual.
+    Written with torch operations; it stands for any norm a user might add."""
+
+    def __init__(self, spec, rt):
+        self.size = spec.params["size"]
+        self.eps = spec.params["eps"]
+        self.prefix = spec.prefix
+
+    def weight_specs(self):
+        from firefly_b200.weights import WeightSpec
+        return [WeightSpec(f"{self.prefix}.weight", (self.size,), init="norm")]
+
+    def bind(self, tensors):
+        self.weight = tensors[f"{self.prefix}.weight"].float()
+
+    def forward(self, residual, delta, ctx, *, tag="normed", row_idx=None, may_defer=False):
+        if delta is not None:
+            residual += delta.float()
+        v = residual if row_idx is None else residual[row_idx.long()]
+        return (v / (v.abs().mean(dim=-1, keepdim=True) + self.eps) * self.weight).to(ctx.dtype)
+
+
+def _toy_parallel_block():
+    from firefly_b200.parts.block import Block
+
+    class ToyParallelBlock(Block):
+        """h += mixer(norm(h)) + feed_forward(norm(h)): one norm, both parts read the same rows."""
+        n_norms = 1
+
+        def forward(self, residual, pending, ctx, slot, write_cache):
+            x = self.norms[0].forward(residual, pending, ctx)
+            a = self.mixer.forward(x, ctx, slot, write_cache)
+            f = self.feed_forward.forward(x, ctx)
+            return residual, a.float() + f.float()          # one pending delta for the next norm
+    return ToyParallelBlock
+
+
+def _toy_architecture():
+    """A configuration class with keys of its own and a spec builder: what a user writes to add an
+    architecture (here: parallel blocks, the toy norm, attention without q/k norms, tied head)."""
+    from firefly_b200.config import ConfigError, LayerSpec, ModelConfig, ModelSpec, PartSpec, ScheduleEntry
+
+    @dataclasses.dataclass(frozen=True)
+    class ToyConfig(ModelConfig):
+        architecture = "ToyParallelForCausalLM"
+        width: int = 0
+        depth: int = 0
+        heads: int = 0
+        kv_heads: int = 0
+        head_size: int = 0
+        ffn_width: int = 0
+        vocab: int = 0
+        positions: int = 0
+        norm_eps: float = 1e-5
+        theta: float = 10000.0
+
+        @classmethod
+        def from_dict(cls, raw):
+            keys = [f.name for f in dataclasses.fields(cls)]
+            cfg = cls(**{k: raw[k] for k in keys if k in raw})
+            cfg.validate()
+            return cfg
+
+        def validate(self):
+            if min(self.width, self.depth, self.heads, self.kv_heads, self.head_size, self.ffn_width, self.vocab) <= 0:
+                raise ConfigError("toy config: every size must be positive")
+
+    def toy_spec(cfg):
+        rope = PartSpec("rotary", dict(head_dim=cfg.head_size, rotary_dim=cfg.head_size, theta=cfg.theta,
+                                       max_positions=cfg.positions))
+        layers = []
+        for i in range(cfg.depth):
+            p = f"blocks.{i}"
+            layers.append(LayerSpec(
+                arrangement="toy_parallel",
+                mixer=PartSpec("gqa_attention", dict(hidden_size=cfg.width, num_heads=cfg.heads,
+                                                     num_kv_heads=cfg.kv_heads, head_dim=cfg.head_size, qk_norm=False,
+                                                     qk_norm_eps=cfg.norm_eps, window=None, scale=None),
+                               prefix=f"{p}.attn"),
+                feed_forward=PartSpec("swiglu_mlp", dict(hidden_size=cfg.width, intermediate_size=cfg.ffn_width),
+                                      prefix=f"{p}.ffn"),
+                norms=(PartSpec("toy_mean_abs", dict(size=cfg.width, eps=cfg.norm_eps), prefix=f"{p}.norm"),),
+                position=rope))
+        return ModelSpec(
+            vocab_size=cfg.vocab, hidden_size=cfg.width, max_positions=cfg.positions,
+            embedding=PartSpec("token_embedding", dict(vocab_size=cfg.vocab, hidden_size=cfg.width), prefix="embed"),
+            layers=tuple(layers), schedule=tuple(ScheduleEntry(i) for i in range(cfg.depth)),
+            final_norm=PartSpec("toy_mean_abs", dict(size=cfg.width, eps=cfg.norm_eps), prefix="out_norm"),
+            head=PartSpec("lm_head", dict(vocab_size=cfg.vocab, hidden_size=cfg.width, tied_to="embed.weight"),
+                          prefix="head"))
+    return ToyConfig, toy_spec
+
+
+def _toy_parallel_plain(raw, w, ids):
+    """The toy architecture on a whole sequence in float64, from the plain implementation's parts."""
+    wd = {k: v.double() for k, v in w.items()}
+    pos = torch.arange(len(ids))
+    nq, nkv, d, T = raw["heads"], raw["kv_heads"], raw["head_size"], len(ids)
+
+    def attn(x, p):                                         # no per-head norms in this architecture
+        q = P.rope((x @ wd[f"{p}.q_proj.weight"].T).view(T, nq, d), pos, raw["theta"])
+        k = P.rope((x @ wd[f"{p}.k_proj.weight"].T).view(T, nkv, d), pos, raw["theta"])
+        v = (x @ wd[f"{p}.v_proj.weight"].T).view(T, nkv, d)
+        return P.attention(q, k, v).reshape(T, nq * d) @ wd[f"{p}.o_proj.weight"].T
+
+    def norm(v, weight):
+        return v / (v.abs().mean(dim=-1, keepdim=True) + raw["norm_eps"]) * weight
+    h = P.embedding(torch.tensor(ids), wd["embed.weight"])
+    for i in range(raw["depth"]):
+        p = f"blocks.{i}"
+        x = norm(h, wd[f"{p}.norm.weight"])
+        a = attn(x, f"{p}.attn")
+        f = P.swiglu_mlp(x, wd[f"{p}.ffn.gate_proj.weight"], wd[f"{p}.ffn.up_proj.weight"], wd[f"{p}.ffn.down_proj.weight"])
+        h = h + a + f
+    return (norm(h, wd["out_norm.weight"]) @ wd["embed.weight"].T).numpy()
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+def test_toy_architecture_with_its_own_config_norm_and_arrangement(dtype, tmp_path):
+    """An architecture is added from outside the package: a configuration class with keys of its
+    own, a norm and an arrangement defined here, registered, written as a model folder with random
+    weights, loaded by name from config.json, replayed and generated from, against a plain version."""
+    import json
+    from firefly_b200 import LLM
+    from firefly_b200.models import config_from_dict, register_architecture
+    from firefly_b200.parts import register_part
+    from firefly_b200.replay import ReplaySession
+    from firefly_b200.weights import write_random_model
+    from firefly_b200.weights.safetensors_io import SafetensorsFile
+    ToyConfig, toy_spec = _toy_architecture()
+    register_part("norm", "toy_mean_abs", ToyMeanAbsNorm, replace=True)
+    register_part("arrangement", "toy_parallel", _toy_parallel_block(), replace=True)
+    register_architecture("ToyParallelForCausalLM", ToyConfig, toy_spec, replace=True)
+    raw = dict(architectures=["ToyParallelForCausalLM"], width=96, depth=3, heads=6, kv_heads=2, head_size=16,
+               ffn_width=208, vocab=331, positions=256, norm_eps=1e-4, theta=5000.0)
+    tdt = torch.float32 if dtype == "float32" else torch.bfloat16
+    folder = str(tmp_path / "toy")
+    write_random_model(config_from_dict(raw), seed=3, out_dir=folder, dtype=tdt)
+    with open(f"{folder}/config.json") as fh:
+        assert json.load(fh)["architectures"] == ["ToyParallelForCausalLM"]
+    f = SafetensorsFile(f"{folder}/model.safetensors")
+    w = {n: f.tensor(n).clone() for n in f.names()}
+    f.close()
+    assert "blocks.2.norm.weight" in w and "blocks.0.attn.q_norm.weight" not in w and "head.weight" not in w
+    reqs = U.make_requests(raw["vocab"], [60, 5, 131, 33], 21)
+    plain = {rid: _toy_parallel_plain(raw, w, toks) for rid, toks in reqs.items()}
+    for steps in (U.trace_whole(reqs), U.trace_tail_decode(reqs, tail=8), U.trace_mixed(reqs, seed=2, max_live=3)):
+        sess = ReplaySession(folder, dtype=dtype, max_tokens=U.peak_tokens(steps), block_size=16)
+        got = U.run_trace(sess, steps)
+        U.compare(got, plain, U.TOL[dtype], f"toy architecture {dtype}")
+        sess.cache.check()
+    if dtype == "float32":
+        prompt = reqs["r1"]
+        got = LLM(folder, dtype="float32", num_kv_blocks=32).generate([prompt], max_tokens=6)[0]
+        toks = list(prompt)
+        for _ in range(6):
+            toks.append(int(np.argmax(_toy_parallel_plain(raw, w, toks)[-1])))
+        assert got == toks[len(prompt):]
