@@ -42,6 +42,8 @@ def build_parser() -> argparse.ArgumentParser:
     ap.add_argument("--max-num-batched-tokens", type=int, default=8192)
     ap.add_argument("--max-model-len", type=int, default=None)
     ap.add_argument("--no-cuda-graphs", action="store_true")
+    ap.add_argument("--no-overlap-decode", action="store_true",
+                    help="read every decode step's tokens before the next step is launched")
     ap.add_argument("--write-random-model", metavar="DIR",
                     help="write config.json and model.safetensors with seeded random weights, then exit")
     ap.add_argument("--config", help="config.json for --write-random-model")
@@ -82,7 +84,7 @@ def main(argv=None) -> int:
               max_batch_size_limit=args.max_batch_size, max_num_batched_tokens=args.max_num_batched_tokens,
               kv_block_size=args.kv_block_size, num_kv_blocks=args.num_kv_blocks,
               max_model_len=args.max_model_len, eos_token_ids=args.eos_token_id,
-              use_cuda_graphs=not args.no_cuda_graphs)
+              use_cuda_graphs=not args.no_cuda_graphs, overlap_decode=not args.no_overlap_decode)
     outs = llm.generate(prompts, max_tokens=args.max_tokens, temperature=args.temperature, seed=args.seed,
                         ignore_eos=args.ignore_eos)
     for i, (p, o) in enumerate(zip(prompts, outs)):
