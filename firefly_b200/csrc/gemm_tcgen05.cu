@@ -361,22 +361,42 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant_
             } else {
 #pragma unroll
                 for (int i = 0; i < 16; ++i) v[i] = 0.f;
-                // peers in a fixed order: the sum is reproducible.  All loads of two peers are issued
-                // before the first value is used: a load from another block's shared memory takes
-                // about as long as one from the L2 cache, and one after the other they would add up.
-                for (int z = 0; z < a.splits; z += 2) {
-                    float p0[16], p1[16];
-                    const bool two = z + 1 < a.splits;
+                // peers in a fixed order: the sum is reproducible.  Loads are issued in batches of 32
+                // before the first of them is used (a load from another block's shared memory takes about
+                // as long as one from the L2 cache, and one after the other they would add up): all
+                // peers at once when the slice has at most four tokens, else two peers at a time.
+                if (cn <= 4) {
+                    float p[8][4];
 #pragma unroll
-                    for (int i = 0; i < 16; ++i) {
-                        const uint32_t addr = mine_addr + (uint32_t)((c0 + i) * BN + row) * 4u;
-                        p0[i] = i < cn ? ld_peer_smem(addr, (uint32_t)z) : 0.f;
-                        p1[i] = (two && i < cn) ? ld_peer_smem(addr, (uint32_t)(z + 1)) : 0.f;
+                    for (int z = 0; z < 8; ++z) {
+#pragma unroll
+                        for (int i = 0; i < 4; ++i) {
+                            const uint32_t addr = mine_addr + (uint32_t)((c0 + i) * BN + row) * 4u;
+                            p[z][i] = (z < a.splits && i < cn) ? ld_peer_smem(addr, (uint32_t)z) : 0.f;
+                        }
                     }
 #pragma unroll
-                    for (int i = 0; i < 16; ++i) {
-                        v[i] += p0[i];
-                        if (two) v[i] += p1[i];
+                    for (int z = 0; z < 8; ++z) {
+                        if (z < a.splits) {
+#pragma unroll
+                            for (int i = 0; i < 4; ++i) v[i] += p[z][i];
+                        }
+                    }
+                } else {
+                    for (int z = 0; z < a.splits; z += 2) {
+                        float p0[16], p1[16];
+                        const bool two = z + 1 < a.splits;
+#pragma unroll
+                        for (int i = 0; i < 16; ++i) {
+                            const uint32_t addr = mine_addr + (uint32_t)((c0 + i) * BN + row) * 4u;
+                            p0[i] = i < cn ? ld_peer_smem(addr, (uint32_t)z) : 0.f;
+                            p1[i] = (two && i < cn) ? ld_peer_smem(addr, (uint32_t)(z + 1)) : 0.f;
+                        }
+#pragma unroll
+                        for (int i = 0; i < 16; ++i) {
+                            v[i] += p0[i];
+                            if (two) v[i] += p1[i];
+                        }
                     }
                 }
             }
