@@ -167,6 +167,9 @@ def main() -> int:
     full_layers = shape["num_hidden_layers"]
     if args.layers:
         shape["num_hidden_layers"] = args.layers
+    # room for the prompt and every decode step of the run (a long --steps grows the context)
+    need_ctx = args.prompt_len + 1 + args.warmup + 2 * args.steps + 6 + max(args.batch, 64)
+    args.context = max(args.context, need_ctx)
     shape["max_position_embeddings"] = max(shape["max_position_embeddings"], args.context)
     cfg = config_from_dict(shape)
     dev = torch.device("cuda:0")
@@ -187,15 +190,14 @@ def main() -> int:
     P = args.prompt_len
     K_steps, W = args.steps, args.warmup
     need_new = 1 + W + 2 * K_steps + 6
-    if P + need_new + max(args.batch, 64) > args.context:
-        print(f"bench.py: {P} prompt + {need_new + max(args.batch, 64)} decode tokens exceed the context {args.context}")
-        return 2
     gen = torch.Generator().manual_seed(1234)
 
-    def make_engine(B):
+    def make_engine(B, steps=None):
+        # pages for what this engine's requests will hold, not for the whole context
+        ctx = args.context if steps is None else min(args.context, P + 1 + W + 2 * steps + 6 + max(B, 64))
         opts = EngineOptions(max_prefill_chunk_size=P, max_batch_size_limit=max(B, 1),
                              max_num_batched_tokens=max(P, B), kv_block_size=16,
-                             num_kv_blocks=B * (-(-args.context // 16)), max_model_len=args.context,
+                             num_kv_blocks=B * (-(-ctx // 16)), max_model_len=args.context,
                              eos_token_ids=[], graph_batch_sizes=(1, 2, 4, 8, 16, 32, 64))
         return Engine(model, cfg, options=opts)
 
@@ -265,7 +267,7 @@ def main() -> int:
         return dt, produced, b.layout.size * 4, n * 4
 
     def decode_point(B, steps, with_e2e):
-        eng = make_engine(B)
+        eng = make_engine(B, steps)
         reqs = start_requests(eng, B)
         for _ in range(W):
             eng.step()
