@@ -570,14 +570,3 @@ FF_EXPORT int ff_attn_decode(const void* q, int q_stride, const void* cache, con
     }
     return 0;
 }
-
-// The join of split-KV partial results alone (for kernels of other files that write the same scratch layout).
-FF_EXPORT int ff_attn_combine(const float* part_o, const float* part_ml, const int* cu_q, int n_seqs, void* out,
-                              int out_stride, int nq, int num_splits, cudaStream_t stream) {
-    if (n_seqs <= 0 || num_splits <= 1) return 0;
-    dim3 cgrid(n_seqs, nq);
-    FF_LAUNCH((attn_combine_kernel), cgrid, D >= 128 ? 128 : 64, 0, stream, part_o, part_ml, cu_q, (bf16*)out,
-              out_stride, nq, num_splits);
-    FF_LAUNCH_CHECK();
-    return 0;
-}

@@ -48,8 +48,7 @@ _STATUS = {1: "a token id outside the vocabulary reached the embedding kernel",
            102: "matrix product: the wait for a loaded stage ran out",
            103: "matrix product: the wait for the accumulator ran out",
            107: "attention (tcgen05): a bounded wait ran out",
-           108: "attention (tcgen05): a sequence's page list does not fit the kernel's shared memory",
-           109: "decode attention (tcgen05): a bounded wait ran out"}
+           108: "attention (tcgen05): a sequence's page list does not fit the kernel's shared memory"}
 
 
 class MetaLayout:

@@ -75,7 +75,6 @@ _MODULES = {
     "attention_simt": ("attention_simt.cu", None),
     "sampling": ("sampling.cu", None),
     "gemm_tcgen05": ("gemm_tcgen05.cu", None),
-    "attention_decode_tc": ("attention_decode_tc.cu", None),
 }
 
 
@@ -385,35 +384,6 @@ def attn_decode(q, q_stride, pages, table, cu_q, ctx_lens, n_seqs, out, part_o, 
         LAUNCHES += 1     # the kernel that joins the splits
 
 
-# The tcgen05 split-KV decode kernel (head size 128) is correct and tested but measured slower than the
-# mma.sync one at pages of 16 tokens (decode step at batch 8: 4.02 against 3.71 ms; batch 64: 8.54 against 8.03):
-# its 2 KB page boxes hold an SM's TMA unit to about 45 GB/s, and a block that fills the SM leaves no room for
-# the neighbouring products' blocks.  Off unless switched on here.
-USE_TC_DECODE_ATTENTION = False
-
-
-def tc_decode_attention_supported(dtype: torch.dtype, d: int, block_size: int, G: int) -> bool:
-    return dtype == torch.bfloat16 and d == 128 and block_size in (8, 16, 32, 64) and G <= 16
-
-
-def attn_decode_tc(q, q_stride, pages, table, cu_q, ctx_lens, n_seqs, out, part_o, part_ml, nq, nkv, d,
-                   scale, window, num_splits, status) -> None:
-    """Split-KV decode attention on tcgen05 (bfloat16, head size 128): keys and values streamed by TMA,
-    S^T and O^T in tensor memory; the join of the ranges by the same kernel as ``attn_decode``."""
-    _need_cuda(pages, table, cu_q, ctx_lens, out, part_o, part_ml, status)
-    assert d == 128
-    num_blocks, _, _, block_size, _ = pages.shape
-    _check(_lib("attention_decode_tc").ff_attn_dec_tc(
-        _p(q), c_int(q_stride), _p(pages), _p(table), c_int(table.shape[1]), _p(cu_q), _p(ctx_lens),
-        c_int(n_seqs), _p(out), c_int(out.shape[1]), _p(part_o), _p(part_ml), c_int(nq), c_int(nkv),
-        c_int(block_size), c_int(num_blocks), c_float(scale), c_int(window), c_int(num_splits), _p(status),
-        _stream()), "attn_decode_tc")
-    if num_splits > 1:
-        _check(_attn_lib(d).ff_attn_combine(_p(part_o), _p(part_ml), _p(cu_q), c_int(n_seqs), _p(out),
-                                            c_int(out.shape[1]), c_int(nq), c_int(num_splits), _stream()),
-               "attn_combine")
-
-
 USE_TC_ATTENTION = True     # tcgen05 attention for prompt portions where the sizes allow
 
 
@@ -451,13 +421,6 @@ def decode_splits(n_seqs: int, nkv: int, max_kv_len: int) -> int:
     return max(1, min(want, tiles, 64))
 
 
-def decode_splits_tc(n_seqs: int, nkv: int, max_kv_len: int) -> int:
-    """Ranges of keys for the tcgen05 decode kernel: one block fills an SM."""
-    tiles = max(1, -(-max_kv_len // 128))
-    want = max(1, _SM_COUNT // max(1, n_seqs * nkv))
-    return max(1, min(want, tiles, 20))
-
-
 def paged_attention(q: torch.Tensor, q_stride: int, pages: torch.Tensor, table: torch.Tensor, ctx,
                     out: torch.Tensor, nq: int, nkv: int, d: int, scale: float, window: int) -> None:
     """Attention of a step's tokens over the paged cache; picks the kernel: the
@@ -477,13 +440,8 @@ def paged_attention(q: torch.Tensor, q_stride: int, pages: torch.Tensor, table: 
         cap = max(n_dec * nq * splits, G * _SM_TARGET_CTAS + n_dec * nq)
         part_o = ctx.workspace.get("attn.part_o", (cap * d,), torch.float32)
         part_ml = ctx.workspace.get("attn.part_ml", (cap * 2,), torch.float32)
-        if USE_TC_DECODE_ATTENTION and tc_decode_attention_supported(q.dtype, d, pages.shape[3], G):
-            tsplits = decode_splits_tc(n_dec, nkv, ctx.max_kv_len)
-            attn_decode_tc(q, q_stride, pages, table, ctx.cu_q, ctx.ctx_lens, n_dec, out, part_o, part_ml, nq, nkv,
-                           d, scale, window, min(tsplits, splits), ctx.status)
-        else:
-            attn_decode(q, q_stride, pages, table, ctx.cu_q, ctx.ctx_lens, n_dec, out, part_o, part_ml, nq, nkv, d,
-                        scale, window, splits)
+        attn_decode(q, q_stride, pages, table, ctx.cu_q, ctx.ctx_lens, n_dec, out, part_o, part_ml, nq, nkv, d,
+                    scale, window, splits)
     if n_dec < n:
         # portions of prompts: tiled kernel over the remaining sequences (token offsets in cu_q are absolute)
         if USE_TC_ATTENTION and tc_attention_supported(q.dtype, d, pages.shape[3], ctx.max_kv_len):

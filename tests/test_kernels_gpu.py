@@ -267,29 +267,6 @@ def test_attention_decode_tensor_core(d, nq, nkv, block, window, splits):
     assert float(err) < 2e-2, float(err)
 
 
-@pytest.mark.parametrize("nq,nkv,block", [(8, 2, 16), (32, 8, 16), (4, 4, 32), (16, 1, 8), (6, 2, 64)])
-@pytest.mark.parametrize("window", [None, 100])
-@pytest.mark.parametrize("splits", [1, 2, 5])
-def test_attention_decode_tcgen05(nq, nkv, block, window, splits):
-    """The transposed tcgen05 decode kernel (head size 128): contexts from one key to several tiles of
-    128, ranges that get no key at all, a window."""
-    d = 128
-    seqs = [(0, 1), (1, 1), (127, 1), (128, 1), (200, 1), (517, 1), (15, 1), (900, 1)]
-    c = _attention_case(d, nq, nkv, block, seqs, window, torch.bfloat16, seed=3)
-    n = len(seqs)
-    part_o = torch.full((n * nq * splits * d,), float("nan"), device="cuda")
-    part_ml = torch.full((n * nq * splits * 2,), float("nan"), device="cuda")
-    for _ in range(2):
-        out = torch.zeros(c["q"].shape, dtype=torch.bfloat16, device="cuda")
-        status = torch.zeros(1, dtype=torch.int32, device="cuda")
-        K().attn_decode_tc(dev(c["q"]), nq * d, dev(c["pages"]), dev(c["table"]), dev(c["cu_q"]), dev(c["ctx_lens"]),
-                           n, out, part_o, part_ml, nq, nkv, d, 1 / math.sqrt(d), window or 0, splits, status)
-        torch.cuda.synchronize()
-        assert int(status) == 0
-        err = (out.cpu().double() - c["want"]).abs().max() / c["want"].abs().max()
-        assert float(err) < 2e-2, float(err)
-
-
 def test_attention_q_inside_wider_buffer():
     """q read in place from a [T, (nq+2nkv)*d] projection output."""
     d, nq, nkv, block = 64, 4, 2, 16
