@@ -206,3 +206,24 @@ def test_launch_ahead_stops_for_new_requests_and_scarce_pages(models):
     assert rb.generated_tokens == P.greedy_generate(cfg, w, b, 30)
     eng.cache.check()
     assert not eng.cache.live
+
+
+@pytest.mark.parametrize("seed", [0, 1])
+def test_many_requests_few_pages_random_lengths(models, seed):
+    """Two dozen requests of random lengths on a pool that holds a few of them: admission, portions,
+    steps launched ahead, ends by length at every step, preemption and recomputation all meet; every
+    request still gets the plain implementation's greedy tokens and every page comes back."""
+    from firefly_b200 import SamplingParams
+    path, cfg, w = models["B"]
+    rng = np.random.RandomState(100 + seed)
+    prompts = [list(map(int, rng.randint(0, cfg["vocab_size"], size=int(rng.randint(1, 41))))) for _ in range(24)]
+    limits = [int(rng.randint(1, 21)) for _ in prompts]
+    llm = _llm(path, dtype="float32", kv_block_size=8, num_kv_blocks=14, max_prefill_chunk_size=16,
+               max_batch_size_limit=6, max_num_batched_tokens=48)
+    got = llm.generate(prompts, sampling=[SamplingParams(max_tokens=m) for m in limits])
+    st = llm.engine.stats
+    assert st["preemptions"] > 0 and st["launched_ahead"] > 0
+    for p, m, g in zip(prompts, limits, got):
+        assert g == P.greedy_generate(cfg, w, p, m)
+    llm.engine.cache.check()
+    assert not llm.engine.cache.live and llm.engine._inflight is None
