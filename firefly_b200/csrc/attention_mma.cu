@@ -345,15 +345,94 @@ attn_tiled_kernel(const bf16* __restrict__ q, int q_stride, const bf16* __restri
 // One token per sequence.  grid (sequence, kv head, split).  The block's four warps
 // share each tile of 64 keys, 16 keys a warp, and join their states at the end.
 // With one split the output is final; else partial (o, m, l) go to scratch memory.
-__global__ void __launch_bounds__(NTHREADS)
-attn_decode_kernel(const bf16* __restrict__ q, int q_stride, const bf16* __restrict__ cache,
-                   const int* __restrict__ block_table, int max_blocks, const int* __restrict__ cu_q,
-                   const int* __restrict__ ctx_lens, bf16* __restrict__ out, int out_stride,
-                   float* __restrict__ part_o, float* __restrict__ part_ml, int nq, int nkv,
-                   int block_size, int num_blocks, float scale_log2, int window, int num_splits) {
-    // The kernel in front of this one (per-head norm, rotation, cache write) produces q and the
-    // newest key and value only.  The step's metadata and every older key do not depend on it: they
-    // are fetched before the wait for that kernel, so the first tile is on its way when it ends.
+//
+// HEADS = true: the kernel also finishes the heads of the newest token, which then come straight
+// from the q|k|v projection (`q` is that buffer, a row being the q heads, the k heads, the v heads):
+// each block normalises and rotates the query heads of its group on their way into shared memory,
+// and the block whose range of keys holds the newest one does the same for that key, writes it and
+// its value into the cache page and puts both into its tile.  One kernel and one pass over q|k|v
+// less per layer than with the separate kernel of qk_rope_store.cu; the arithmetic is the same.
+struct DecodeHeads {
+    const float* q_norm_w;     // [D] or null: no per-head norm
+    const float* k_norm_w;
+    float eps;
+    const float* cos_sin;      // [max_positions][D/2][2] or null: no rotation
+    int max_positions;
+    bf16* cache_w;             // the cache again, to write the newest key and value
+    int* status;               // 2: page of the newest token missing, 3: position beyond the table
+};
+constexpr int HC = D / 64;     // elements of each half of a head that a lane holds (heads finished in a warp)
+
+template <int C> __device__ __forceinline__ void load_run(bf16 (&a)[C], const bf16* p) {
+    if constexpr (C % 4 == 0) {
+#pragma unroll
+        for (int j = 0; j < C / 4; ++j) reinterpret_cast<uint2*>(a)[j] = reinterpret_cast<const uint2*>(p)[j];
+    } else if constexpr (C % 2 == 0) {
+#pragma unroll
+        for (int j = 0; j < C / 2; ++j) reinterpret_cast<uint32_t*>(a)[j] = reinterpret_cast<const uint32_t*>(p)[j];
+    } else {
+#pragma unroll
+        for (int j = 0; j < C; ++j) a[j] = p[j];
+    }
+}
+template <int C> __device__ __forceinline__ void store_run(bf16* p, const bf16 (&a)[C]) {
+    if constexpr (C % 4 == 0) {
+#pragma unroll
+        for (int j = 0; j < C / 4; ++j) reinterpret_cast<uint2*>(p)[j] = reinterpret_cast<const uint2*>(a)[j];
+    } else if constexpr (C % 2 == 0) {
+#pragma unroll
+        for (int j = 0; j < C / 2; ++j) reinterpret_cast<uint32_t*>(p)[j] = reinterpret_cast<const uint32_t*>(a)[j];
+    } else {
+#pragma unroll
+        for (int j = 0; j < C; ++j) p[j] = a[j];
+    }
+}
+// One head in a warp: lane l holds elements l*C.. of the first half (a) and their partners of the
+// second half (b).  RMS norm over the head with weights (wl, wh) if `norm`, then each pair (a, b)
+// turned by its angle if `rotate`; 32-bit throughout, rounded once at the end.
+template <int C>
+__device__ __forceinline__ void finish_head(bf16 (&a)[C], bf16 (&b)[C], bool norm, const float (&wl)[C],
+                                            const float (&wh)[C], float eps, bool rotate,
+                                            const float (&cs_c)[C], const float (&cs_s)[C]) {
+    float lo[C], hi[C];
+#pragma unroll
+    for (int j = 0; j < C; ++j) { lo[j] = __bfloat162float(a[j]); hi[j] = __bfloat162float(b[j]); }
+    if (norm) {
+        float ss = 0.f;
+#pragma unroll
+        for (int j = 0; j < C; ++j) ss += lo[j] * lo[j] + hi[j] * hi[j];
+        ss = warp_sum(ss);
+        const float inv = 1.0f / sqrtf(ss / (float)(64 * C) + eps);
+#pragma unroll
+        for (int j = 0; j < C; ++j) {
+            lo[j] = lo[j] * inv * wl[j];
+            hi[j] = hi[j] * inv * wh[j];
+        }
+    }
+    if (rotate) {
+#pragma unroll
+        for (int j = 0; j < C; ++j) {
+            const float x = lo[j], y = hi[j];
+            lo[j] = x * cs_c[j] - y * cs_s[j];
+            hi[j] = y * cs_c[j] + x * cs_s[j];
+        }
+    }
+#pragma unroll
+    for (int j = 0; j < C; ++j) { a[j] = __float2bfloat16_rn(lo[j]); b[j] = __float2bfloat16_rn(hi[j]); }
+}
+
+template <bool HEADS>
+__device__ __forceinline__ void
+attn_decode_body(const bf16* __restrict__ q, int q_stride, const bf16* __restrict__ cache,
+                 const int* __restrict__ block_table, int max_blocks, const int* __restrict__ cu_q,
+                 const int* __restrict__ ctx_lens, bf16* __restrict__ out, int out_stride,
+                 float* __restrict__ part_o, float* __restrict__ part_ml, int nq, int nkv,
+                 int block_size, int num_blocks, float scale_log2, int window, int num_splits,
+                 const DecodeHeads& hd) {
+    // The kernel in front of this one (per-head norm, rotation and cache write, or the projection
+    // itself) produces q and the newest key and value only.  The step's metadata and every older key
+    // do not depend on it: they are fetched before the wait for that kernel, so the first tile is
+    // on its way when it ends.
     asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
     extern __shared__ __align__(16) unsigned char smem_raw[];
     bf16* Qs = reinterpret_cast<bf16*>(smem_raw);                 // [16][KSTR]
@@ -378,14 +457,83 @@ attn_decode_kernel(const bf16* __restrict__ q, int q_stride, const bf16* __restr
     if (t_begin + 1 < t_end)
         kv_row_offsets(s_row_off[1], bt, max_blocks, num_blocks, nkv, kh, block_size, (t_begin + 1) * BN, kv_lo, kv_hi);
     __syncthreads();
-    const bool early = t_begin < t_end && (t_begin + 1) * BN <= pos;   // the first tile ends before the newest key
+    // the first tile can go early if it ends before the newest key, or if that key is put into the tile later
+    const bool early = t_begin < t_end && (HEADS || (t_begin + 1) * BN <= pos);
     if (early) load_kv_tile(Ks, Vs, cache, s_row_off[0], v_off);
+    // HEADS: what the finishing of the heads needs besides the projection's output
+    constexpr int C = HC > 0 ? HC : 1;
+    const int t_last = pos / BN;                                  // the tile of the newest key
+    const bool owner = HEADS && t_begin <= t_last && t_last < t_end;
+    const int e0 = lane * C;
+    float wl[C], wh[C], cs_c[C], cs_s[C];
+    __align__(8) bf16 new_a[C], new_b[C];                         // warp 0: the newest key, warp 1: its value
+    bool rotate = false, pos_ok = true;
+    int new_page = -1;
+    if constexpr (HEADS) {
+        rotate = hd.cos_sin != nullptr;
+        pos_ok = pos >= 0 && pos < hd.max_positions;
+#pragma unroll
+        for (int j = 0; j < C; ++j) {
+            wl[j] = hd.q_norm_w ? hd.q_norm_w[e0 + j] : 1.f;
+            wh[j] = hd.q_norm_w ? hd.q_norm_w[D / 2 + e0 + j] : 1.f;
+            cs_c[j] = 1.f;
+            cs_s[j] = 0.f;
+            if (rotate && pos_ok) {
+                const float* cs = hd.cos_sin + (size_t)pos * D + 2 * (e0 + j);
+                cs_c[j] = cs[0];
+                cs_s[j] = cs[1];
+            }
+        }
+        if (owner && warp < 2) new_page = (pos >= 0 && pos / block_size < max_blocks) ? bt[pos / block_size] : -1;
+        // rows of the tile beyond the group are zeros
+        for (int c = G * CHUNKS + threadIdx.x; c < 16 * CHUNKS; c += NTHREADS)
+            *reinterpret_cast<uint4*>(Qs + (c / CHUNKS) * KSTR + (c % CHUNKS) * 8) = make_uint4(0, 0, 0, 0);
+    }
     asm volatile("griddepcontrol.wait;" ::: "memory");
-    for (int c = threadIdx.x; c < 16 * CHUNKS; c += NTHREADS) {
-        const int r = c / CHUNKS, ch = c % CHUNKS;
-        const bool ok = r < G;
-        const bf16* src = ok ? q + (size_t)tok * q_stride + (size_t)(kh * G + r) * D + ch * 8 : q;
-        cp_async16(Qs + r * KSTR + ch * 8, src, ok);
+    if constexpr (HEADS) {
+        const bf16* row = q + (size_t)tok * q_stride;
+        if (owner && warp < 2) {
+            // the newest key (warp 0) and value (warp 1) are asked for beside the query heads
+            const bf16* src = row + (size_t)(nq + warp * nkv + kh) * D;
+            load_run<C>(new_a, src + e0);
+            load_run<C>(new_b, src + D / 2 + e0);
+        }
+        for (int r = warp; r < G; r += NTHREADS / 32) {
+            __align__(8) bf16 a[C], b[C];
+            const bf16* src = row + (size_t)(kh * G + r) * D;
+            load_run<C>(a, src + e0);
+            load_run<C>(b, src + D / 2 + e0);
+            finish_head<C>(a, b, hd.q_norm_w != nullptr, wl, wh, hd.eps, rotate && pos_ok, cs_c, cs_s);
+            store_run<C>(Qs + r * KSTR + e0, a);
+            store_run<C>(Qs + r * KSTR + D / 2 + e0, b);
+        }
+        if (rotate && !pos_ok && threadIdx.x == 0) atomicExch(hd.status, 3);
+        if (owner && warp < 2) {
+            if (warp == 0) {
+                float kl[C], kh_w[C];
+#pragma unroll
+                for (int j = 0; j < C; ++j) {
+                    kl[j] = hd.k_norm_w ? hd.k_norm_w[e0 + j] : 1.f;
+                    kh_w[j] = hd.k_norm_w ? hd.k_norm_w[D / 2 + e0 + j] : 1.f;
+                }
+                finish_head<C>(new_a, new_b, hd.k_norm_w != nullptr, kl, kh_w, hd.eps, rotate && pos_ok, cs_c, cs_s);
+            }
+            if (new_page >= 0 && new_page < num_blocks) {
+                bf16* dst = hd.cache_w +
+                            ((((size_t)new_page * 2 + warp) * nkv + kh) * block_size + pos % block_size) * D;
+                store_run<C>(dst + e0, new_a);
+                store_run<C>(dst + D / 2 + e0, new_b);
+            } else if (lane == 0) {
+                atomicExch(hd.status, 2);
+            }
+        }
+    } else {
+        for (int c = threadIdx.x; c < 16 * CHUNKS; c += NTHREADS) {
+            const int r = c / CHUNKS, ch = c % CHUNKS;
+            const bool ok = r < G;
+            const bf16* src = ok ? q + (size_t)tok * q_stride + (size_t)(kh * G + r) * D + ch * 8 : q;
+            cp_async16(Qs + r * KSTR + ch * 8, src, ok);
+        }
     }
     if (!early && t_begin < t_end) load_kv_tile(Ks, Vs, cache, s_row_off[0], v_off);
     cp_async_commit();
@@ -403,6 +551,16 @@ attn_decode_kernel(const bf16* __restrict__ q, int q_stride, const bf16* __restr
             cp_async_wait<0>();
         }
         __syncthreads();
+        if (HEADS && owner && t == t_last) {
+            // the tile's copy of the newest row may be older than this block's write to the page:
+            // the finished key and value go into the tile from the registers that hold them
+            if (warp < 2) {
+                bf16* dst = (warp == 0 ? Ks : Vs) + (buf * BN + (pos - t_last * BN)) * KSTR;
+                store_run<C>(dst + e0, new_a);
+                store_run<C>(dst + D / 2 + e0, new_b);
+            }
+            __syncthreads();
+        }
         // the offsets of tile t are used up: look up those of tile t+2.  The page id is asked for now and
         // written to shared memory after this tile's arithmetic, so its trip to memory costs nothing.
         const bool look = t + 2 < t_end && threadIdx.x < BN;
@@ -459,6 +617,27 @@ attn_decode_kernel(const bf16* __restrict__ q, int q_stride, const bf16* __restr
             if (col == 0) { part_ml[p * 2] = M; part_ml[p * 2 + 1] = L; }
         }
     }
+}
+
+__global__ void __launch_bounds__(NTHREADS)
+attn_decode_kernel(const bf16* __restrict__ q, int q_stride, const bf16* __restrict__ cache,
+                   const int* __restrict__ block_table, int max_blocks, const int* __restrict__ cu_q,
+                   const int* __restrict__ ctx_lens, bf16* __restrict__ out, int out_stride,
+                   float* __restrict__ part_o, float* __restrict__ part_ml, int nq, int nkv,
+                   int block_size, int num_blocks, float scale_log2, int window, int num_splits) {
+    attn_decode_body<false>(q, q_stride, cache, block_table, max_blocks, cu_q, ctx_lens, out, out_stride, part_o,
+                            part_ml, nq, nkv, block_size, num_blocks, scale_log2, window, num_splits, DecodeHeads{});
+}
+__global__ void __launch_bounds__(NTHREADS)
+attn_decode_heads_kernel(const bf16* __restrict__ qkv, int row_width, const bf16* __restrict__ cache,
+                         const int* __restrict__ block_table, int max_blocks, const int* __restrict__ cu_q,
+                         const int* __restrict__ ctx_lens, bf16* __restrict__ out, int out_stride,
+                         float* __restrict__ part_o, float* __restrict__ part_ml, int nq, int nkv,
+                         int block_size, int num_blocks, float scale_log2, int window, int num_splits,
+                         DecodeHeads hd) {
+    if constexpr (D % 64 == 0)
+        attn_decode_body<true>(qkv, row_width, cache, block_table, max_blocks, cu_q, ctx_lens, out, out_stride,
+                               part_o, part_ml, nq, nkv, block_size, num_blocks, scale_log2, window, num_splits, hd);
 }
 
 // out[token of seq, head, :] = sum_s w_s o_s / sum_s w_s l_s,  w_s = 2^(m_s - max m).
@@ -561,6 +740,41 @@ FF_EXPORT int ff_attn_decode(const void* q, int q_stride, const void* cache, con
     FF_LAUNCH((attn_decode_kernel), grid, NTHREADS, DECODE_SMEM, stream, 
         (const bf16*)q, q_stride, (const bf16*)cache, block_table, max_blocks, cu_q, ctx_lens, (bf16*)out,
         out_stride, part_o, part_ml, nq, nkv, block_size, num_blocks, scale * LOG2E, window, num_splits);
+    FF_LAUNCH_CHECK();
+    if (num_splits > 1) {
+        dim3 cgrid(n_seqs, nq);
+        FF_LAUNCH((attn_combine_kernel), cgrid, D >= 128 ? 128 : 64, 0, stream, part_o, part_ml, cu_q, (bf16*)out,
+                                                                     out_stride, nq, num_splits);
+        FF_LAUNCH_CHECK();
+    }
+    return 0;
+}
+
+// The same with the heads of the newest token finished inside the kernel: `qkv` is the raw output
+// of the q|k|v projection ([tokens][row_width]: q heads, k heads, v heads), the norm weights may be
+// null (no per-head norm), cos_sin may be null (no rotation; else the whole head is rotated).
+// Head sizes that are multiples of 64 only.
+FF_EXPORT int ff_attn_decode_heads(const void* qkv, int row_width, void* cache, const int* block_table,
+                                   int max_blocks, const int* cu_q, const int* ctx_lens, int n_seqs, void* out,
+                                   int out_stride, float* part_o, float* part_ml, int nq, int nkv,
+                                   int block_size, int num_blocks, float scale, int window, int num_splits,
+                                   const float* q_norm_w, const float* k_norm_w, float eps,
+                                   const float* cos_sin, int max_positions, int* status, cudaStream_t stream) {
+    if (n_seqs <= 0) return 0;
+    if (nkv <= 0 || nq % nkv || num_splits < 1 || status == nullptr) return FF_ERR_BAD_ARG;
+    if (nq / nkv > 16 || D % 64 != 0) return FF_ERR_UNSUPPORTED;
+    static bool attr_set = false;
+    if (!attr_set) {
+        cudaError_t e = cudaFuncSetAttribute(attn_decode_heads_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                             (int)DECODE_SMEM);
+        if (e != cudaSuccess) return (int)e;
+        attr_set = true;
+    }
+    DecodeHeads hd{q_norm_w, k_norm_w, eps, cos_sin, max_positions, (bf16*)cache, status};
+    dim3 grid(n_seqs, nkv, num_splits);
+    FF_LAUNCH((attn_decode_heads_kernel), grid, NTHREADS, DECODE_SMEM, stream,
+        (const bf16*)qkv, row_width, (const bf16*)cache, block_table, max_blocks, cu_q, ctx_lens, (bf16*)out,
+        out_stride, part_o, part_ml, nq, nkv, block_size, num_blocks, scale * LOG2E, window, num_splits, hd);
     FF_LAUNCH_CHECK();
     if (num_splits > 1) {
         dim3 cgrid(n_seqs, nq);

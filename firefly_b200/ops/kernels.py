@@ -384,6 +384,42 @@ def attn_decode(q, q_stride, pages, table, cu_q, ctx_lens, n_seqs, out, part_o, 
         LAUNCHES += 1     # the kernel that joins the splits
 
 
+DECODE_FINISHES_HEADS = True    # pure decode steps: per-head norm, rotation and cache write inside the attention kernel
+
+
+def decode_finishes_heads(ctx, dtype: torch.dtype, nq: int, nkv: int, d: int, rotary_dim: int) -> bool:
+    """True if this step's attention kernel can take the raw q|k|v projection: every sequence
+    decodes one token, bfloat16, a head size in steps of 64 that is rotated whole or not at all,
+    and at most 16 query heads per kv head."""
+    return (DECODE_FINISHES_HEADS and not _ATTN_FORCE_SIMT and ctx.num_seqs > 0
+            and ctx.num_decode_seqs == ctx.num_seqs and dtype == torch.bfloat16 and d % 64 == 0 and d <= 256
+            and nkv > 0 and nq // nkv <= 16 and rotary_dim in (0, d))
+
+
+def attn_decode_heads(qkv, pages, table, ctx, out, nq, nkv, d, scale, window, q_norm_w, k_norm_w, eps,
+                      cos_sin, num_splits: Optional[int] = None) -> None:
+    """The split-KV decode attention fed with the raw q|k|v projection ``[T, (nq + 2 nkv) d]``:
+    it finishes the heads itself (per-head RMSNorm, rotation, cache write of the newest key and
+    value) and replaces `qk_norm_rope_store` + `attn_decode` in steps that only decode."""
+    _need_cuda(qkv, pages, table, out, q_norm_w, k_norm_w, cos_sin)
+    num_blocks, _, _, block_size, _ = pages.shape
+    n = ctx.num_seqs
+    splits = num_splits or decode_splits(n, nkv, ctx.max_kv_len)
+    G = nq // nkv
+    cap = max(n * nq * splits, G * _SM_TARGET_CTAS + n * nq)
+    part_o = ctx.workspace.get("attn.part_o", (cap * d,), torch.float32)
+    part_ml = ctx.workspace.get("attn.part_ml", (cap * 2,), torch.float32)
+    _check(_attn_lib(d).ff_attn_decode_heads(
+        _p(qkv), c_int(qkv.shape[1]), _p(pages), _p(table), c_int(table.shape[1]), _p(ctx.cu_q), _p(ctx.ctx_lens),
+        c_int(n), _p(out), c_int(out.shape[1]), _p(part_o), _p(part_ml), c_int(nq), c_int(nkv),
+        c_int(block_size), c_int(num_blocks), c_float(scale), c_int(window), c_int(splits),
+        _p(q_norm_w), _p(k_norm_w), c_float(eps), _p(cos_sin), c_int(cos_sin.shape[0] if cos_sin is not None else 0),
+        _p(ctx.status), _stream()), "attn_decode_heads")
+    global LAUNCHES
+    if splits > 1:
+        LAUNCHES += 1     # the kernel that joins the splits
+
+
 USE_TC_ATTENTION = True     # tcgen05 attention for prompt portions where the sizes allow
 
 

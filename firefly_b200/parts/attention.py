@@ -101,12 +101,18 @@ class GQAttention(Part):
         pages, table = ctx.kv(slot)
         rot = self.position.rotary_table() if self.position is not None else None
         cos_sin, rotary_dim = rot if rot is not None else (None, 0)
-        K.qk_norm_rope_store(qkv, self.nq, nkv_w, self.d, self.q_norm_w,
-                             self.k_norm_w if write_cache else None, self.eps, cos_sin, rotary_dim,
-                             ctx.positions, ctx.token_seq, table if write_cache else None,
-                             pages if write_cache else None, ctx.status)
         att = ws.get("attn.out", (T, self.nq * self.d), ctx.dtype)
-        self._attend(qkv, width, pages, table, ctx, att)
+        if write_cache and K.decode_finishes_heads(ctx, ctx.dtype, self.nq, self.nkv, self.d, rotary_dim):
+            # a step of single tokens: the attention kernel finishes the heads itself
+            K.attn_decode_heads(qkv, pages, table, ctx, att, self.nq, self.nkv, self.d, self.scale,
+                                0 if self.window is None else int(self.window), self.q_norm_w,
+                                self.k_norm_w, self.eps, cos_sin)
+        else:
+            K.qk_norm_rope_store(qkv, self.nq, nkv_w, self.d, self.q_norm_w,
+                                 self.k_norm_w if write_cache else None, self.eps, cos_sin, rotary_dim,
+                                 ctx.positions, ctx.token_seq, table if write_cache else None,
+                                 pages if write_cache else None, ctx.status)
+            self._attend(qkv, width, pages, table, ctx, att)
         return linear_into_residual(att, self.w_o, accumulate_into, ctx, "attn.proj", then_norm)
 
     def _attend(self, qkv, width, pages, table, ctx, att) -> None:

@@ -267,6 +267,100 @@ def test_attention_decode_tensor_core(d, nq, nkv, block, window, splits):
     assert float(err) < 2e-2, float(err)
 
 
+class _Scratch:
+    def __init__(self):
+        self.bufs = {}
+
+    def get(self, name, shape, dtype):
+        key = (name, tuple(shape), dtype)
+        if key not in self.bufs:
+            self.bufs[key] = torch.full(tuple(shape), float("nan"), dtype=dtype, device="cuda")
+        return self.bufs[key]
+
+
+@pytest.mark.parametrize("d,nq,nkv,block", [(64, 8, 1, 16), (128, 8, 2, 16), (192, 5, 5, 8), (256, 4, 2, 64),
+                                            (128, 32, 2, 32), (64, 6, 2, 4)])
+@pytest.mark.parametrize("window", [None, 100])
+@pytest.mark.parametrize("splits", [1, 2, 5])
+@pytest.mark.parametrize("norm,rot", [(True, True), (False, True), (True, False)])
+def test_attention_decode_that_finishes_the_heads(d, nq, nkv, block, window, splits, norm, rot):
+    """The decode kernel fed with the raw q|k|v projection against the two-kernel route (head kernel,
+    then attention), which it equals bit for bit in its output and in the pages where both do the
+    same arithmetic, and against the plain attention over the finished heads.  Contexts end on and beside tile and page edges."""
+    from types import SimpleNamespace
+    ctxs = [0, 1, 15, 63, 64, 65, 127, 128, 200, 517]
+    n = len(ctxs)
+    seqs = [(c, 1) for c in ctxs]
+    theta, eps = 9000.0, 1e-5
+    torch.manual_seed(d + nq)
+    # history: finished keys and values in the pages; the row of the newest token holds stale data
+    c = _attention_case(d, nq, nkv, block, seqs, window, torch.bfloat16, seed=11, spike=False)
+    width = (nq + 2 * nkv) * d
+    raw = torch.randn(n, width).to(torch.bfloat16)
+    qw = (1 + 0.1 * torch.randn(d)) if norm else None
+    kw = (1 + 0.1 * torch.randn(d)) if norm else None
+    half = d // 2
+    freq = torch.pow(torch.tensor(theta, dtype=torch.float64), -2.0 * torch.arange(half, dtype=torch.float64) / d)
+    ang = torch.arange(max(ctxs) + 2, dtype=torch.float64)[:, None] * freq[None]
+    cs = torch.stack([torch.cos(ang), torch.sin(ang)], -1).float() if rot else None
+    pages0 = c["pages"].clone()
+    for i, p in enumerate(ctxs):                    # stale rows where the newest token goes
+        pages0[int(c["table"][i, p // block]), :, :, p % block] = 77.0
+    g = lambda t: None if t is None else dev(t)
+    table, cu_q, ctx_lens = dev(c["table"]), dev(c["cu_q"]), dev(c["ctx_lens"])
+    scale, win = 1 / math.sqrt(d), window or 0
+
+    # two kernels
+    qkv_a, pages_a = dev(raw.clone()), dev(pages0.clone())
+    out_a = torch.zeros(n, nq * d, dtype=torch.bfloat16, device="cuda")
+    status = torch.zeros(1, dtype=torch.int32, device="cuda")
+    K().qk_norm_rope_store(qkv_a, nq, nkv, d, g(qw), g(kw), eps, g(cs), d if rot else 0, ctx_lens,
+                           dev(torch.arange(n, dtype=torch.int32)), table, pages_a, status)
+    part_o = torch.full((n * nq * splits * d,), float("nan"), device="cuda")
+    part_ml = torch.full((n * nq * splits * 2,), float("nan"), device="cuda")
+    K().attn_decode(qkv_a, width, pages_a, table, cu_q, ctx_lens, n, out_a, part_o, part_ml, nq, nkv, d, scale,
+                    win, splits)
+    # one kernel
+    qkv_b, pages_b = dev(raw.clone()), dev(pages0.clone())
+    out_b = torch.zeros(n, nq * d, dtype=torch.bfloat16, device="cuda")
+    ctx = SimpleNamespace(num_seqs=n, cu_q=cu_q, ctx_lens=ctx_lens, max_kv_len=max(ctxs) + 1, workspace=_Scratch(),
+                          status=status)
+    K().attn_decode_heads(qkv_b, pages_b, table, ctx, out_b, nq, nkv, d, scale, win, g(qw), g(kw), eps, g(cs),
+                          num_splits=splits)
+    torch.cuda.synchronize()
+    assert int(status) == 0
+    assert torch.equal(qkv_b.cpu(), raw)                           # the projection's output is left as it was
+    if d in (128, 256):          # the head kernel's register form does the same arithmetic in the same order
+        assert torch.equal(pages_a.cpu(), pages_b.cpu())
+        assert torch.equal(out_a.cpu(), out_b.cpu())
+    else:
+        assert torch.allclose(pages_a.cpu().float(), pages_b.cpu().float(), atol=2e-2, rtol=2e-2)
+        assert torch.allclose(out_a.cpu().float(), out_b.cpu().float(), atol=2e-2, rtol=2e-2)
+    # and the plain result: heads finished in 64-bit, attention over history + newest token
+    x = raw.double()
+    q = x[:, :nq * d].view(n, nq, d)
+    k = x[:, nq * d:(nq + nkv) * d].view(n, nkv, d)
+    v = x[:, (nq + nkv) * d:].view(n, nkv, d)
+    pos = torch.tensor(ctxs, dtype=torch.int32)
+    if norm:
+        q, k = P.rms_norm(q, qw.double(), eps), P.rms_norm(k, kw.double(), eps)
+    if rot:
+        q, k = P.rope(q, pos, theta), P.rope(k, pos, theta)
+    gp = pages_b.cpu().double()
+    G = nq // nkv
+    for i, p in enumerate(ctxs):
+        pg = int(c["table"][i, p // block])
+        assert torch.allclose(gp[pg, 0, :, p % block], k[i], atol=2e-2, rtol=2e-2)
+        assert torch.equal(gp[pg, 1, :, p % block], v[i])
+        ks = torch.stack([gp[int(c["table"][i, t // block]), 0, :, t % block] for t in range(p + 1)])
+        vs = torch.stack([gp[int(c["table"][i, t // block]), 1, :, t % block] for t in range(p + 1)])
+        qs = torch.zeros(p + 1, nq, d, dtype=torch.float64)
+        qs[p] = q[i].to(torch.bfloat16).double()
+        want = P.attention(qs, ks, vs, window=window)[p].reshape(-1)
+        got = out_b[i].cpu().double()
+        assert float((got - want).abs().max() / want.abs().max()) < 2e-2
+
+
 def test_attention_q_inside_wider_buffer():
     """q read in place from a [T, (nq+2nkv)*d] projection output."""
     d, nq, nkv, block = 64, 4, 2, 16
