@@ -460,6 +460,11 @@ attn_decode_body(const bf16* __restrict__ q, int q_stride, const bf16* __restric
     // the first tile can go early if it ends before the newest key, or if that key is put into the tile later
     const bool early = t_begin < t_end && (HEADS || (t_begin + 1) * BN <= pos);
     if (early) load_kv_tile(Ks, Vs, cache, s_row_off[0], v_off);
+    if constexpr (HEADS) {           // no key in the pages depends on the kernel in front: the second tile goes too
+        cp_async_commit();
+        if (t_begin + 1 < t_end) load_kv_tile(Ks + BN * KSTR, Vs + BN * KSTR, cache, s_row_off[1], v_off);
+        cp_async_commit();
+    }
     // HEADS: what the finishing of the heads needs besides the projection's output
     constexpr int C = HC > 0 ? HC : 1;
     const int t_last = pos / BN;                                  // the tile of the newest key
@@ -535,8 +540,12 @@ attn_decode_body(const bf16* __restrict__ q, int q_stride, const bf16* __restric
             cp_async16(Qs + r * KSTR + ch * 8, src, ok);
         }
     }
-    if (!early && t_begin < t_end) load_kv_tile(Ks, Vs, cache, s_row_off[0], v_off);
-    cp_async_commit();
+    if constexpr (!HEADS) {
+        if (!early && t_begin < t_end) load_kv_tile(Ks, Vs, cache, s_row_off[0], v_off);
+        cp_async_commit();
+        if (t_begin + 1 < t_end) load_kv_tile(Ks + BN * KSTR, Vs + BN * KSTR, cache, s_row_off[1], v_off);
+        cp_async_commit();
+    }
 
     int lo[2] = {kv_lo, kv_lo}, hi[2] = {kv_hi, kv_hi};
     WarpState<16> st;
@@ -544,8 +553,10 @@ attn_decode_body(const bf16* __restrict__ q, int q_stride, const bf16* __restric
     for (int t = t_begin; t < t_end; ++t) {
         const int buf = (t - t_begin) & 1;
         if (t + 1 < t_end) {
-            load_kv_tile(Ks + (buf ^ 1) * BN * KSTR, Vs + (buf ^ 1) * BN * KSTR, cache, s_row_off[buf ^ 1], v_off);
-            cp_async_commit();
+            if (t != t_begin) {      // the first two tiles were asked for above
+                load_kv_tile(Ks + (buf ^ 1) * BN * KSTR, Vs + (buf ^ 1) * BN * KSTR, cache, s_row_off[buf ^ 1], v_off);
+                cp_async_commit();
+            }
             cp_async_wait<1>();
         } else {
             cp_async_wait<0>();
@@ -579,20 +590,22 @@ attn_decode_body(const bf16* __restrict__ q, int q_stride, const bf16* __restric
     cp_async_wait<0>();
     st.finish_sums();
     __syncthreads();
-    // join the four warps (rows g and g+8 of each; only rows < G matter)
-    float* sm_o = reinterpret_cast<float*>(Ks);                   // [4][16][D]
-    float* sm_m = sm_o + 4 * 16 * D;                              // [4][16]
+    // join the four warps: rows g and g+8 of each, of which only the group's rows (< G) are kept.
+    // A row is D + 8 floats apart from the next, so the quads of a warp store to distinct banks.
+    constexpr int JSTR = D + 8;
+    float* sm_o = reinterpret_cast<float*>(Ks);                   // [4][16][JSTR]
+    float* sm_m = sm_o + 4 * 16 * JSTR;                           // [4][16]
     float* sm_l = sm_m + 4 * 16;                                  // [4][16]
     const int g = lane >> 2, t4 = lane & 3;
 #pragma unroll
     for (int r = 0; r < 2; ++r) {
         const int row = g + 8 * r;
+        if (row >= G) continue;
         if (t4 == 0) { sm_m[warp * 16 + row] = st.m[r]; sm_l[warp * 16 + row] = st.l[r]; }
 #pragma unroll
-        for (int i = 0; i < D / 8; ++i) {
-            sm_o[(warp * 16 + row) * D + i * 8 + 2 * t4] = st.o[i][2 * r];
-            sm_o[(warp * 16 + row) * D + i * 8 + 2 * t4 + 1] = st.o[i][2 * r + 1];
-        }
+        for (int i = 0; i < D / 8; ++i)
+            *reinterpret_cast<float2*>(sm_o + (warp * 16 + row) * JSTR + i * 8 + 2 * t4) =
+                make_float2(st.o[i][2 * r], st.o[i][2 * r + 1]);
     }
     __syncthreads();
     for (int idx = threadIdx.x; idx < G * D; idx += NTHREADS) {
@@ -606,7 +619,7 @@ attn_decode_body(const bf16* __restrict__ q, int q_stride, const bf16* __restric
             const float mw = sm_m[w * 16 + row];
             const float wt = mw == -CUDART_INF_F ? 0.f : exp2f(mw - M);
             L += wt * sm_l[w * 16 + row];
-            O += wt * sm_o[(w * 16 + row) * D + col];
+            O += wt * sm_o[(w * 16 + row) * JSTR + col];
         }
         const int head = kh * G + row;
         if (num_splits == 1) {
@@ -686,7 +699,7 @@ __global__ void attn_combine_kernel(const float* __restrict__ part_o, const floa
 
 constexpr size_t TILED_SMEM = (size_t)(BM + 4 * BN) * KSTR * sizeof(bf16);
 constexpr size_t DECODE_KV_SMEM = (size_t)(4 * BN) * KSTR * sizeof(bf16);
-constexpr size_t DECODE_JOIN_SMEM = (size_t)(4 * 16 * D + 2 * 4 * 16) * sizeof(float);
+constexpr size_t DECODE_JOIN_SMEM = (size_t)(4 * 16 * (D + 8) + 2 * 4 * 16) * sizeof(float);
 constexpr size_t DECODE_SMEM = (size_t)16 * KSTR * sizeof(bf16) +
                                (DECODE_KV_SMEM > DECODE_JOIN_SMEM ? DECODE_KV_SMEM : DECODE_JOIN_SMEM);
 
