@@ -421,14 +421,26 @@ __device__ __forceinline__ void finish_head(bf16 (&a)[C], bf16 (&b)[C], bool nor
     for (int j = 0; j < C; ++j) { a[j] = __float2bfloat16_rn(lo[j]); b[j] = __float2bfloat16_rn(hi[j]); }
 }
 
-template <bool HEADS>
+// UNITS = true: the ranges of keys are given out by length.  grid (kv head, unit): the units are
+// shared out among the sequences in proportion to their tiles of keys, one at least for each, so
+// that a step's blocks fill the SMs' places exactly once whatever the lengths are (a fixed number
+// of ranges per sequence leaves places empty or starts a second round).  Every block works the
+// share-out out for itself from the context lengths, before it waits for the kernel in front.
+struct DecodeUnits {
+    int n_seqs;                // at most NTHREADS, at most gridDim.y
+    int max_ranges;            // no sequence is cut into more ranges than this
+    int* seq_ranges;           // [n_seqs] out: the number of ranges of each sequence, for the join
+    int part_stride;           // partial results of a (sequence, head) lie this many apart
+};
+
+template <bool HEADS, bool UNITS>
 __device__ __forceinline__ void
 attn_decode_body(const bf16* __restrict__ q, int q_stride, const bf16* __restrict__ cache,
                  const int* __restrict__ block_table, int max_blocks, const int* __restrict__ cu_q,
                  const int* __restrict__ ctx_lens, bf16* __restrict__ out, int out_stride,
                  float* __restrict__ part_o, float* __restrict__ part_ml, int nq, int nkv,
                  int block_size, int num_blocks, float scale_log2, int window, int num_splits,
-                 const DecodeHeads& hd) {
+                 const DecodeHeads& hd, const DecodeUnits& un) {
     // The kernel in front of this one (per-head norm, rotation and cache write, or the projection
     // itself) produces q and the newest key and value only.  The step's metadata and every older key
     // do not depend on it: they are fetched before the wait for that kernel, so the first tile is
@@ -439,16 +451,75 @@ attn_decode_body(const bf16* __restrict__ q, int q_stride, const bf16* __restric
     bf16* Ks = Qs + 16 * KSTR;                                    // [2][BN][KSTR]
     bf16* Vs = Ks + 2 * BN * KSTR;                                // [2][BN][KSTR]
     const int G = nq / nkv;
-    const int seq = blockIdx.x, kh = blockIdx.y, split = blockIdx.z;
     const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+    int seq, kh, split, ranges, part_stride, pos;
+    if constexpr (UNITS) {
+        __shared__ int s_warp_tiles[NTHREADS / 32];
+        __shared__ int s_mine[4];
+        kh = blockIdx.x;
+        const int unit = blockIdx.y, units = gridDim.y, n = un.n_seqs;
+        const int i = threadIdx.x;                                 // thread i looks at sequence i
+        int tiles = 0, p = 0;
+        if (i < n) {
+            p = ctx_lens[i];
+            tiles = (p + BN) / BN - (window > 0 ? max(0, p - window + 1) : 0) / BN;
+        }
+        int incl = tiles;
+#pragma unroll
+        for (int o = 1; o < 32; o <<= 1) {
+            const int v = __shfl_up_sync(0xffffffffu, incl, o);
+            if (lane >= o) incl += v;
+        }
+        if (lane == 31) s_warp_tiles[warp] = incl;
+        if (i == 0) s_mine[0] = -1;
+        __syncthreads();
+        int before = 0, all = 0;
+#pragma unroll
+        for (int w = 0; w < NTHREADS / 32; ++w) {
+            if (w < warp) before += s_warp_tiles[w];
+            all += s_warp_tiles[w];
+        }
+        // sequence i owns the units [i + spare * tiles before it / all, i + 1 + spare * tiles up to it / all);
+        // the host has seen to it that spare * all fits 31 bits
+        const unsigned spare = units - n;
+        const unsigned excl = before + incl - tiles;
+        const int u0 = i + (int)(spare * excl / (unsigned)all);
+        const int u1 = i + 1 + (int)(spare * (excl + tiles) / (unsigned)all);
+        if (i < n && unit >= u0 && unit < u1) {
+            s_mine[0] = i;
+            s_mine[1] = unit - u0;
+            s_mine[2] = min(min(u1 - u0, tiles), un.max_ranges);
+            s_mine[3] = p;
+        }
+        __syncthreads();
+        seq = s_mine[0];
+        split = s_mine[1];
+        ranges = s_mine[2];
+        part_stride = un.part_stride;
+        if (seq < 0 || split >= ranges) return;                    // a unit without work
+        pos = s_mine[3];
+    } else {
+        seq = blockIdx.x;
+        kh = blockIdx.y;
+        split = blockIdx.z;
+        ranges = num_splits;
+        part_stride = num_splits;
+        pos = ctx_lens[seq];
+    }
     const int tok = cu_q[seq];
-    const int pos = ctx_lens[seq];
     const int kv_hi = pos + 1;
     const int kv_lo = window > 0 ? max(0, pos - window + 1) : 0;
     const int* bt = block_table + (size_t)seq * max_blocks;
     const int t0 = kv_lo / BN, t1 = (kv_hi + BN - 1) / BN;
-    const int per = (t1 - t0 + num_splits - 1) / num_splits;
-    const int t_begin = t0 + split * per, t_end = min(t1, t_begin + per);
+    int t_begin, t_end;
+    if constexpr (UNITS) {       // ranges <= tiles: none is empty, and they differ by one tile at most
+        t_begin = t0 + (unsigned)((t1 - t0) * split) / (unsigned)ranges;
+        t_end = t0 + (unsigned)((t1 - t0) * (split + 1)) / (unsigned)ranges;
+    } else {
+        const int per = (t1 - t0 + ranges - 1) / ranges;
+        t_begin = t0 + split * per;
+        t_end = min(t1, t_begin + per);
+    }
 
     const size_t v_off = (size_t)nkv * block_size * D;
     __shared__ long long s_row_off[2][BN];
@@ -495,6 +566,9 @@ attn_decode_body(const bf16* __restrict__ q, int q_stride, const bf16* __restric
             *reinterpret_cast<uint4*>(Qs + (c / CHUNKS) * KSTR + (c % CHUNKS) * 8) = make_uint4(0, 0, 0, 0);
     }
     asm volatile("griddepcontrol.wait;" ::: "memory");
+    if constexpr (UNITS) {
+        if (split == 0 && kh == 0 && threadIdx.x == 0) un.seq_ranges[seq] = ranges;
+    }
     if constexpr (HEADS) {
         const bf16* row = q + (size_t)tok * q_stride;
         if (owner && warp < 2) {
@@ -622,10 +696,10 @@ attn_decode_body(const bf16* __restrict__ q, int q_stride, const bf16* __restric
             O += wt * sm_o[(w * 16 + row) * JSTR + col];
         }
         const int head = kh * G + row;
-        if (num_splits == 1) {
+        if (ranges == 1) {
             out[(size_t)tok * out_stride + (size_t)head * D + col] = __float2bfloat16_rn(O / L);
         } else {
-            const size_t p = ((size_t)seq * nq + head) * num_splits + split;
+            const size_t p = ((size_t)seq * nq + head) * part_stride + split;
             part_o[p * D + col] = O;
             if (col == 0) { part_ml[p * 2] = M; part_ml[p * 2 + 1] = L; }
         }
@@ -638,8 +712,9 @@ attn_decode_kernel(const bf16* __restrict__ q, int q_stride, const bf16* __restr
                    const int* __restrict__ ctx_lens, bf16* __restrict__ out, int out_stride,
                    float* __restrict__ part_o, float* __restrict__ part_ml, int nq, int nkv,
                    int block_size, int num_blocks, float scale_log2, int window, int num_splits) {
-    attn_decode_body<false>(q, q_stride, cache, block_table, max_blocks, cu_q, ctx_lens, out, out_stride, part_o,
-                            part_ml, nq, nkv, block_size, num_blocks, scale_log2, window, num_splits, DecodeHeads{});
+    attn_decode_body<false, false>(q, q_stride, cache, block_table, max_blocks, cu_q, ctx_lens, out, out_stride,
+                                   part_o, part_ml, nq, nkv, block_size, num_blocks, scale_log2, window, num_splits,
+                                   DecodeHeads{}, DecodeUnits{});
 }
 __global__ void __launch_bounds__(NTHREADS)
 attn_decode_heads_kernel(const bf16* __restrict__ qkv, int row_width, const bf16* __restrict__ cache,
@@ -649,33 +724,58 @@ attn_decode_heads_kernel(const bf16* __restrict__ qkv, int row_width, const bf16
                          int block_size, int num_blocks, float scale_log2, int window, int num_splits,
                          DecodeHeads hd) {
     if constexpr (D % 64 == 0)
-        attn_decode_body<true>(qkv, row_width, cache, block_table, max_blocks, cu_q, ctx_lens, out, out_stride,
-                               part_o, part_ml, nq, nkv, block_size, num_blocks, scale_log2, window, num_splits, hd);
+        attn_decode_body<true, false>(qkv, row_width, cache, block_table, max_blocks, cu_q, ctx_lens, out,
+                                      out_stride, part_o, part_ml, nq, nkv, block_size, num_blocks, scale_log2,
+                                      window, num_splits, hd, DecodeUnits{});
+}
+// grid (kv head, unit); HEADS as above
+template <bool HEADS>
+__global__ void __launch_bounds__(NTHREADS)
+attn_decode_units_kernel(const bf16* __restrict__ q, int q_stride, const bf16* __restrict__ cache,
+                         const int* __restrict__ block_table, int max_blocks, const int* __restrict__ cu_q,
+                         const int* __restrict__ ctx_lens, bf16* __restrict__ out, int out_stride,
+                         float* __restrict__ part_o, float* __restrict__ part_ml, int nq, int nkv,
+                         int block_size, int num_blocks, float scale_log2, int window, DecodeHeads hd,
+                         DecodeUnits un) {
+    if constexpr (!HEADS || D % 64 == 0)
+        attn_decode_body<HEADS, true>(q, q_stride, cache, block_table, max_blocks, cu_q, ctx_lens, out, out_stride,
+                                      part_o, part_ml, nq, nkv, block_size, num_blocks, scale_log2, window, 0, hd,
+                                      un);
 }
 
 // out[token of seq, head, :] = sum_s w_s o_s / sum_s w_s l_s,  w_s = 2^(m_s - max m).
 // The splits are taken eight at a time, all their loads issued before the first is used (one
 // trip to memory for up to eight splits), with a running maximum over the groups of eight.
-__global__ void attn_combine_kernel(const float* __restrict__ part_o, const float* __restrict__ part_ml,
-                                    const int* __restrict__ cu_q, bf16* __restrict__ out, int out_stride,
-                                    int nq, int num_splits) {
+// seq_ranges given: sequence s has seq_ranges[s] partial results, part_stride apart per (sequence,
+// head); with one range its output is final already.
+__device__ __forceinline__ void attn_combine_body(const float* __restrict__ part_o,
+                                                  const float* __restrict__ part_ml,
+                                                  const int* __restrict__ cu_q, bf16* __restrict__ out,
+                                                  int out_stride, int nq, int num_splits,
+                                                  const int* __restrict__ seq_ranges, int part_stride) {
     pdl_prologue();
     const int seq = blockIdx.x, head = blockIdx.y;
-    const size_t base = ((size_t)seq * nq + head) * num_splits;
+    // The count of a sequence's partial results is asked for together with the first eight of them
+    // (which may lie beyond the count: they are read from the scratch memory and then ignored).
+    const int readable = seq_ranges != nullptr ? part_stride : num_splits;
+    if (seq_ranges != nullptr) num_splits = seq_ranges[seq];
+    const size_t base = ((size_t)seq * nq + head) * part_stride;
     const int tok = cu_q[seq];
     for (int col = threadIdx.x; col < D; col += blockDim.x) {
         float M = -CUDART_INF_F, L = 0.f, O = 0.f;
-        for (int s0 = 0; s0 < num_splits; s0 += 8) {
+        for (int s0 = 0; s0 == 0 || s0 < num_splits; s0 += 8) {
             float ms[8], ls[8], os[8];
 #pragma unroll
             for (int k = 0; k < 8; ++k) {
-                const bool have = s0 + k < num_splits;
-                const size_t p = base + min(s0 + k, num_splits - 1);
+                const size_t p = base + min(s0 + k, readable - 1);
                 ms[k] = part_ml[p * 2];
                 ls[k] = part_ml[p * 2 + 1];
                 os[k] = part_o[p * D + col];
-                if (!have) ms[k] = -CUDART_INF_F;
             }
+            if (seq_ranges != nullptr && num_splits <= 1) return;   // one range: the output is final already
+#pragma unroll
+            for (int k = 0; k < 8; ++k)
+                if (s0 + k >= num_splits) ms[k] = -CUDART_INF_F;
             float Mn = M;
 #pragma unroll
             for (int k = 0; k < 8; ++k) Mn = fmaxf(Mn, ms[k]);
@@ -695,6 +795,16 @@ __global__ void attn_combine_kernel(const float* __restrict__ part_o, const floa
         }
         out[(size_t)tok * out_stride + (size_t)head * D + col] = __float2bfloat16_rn(O / L);
     }
+}
+__global__ void attn_combine_kernel(const float* __restrict__ part_o, const float* __restrict__ part_ml,
+                                    const int* __restrict__ cu_q, bf16* __restrict__ out, int out_stride,
+                                    int nq, int num_splits) {
+    attn_combine_body(part_o, part_ml, cu_q, out, out_stride, nq, num_splits, nullptr, num_splits);
+}
+__global__ void attn_combine_units_kernel(const float* __restrict__ part_o, const float* __restrict__ part_ml,
+                                          const int* __restrict__ cu_q, bf16* __restrict__ out, int out_stride,
+                                          int nq, const int* __restrict__ seq_ranges, int part_stride) {
+    attn_combine_body(part_o, part_ml, cu_q, out, out_stride, nq, 0, seq_ranges, part_stride);
 }
 
 constexpr size_t TILED_SMEM = (size_t)(BM + 4 * BN) * KSTR * sizeof(bf16);
@@ -796,4 +906,63 @@ FF_EXPORT int ff_attn_decode_heads(const void* qkv, int row_width, void* cache, 
         FF_LAUNCH_CHECK();
     }
     return 0;
+}
+
+// The ranges of keys shared out by length (see DecodeUnits): `units` blocks per kv head, of which
+// every sequence gets one at least (n_seqs <= units, n_seqs <= 128).  part_o: float
+// [n_seqs*nq*units*D], part_ml: float [n_seqs*nq*units*2], seq_ranges: int [n_seqs].
+// finish_heads != 0: `q` is the raw q|k|v projection and the arguments behind it are used as in
+// ff_attn_decode_heads; else they are ignored and q holds finished heads.
+FF_EXPORT int ff_attn_decode_units(const void* q, int q_stride, void* cache, const int* block_table,
+                                   int max_blocks, const int* cu_q, const int* ctx_lens, int n_seqs, void* out,
+                                   int out_stride, float* part_o, float* part_ml, int* seq_ranges, int nq,
+                                   int nkv, int block_size, int num_blocks, float scale, int window, int units,
+                                   int max_ranges, int finish_heads, const float* q_norm_w,
+                                   const float* k_norm_w, float eps, const float* cos_sin, int max_positions,
+                                   int* status, cudaStream_t stream) {
+    if (n_seqs <= 0) return 0;
+    if (nkv <= 0 || nq % nkv || units < n_seqs || n_seqs > NTHREADS || max_ranges < 1 || seq_ranges == nullptr)
+        return FF_ERR_BAD_ARG;
+    // the share-out multiplies (units - n_seqs) by a count of tiles: both within 31 bits together
+    const long long most_tiles = ((long long)max_blocks * block_size / BN + 2) * n_seqs;
+    if (most_tiles * (units - n_seqs + max_ranges) >= (1ll << 31)) return FF_ERR_UNSUPPORTED;
+    if (nq / nkv > 16) return FF_ERR_UNSUPPORTED;
+    if (finish_heads && (D % 64 != 0 || status == nullptr)) return FF_ERR_UNSUPPORTED;
+    static bool attr_set = false;
+    if (!attr_set) {
+        cudaError_t e = cudaFuncSetAttribute(attn_decode_units_kernel<true>,
+                                             cudaFuncAttributeMaxDynamicSharedMemorySize, (int)DECODE_SMEM);
+        if (e != cudaSuccess) return (int)e;
+        e = cudaFuncSetAttribute(attn_decode_units_kernel<false>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                 (int)DECODE_SMEM);
+        if (e != cudaSuccess) return (int)e;
+        attr_set = true;
+    }
+    DecodeHeads hd{q_norm_w, k_norm_w, eps, cos_sin, max_positions, (bf16*)cache, status};
+    DecodeUnits un{n_seqs, max_ranges, seq_ranges, units};
+    dim3 grid(nkv, units);
+    if (finish_heads)
+        FF_LAUNCH((attn_decode_units_kernel<true>), grid, NTHREADS, DECODE_SMEM, stream,
+            (const bf16*)q, q_stride, (const bf16*)cache, block_table, max_blocks, cu_q, ctx_lens, (bf16*)out,
+            out_stride, part_o, part_ml, nq, nkv, block_size, num_blocks, scale * LOG2E, window, hd, un);
+    else
+        FF_LAUNCH((attn_decode_units_kernel<false>), grid, NTHREADS, DECODE_SMEM, stream,
+            (const bf16*)q, q_stride, (const bf16*)cache, block_table, max_blocks, cu_q, ctx_lens, (bf16*)out,
+            out_stride, part_o, part_ml, nq, nkv, block_size, num_blocks, scale * LOG2E, window, hd, un);
+    FF_LAUNCH_CHECK();
+    if (units > n_seqs && max_ranges > 1) {
+        dim3 cgrid(n_seqs, nq);
+        FF_LAUNCH((attn_combine_units_kernel), cgrid, D >= 128 ? 128 : 64, 0, stream, part_o, part_ml, cu_q,
+                  (bf16*)out, out_stride, nq, (const int*)seq_ranges, units);
+        FF_LAUNCH_CHECK();
+    }
+    return 0;
+}
+
+// Blocks of the decode kernel that one SM holds at a time (shared memory and registers).
+FF_EXPORT int ff_attn_decode_blocks_per_sm() {
+    // an SM has 228 KB for its blocks, each taking 1 KB besides what it asks for; 64 K registers at up to 128 a thread
+    const int by_smem = (int)((228 * 1024) / (DECODE_SMEM + 1024 + 1088));
+    const int by_regs = 65536 / (128 * NTHREADS);
+    return by_smem < 1 ? 1 : (by_smem > by_regs ? by_regs : by_smem);
 }

@@ -86,6 +86,7 @@ class StepContext:
     pure_decode: bool = False
     num_decode_seqs: int = 0           # the first this-many sequences have exactly one token
     captured: bool = False             # being captured into a CUDA graph: launch shapes must be static
+    ranges_by_length: bool = False     # the decoding sequences differ much in length (a hint for the attention)
 
     def kv(self, slot: int) -> Tuple[torch.Tensor, torch.Tensor]:
         """Pages of cache slot ``slot`` and the block table of its group."""

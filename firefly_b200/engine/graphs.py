@@ -25,7 +25,7 @@ from .runner import MetaLayout, ModelRunner, StepEntry
 
 class _Bucket:
     __slots__ = ("size", "layout", "meta_host", "meta_stage", "meta_dev", "graph", "logits", "tokens", "h_tokens",
-                 "events", "launches", "lanes", "turn")
+                 "events", "launches", "lanes", "turn", "by_length")
 
 
 class LaunchedStep:
@@ -41,6 +41,7 @@ class DecodeGraphs:
         self.workspace = Workspace(runner.device)
         self.buckets: Dict[int, _Bucket] = {}
         self.replays = 0
+        self.replays_by_length = 0
         self.kernel_launches = 0
 
     def supports(self, n: int) -> bool:
@@ -155,6 +156,23 @@ class DecodeGraphs:
             b.logits = r.model.forward(ctx)
             K.sample(b.logits, b.tokens)
         b.launches = K.LAUNCHES - before      # own kernels in one replay
+        # A second graph of the same step for requests of very different lengths, if any kernel
+        # makes something of that hint (the attention then shares its blocks out by length).
+        # Both graphs work on the same buffers; (graph, logits, launches) or None.
+        b.by_length = None
+        ctx.ranges_by_length = True
+        calls = K.BY_LENGTH_CALLS
+        with torch.cuda.stream(side):
+            r.model.forward(ctx)              # warm-up of the kernels that only this form uses
+        torch.cuda.current_stream().wait_stream(side)
+        torch.cuda.synchronize(r.device)
+        if K.BY_LENGTH_CALLS != calls:
+            g2 = torch.cuda.CUDAGraph()
+            before = K.LAUNCHES
+            with torch.cuda.graph(g2):
+                logits2 = r.model.forward(ctx)
+                K.sample(logits2, b.tokens)
+            b.by_length = (g2, logits2, K.LAUNCHES - before)
         return b
 
     def launch(self, entries: Sequence[StepEntry], want_tokens: bool = True,
@@ -175,11 +193,15 @@ class DecodeGraphs:
         if tokens_from_last_replay:
             lay = b.layout
             b.meta_dev[lay.token_ids: lay.token_ids + n].copy_(b.tokens[:n], non_blocking=True)
-        b.graph.replay()
+        graph, logits, launches = b.graph, b.logits, b.launches
+        if b.by_length is not None and K.lengths_differ_much([e.cache.num_tokens for e in entries]):
+            graph, logits, launches = b.by_length
+            self.replays_by_length += 1
+        graph.replay()
         self.replays += 1
-        self.kernel_launches += b.launches
+        self.kernel_launches += launches
         step = LaunchedStep()
-        step.bucket, step.n, step.logits = b, n, b.logits[:n]
+        step.bucket, step.n, step.logits = b, n, logits[:n]
         step.h_tokens, step.event = None, None
         if want_tokens:
             step.h_tokens = b.h_tokens[k]

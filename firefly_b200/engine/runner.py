@@ -182,7 +182,8 @@ class ModelRunner:
             max_q_len=max(q_lens, default=0),
             max_kv_len=max((c + q for c, q in zip(ctx_lens, q_lens)), default=0),
             workspace=self.workspace, status=self.status, cache=self.cache, dtype=self.dtype,
-            pure_decode=all(q == 1 for q in q_lens), num_decode_seqs=sum(1 for q in q_lens if q == 1))
+            pure_decode=all(q == 1 for q in q_lens), num_decode_seqs=sum(1 for q in q_lens if q == 1),
+            ranges_by_length=K.lengths_differ_much([c for c, q in zip(ctx_lens, q_lens) if q == 1]))
 
     # ------------------------------------------------------------------------------
     def step(self, entries: Sequence[StepEntry]) -> torch.Tensor:

@@ -8,6 +8,7 @@ tensor that is not on a CUDA device, or a kernel that cannot be built, raises.
 from __future__ import annotations
 
 import ctypes
+import functools
 from ctypes import c_float, c_int, c_size_t, c_void_p
 from typing import Optional
 
@@ -404,18 +405,21 @@ def attn_decode_heads(qkv, pages, table, ctx, out, nq, nkv, d, scale, window, q_
     _need_cuda(qkv, pages, table, out, q_norm_w, k_norm_w, cos_sin)
     num_blocks, _, _, block_size, _ = pages.shape
     n = ctx.num_seqs
+    global LAUNCHES
+    units = 0 if num_splits else decode_units(n, nkv, d, ctx.ranges_by_length)
     splits = num_splits or decode_splits(n, nkv, ctx.max_kv_len)
-    G = nq // nkv
-    cap = max(n * nq * splits, G * _SM_TARGET_CTAS + n * nq)
-    part_o = ctx.workspace.get("attn.part_o", (cap * d,), torch.float32)
-    part_ml = ctx.workspace.get("attn.part_ml", (cap * 2,), torch.float32)
+    part_o, part_ml, seq_ranges = _decode_scratch(ctx.workspace, n, nq, nkv, d, splits)
+    if units:
+        attn_decode_units(qkv, qkv.shape[1], pages, table, ctx.cu_q, ctx.ctx_lens, n, out, part_o, part_ml,
+                          seq_ranges, nq, nkv, d, scale, window, units, DECODE_MAX_RANGES,
+                          heads=(q_norm_w, k_norm_w, eps, cos_sin), status=ctx.status)
+        return
     _check(_attn_lib(d).ff_attn_decode_heads(
         _p(qkv), c_int(qkv.shape[1]), _p(pages), _p(table), c_int(table.shape[1]), _p(ctx.cu_q), _p(ctx.ctx_lens),
         c_int(n), _p(out), c_int(out.shape[1]), _p(part_o), _p(part_ml), c_int(nq), c_int(nkv),
         c_int(block_size), c_int(num_blocks), c_float(scale), c_int(window), c_int(splits),
         _p(q_norm_w), _p(k_norm_w), c_float(eps), _p(cos_sin), c_int(cos_sin.shape[0] if cos_sin is not None else 0),
         _p(ctx.status), _stream()), "attn_decode_heads")
-    global LAUNCHES
     if splits > 1:
         LAUNCHES += 1     # the kernel that joins the splits
 
@@ -457,6 +461,73 @@ def decode_splits(n_seqs: int, nkv: int, max_kv_len: int) -> int:
     return max(1, min(want, tiles, 64))
 
 
+DECODE_BY_UNITS = True      # few sequences: ranges of keys shared out by length so that the blocks fill the SMs once
+DECODE_MAX_RANGES = 24      # a sequence is cut into at most this many ranges (batch 1 measured best near it)
+
+
+@functools.lru_cache(maxsize=None)
+def _decode_places_per_kv_head(nkv: int, d: int) -> int:
+    return _SM_COUNT * int(_attn_lib(d).ff_attn_decode_blocks_per_sm()) // nkv
+
+
+def lengths_differ_much(ctx_lens) -> bool:
+    """True if the longest of these decoding sequences has a quarter more tiles of keys than the
+    average: then a fixed number of ranges per sequence makes blocks of very different length, and
+    the attention shares its blocks out by length instead (`decode_units`)."""
+    if len(ctx_lens) < 2:
+        return False
+    tiles = [c // 64 + 1 for c in ctx_lens]
+    return max(tiles) >= 4 and max(tiles) * len(tiles) >= 1.25 * sum(tiles)
+
+
+BY_LENGTH_CALLS = 0         # how often the kernel that shares its blocks out by length was chosen
+
+
+def decode_units(n_seqs: int, nkv: int, d: int, by_length: bool) -> int:
+    """Blocks per kv head when the ranges of keys are shared out by length (as many as fill every
+    SM's places once, at most `DECODE_MAX_RANGES` a sequence), or 0 for the fixed number of ranges
+    of `decode_splits`.  Measured on the 8B shape, kernel and join alone, us: eight sequences of
+    200 to 6000 tokens 18.6 against 31.4 (six ranges each); seven of 100 and one of 16000 28 against
+    70; eight of 2100 17.7 against 17.2 (the share-out costs every block a scan of the lengths), so
+    equal lengths keep the fixed ranges.  Each sequence should get two units at least."""
+    if not (DECODE_BY_UNITS and by_length):
+        return 0
+    units = min(_decode_places_per_kv_head(nkv, d), n_seqs * DECODE_MAX_RANGES)
+    return units if 2 * n_seqs <= units and n_seqs <= 128 else 0
+
+
+def _decode_scratch(ws, n: int, nq: int, nkv: int, d: int, splits: int):
+    """Scratch memory of the decode attention: partial outputs, their (max, sum) pairs and the
+    number of ranges per sequence.  The extent never shrinks as the batch grows (captured graphs
+    of every batch size share the buffers that the largest one sized)."""
+    units = _decode_places_per_kv_head(nkv, d) if DECODE_BY_UNITS else 0
+    cap = max(n * nq * splits, (nq // nkv) * _SM_TARGET_CTAS + n * nq, nq * units * (units // 2))
+    return (ws.get("attn.part_o", (cap * d,), torch.float32), ws.get("attn.part_ml", (cap * 2,), torch.float32),
+            ws.get("attn.seq_ranges", (max(n, 128),), torch.int32))
+
+
+def attn_decode_units(q, q_stride, pages, table, cu_q, ctx_lens, n_seqs, out, part_o, part_ml, seq_ranges,
+                      nq, nkv, d, scale, window, units, max_ranges, heads=None, status=None) -> None:
+    """Split-KV decode attention with `units` blocks per kv head shared out among the sequences
+    in proportion to their lengths.  ``heads = (q_norm_w, k_norm_w, eps, cos_sin)``: q is the raw
+    q|k|v projection and the kernel finishes the heads itself."""
+    _need_cuda(q, pages, table, cu_q, ctx_lens, out, part_o, part_ml, seq_ranges)
+    num_blocks, _, _, block_size, _ = pages.shape
+    assert part_o.numel() >= n_seqs * nq * units * d and part_ml.numel() >= n_seqs * nq * units * 2
+    qw, kw, eps, cos_sin = heads if heads is not None else (None, None, 0.0, None)
+    _need_cuda(qw, kw, cos_sin, status)
+    _check(_attn_lib(d).ff_attn_decode_units(
+        _p(q), c_int(q_stride), _p(pages), _p(table), c_int(table.shape[1]), _p(cu_q), _p(ctx_lens),
+        c_int(n_seqs), _p(out), c_int(out.shape[1]), _p(part_o), _p(part_ml), _p(seq_ranges), c_int(nq),
+        c_int(nkv), c_int(block_size), c_int(num_blocks), c_float(scale), c_int(window), c_int(units),
+        c_int(max_ranges), c_int(1 if heads is not None else 0), _p(qw), _p(kw), c_float(eps), _p(cos_sin),
+        c_int(cos_sin.shape[0] if cos_sin is not None else 0), _p(status), _stream()), "attn_decode_units")
+    global LAUNCHES, BY_LENGTH_CALLS
+    BY_LENGTH_CALLS += 1
+    if units > n_seqs and max_ranges > 1:
+        LAUNCHES += 1     # the kernel that joins the ranges
+
+
 def paged_attention(q: torch.Tensor, q_stride: int, pages: torch.Tensor, table: torch.Tensor, ctx,
                     out: torch.Tensor, nq: int, nkv: int, d: int, scale: float, window: int) -> None:
     """Attention of a step's tokens over the paged cache; picks the kernel: the
@@ -472,12 +543,14 @@ def paged_attention(q: torch.Tensor, q_stride: int, pages: torch.Tensor, table: 
     if n_dec:
         # one-token sequences: split-KV kernel
         splits = decode_splits(n_dec, nkv, ctx.max_kv_len)
-        # n*nq*splits < G*target + n*nq for every n: the largest batch needs the most
-        cap = max(n_dec * nq * splits, G * _SM_TARGET_CTAS + n_dec * nq)
-        part_o = ctx.workspace.get("attn.part_o", (cap * d,), torch.float32)
-        part_ml = ctx.workspace.get("attn.part_ml", (cap * 2,), torch.float32)
-        attn_decode(q, q_stride, pages, table, ctx.cu_q, ctx.ctx_lens, n_dec, out, part_o, part_ml, nq, nkv, d,
-                    scale, window, splits)
+        units = decode_units(n_dec, nkv, d, ctx.ranges_by_length)
+        part_o, part_ml, seq_ranges = _decode_scratch(ctx.workspace, n_dec, nq, nkv, d, splits)
+        if units:
+            attn_decode_units(q, q_stride, pages, table, ctx.cu_q, ctx.ctx_lens, n_dec, out, part_o, part_ml,
+                              seq_ranges, nq, nkv, d, scale, window, units, DECODE_MAX_RANGES)
+        else:
+            attn_decode(q, q_stride, pages, table, ctx.cu_q, ctx.ctx_lens, n_dec, out, part_o, part_ml, nq, nkv,
+                        d, scale, window, splits)
     if n_dec < n:
         # portions of prompts: tiled kernel over the remaining sequences (token offsets in cu_q are absolute)
         if USE_TC_ATTENTION and tc_attention_supported(q.dtype, d, pages.shape[3], ctx.max_kv_len):

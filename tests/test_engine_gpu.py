@@ -78,6 +78,31 @@ def test_bfloat16_generation_picks_a_top_token(models):
             ids.append(t)
 
 
+@pytest.mark.parametrize("graphs", [False, True])
+def test_bfloat16_requests_of_very_different_lengths(models, graphs):
+    """One long request beside short ones: the decode attention shares its blocks out by length
+    (from a graph of its own when graphs are on); the tokens stay within rounding of the best."""
+    from firefly_b200.ops import kernels as K
+    path, cfg, w = models["B"]
+    rng = np.random.RandomState(21)
+    prompts = [list(map(int, rng.randint(0, cfg["vocab_size"], size=n))) for n in (200, 5, 12)]
+    llm = _llm(path, dtype="bfloat16", kv_block_size=8, num_kv_blocks=96, use_cuda_graphs=graphs)
+    calls = K.BY_LENGTH_CALLS
+    got = llm.generate(prompts, max_tokens=6)
+    if graphs:
+        assert llm.engine.graphs.replays_by_length > 0
+    else:
+        assert K.BY_LENGTH_CALLS > calls
+    for p, g in zip(prompts, got):
+        assert len(g) == 6
+        ids = list(p)
+        for t in g:
+            row = P.forward(cfg, w, ids)[-1]
+            assert float(row.max() - row[t]) <= U.TOL["bfloat16"] * float(row.abs().max())
+            ids.append(t)
+    llm.engine.cache.check()
+
+
 def test_temperature_sampling_is_seeded_and_follows_softmax(models):
     path, cfg, w = models["A"]
     llm = _llm(path, dtype="float32", num_kv_blocks=32)

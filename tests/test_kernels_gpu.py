@@ -267,6 +267,34 @@ def test_attention_decode_tensor_core(d, nq, nkv, block, window, splits):
     assert float(err) < 2e-2, float(err)
 
 
+@pytest.mark.parametrize("d,nq,nkv,block", ATT_SHAPES)
+@pytest.mark.parametrize("window", [None, 100])
+@pytest.mark.parametrize("units,max_ranges", [(9, 24), (10, 24), (55, 24), (200, 24), (55, 2), (31, 1)])
+def test_attention_decode_ranges_shared_out_by_length(d, nq, nkv, block, window, units, max_ranges):
+    """Sequences of very different lengths, and as many units as sequences (one range each, no
+    join), one more, many more than there are tiles of keys, and a cap on the ranges."""
+    seqs = [(0, 1), (1, 1), (63, 1), (64, 1), (200, 1), (1517, 1), (15, 1), (700, 1), (127, 1)]
+    c = _attention_case(d, nq, nkv, block, seqs, window, torch.bfloat16, seed=4)
+    n = len(seqs)
+    out = torch.zeros(c["q"].shape, dtype=torch.bfloat16, device="cuda")
+    part_o = torch.full((n * nq * units * d,), float("nan"), device="cuda")
+    part_ml = torch.full((n * nq * units * 2,), float("nan"), device="cuda")
+    seq_ranges = torch.full((n,), -7, dtype=torch.int32, device="cuda")
+    K().attn_decode_units(dev(c["q"]), nq * d, dev(c["pages"]), dev(c["table"]), dev(c["cu_q"]),
+                          dev(c["ctx_lens"]), n, out, part_o, part_ml, seq_ranges, nq, nkv, d, 1 / math.sqrt(d),
+                          window or 0, units, max_ranges)
+    torch.cuda.synchronize()
+    err = (out.cpu().double() - c["want"]).abs().max() / c["want"].abs().max()
+    assert float(err) < 2e-2, float(err)
+    # every sequence got a range at least, none more than it has tiles or than the cap, all of them within the units
+    got = seq_ranges.cpu().tolist()
+    tiles = [(cl + 64) // 64 - (max(0, cl - window + 1) // 64 if window else 0) for cl, _ in seqs]
+    assert all(1 <= g <= min(t, max_ranges) for g, t in zip(got, tiles)), (got, tiles)
+    assert sum(got) <= units
+    if units >= 55 and max_ranges >= 24:
+        assert window or (got[5] == max(got) and got[5] > got[7] > got[4])       # by length
+
+
 class _Scratch:
     def __init__(self):
         self.bufs = {}
@@ -274,14 +302,15 @@ class _Scratch:
     def get(self, name, shape, dtype):
         key = (name, tuple(shape), dtype)
         if key not in self.bufs:
-            self.bufs[key] = torch.full(tuple(shape), float("nan"), dtype=dtype, device="cuda")
+            fill = float("nan") if dtype.is_floating_point else -7
+            self.bufs[key] = torch.full(tuple(shape), fill, dtype=dtype, device="cuda")
         return self.bufs[key]
 
 
 @pytest.mark.parametrize("d,nq,nkv,block", [(64, 8, 1, 16), (128, 8, 2, 16), (192, 5, 5, 8), (256, 4, 2, 64),
                                             (128, 32, 2, 32), (64, 6, 2, 4)])
 @pytest.mark.parametrize("window", [None, 100])
-@pytest.mark.parametrize("splits", [1, 2, 5])
+@pytest.mark.parametrize("splits", [1, 2, 5, 0])                  # 0: ranges shared out by length
 @pytest.mark.parametrize("norm,rot", [(True, True), (False, True), (True, False)])
 def test_attention_decode_that_finishes_the_heads(d, nq, nkv, block, window, splits, norm, rot):
     """The decode kernel fed with the raw q|k|v projection against the two-kernel route (head kernel,
@@ -316,22 +345,24 @@ def test_attention_decode_that_finishes_the_heads(d, nq, nkv, block, window, spl
     status = torch.zeros(1, dtype=torch.int32, device="cuda")
     K().qk_norm_rope_store(qkv_a, nq, nkv, d, g(qw), g(kw), eps, g(cs), d if rot else 0, ctx_lens,
                            dev(torch.arange(n, dtype=torch.int32)), table, pages_a, status)
-    part_o = torch.full((n * nq * splits * d,), float("nan"), device="cuda")
-    part_ml = torch.full((n * nq * splits * 2,), float("nan"), device="cuda")
+    part_o = torch.full((n * nq * max(splits, 1) * d,), float("nan"), device="cuda")
+    part_ml = torch.full((n * nq * max(splits, 1) * 2,), float("nan"), device="cuda")
     K().attn_decode(qkv_a, width, pages_a, table, cu_q, ctx_lens, n, out_a, part_o, part_ml, nq, nkv, d, scale,
-                    win, splits)
+                    win, max(splits, 1))
     # one kernel
     qkv_b, pages_b = dev(raw.clone()), dev(pages0.clone())
     out_b = torch.zeros(n, nq * d, dtype=torch.bfloat16, device="cuda")
     ctx = SimpleNamespace(num_seqs=n, cu_q=cu_q, ctx_lens=ctx_lens, max_kv_len=max(ctxs) + 1, workspace=_Scratch(),
-                          status=status)
+                          status=status, ranges_by_length=True)
     K().attn_decode_heads(qkv_b, pages_b, table, ctx, out_b, nq, nkv, d, scale, win, g(qw), g(kw), eps, g(cs),
-                          num_splits=splits)
+                          num_splits=splits or None)
     torch.cuda.synchronize()
+    assert splits or K().decode_units(n, nkv, d, True) > 0
     assert int(status) == 0
     assert torch.equal(qkv_b.cpu(), raw)                           # the projection's output is left as it was
     if d in (128, 256):          # the head kernel's register form does the same arithmetic in the same order
         assert torch.equal(pages_a.cpu(), pages_b.cpu())
+    if d in (128, 256) and splits:
         assert torch.equal(out_a.cpu(), out_b.cpu())
     else:
         assert torch.allclose(pages_a.cpu().float(), pages_b.cpu().float(), atol=2e-2, rtol=2e-2)
