@@ -65,6 +65,10 @@ class Qwen3Config(ModelConfig):
         if g(raw, "use_sliding_window", bool, False):
             raise ConfigError("config.json: use_sliding_window=true is not supported by "
                               "Qwen3ForCausalLM in this engine")
+        lt = raw.get("layer_types")
+        if lt is not None and any(t != "full_attention" for t in lt):
+            raise ConfigError("config.json: layer_types other than 'full_attention' are not supported "
+                              "(every Qwen3 dense layer attends to all earlier tokens)")
         if raw.get("rope_scaling") is not None:
             raise ConfigError("config.json: rope_scaling is not supported "
                               "(plain rotary position encoding only)")

@@ -9,10 +9,11 @@ results arrive on a ``ResultQueue`` as (request id, new token ids, is_finished)
 One iteration is ``Engine.step()``: the scheduler picks portions and decode
 tokens, the step function runs them as one batch, the sampler picks next tokens.
 
-Greedy decode steps that run from a CUDA graph are overlapped with the host's work
+Decode steps that run from a CUDA graph are overlapped with the host's work
 (``overlap_decode``): while step n runs, step n+1 for the same requests is put on
-the stream, its input tokens copied on the device from step n's output, and only
-then are step n's tokens read.  The device never waits for the scheduler.  A step
+the stream, its input tokens copied on the device from step n's output (the arg-max
+or the temperature draw: the sampler is part of the graph), and only then are step
+n's tokens read.  The device never waits for the scheduler.  A step
 is launched ahead only when no request of the batch can end by length at step n,
 none waits for admission and every request gets its next page; a request that ends
 at step n by an end-of-sequence token has one more token computed, which is dropped.
@@ -218,8 +219,6 @@ class Engine:
             # cur's token makes generated+1 and total+1; the request must go on after it
             if len(req.generated_tokens) + 1 >= req.max_tokens or req.get_total_len() + 1 >= self.max_model_len:
                 return False
-            if req.sampling.temperature > 0:
-                return False
         # the next page of every request, all or nothing
         if not all(self.cache.can_grow(req.cache, req.cache.num_tokens + 1) for req in cur.requests):
             return False
@@ -232,10 +231,19 @@ class Engine:
             ok = self.cache.grow(req.cache, req.cache.num_tokens + 1)
             assert ok
         entries = [StepEntry(req.cache, [0], [0]) for req in cur.requests]     # ids come from cur on the device
-        step = self.graphs.launch(entries, want_tokens=True, tokens_from_last_replay=True)
+        # cur's token is not recorded yet: the step after it draws with the next counter
+        step = self.graphs.launch(entries, want_tokens=True, tokens_from_last_replay=True,
+                                  sampling=self._lane_sampling(cur.requests, ahead=1))
         self.stats["graph_steps"] += 1
         self.stats["launched_ahead"] += 1
         return _InFlight(step, list(cur.requests), [False] * len(cur.requests))
+
+    @staticmethod
+    def _lane_sampling(requests, ahead: int = 0):
+        """Per request (temperature, seed, counter of the draw); None when all are greedy."""
+        if all(r.sampling.temperature <= 0 for r in requests):
+            return None
+        return [(r.sampling.temperature, r.sampling.seed, len(r.generated_tokens) + ahead) for r in requests]
 
     def drain(self) -> List[StepOutput]:
         """Read the tokens of a step that is still on the stream, launching nothing new."""
@@ -285,14 +293,14 @@ class Engine:
         if (self.graphs is not None and len(sampling_items) == len(batch.items)
                 and all(it.num_tokens == 1 for it in batch.items)
                 and self.graphs.supports(len(entries))):
-            greedy = all(p.temperature <= 0 for p in params)
-            if greedy and self.options.overlap_decode:
-                self.stats["graph_steps"] += 1
-                self._inflight = _InFlight(self.graphs.launch(entries, want_tokens=True),
-                                           [it.request for it in batch.items], [False] * len(entries))
-                return outputs + self._finish_inflight()
-            logits, tokens = self.graphs.run(entries, want_tokens=greedy)
+            reqs = [it.request for it in batch.items]
+            lanes = self._lane_sampling(reqs)
             self.stats["graph_steps"] += 1
+            if self.options.overlap_decode:
+                self._inflight = _InFlight(self.graphs.launch(entries, want_tokens=True, sampling=lanes),
+                                           reqs, [False] * len(entries))
+                return outputs + self._finish_inflight()
+            logits, tokens = self.graphs.run(entries, want_tokens=True, sampling=lanes)
         else:
             logits = self.runner.step(entries)
         if tokens is None:

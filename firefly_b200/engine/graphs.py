@@ -5,7 +5,11 @@ the requests are; only the integer metadata differs.  For each batch-size bucket
 (the reference's {1,2,4,8,16,32,64}, include/firefly/engine.h:72, captured in
 src/engine.cc:121-169) the model's forward and the arg-max are captured once
 over a static metadata buffer; a decode step then fills that buffer, uploads it
-with one copy and replays.  Unused lanes of a bucket decode a dummy token at
+with one copy and replays.  The captured sampler reads a temperature, a seed and a
+counter per lane from a second static buffer, so requests that sample with a
+temperature run from the same graph as greedy ones (a lane with temperature 0 is an
+arg-max) and their tokens, too, can feed the next step without leaving the device.
+Unused lanes of a bucket decode a dummy token at
 position 0 into the reserved scratch page, so they never touch a live page.
 Unlike the reference, the block-table rows are bounded by the model length, not
 by the size of the whole pool, and nothing is allocated inside the capture.
@@ -25,7 +29,7 @@ from .runner import MetaLayout, ModelRunner, StepEntry
 
 class _Bucket:
     __slots__ = ("size", "layout", "meta_host", "meta_stage", "meta_dev", "graph", "logits", "tokens", "h_tokens",
-                 "events", "launches", "lanes", "turn", "by_length")
+                 "events", "launches", "lanes", "turn", "by_length", "samp_stage", "samp_dev", "samp_greedy")
 
 
 class LaunchedStep:
@@ -130,6 +134,11 @@ class DecodeGraphs:
         b.meta_stage = [torch.zeros(b.layout.size, dtype=torch.int32).pin_memory() for _ in range(2)]
         b.meta_dev = torch.zeros(b.layout.size, dtype=torch.int32, device=r.device)
         b.tokens = torch.zeros(size, dtype=torch.int32, device=r.device)
+        # per lane: seed (int64), counter (int64), temperature (float32), in this order so that the
+        # 64-bit values are aligned whatever the size; all zero = every lane greedy
+        b.samp_stage = [torch.zeros(5 * size, dtype=torch.int32).pin_memory() for _ in range(2)]
+        b.samp_dev = torch.zeros(5 * size, dtype=torch.int32, device=r.device)
+        b.samp_greedy = True
         b.h_tokens = [torch.zeros(size, dtype=torch.int32).pin_memory() for _ in range(2)]
         b.events = [torch.cuda.Event() for _ in range(2)]
         b.turn = 0
@@ -145,7 +154,7 @@ class DecodeGraphs:
         side.wait_stream(torch.cuda.current_stream())
         with torch.cuda.stream(side):
             logits = r.model.forward(ctx)     # warm-up: library handles, lazy module loads
-            K.sample(logits, b.tokens)
+            self._sample(b, logits)
         torch.cuda.current_stream().wait_stream(side)
         torch.cuda.synchronize(r.device)
         if not capture:
@@ -154,7 +163,7 @@ class DecodeGraphs:
         before = K.LAUNCHES
         with torch.cuda.graph(b.graph):
             b.logits = r.model.forward(ctx)
-            K.sample(b.logits, b.tokens)
+            self._sample(b, b.logits)
         b.launches = K.LAUNCHES - before      # own kernels in one replay
         # A second graph of the same step for requests of very different lengths, if any kernel
         # makes something of that hint (the attention then shares its blocks out by length).
@@ -171,22 +180,46 @@ class DecodeGraphs:
             before = K.LAUNCHES
             with torch.cuda.graph(g2):
                 logits2 = r.model.forward(ctx)
-                K.sample(logits2, b.tokens)
+                self._sample(b, logits2)
             b.by_length = (g2, logits2, K.LAUNCHES - before)
         return b
 
+    def _sample(self, b: _Bucket, logits: torch.Tensor) -> None:
+        d, n = b.samp_dev, b.size
+        K.sample(logits, b.tokens, d[4 * n:].view(torch.float32), d[:2 * n].view(torch.int64),
+                 d[2 * n: 4 * n].view(torch.int64))
+
+    def _upload_sampling(self, b: _Bucket, k: int, sampling) -> None:
+        """Per-lane (temperature, seed, counter) for the next replay; nothing is copied while
+        every lane stays greedy."""
+        greedy = sampling is None or all(t <= 0 for t, _, _ in sampling)
+        if greedy and b.samp_greedy:
+            return
+        stage = b.samp_stage[k]
+        h, n = stage.numpy(), b.size
+        h[:] = 0
+        if not greedy:
+            m = len(sampling)
+            h[:2 * n].view(np.int64)[:m] = [seed for _, seed, _ in sampling]
+            h[2 * n: 4 * n].view(np.int64)[:m] = [counter for _, _, counter in sampling]
+            h[4 * n:].view(np.float32)[:m] = [max(t, 0.0) for t, _, _ in sampling]
+        b.samp_dev.copy_(stage, non_blocking=True)
+        b.samp_greedy = greedy
+
     def launch(self, entries: Sequence[StepEntry], want_tokens: bool = True,
-               tokens_from_last_replay: bool = False) -> LaunchedStep:
+               tokens_from_last_replay: bool = False, sampling=None) -> LaunchedStep:
         """Put one decode step for ``entries`` (one token each) on the stream without waiting
         for it.  With ``tokens_from_last_replay`` the token of lane i is taken, on the device,
         from what this bucket's previous replay sampled for lane i (the host does not know it
         yet; the ids in ``entries`` are placeholders).  At most two launched steps of a bucket may
-        be outstanding."""
+        be outstanding.  ``sampling``: per entry (temperature, seed, tokens generated so far),
+        or None when every request is greedy."""
         n = len(entries)
         b = self._bucket_for(n)
         self._fill(b, entries)
         k = b.turn
         b.turn ^= 1
+        self._upload_sampling(b, k, sampling)
         stage = b.meta_stage[k]
         stage.copy_(b.meta_host)
         b.meta_dev.copy_(stage, non_blocking=True)
@@ -215,16 +248,16 @@ class DecodeGraphs:
 
     @staticmethod
     def collect(step: LaunchedStep) -> Optional[List[int]]:
-        """Wait for a launched step; its arg-max tokens (None if they were not asked for)."""
+        """Wait for a launched step; its sampled tokens (None if they were not asked for)."""
         if step.event is None:
             return None
         step.event.synchronize()
         return step.h_tokens[:step.n].tolist()
 
-    def run(self, entries: Sequence[StepEntry], want_tokens: bool = True
+    def run(self, entries: Sequence[StepEntry], want_tokens: bool = True, sampling=None
             ) -> Tuple[torch.Tensor, Optional[List[int]]]:
         """One decode step for ``entries`` (one token each).  Returns the logits
         [n, vocab] (valid until the next replay of this bucket) and, when asked,
-        the arg-max tokens already copied to the host."""
-        step = self.launch(entries, want_tokens)
+        the sampled tokens already copied to the host."""
+        step = self.launch(entries, want_tokens, sampling=sampling)
         return step.logits, self.collect(step)

@@ -41,6 +41,7 @@ def test_config_defaults_follow_reference():
     ({"vocab_size": 0}, "vocab_size"),
     ({"attention_bias": True}, "attention_bias"),
     ({"use_sliding_window": True}, "sliding"),
+    ({"layer_types": ["full_attention", "sliding_attention"]}, "layer_types"),
     ({"rope_scaling": {"type": "yarn"}}, "rope_scaling"),
     ({"hidden_act": "gelu"}, "hidden_act"),
     ({"rms_norm_eps": 0.0}, "rms_norm_eps"),

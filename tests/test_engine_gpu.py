@@ -130,6 +130,30 @@ def test_temperature_sampling_is_seeded_and_follows_softmax(models):
     assert int(out2[0]) == int(torch.argmax(logits))
 
 
+def test_temperature_draws_do_not_depend_on_graphs_or_launching_ahead(models):
+    """The sampler inside the captured step draws what the sampler outside it draws: the same
+    tokens with graphs and steps launched ahead, with graphs alone and without graphs, for a
+    batch that mixes greedy requests with requests of different temperatures and lengths."""
+    from firefly_b200 import SamplingParams
+    path, cfg, w = models["B"]
+    rng = np.random.RandomState(21)
+    prompts = [list(map(int, rng.randint(0, cfg["vocab_size"], size=n))) for n in (4, 21, 9, 2, 30)]
+    params = [SamplingParams(temperature=t, seed=s, max_tokens=m)
+              for t, s, m in ((0.9, 3, 24), (0.0, 0, 11), (1.3, 4, 17), (0.6, 5, 24), (0.0, 0, 5))]
+    got = {}
+    for graphs, overlap in ((True, True), (True, False), (False, False)):
+        llm = _llm(path, dtype="float32", kv_block_size=8, num_kv_blocks=64, max_prefill_chunk_size=16,
+                   use_cuda_graphs=graphs, overlap_decode=overlap)
+        got[(graphs, overlap)] = llm.generate(prompts, sampling=params)
+        if overlap:
+            assert llm.engine.stats["launched_ahead"] > 0
+        llm.engine.cache.check()
+        assert not llm.engine.cache.live and llm.engine._inflight is None
+    assert got[(True, True)] == got[(False, False)] == got[(True, False)]
+    assert [len(t) for t in got[(True, True)]] == [p.max_tokens for p in params]
+    assert got[(True, True)][1] == P.greedy_generate(cfg, w, prompts[1], 11)     # greedy lanes stay greedy
+
+
 def test_argmax_ties_go_to_lowest_index():
     from firefly_b200.ops import kernels as K
     V = 151936 + 5
