@@ -100,3 +100,38 @@ def test_trace_run_program(folders, tmp_path):
     proc.stdin.close()
     assert proc.wait(timeout=60) == 0
     U.compare(got, plain, U.TOL["float32"], "trace_run program")
+
+
+def _odd(h, i, L, nq, nkv, d, v, tied):
+    return dict(architectures=["Qwen3ForCausalLM"], hidden_size=h, intermediate_size=i, num_hidden_layers=L,
+                num_attention_heads=nq, num_key_value_heads=nkv, head_dim=d, vocab_size=v,
+                max_position_embeddings=512, rms_norm_eps=1e-6, rope_theta=10000.0, tie_word_embeddings=tied)
+
+
+# sizes at the edges of what the kernels take: a width and an intermediate size that are no multiple of
+# 8 (no vector loads, no tensor-core product), head sizes that are no multiple of 16 (plain attention
+# kernel also in bfloat16), a head size between the compiled classes, a group of 17 query heads per
+# key/value head (more than the decode kernel's 16), many heads of a small size
+ODD = {"width100": _odd(100, 150, 2, 5, 5, 16, 257, False),
+       "head24": _odd(52, 36, 2, 3, 1, 24, 101, True),
+       "head6": _odd(30, 50, 1, 5, 5, 6, 33, False),
+       "head144": _odd(64, 128, 1, 2, 2, 144, 300, False),
+       "group17": _odd(128, 256, 1, 34, 2, 64, 640, True),
+       "heads40": _odd(256, 512, 1, 40, 8, 32, 2048, False)}
+
+
+@pytest.mark.parametrize("name", sorted(ODD))
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+def test_replay_sizes_at_the_kernels_edges(tmp_path, name, dtype):
+    cfg = ODD[name]
+    tdt = torch.float32 if dtype == "float32" else torch.bfloat16
+    w = P.random_weights(cfg, 7, dtype=tdt, scale=0.05)
+    U.write_model_dir(str(tmp_path), cfg, w, tdt)
+    reqs = U.make_requests(cfg["vocab_size"], [70, 3, 129, 45], 3)
+    plain = U.plain_all(cfg, w, reqs)
+    for family, block in (("whole", 16), ("mixed", 8)):
+        steps = (U.trace_whole if family == "whole" else U.trace_mixed)(reqs)
+        sess = _session(str(tmp_path), dtype, U.peak_tokens(steps), block)
+        U.compare(U.run_trace(sess, steps), plain, U.TOL[dtype], f"{name}/{dtype}/{family}")
+        sess.cache.check()
+        assert not sess.cache.live
