@@ -89,7 +89,8 @@ class ModelRunner:
         self.workspace = Workspace(self.device)
         self.status = torch.zeros(1, dtype=torch.int32, device=self.device)
         self._meta_cap = 0
-        self._meta_host: Optional[torch.Tensor] = None
+        self._meta_ring: List[list] = []      # [pinned buffer, event of its last upload]
+        self._meta_turn = 0
         self._meta_dev: Optional[torch.Tensor] = None
         self._ensure_meta(MetaLayout(max_batched_tokens, max_seqs, max_seqs, len(cache.groups),
                                      self.max_blocks_per_seq).size)
@@ -97,11 +98,26 @@ class ModelRunner:
         self.kernel_launches = 0
 
     # ------------------------------------------------------------------------------
+    META_RING = 4     # pinned metadata buffers in rotation
+
     def _ensure_meta(self, size: int) -> None:
         if size > self._meta_cap:
             self._meta_cap = size
-            self._meta_host = torch.empty(size, dtype=torch.int32).pin_memory()
+            self._meta_ring = [[torch.empty(size, dtype=torch.int32).pin_memory(), None]
+                               for _ in range(self.META_RING)]
+            self._meta_turn = 0
             self._meta_dev = torch.empty(size, dtype=torch.int32, device=self.device)
+
+    def _next_meta_host(self) -> list:
+        """The pinned buffer for the next step's metadata.  The upload of a step is only queued
+        when ``step`` returns, and a step without wanted logits is never waited for, so the host
+        may be several steps ahead of the device: a buffer is written again only after the upload
+        that last read it has happened."""
+        slot = self._meta_ring[self._meta_turn]
+        self._meta_turn = (self._meta_turn + 1) % self.META_RING
+        if slot[1] is not None:
+            slot[1].synchronize()
+        return slot
 
     def build_context(self, entries: Sequence[StepEntry], *, meta_host: Optional[torch.Tensor] = None,
                       meta_dev: Optional[torch.Tensor] = None, upload: bool = True) -> StepContext:
@@ -128,9 +144,11 @@ class ModelRunner:
                                     f"{ql} tokens of this step")
                 wants.append(starts[id(e)] + w)
         lay = MetaLayout(T, n, len(wants), len(self.cache.groups), self.max_blocks_per_seq)
+        slot = None
         if meta_host is None:
             self._ensure_meta(lay.size)
-            meta_host, meta_dev = self._meta_host, self._meta_dev
+            slot = self._next_meta_host()
+            meta_host, meta_dev = slot[0], self._meta_dev
         elif lay.size > meta_host.numel():
             raise StepError("metadata buffer too small for this step")
         h = meta_host.numpy()
@@ -163,6 +181,10 @@ class ModelRunner:
             h[lay.logits_rows: lay.logits_rows + len(wants)] = wants
         if upload:
             meta_dev[:lay.size].copy_(meta_host[:lay.size], non_blocking=True)
+            if slot is not None:
+                if slot[1] is None:
+                    slot[1] = torch.cuda.Event()
+                slot[1].record()
         return self.context_from_layout(lay, meta_dev, q_lens, ctx_lens)
 
     def context_from_layout(self, lay: MetaLayout, meta_dev: torch.Tensor, q_lens: List[int],

@@ -276,3 +276,38 @@ def test_many_requests_few_pages_random_lengths(models, seed):
         assert g == P.greedy_generate(cfg, w, p, m)
     llm.engine.cache.check()
     assert not llm.engine.cache.live and llm.engine._inflight is None
+
+
+def test_host_may_run_steps_ahead_of_the_device(tmp_path):
+    """Steps without wanted logits are never waited for, so the host can queue several of them while
+    the device is still busy; each must run with its own metadata.  The device is held up by a
+    spinning kernel while a prompt is queued in more portions than there are metadata buffers; the
+    model allows long sequences, so that a step's block table is tens of kilobytes (a copy that
+    small enough may be taken at the time it is queued and would hide the fault)."""
+    from firefly_b200.engine.runner import StepEntry
+    from firefly_b200.replay import ReplaySession
+    cfg = dict(P.TINY_B, max_position_embeddings=65536)
+    w = P.random_weights(cfg, 1, dtype=torch.float32, scale=0.05)
+    path = U.write_model_dir(str(tmp_path), cfg, w, torch.float32)
+    rng = np.random.RandomState(4)
+    toks = list(map(int, rng.randint(0, cfg["vocab_size"], size=60)))
+    want = P.forward(cfg, w, toks)[-1].numpy()
+    for hold in (False, True):
+        s = ReplaySession(path, dtype="float32", max_tokens=65536, block_size=8)
+        assert s.runner.max_blocks_per_seq == 8192
+        warm = s.cache.admit("warm")                    # scratch buffers get their sizes before the hold
+        assert s.cache.grow(warm, 13)
+        s.runner.step([StepEntry(warm, toks[:13], [])])
+        torch.cuda.synchronize()
+        s.cache.free(warm)
+        rc = s.cache.admit("a")
+        if hold:
+            torch.cuda._sleep(int(3e8))                 # some tenths of a second
+        p = 0
+        for n in (7, 2, 13, 5, 9, 11, 3, 10):
+            assert s.cache.grow(rc, p + n)
+            last = s.runner.step([StepEntry(rc, toks[p:p + n], [n - 1] if p + n == len(toks) else [])])
+            p += n
+        got = last[0].cpu().numpy()
+        s.runner.check_status()
+        assert U.rel_err(got, want) <= U.TOL["float32"], f"hold={hold}"
