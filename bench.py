@@ -346,7 +346,9 @@ def main() -> int:
                    "parallelism": "single GPU", "layers": L, "layers_of_config": full_layers, "hidden": H,
                    "q_heads": nq, "kv_heads": nkv, "head_dim": d, "intermediate": I, "vocab": V,
                    "prompt_len": P, "new_tokens": need_new, "kv_block": 16, "cuda_graphs": True,
-                   "l2": "inputs>L2: each step streams all weights (>15 GB)",
+                   "l2": (f"inputs>L2: each step streams {step_bytes / 1e9:.1f} GB of weights, keys and values"
+                          if step_bytes > 2 * 126e6 else
+                          f"step reads {step_bytes / 1e6:.0f} MB, not larger than L2; no flush between steps"),
                    "peaks": pk["source"], "model_build_s": round(build_s, 1)},
         "clocks": clock_info,
         "e2e": main_res["e2e"],
