@@ -311,3 +311,24 @@ def test_host_may_run_steps_ahead_of_the_device(tmp_path):
         got = last[0].cpu().numpy()
         s.runner.check_status()
         assert U.rel_err(got, want) <= U.TOL["float32"], f"hold={hold}"
+
+
+def test_serving_benchmark_counts_and_figures(models):
+    """The closed-loop load tool on the asynchronous interface: every request is served, with
+    the tokens asked for, and the figures are those of the reference's tool."""
+    from firefly_b200.engine import load_model
+    from firefly_b200.engine.engine import Engine, EngineOptions, ResultQueue
+    from firefly_b200.serving_bench import report, run_load
+    path, cfg, w = models["A"]
+    model, config = load_model(path, dtype="float32")
+    q = ResultQueue()
+    eng = Engine(model, config, result_queue=q,
+                 options=EngineOptions(kv_block_size=16, num_kv_blocks=24, max_prefill_chunk_size=8))
+    rng = np.random.RandomState(9)
+    prompts = [list(map(int, rng.randint(0, cfg["vocab_size"], size=n))) for n in (5, 30, 12, 1, 22, 9, 17)]
+    res = run_load(eng, q, prompts, concurrency=3, max_tokens=6)
+    assert res["successful"] == 7 and res["failed"] == 0 and res["total_tokens"] == 42
+    assert res["ttft_s"]["median"] > 0 and res["tpot_s"]["p99"] >= res["tpot_s"]["median"] > 0
+    assert "Mean TPOT" in report(res) and "Throughput" in report(res)
+    eng.cache.check()
+    assert not eng.cache.live
