@@ -21,7 +21,7 @@ device tensors; the bookkeeping is usable (and tested) without a GPU.
 from __future__ import annotations
 
 from dataclasses import dataclass, field
-from typing import Dict, List, Optional, Sequence, Tuple
+from typing import Dict, List, Optional, Tuple
 
 import torch
 

@@ -7,8 +7,8 @@ position; that is all the kernels need to find its keys, whatever the cut.
 """
 from __future__ import annotations
 
-from dataclasses import dataclass, field
-from typing import Dict, List, Optional, Sequence, Tuple
+from dataclasses import dataclass
+from typing import Dict, List, Sequence, Tuple
 
 import torch
 

@@ -14,13 +14,13 @@ with one copy.
 """
 from __future__ import annotations
 
-from dataclasses import dataclass, field
-from typing import Dict, List, Optional, Sequence, Tuple
+from dataclasses import dataclass
+from typing import List, Optional, Sequence
 
 import numpy as np
 import torch
 
-from ..cache.manager import SCRATCH_PAGE, CacheManager, OutOfPages, RequestCache
+from ..cache.manager import CacheManager, OutOfPages, RequestCache
 from ..models.decoder import DecoderModel
 from ..ops import kernels as K
 from .context import StepContext, Workspace

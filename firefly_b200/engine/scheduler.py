@@ -31,7 +31,7 @@ from __future__ import annotations
 
 from collections import deque
 from dataclasses import dataclass, field
-from typing import Deque, Dict, List, Optional, Sequence
+from typing import Deque, List, Sequence
 
 from ..cache.manager import CacheManager
 from .request import GenerationRequest, RequestStatus

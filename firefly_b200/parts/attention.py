@@ -21,7 +21,7 @@ projections and only ever reads another run's cache).
 from __future__ import annotations
 
 import math
-from typing import List, Mapping, Optional
+from typing import List, Mapping
 
 import torch
 

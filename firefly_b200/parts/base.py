@@ -28,7 +28,7 @@ Registering a new kind: ``register_part("mixer", "my_mixer", MyMixer)``; a
 from __future__ import annotations
 
 from dataclasses import dataclass, field
-from typing import Any, Callable, Dict, List, Mapping, Optional, Type
+from typing import Any, Dict, List, Mapping
 
 import torch
 

@@ -9,7 +9,7 @@ each sum is done once, in 32-bit, without a pass of its own.
 from __future__ import annotations
 
 import inspect
-from typing import List, Mapping, Optional, Tuple
+from typing import List, Mapping
 
 import torch
 

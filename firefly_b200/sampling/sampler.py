@@ -1,7 +1,7 @@
 """Turns a step's logits into next tokens on the device."""
 from __future__ import annotations
 
-from typing import List, Optional, Sequence
+from typing import List, Sequence
 
 import torch
 

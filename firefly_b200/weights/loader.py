@@ -16,7 +16,7 @@ unexpected and mis-shaped tensors are listed in one ``WeightError``.
 from __future__ import annotations
 
 from dataclasses import dataclass
-from typing import Dict, Iterable, List, Optional, Sequence, Tuple
+from typing import Dict, Iterable, Sequence, Tuple
 
 import torch
 

@@ -278,6 +278,25 @@ def test_many_requests_few_pages_random_lengths(models, seed):
     assert not llm.engine.cache.live and llm.engine._inflight is None
 
 
+def test_sampled_requests_survive_preemption_with_the_same_draws(models):
+    """A preempted request recomputes its prompt and the tokens it had drawn, and goes on with the
+    counter where it stood: sampled with a temperature on a pool that forces preemptions, every
+    request gets the tokens it gets on a pool with room for all."""
+    from firefly_b200 import SamplingParams
+    path, cfg, w = models["B"]
+    rng = np.random.RandomState(33)
+    prompts = [list(map(int, rng.randint(0, cfg["vocab_size"], size=n))) for n in (30, 28, 21, 5, 17, 9)]
+    params = [SamplingParams(temperature=0.7 + 0.1 * i, seed=50 + i, max_tokens=16) for i in range(len(prompts))]
+    got = {}
+    for pages in (10, 96):
+        llm = _llm(path, dtype="float32", kv_block_size=8, num_kv_blocks=pages, max_prefill_chunk_size=16)
+        got[pages] = llm.generate(prompts, sampling=params)
+        assert (llm.engine.stats["preemptions"] > 0) == (pages == 10)
+        llm.engine.cache.check()
+        assert not llm.engine.cache.live
+    assert got[10] == got[96]
+
+
 def test_host_may_run_steps_ahead_of_the_device(tmp_path):
     """Steps without wanted logits are never waited for, so the host can queue several of them while
     the device is still busy; each must run with its own metadata.  The device is held up by a
