@@ -61,6 +61,7 @@ __global__ void sample_kernel(const float* __restrict__ logits, int V, size_t ro
                               float* __restrict__ part_val, int* __restrict__ part_idx) {
     __shared__ float s_val[32];
     __shared__ int s_idx[32];
+    pdl_prologue();      // the logits come from the kernel in front
     const int r = blockIdx.x, chunks = gridDim.y, c = blockIdx.y;
     const float* row = logits + (size_t)r * row_stride;
     const float temp = temperature ? temperature[r] : 0.f;
@@ -83,6 +84,7 @@ __global__ void sample_final_kernel(const float* __restrict__ part_val, const in
                                     int chunks, int* __restrict__ out) {
     __shared__ float s_val[32];
     __shared__ int s_idx[32];
+    pdl_prologue();      // the chunks' results come from sample_kernel
     const int r = blockIdx.x;
     float best = -CUDART_INF_F;
     int best_i = 0x7fffffff;

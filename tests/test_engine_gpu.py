@@ -167,6 +167,29 @@ def test_argmax_ties_go_to_lowest_index():
     assert out.tolist() == [70000, V - 1, 0]
 
 
+def test_sampling_waits_for_the_product_that_writes_the_logits():
+    """The sampler is launched right behind the output head's product, which lets its dependents
+    start early: it must still see the finished logits.  A vocabulary of real size (two sampling
+    kernels, a product that runs for a while), fresh activations every round so that stale logits
+    would give another token."""
+    from firefly_b200.ops import kernels as K
+    V, H, T = 151936, 2048, 3
+    g = torch.Generator(device="cuda").manual_seed(3)
+    w = (torch.randn(V, H, device="cuda", generator=g) * 0.02).to(torch.bfloat16)
+    logits = torch.zeros(T, V, device="cuda")
+    out = torch.empty(T, dtype=torch.int32, device="cuda")
+    status = torch.zeros(1, dtype=torch.int32, device="cuda")
+    for _ in range(8):
+        x = torch.randn(T, H, device="cuda", generator=g).to(torch.bfloat16)
+        K.gemm_tc(x, w, logits, K.EPI_F32, 1, status)
+        K.sample(logits, out)
+        torch.cuda.synchronize()
+        best = logits.max(dim=1).values
+        picked = logits[torch.arange(T, device="cuda"), out.long()]
+        assert torch.equal(picked, best), (picked - best).tolist()
+    assert int(status) == 0
+
+
 def test_async_engine_interface(models):
     path, cfg, w = models["A"]
     from firefly_b200 import Engine, ResultQueue
