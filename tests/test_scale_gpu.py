@@ -1,0 +1,42 @@
+"""The engine at the layer sizes of a real model (4096 wide, 32/8 heads of 128, 12288 intermediate,
+a vocabulary of 151936; two layers, random weights, bfloat16).  Tiny models leave some faults
+unseen: kernels there end before the next one starts, the vocabulary fits one sampling block and the
+host is slower than the device.  Here generation through graphs and steps launched ahead is held
+against the engine's own replay of the same tokens (whose logits the other tests hold against the
+plain implementation): every generated token must be the replay's best, within rounding."""
+import numpy as np
+import pytest
+import torch
+
+pytestmark = pytest.mark.gpu
+
+REAL_SIZES = dict(architectures=["Qwen3ForCausalLM"], hidden_size=4096, intermediate_size=12288,
+                  num_hidden_layers=2, num_attention_heads=32, num_key_value_heads=8, head_dim=128,
+                  vocab_size=151936, max_position_embeddings=4096, rms_norm_eps=1e-6, rope_theta=1000000.0,
+                  tie_word_embeddings=False)
+
+
+@pytest.mark.parametrize("options", [dict(), dict(max_prefill_chunk_size=1024), dict(use_cuda_graphs=False)],
+                         ids=["portions", "whole-prompts", "no-graphs"])
+def test_generated_tokens_are_the_replays_best_at_real_layer_sizes(options):
+    from firefly_b200 import LLM
+    from firefly_b200.models import config_from_dict
+    from firefly_b200.replay import ReplaySession
+    cfg = config_from_dict(REAL_SIZES)
+    rng = np.random.RandomState(5)
+    prompts = [list(map(int, rng.randint(0, cfg.vocab_size, size=n))) for n in (45, 100, 520)]
+    llm = LLM(cfg, seed=3, dtype="bfloat16", num_kv_blocks=256, **options)
+    outs = llm.generate(prompts, max_tokens=6)
+    if options.get("use_cuda_graphs", True):
+        assert llm.engine.stats["launched_ahead"] > 0
+    llm.engine.runner.check_status()
+    for p, g in zip(prompts, outs):
+        assert len(g) == 6
+        ids = list(p) + list(g)
+        sess = ReplaySession(model=llm.model, max_tokens=len(ids) + 64)
+        want = list(range(len(p) - 1, len(ids) - 1))
+        rows = sess.run_step({"step": 0, "entries": [{"id": "x", "tokens": ids, "want": want}], "end": ["x"]})
+        for k, t in enumerate(g):
+            gap = float(rows[k].max() - rows[k][t]) / float(np.abs(rows[k]).max())
+            assert gap <= 2e-2, f"prompt of {len(p)}: token {k} lies {gap:.3f} of the row's scale below the best"
+        del sess
