@@ -40,3 +40,24 @@ def test_generated_tokens_are_the_replays_best_at_real_layer_sizes(options):
             gap = float(rows[k].max() - rows[k][t]) / float(np.abs(rows[k]).max())
             assert gap <= 2e-2, f"prompt of {len(p)}: token {k} lies {gap:.3f} of the row's scale below the best"
         del sess
+
+
+def test_replay_matches_the_plain_implementation_at_real_layer_sizes(tmp_path):
+    """The plain implementation (32-bit, on the CPU) against the replay at these sizes: a request
+    whole, its last tokens one by one, and mixed with two others of very different lengths."""
+    import plain_qwen3 as P
+    import replay_util as U
+    from firefly_b200.replay import ReplaySession
+    cfg = dict(REAL_SIZES, tie_word_embeddings=True)       # one matrix of 151936 x 4096 less to draw on the CPU
+    w = P.random_weights(cfg, 3, dtype=torch.bfloat16, scale=0.02)
+    U.write_model_dir(str(tmp_path), cfg, w, torch.bfloat16)
+    reqs = U.make_requests(cfg["vocab_size"], [150, 20, 330], 5)
+    w32 = {k: v.float() for k, v in w.items()}
+    plain = {rid: P.forward(cfg, w32, toks, dtype=torch.float32).numpy() for rid, toks in reqs.items()}
+    del w32
+    for family in ("whole", "tail", "mixed"):
+        steps = {"whole": U.trace_whole, "tail": U.trace_tail_decode, "mixed": U.trace_mixed}[family](reqs)
+        sess = ReplaySession(str(tmp_path), dtype="bfloat16", max_tokens=U.peak_tokens(steps))
+        U.compare(U.run_trace(sess, steps), plain, U.TOL["bfloat16"], f"real sizes/{family}")
+        sess.cache.check()
+        del sess
