@@ -25,7 +25,7 @@ import torch
 
 from .cache.manager import CacheManager, OutOfPages, RequestCache
 from .engine.loading import load_model
-from .engine.runner import ModelRunner, StepEntry
+from .engine.runner import ModelRunner, StepEntry, StepError
 
 PAGE_ROUNDING = 64   # a request's token count is rounded up to this for --max-tokens
 
@@ -112,12 +112,21 @@ def main(argv=None) -> int:
         line = line.strip()
         if not line:
             continue
-        rec = json.loads(line)
+        try:
+            rec = json.loads(line)
+            if not isinstance(rec, dict) or "step" not in rec:
+                raise ValueError("a step is a JSON object with 'step', 'entries' and 'end'")
+        except ValueError as e:
+            print(f"trace_run: bad input line: {e}", file=sys.stderr)
+            return 4
         try:
             arr = session.run_step(rec)
         except OutOfPages as e:
             print(f"trace_run: {e}", file=sys.stderr)
             return 3
+        except (StepError, KeyError, TypeError, ValueError) as e:
+            print(f"trace_run: step {rec.get('step')}: {type(e).__name__}: {e}", file=sys.stderr)
+            return 4
         if arr is not None:
             with open(os.path.join(args.out, f"{rec['step']}.f32"), "wb") as fh:
                 fh.write(arr.tobytes())
