@@ -5,6 +5,7 @@
 #include "attention_mma.cu"
 #include "attention_decode_static.h"
 
+#include <atomic>
 #include <cstdio>
 #include <mutex>
 
@@ -16,7 +17,7 @@ __device__ __align__(256) float g_static_part_ml[(size_t)FF_ATTN_STATIC_MAX_PART
 
 constexpr int kMaxDevices = 64;
 std::mutex g_setup_mutex;
-bool g_ready[kMaxDevices];
+std::atomic<bool> g_ready[kMaxDevices];   // set (release) after the addresses below are written
 float* g_part_o_addr[kMaxDevices];
 float* g_part_ml_addr[kMaxDevices];
 
@@ -25,7 +26,7 @@ float* g_part_ml_addr[kMaxDevices];
 // kernels' dynamic shared-memory limit.
 int setup_device(int dev) {
     std::lock_guard<std::mutex> lock(g_setup_mutex);
-    if (g_ready[dev]) return 0;
+    if (g_ready[dev].load(std::memory_order_acquire)) return 0;
     float* po = nullptr;
     float* pml = nullptr;
     cudaError_t e = cudaGetSymbolAddress((void**)&po, g_static_part_o);
@@ -37,7 +38,7 @@ int setup_device(int dev) {
     if (e != cudaSuccess) return (int)e;
     g_part_o_addr[dev] = po;
     g_part_ml_addr[dev] = pml;
-    g_ready[dev] = true;
+    g_ready[dev].store(true, std::memory_order_release);
     return 0;
 }
 
@@ -65,7 +66,7 @@ int ff_attn_decode_static(const void* q, int q_stride, const void* cache, const 
     cudaError_t e = cudaGetDevice(&dev);
     if (e != cudaSuccess) return (int)e;
     if (dev < 0 || dev >= kMaxDevices) return FF_ERR_UNSUPPORTED;
-    if (!g_ready[dev]) {
+    if (!g_ready[dev].load(std::memory_order_acquire)) {
         const int rc = setup_device(dev);
         if (rc != 0) return rc;
     }

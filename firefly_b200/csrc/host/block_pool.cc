@@ -54,11 +54,11 @@ FFH_EXPORT int ffh_pool_free(void* h, const int* ids, int n, int* bad_id) {
     Pool* p = static_cast<Pool*>(h);
     for (int i = 0; i < n; ++i) {
         const int idx = ids[i] - p->first_id;
-        if (idx < 0 || idx >= p->num_blocks) { *bad_id = ids[i]; return 1; }
-        if (p->held[(size_t)idx] != 1) {
+        const bool foreign = idx < 0 || idx >= p->num_blocks;
+        if (foreign || p->held[(size_t)idx] != 1) {
             *bad_id = ids[i];
             for (int j = 0; j < i; ++j) p->held[(size_t)(ids[j] - p->first_id)] = 1;   // undo the marks
-            return 2;
+            return foreign ? 1 : 2;
         }
         p->held[(size_t)idx] = 2;   // marks a second mention within this call
     }

@@ -4,15 +4,18 @@ It is the oracle of the tests.  It shares no code with ``firefly_b200``: it take
 a plain dict of config.json keys and a dict ``{tensor name: torch tensor}``, runs
 on the CPU in float64 (or any dtype asked for), and has one function per part.
 
-It rests on the reference's formulas, not on running the reference: the
-reference's model code is CUDA-only FP16 (no CPU path), needs CUTLASS, mdspan
-and a gRPC tool-chain fetched over the network, and supports neither these head
-sizes nor tied embeddings, so it can be neither imported nor compiled here.
-Each function cites the file and lines of the reference whose arithmetic it
-restates.  Where the reference is wrong for a general batch (prefill attention
-that ignores earlier portions, src/model/qwen_model.cu:147-151 with the
-chunk-local mask of src/kernels/attention.cu:173) this file follows the
-formula with absolute positions.
+It is written from the reference's formulas; each function cites the file and
+lines whose arithmetic it restates.  The reference's engine as a whole cannot be
+run here (CUDA-only FP16, a gRPC tool-chain fetched over the network, head size
+128 only, no tied embeddings), but its kernels can be compiled unchanged behind a
+small stand-in for its Tensor class: ``tests/golden/ref_kernels_golden.npz`` holds
+what its RMSNorm, rotary, SwiGLU, residual-add, embedding, arg-max and decode
+attention kernels computed on a B200, and ``tests/test_ref_kernel_golden.py``
+holds the functions of this file to them.  Where the reference is wrong for a
+general batch (prefill attention that ignores earlier portions,
+src/model/qwen_model.cu:147-151 with the chunk-local mask of
+src/kernels/attention.cu:173) this file follows the formula with absolute
+positions.
 """
 from __future__ import annotations
 
@@ -147,6 +150,14 @@ def forward(cfg: Mapping, weights: Mapping[str, torch.Tensor], ids: Sequence[int
     return x @ head.T
 
 
+def greedy_pick(logits: torch.Tensor) -> int:
+    """Index of the largest logit, the lowest such index on ties.  The reference's kernel keeps
+    the lowest index within a thread by a strict '>' and leaves ties between threads to its block
+    reduction (src/kernels/sampling.cu:27-37)."""
+    top = logits.max()
+    return int(torch.nonzero(logits == top)[0])
+
+
 def greedy_generate(cfg, weights, prompt: Sequence[int], n_new: int, *, dtype=torch.float64) -> List[int]:
     """Arg-max decoding (lowest index on ties), recomputing the whole sequence
     each time (src/kernels/sampling.cu:27-37 for the arg-max)."""
@@ -154,7 +165,7 @@ def greedy_generate(cfg, weights, prompt: Sequence[int], n_new: int, *, dtype=to
     out = []
     for _ in range(n_new):
         logits = forward(cfg, weights, ids, dtype=dtype)[-1]
-        nxt = int(torch.argmax(logits))
+        nxt = greedy_pick(logits)
         out.append(nxt)
         ids.append(nxt)
     return out

@@ -27,7 +27,10 @@ def test_allocator_lifo_and_errors():
     with pytest.raises(PageError, match="twice"):
         a.free([got[0], got[1], got[0]])                    # named twice in one call: nothing is freed
     assert a.num_free == before
-    a.free(got)
+    with pytest.raises(PageError, match="does not belong"):
+        a.free([got[0], got[1], 77])                        # a foreign id behind valid ones: nothing is freed
+    assert a.num_free == before
+    a.free(got)                                             # ... and the valid ones can still be freed
     a.check()
     big = BlockAllocator(100000)
     ids = big.allocate(100000)

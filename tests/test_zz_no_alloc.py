@@ -43,7 +43,11 @@ def test_static_scratch_entry_matches_regular_entry_twice():
         K.attn_decode(dev["q"], nq * d, dev["pages"], dev["table"], dev["cu_q"], dev["ctx_lens"], n, want,
                       part_o, part_ml, nq, nkv, d, 1 / math.sqrt(d), window, splits)
         got = torch.zeros_like(want)
+        # the driver's own count of free bytes sees every allocation on the device, also one that
+        # bypasses torch's allocator; the first call's set-up (a symbol look-up) allocates nothing
+        torch.cuda.synchronize()
         before = torch.cuda.memory_allocated()
+        free_before, _ = torch.cuda.mem_get_info()
         rc = fn(_ptr(dev["q"]), c_int(nq * d), _ptr(dev["pages"]), _ptr(dev["table"]),
                 c_int(dev["table"].shape[1]), _ptr(dev["cu_q"]), _ptr(dev["ctx_lens"]), c_int(n), _ptr(got),
                 c_int(nq * d), c_int(nq), c_int(nkv), c_int(block), c_int(dev["pages"].shape[0]),
@@ -51,6 +55,8 @@ def test_static_scratch_entry_matches_regular_entry_twice():
         assert rc == 0, f"call {call}: return code {rc}"
         torch.cuda.synchronize()
         assert torch.cuda.memory_allocated() == before
+        free_after, _ = torch.cuda.mem_get_info()
+        assert free_after >= free_before, f"call {call}: {free_before - free_after} bytes of device memory were taken"
         ref = c["want"]
         scale = float(ref.abs().max())
         assert float((got.cpu().double() - want.cpu().double()).abs().max()) <= 2e-2 * scale
