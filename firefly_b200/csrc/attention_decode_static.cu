@@ -15,11 +15,11 @@ namespace {
 __device__ __align__(256) float g_static_part_o[(size_t)FF_ATTN_STATIC_MAX_PARTIALS * ff::D];
 __device__ __align__(256) float g_static_part_ml[(size_t)FF_ATTN_STATIC_MAX_PARTIALS * 2];
 
-constexpr int kMaxDevices = 64;
+constexpr int kStaticMaxDevices = 64;
 std::mutex g_setup_mutex;
-std::atomic<bool> g_ready[kMaxDevices];   // set (release) after the addresses below are written
-float* g_part_o_addr[kMaxDevices];
-float* g_part_ml_addr[kMaxDevices];
+std::atomic<bool> g_ready[kStaticMaxDevices];   // set (release) after the addresses below are written
+float* g_part_o_addr[kStaticMaxDevices];
+float* g_part_ml_addr[kStaticMaxDevices];
 
 // Once per device, with that device current: the arrays' device addresses (in host
 // code the symbols are only stand-ins, never to be handed to a kernel) and the
@@ -65,7 +65,7 @@ int ff_attn_decode_static(const void* q, int q_stride, const void* cache, const 
     int dev = 0;
     cudaError_t e = cudaGetDevice(&dev);
     if (e != cudaSuccess) return (int)e;
-    if (dev < 0 || dev >= kMaxDevices) return FF_ERR_UNSUPPORTED;
+    if (dev < 0 || dev >= kStaticMaxDevices) return FF_ERR_UNSUPPORTED;
     if (!g_ready[dev].load(std::memory_order_acquire)) {
         const int rc = setup_device(dev);
         if (rc != 0) return rc;
@@ -75,7 +75,8 @@ int ff_attn_decode_static(const void* q, int q_stride, const void* cache, const 
     dim3 grid(n_seqs, nkv, num_splits);
     attn_decode_kernel<<<grid, NTHREADS, DECODE_SMEM, stream>>>(
         (const bf16*)q, q_stride, (const bf16*)cache, block_table, max_blocks, cu_q, ctx_lens, (bf16*)out,
-        out_stride, part_o, part_ml, nq, nkv, block_size, num_blocks, scale * LOG2E, window, num_splits);
+        out_stride, part_o, part_ml, nq, nkv, block_size, num_blocks, scale * LOG2E, window, num_splits,
+        (int*)nullptr);
     FF_LAUNCH_CHECK();
     if (num_splits > 1) {
         dim3 cgrid(n_seqs, nq);

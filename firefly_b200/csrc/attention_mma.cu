@@ -66,23 +66,28 @@ static_assert((BN * CHUNKS) % NTHREADS == 0, "the copy loop has no tail");
 // Where each key row of the tile that starts at key0 lies in the cache, as an element offset
 // of its K row (the V row is v_off further), or -1 when the key is outside [kv_lo, kv_hi) or
 // its page is missing.  Thread r < BN looks up row r: one block-table read per row and tile.
+// A key that should be read but has no valid page raises status 4 (a fault of the bookkeeping: the
+// row then counts as a key of zeros, and the host must not trust the step's output).
 __device__ __forceinline__ long long kv_row_offset(const int* __restrict__ bt, int max_blocks, int num_blocks,
-                                                   int nkv, int kh, int block_size, int key, int kv_lo, int kv_hi) {
+                                                   int nkv, int kh, int block_size, int key, int kv_lo, int kv_hi,
+                                                   int* status) {
     long long off = -1;
     if (key >= kv_lo && key < kv_hi) {
         const int pi = key / block_size;
         const int page = pi < max_blocks ? bt[pi] : -1;
         if (page >= 0 && page < num_blocks)
             off = ((((long long)page * 2) * nkv + kh) * block_size + (key - pi * block_size)) * D;
+        else if (status != nullptr)
+            atomicExch(status, 4);
     }
     return off;
 }
 __device__ __forceinline__ void kv_row_offsets(long long* row_off, const int* __restrict__ bt, int max_blocks,
                                                int num_blocks, int nkv, int kh, int block_size, int key0,
-                                               int kv_lo, int kv_hi) {
+                                               int kv_lo, int kv_hi, int* status) {
     if (threadIdx.x < BN)
         row_off[threadIdx.x] = kv_row_offset(bt, max_blocks, num_blocks, nkv, kh, block_size, key0 + threadIdx.x,
-                                             kv_lo, kv_hi);
+                                             kv_lo, kv_hi, status);
 }
 
 // Copy a tile's K and V rows into shared memory, 16 bytes a thread, neighbouring threads on
@@ -216,7 +221,8 @@ __global__ void __launch_bounds__(NTHREADS)
 attn_tiled_kernel(const bf16* __restrict__ q, int q_stride, const bf16* __restrict__ cache,
                   const int* __restrict__ block_table, int max_blocks, const int* __restrict__ cu_q,
                   const int* __restrict__ ctx_lens, int n_seqs, bf16* __restrict__ out, int out_stride,
-                  int nq, int nkv, int block_size, int num_blocks, float scale_log2, int window) {
+                  int nq, int nkv, int block_size, int num_blocks, float scale_log2, int window,
+                  int* __restrict__ status) {
     pdl_prologue();
     extern __shared__ __align__(16) unsigned char smem_raw[];
     bf16* Qs = reinterpret_cast<bf16*>(smem_raw);                 // [BM][KSTR]
@@ -277,9 +283,9 @@ attn_tiled_kernel(const bf16* __restrict__ q, int q_stride, const bf16* __restri
 
     const size_t v_off = (size_t)nkv * block_size * D;
     __shared__ long long s_row_off[2][BN];
-    kv_row_offsets(s_row_off[0], bt, max_blocks, num_blocks, nkv, kh, block_size, t_begin * BN, kv_lo, kv_hi);
+    kv_row_offsets(s_row_off[0], bt, max_blocks, num_blocks, nkv, kh, block_size, t_begin * BN, kv_lo, kv_hi, status);
     if (t_begin + 1 < t_end)
-        kv_row_offsets(s_row_off[1], bt, max_blocks, num_blocks, nkv, kh, block_size, (t_begin + 1) * BN, kv_lo, kv_hi);
+        kv_row_offsets(s_row_off[1], bt, max_blocks, num_blocks, nkv, kh, block_size, (t_begin + 1) * BN, kv_lo, kv_hi, status);
     __syncthreads();
     load_kv_tile(Ks, Vs, cache, s_row_off[0], v_off);
     cp_async_commit();
@@ -315,7 +321,7 @@ attn_tiled_kernel(const bf16* __restrict__ q, int q_stride, const bf16* __restri
         __syncthreads();
         // the offsets of tile t are used up: look up those of tile t+2 (read after the next barrier)
         if (t + 2 < t_end)
-            kv_row_offsets(s_row_off[buf], bt, max_blocks, num_blocks, nkv, kh, block_size, (t + 2) * BN, kv_lo, kv_hi);
+            kv_row_offsets(s_row_off[buf], bt, max_blocks, num_blocks, nkv, kh, block_size, (t + 2) * BN, kv_lo, kv_hi, status);
         const int key0 = t * BN;
         if (warp_active && key0 <= warp_last_pos && key0 + BN > warp_lo) {   // warp-uniform
             const bool need_mask = key0 + BN > warp_first_pos + 1 || key0 < full_lo || key0 < kv_lo;
@@ -359,7 +365,7 @@ struct DecodeHeads {
     const float* cos_sin;      // [max_positions][D/2][2] or null: no rotation
     int max_positions;
     bf16* cache_w;             // the cache again, to write the newest key and value
-    int* status;               // 2: page of the newest token missing, 3: position beyond the table
+    int* status;               // 2: page of the newest token missing, 3: position beyond the table, 4: a key's page missing
 };
 constexpr int HC = D / 64;     // elements of each half of a head that a lane holds (heads finished in a warp)
 
@@ -524,9 +530,9 @@ attn_decode_body(const bf16* __restrict__ q, int q_stride, const bf16* __restric
     const size_t v_off = (size_t)nkv * block_size * D;
     __shared__ long long s_row_off[2][BN];
     if (t_begin < t_end)
-        kv_row_offsets(s_row_off[0], bt, max_blocks, num_blocks, nkv, kh, block_size, t_begin * BN, kv_lo, kv_hi);
+        kv_row_offsets(s_row_off[0], bt, max_blocks, num_blocks, nkv, kh, block_size, t_begin * BN, kv_lo, kv_hi, hd.status);
     if (t_begin + 1 < t_end)
-        kv_row_offsets(s_row_off[1], bt, max_blocks, num_blocks, nkv, kh, block_size, (t_begin + 1) * BN, kv_lo, kv_hi);
+        kv_row_offsets(s_row_off[1], bt, max_blocks, num_blocks, nkv, kh, block_size, (t_begin + 1) * BN, kv_lo, kv_hi, hd.status);
     __syncthreads();
     // the first tile can go early if it ends before the newest key, or if that key is put into the tile later
     const bool early = t_begin < t_end && (HEADS || (t_begin + 1) * BN <= pos);
@@ -651,7 +657,7 @@ attn_decode_body(const bf16* __restrict__ q, int q_stride, const bf16* __restric
         const bool look = t + 2 < t_end && threadIdx.x < BN;
         long long off_next = -1;
         if (look)
-            off_next = kv_row_offset(bt, max_blocks, num_blocks, nkv, kh, block_size, (t + 2) * BN + threadIdx.x, kv_lo, kv_hi);
+            off_next = kv_row_offset(bt, max_blocks, num_blocks, nkv, kh, block_size, (t + 2) * BN + threadIdx.x, kv_lo, kv_hi, hd.status);
         const int key0 = t * BN + warp * 16;
         if (key0 < kv_hi && key0 + 16 > kv_lo) {
             const bool need_mask = key0 + 16 > kv_hi || key0 < kv_lo;
@@ -711,10 +717,13 @@ attn_decode_kernel(const bf16* __restrict__ q, int q_stride, const bf16* __restr
                    const int* __restrict__ block_table, int max_blocks, const int* __restrict__ cu_q,
                    const int* __restrict__ ctx_lens, bf16* __restrict__ out, int out_stride,
                    float* __restrict__ part_o, float* __restrict__ part_ml, int nq, int nkv,
-                   int block_size, int num_blocks, float scale_log2, int window, int num_splits) {
+                   int block_size, int num_blocks, float scale_log2, int window, int num_splits,
+                   int* __restrict__ status) {
+    DecodeHeads hd{};
+    hd.status = status;           // may be null: a missing page is then not reported
     attn_decode_body<false, false>(q, q_stride, cache, block_table, max_blocks, cu_q, ctx_lens, out, out_stride,
                                    part_o, part_ml, nq, nkv, block_size, num_blocks, scale_log2, window, num_splits,
-                                   DecodeHeads{}, DecodeUnits{});
+                                   hd, DecodeUnits{});
 }
 __global__ void __launch_bounds__(NTHREADS)
 attn_decode_heads_kernel(const bf16* __restrict__ qkv, int row_width, const bf16* __restrict__ cache,
@@ -824,20 +833,14 @@ FF_EXPORT int ff_attn_block_m() { return BM; }
 FF_EXPORT int ff_attn_tiled(const void* q, int q_stride, const void* cache, const int* block_table,
                             int max_blocks, const int* cu_q, const int* ctx_lens, int n_seqs,
                             int total_tiles, void* out, int out_stride, int nq, int nkv, int block_size,
-                            int num_blocks, float scale, int window, cudaStream_t stream) {
+                            int num_blocks, float scale, int window, int* status, cudaStream_t stream) {
     if (n_seqs <= 0 || total_tiles <= 0) return 0;
     if (nkv <= 0 || nq % nkv) return FF_ERR_BAD_ARG;
-    static bool attr_set = false;
-    if (!attr_set) {
-        cudaError_t e = cudaFuncSetAttribute(attn_tiled_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                                             (int)TILED_SMEM);
-        if (e != cudaSuccess) return (int)e;
-        attr_set = true;
-    }
+    FF_SMEM_LIMIT(attn_tiled_kernel, TILED_SMEM);
     dim3 grid(total_tiles, nkv);
     FF_LAUNCH((attn_tiled_kernel), grid, NTHREADS, TILED_SMEM, stream, 
         (const bf16*)q, q_stride, (const bf16*)cache, block_table, max_blocks, cu_q, ctx_lens, n_seqs,
-        (bf16*)out, out_stride, nq, nkv, block_size, num_blocks, scale * LOG2E, window);
+        (bf16*)out, out_stride, nq, nkv, block_size, num_blocks, scale * LOG2E, window, status);
     FF_LAUNCH_CHECK();
     return 0;
 }
@@ -848,21 +851,15 @@ FF_EXPORT int ff_attn_decode(const void* q, int q_stride, const void* cache, con
                              int max_blocks, const int* cu_q, const int* ctx_lens, int n_seqs, void* out,
                              int out_stride, float* part_o, float* part_ml, int nq, int nkv,
                              int block_size, int num_blocks, float scale, int window, int num_splits,
-                             cudaStream_t stream) {
+                             int* status, cudaStream_t stream) {
     if (n_seqs <= 0) return 0;
     if (nkv <= 0 || nq % nkv || num_splits < 1) return FF_ERR_BAD_ARG;
     if (nq / nkv > 16) return FF_ERR_UNSUPPORTED;
-    static bool attr_set = false;
-    if (!attr_set) {
-        cudaError_t e = cudaFuncSetAttribute(attn_decode_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                                             (int)DECODE_SMEM);
-        if (e != cudaSuccess) return (int)e;
-        attr_set = true;
-    }
+    FF_SMEM_LIMIT(attn_decode_kernel, DECODE_SMEM);
     dim3 grid(n_seqs, nkv, num_splits);
     FF_LAUNCH((attn_decode_kernel), grid, NTHREADS, DECODE_SMEM, stream, 
         (const bf16*)q, q_stride, (const bf16*)cache, block_table, max_blocks, cu_q, ctx_lens, (bf16*)out,
-        out_stride, part_o, part_ml, nq, nkv, block_size, num_blocks, scale * LOG2E, window, num_splits);
+        out_stride, part_o, part_ml, nq, nkv, block_size, num_blocks, scale * LOG2E, window, num_splits, status);
     FF_LAUNCH_CHECK();
     if (num_splits > 1) {
         dim3 cgrid(n_seqs, nq);
@@ -886,13 +883,7 @@ FF_EXPORT int ff_attn_decode_heads(const void* qkv, int row_width, void* cache, 
     if (n_seqs <= 0) return 0;
     if (nkv <= 0 || nq % nkv || num_splits < 1 || status == nullptr) return FF_ERR_BAD_ARG;
     if (nq / nkv > 16 || D % 64 != 0) return FF_ERR_UNSUPPORTED;
-    static bool attr_set = false;
-    if (!attr_set) {
-        cudaError_t e = cudaFuncSetAttribute(attn_decode_heads_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                                             (int)DECODE_SMEM);
-        if (e != cudaSuccess) return (int)e;
-        attr_set = true;
-    }
+    FF_SMEM_LIMIT(attn_decode_heads_kernel, DECODE_SMEM);
     DecodeHeads hd{q_norm_w, k_norm_w, eps, cos_sin, max_positions, (bf16*)cache, status};
     dim3 grid(n_seqs, nkv, num_splits);
     FF_LAUNCH((attn_decode_heads_kernel), grid, NTHREADS, DECODE_SMEM, stream,
@@ -928,16 +919,8 @@ FF_EXPORT int ff_attn_decode_units(const void* q, int q_stride, void* cache, con
     if (most_tiles * (units - n_seqs + max_ranges) >= (1ll << 31)) return FF_ERR_UNSUPPORTED;
     if (nq / nkv > 16) return FF_ERR_UNSUPPORTED;
     if (finish_heads && (D % 64 != 0 || status == nullptr)) return FF_ERR_UNSUPPORTED;
-    static bool attr_set = false;
-    if (!attr_set) {
-        cudaError_t e = cudaFuncSetAttribute(attn_decode_units_kernel<true>,
-                                             cudaFuncAttributeMaxDynamicSharedMemorySize, (int)DECODE_SMEM);
-        if (e != cudaSuccess) return (int)e;
-        e = cudaFuncSetAttribute(attn_decode_units_kernel<false>, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                                 (int)DECODE_SMEM);
-        if (e != cudaSuccess) return (int)e;
-        attr_set = true;
-    }
+    FF_SMEM_LIMIT(attn_decode_units_kernel<true>, DECODE_SMEM);
+    FF_SMEM_LIMIT(attn_decode_units_kernel<false>, DECODE_SMEM);
     DecodeHeads hd{q_norm_w, k_norm_w, eps, cos_sin, max_positions, (bf16*)cache, status};
     DecodeUnits un{n_seqs, max_ranges, seq_ranges, units};
     dim3 grid(nkv, units);

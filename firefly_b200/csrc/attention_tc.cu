@@ -301,8 +301,10 @@ attn_tc_kernel(const __grid_constant__ TensorMapArg kv_map, const bf16* __restri
         const int last_page = (kv_hi - 1) / block_size, first_page = kv_lo / block_size;
         for (int i = threadIdx.x; i < n_tiles * pages_per_tile; i += 128) {
             const int pi = t_begin * pages_per_tile + i;
-            int page = (pi >= first_page && pi <= last_page && pi < max_blocks) ? bt[pi] : -1;
+            const bool wanted = pi >= first_page && pi <= last_page;
+            int page = (wanted && pi < max_blocks) ? bt[pi] : -1;
             if (page >= num_blocks) page = -1;
+            if (wanted && page < 0) atomicExch(status, 4);      // a key's page is missing: the bookkeeping is at fault
             s_pages[i] = page;
         }
         // zero the K/V stages once: parts no page is loaded into must hold finite numbers
@@ -584,12 +586,7 @@ FF_EXPORT int ff_attn_tc(const void* q, int q_stride, const void* cache, const i
         return FF_ERR_UNSUPPORTED;
     const long long rows = (long long)num_blocks * 2 * nkv * block_size;
     if (rows >= (1ll << 31)) return FF_ERR_UNSUPPORTED;
-    static bool attr_set = false;
-    if (!attr_set) {
-        cudaError_t e = cudaFuncSetAttribute(attn_tc_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)ATC_SMEM);
-        if (e != cudaSuccess) return (int)e;
-        attr_set = true;
-    }
+    FF_SMEM_LIMIT(attn_tc_kernel, ATC_SMEM);
     CUtensorMap map;
     int rc = cache_map(cache, rows, block_size, &map);
     if (rc) return rc;

@@ -62,6 +62,28 @@ static inline int launch_kernel(void (*kernel)(KArgs...), dim3 grid, dim3 block,
     return launch_kernel_cluster(kernel, grid, block, smem, stream, 1, args...);
 }
 
+// Raise a kernel's dynamic shared-memory limit once per device (a process may use several).
+// `flags` is a static array of kMaxDevices bools owned by the call site.
+constexpr int kMaxDevices = 64;
+template <typename K>
+static inline int set_smem_limit_once(K* kernel, size_t bytes, bool* flags) {
+    int dev = 0;
+    cudaError_t e = cudaGetDevice(&dev);
+    if (e != cudaSuccess) return (int)e;
+    if (dev < 0 || dev >= kMaxDevices) return FF_ERR_UNSUPPORTED;
+    if (flags[dev]) return 0;
+    e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)bytes);
+    if (e != cudaSuccess) return (int)e;
+    flags[dev] = true;
+    return 0;
+}
+#define FF_SMEM_LIMIT(kernel, bytes)                                                \
+    do {                                                                            \
+        static bool _set[ff::kMaxDevices];                                          \
+        int _rc = ff::set_smem_limit_once(kernel, (size_t)(bytes), _set);           \
+        if (_rc) return _rc;                                                        \
+    } while (0)
+
 #define FF_LAUNCH(kernel, grid, block, smem, stream, ...)                                              \
     do {                                                                                               \
         int _rc = ff::launch_kernel(kernel, dim3(grid), dim3(block), (size_t)(smem), stream, __VA_ARGS__); \

@@ -524,13 +524,7 @@ template <int TOK>
 static int launch(const CUtensorMap& mw, const CUtensorMap& mx, const GemmArgs& a_in, int n_tiles, int t_tiles,
                   int pdl, cudaStream_t stream) {
     using Cfg = TileCfg<TOK>;
-    static bool attr_set = false;
-    if (!attr_set) {
-        cudaError_t e = cudaFuncSetAttribute(gemm_tc_kernel<TOK>, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                                             (int)Cfg::smem(Cfg::DEEP));
-        if (e != cudaSuccess) return (int)e;
-        attr_set = true;
-    }
+    FF_SMEM_LIMIT(gemm_tc_kernel<TOK>, Cfg::smem(Cfg::DEEP));
     GemmArgs a = a_in;
     const long long blocks = (long long)n_tiles * t_tiles * a.splits;
     // half an SM's shared memory per block: the next product's blocks can move in beside this one's and

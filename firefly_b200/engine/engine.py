@@ -37,7 +37,7 @@ from ..sampling.params import SamplingParams
 from ..sampling.sampler import Sampler
 from .loading import load_model, random_model
 from .request import GenerationRequest, RequestStatus
-from .runner import ModelRunner, StepEntry
+from .runner import ModelRunner, StepEntry, status_text
 from .scheduler import Scheduler
 
 
@@ -92,7 +92,10 @@ class EngineOptions:
 class Engine:
     def __init__(self, model: DecoderModel, config: Optional[ModelConfig] = None,
                  result_queue: Optional[ResultQueue] = None, max_prefill_chunk_size: int = 256,
-                 options: Optional[EngineOptions] = None, raw_config: Optional[dict] = None):
+                 options: Optional[EngineOptions] = None, raw_config: Optional[dict] = None,
+                 runner=None, sampler=None):
+        """``runner`` / ``sampler``: stand-ins for the step function and the sampler (tests of the
+        loop's decisions that need no device); by default the engine makes its own."""
         opts = options or EngineOptions()
         if options is None:
             opts.max_prefill_chunk_size = max_prefill_chunk_size
@@ -122,9 +125,9 @@ class Engine:
         self.max_model_len = min(max_len, num_blocks * opts.kv_block_size) \
             if not all(g.spec.window is not None for g in self.cache.groups) or not self.cache.groups \
             else max_len
-        self.runner = ModelRunner(model, self.cache, max_model_len=self.max_model_len,
-                                  max_batched_tokens=opts.max_num_batched_tokens,
-                                  max_seqs=opts.max_batch_size_limit)
+        self.runner = runner if runner is not None else ModelRunner(
+            model, self.cache, max_model_len=self.max_model_len,
+            max_batched_tokens=opts.max_num_batched_tokens, max_seqs=opts.max_batch_size_limit)
         eos = opts.eos_token_ids
         if eos is None:
             e = (raw_config or {}).get("eos_token_id")
@@ -133,7 +136,7 @@ class Engine:
                                    max_prefill_chunk_size=opts.max_prefill_chunk_size,
                                    max_num_batched_tokens=opts.max_num_batched_tokens,
                                    max_model_len=self.max_model_len, eos_token_ids=eos)
-        self.sampler = Sampler(self.device, opts.max_batch_size_limit)
+        self.sampler = sampler if sampler is not None else Sampler(self.device, opts.max_batch_size_limit)
         self.graphs = None
         if opts.use_cuda_graphs:
             from .graphs import DecodeGraphs
@@ -143,8 +146,9 @@ class Engine:
         self._running = False
         self.requests: Dict[str, GenerationRequest] = {}
         self.stats = {"steps": 0, "graph_steps": 0, "tokens": 0, "preemptions": 0, "launched_ahead": 0,
-                      "dropped_tokens": 0}
+                      "dropped_tokens": 0, "device_errors": 0}
         self._inflight: Optional[_InFlight] = None
+        self._loop_error: Optional[BaseException] = None
 
     # ---- the reference's interface ----------------------------------------------
     def async_generate(self, id: str, input_ids: Sequence[int], max_tokens: int = 512,
@@ -161,24 +165,70 @@ class Engine:
         self._thread.start()
 
     def stop(self) -> None:
+        """Stop the loop and wait for it.  An exception that ended the loop is raised here (every
+        request that was live then has already been finished with an error on the result queue)."""
         self._running = False
         if self._thread is not None:
             self._thread.join()
             self._thread = None
+        err, self._loop_error = self._loop_error, None
+        if err is not None:
+            raise RuntimeError(f"the engine loop ended with an error: {err}") from err
+
+    def _push(self, out: StepOutput) -> None:
+        if self.result_queue is not None:
+            self.result_queue.push(out)
 
     def _loop(self) -> None:
-        torch.cuda.set_device(self.device)
-        while self._running:
-            self._drain_inbox()
-            if not self.scheduler.has_unfinished_requests() and self._inflight is None:
-                time.sleep(0.0005)
+        try:
+            if self.device.type == "cuda":
+                torch.cuda.set_device(self.device)
+            while self._running:
+                self._drain_inbox()
+                if not self.scheduler.has_unfinished_requests() and self._inflight is None:
+                    time.sleep(0.0005)
+                    continue
+                for out in self.step():
+                    self._push(out)
+            for out in self.drain():                     # a step may still be on the stream
+                self._push(out)
+        except BaseException as e:  # noqa: BLE001 - whatever it is, nobody may be left waiting
+            self._loop_error = e
+            self._running = False
+            self._fail_all(f"error: engine loop failed: {type(e).__name__}: {e}")
+
+    def _fail_all(self, reason: str) -> None:
+        """Finish every request the engine knows of (running, waiting, not yet admitted) with
+        ``reason``, so that no caller waits on the result queue for ever."""
+        self._inflight = None
+        live = list(self.scheduler.active_requests) + list(self.scheduler.pending_requests)
+        while True:
+            try:
+                live.append(self._inbox.get_nowait())
+            except queue.Empty:
+                break
+        for req in live:
+            try:
+                self.scheduler.finish_request(req, reason)
+            except Exception:  # noqa: BLE001 - the bookkeeping itself may be what failed
+                req.status, req.finish_reason = RequestStatus.FINISHED, reason
+            self.requests.pop(req.id, None)
+            self._push(StepOutput(req.id, [], True, reason))
+
+    def _device_error(self, code: int, requests: Sequence[GenerationRequest]) -> List[StepOutput]:
+        """A kernel of the step that ``requests`` were in raised the device status word: end them
+        with an error (which request it was cannot be told), clear the word, launch nothing ahead."""
+        reason = f"error: device status {code}: {status_text(code)}"
+        self.stats["device_errors"] += 1
+        self.runner.clear_status()
+        outs = []
+        for req in requests:
+            if req.status is RequestStatus.FINISHED:
                 continue
-            for out in self.step():
-                if self.result_queue is not None:
-                    self.result_queue.push(out)
-        for out in self.drain():                     # a step may still be on the stream
-            if self.result_queue is not None:
-                self.result_queue.push(out)
+            self.scheduler.finish_request(req, reason)
+            self.requests.pop(req.id, None)
+            outs.append(StepOutput(req.id, [], True, reason))
+        return outs
 
     def _drain_inbox(self) -> None:
         while True:
@@ -257,6 +307,12 @@ class Engine:
         tokens = self.graphs.collect(cur.step)
         outputs: List[StepOutput] = []
         self.stats["steps"] += 1
+        if cur.step.status_code:
+            if nxt is not None:
+                self.graphs.collect(nxt.step)         # it ran on the same, possibly damaged, cache: dropped
+            self._inflight = None
+            live = [r for r, dropped in zip(cur.requests, cur.dropped) if not dropped]
+            return self._device_error(cur.step.status_code, live)
         for lane, (req, tok) in enumerate(zip(cur.requests, tokens)):
             if cur.dropped[lane]:
                 self.stats["dropped_tokens"] += 1
@@ -303,8 +359,14 @@ class Engine:
             logits, tokens = self.graphs.run(entries, want_tokens=True, sampling=lanes)
         else:
             logits = self.runner.step(entries)
+        # the status word is copied behind the step; reading the tokens (below) waits past it
+        status = self.runner.queue_status_read()
         if tokens is None:
             tokens = self.sampler.sample(logits, params, counters)
+        if sampling_items or self._status_due():
+            code = status.code()
+            if code:
+                return outputs + self._device_error(code, [it.request for it in batch.items])
         self.stats["steps"] += 1
         self.stats["tokens"] += batch.num_tokens
         for it, tok in zip(sampling_items, tokens):
@@ -313,6 +375,16 @@ class Engine:
             if done:
                 self.requests.pop(it.request.id, None)
         return outputs
+
+
+    STATUS_EVERY = 16     # steps without any sampled token (prompt portions only) between two looks at the status
+
+    def _status_due(self) -> bool:
+        self._unchecked = getattr(self, "_unchecked", 0) + 1
+        if self._unchecked >= self.STATUS_EVERY:
+            self._unchecked = 0
+            return True
+        return False
 
 
 class LLM:

@@ -29,13 +29,13 @@ from .runner import MetaLayout, ModelRunner, StepEntry
 
 class _Bucket:
     __slots__ = ("size", "layout", "meta_host", "meta_stage", "meta_dev", "graph", "logits", "tokens", "h_tokens",
-                 "events", "launches", "lanes", "turn", "by_length", "samp_stage", "samp_dev", "samp_greedy")
+                 "events", "launches", "lanes", "turn", "by_length", "samp_stage", "samp_dev", "samp_greedy", "h_status")
 
 
 class LaunchedStep:
     """A replay that has been put on the stream: its tokens arrive in ``h_tokens`` once
     ``event`` has passed."""
-    __slots__ = ("bucket", "n", "h_tokens", "event", "logits")
+    __slots__ = ("bucket", "n", "h_tokens", "event", "logits", "h_status", "status_code")
 
 
 class DecodeGraphs:
@@ -140,6 +140,7 @@ class DecodeGraphs:
         b.samp_dev = torch.zeros(5 * size, dtype=torch.int32, device=r.device)
         b.samp_greedy = True
         b.h_tokens = [torch.zeros(size, dtype=torch.int32).pin_memory() for _ in range(2)]
+        b.h_status = [torch.zeros(1, dtype=torch.int32).pin_memory() for _ in range(2)]
         b.events = [torch.cuda.Event() for _ in range(2)]
         b.turn = 0
         b.lanes = None
@@ -235,10 +236,12 @@ class DecodeGraphs:
         self.kernel_launches += launches
         step = LaunchedStep()
         step.bucket, step.n, step.logits = b, n, logits[:n]
-        step.h_tokens, step.event = None, None
+        step.h_tokens, step.event, step.h_status, step.status_code = None, None, None, 0
         if want_tokens:
             step.h_tokens = b.h_tokens[k]
             step.h_tokens[:n].copy_(b.tokens[:n], non_blocking=True)
+            step.h_status = b.h_status[k]              # the status word rides behind the tokens
+            step.h_status.copy_(self.runner.status, non_blocking=True)
             step.event = b.events[k]
             step.event.record()
         for e in entries:
@@ -252,6 +255,7 @@ class DecodeGraphs:
         if step.event is None:
             return None
         step.event.synchronize()
+        step.status_code = int(step.h_status[0])
         return step.h_tokens[:step.n].tolist()
 
     def run(self, entries: Sequence[StepEntry], want_tokens: bool = True, sampling=None

@@ -10,8 +10,8 @@ from ..models.decoder import DecoderModel
 from ..models.registry import load_config, spec_for
 from ..ops import kernels as K
 from ..parts import Runtime
-from ..weights.loader import load_weights
-from ..weights.random_init import random_weights
+from ..weights.arena import RandomSource, WeightArena
+from ..weights.loader import load_weights, plan_arena
 
 _DTYPES = {"bfloat16": torch.bfloat16, "bf16": torch.bfloat16, "float32": torch.float32,
            "fp32": torch.float32, "f32": torch.float32}
@@ -57,29 +57,37 @@ def load_config_with_file_hints(model_dir: str) -> ModelConfig:
     return config_from_dict(raw)
 
 
-def load_model(model_dir: str, *, dtype="bfloat16", device="cuda:0") -> Tuple[DecoderModel, ModelConfig]:
-    """Read ``config.json``, pick the model by its architecture name, bind the
-    tensors of ``model.safetensors`` by name."""
+def load_model(model_dir: str, *, dtype="bfloat16", device="cuda:0", weight_dtype: str = "keep"
+               ) -> Tuple[DecoderModel, ModelConfig]:
+    """Read ``config.json``, pick the model by its architecture name, bind the tensors of
+    ``model.safetensors`` by name.  The weights lie in one device arena (``model.weight_arena``);
+    ``model.load_facts`` tells its size and whether the file could be pinned.  ``weight_dtype``:
+    "keep" leaves tensors stored in 32-bit as they are, "engine" narrows them to the engine's type."""
     dt = parse_dtype(dtype)
     dev = require_cuda(device)
     K.set_exact_matmul()
     config = load_config_with_file_hints(model_dir)
     model = DecoderModel(spec_for(config), Runtime(dev, dt))
-    tensors = load_weights(model_dir, model.weight_specs(), dtype=dt, device=dev)
+    tensors, arena, facts = load_weights(model_dir, model, dtype=dt, device=dev, weight_dtype=weight_dtype)
     model.bind(tensors)
-    del tensors
+    model.weight_arena, model.load_facts = arena, facts
     return model, config
 
 
 def random_model(config: ModelConfig, seed: int, *, dtype="bfloat16", device="cuda:0",
                  num_layers: Optional[int] = None) -> DecoderModel:
-    """A model of ``config``'s shape with seeded random weights drawn on the
-    device (no folder is written)."""
+    """A model of ``config``'s shape with seeded random weights drawn on the device (no folder is
+    written): the same values, bit for bit, that ``write_random_model`` stores for this seed."""
     dt = parse_dtype(dtype)
     dev = require_cuda(device)
     K.set_exact_matmul()
     model = DecoderModel(spec_for(config), Runtime(dev, dt))
-    tensors = random_weights(model.weight_specs(), seed, dtype=dt, device=dev)
-    model.bind(tensors)
-    del tensors
+    specs = [w for w in model.weight_specs() if not w.optional]
+    stored = torch.bfloat16 if dt == torch.bfloat16 else torch.float32
+    available = {w.name: (tuple(w.shape), stored if w.kind == "float" else torch.int32) for w in specs}
+    plan, names = plan_arena(model, available, dtype=dt)
+    arena = WeightArena(plan, dev)
+    RandomSource(specs, seed).fill(arena, names)
+    model.bind(arena.tensors())
+    model.weight_arena, model.load_facts = arena, {"arena_bytes": plan.total_bytes}
     return model

@@ -51,6 +51,24 @@ _STATUS = {1: "a token id outside the vocabulary reached the embedding kernel",
            108: "attention (tcgen05): a sequence's page list does not fit the kernel's shared memory"}
 
 
+def status_text(code: int) -> str:
+    return _STATUS.get(int(code), "unknown")
+
+
+class StatusRead:
+    """The device status word on its way to the host: queued behind a step's work, readable
+    without a stall once the host has waited for anything queued after it."""
+
+    __slots__ = ("buf", "event")
+
+    def __init__(self, buf: torch.Tensor, event: "torch.cuda.Event"):
+        self.buf, self.event = buf, event
+
+    def code(self) -> int:
+        self.event.synchronize()
+        return int(self.buf[0])
+
+
 class MetaLayout:
     """Where each integer array of a step lies in the packed metadata buffer."""
 
@@ -94,8 +112,27 @@ class ModelRunner:
         self._meta_dev: Optional[torch.Tensor] = None
         self._ensure_meta(MetaLayout(max_batched_tokens, max_seqs, max_seqs, len(cache.groups),
                                      self.max_blocks_per_seq).size)
+        self._status_ring = [[torch.zeros(1, dtype=torch.int32).pin_memory(), None] for _ in range(self.META_RING)]
+        self._status_turn = 0
         self.steps_run = 0
         self.kernel_launches = 0
+
+    def queue_status_read(self) -> StatusRead:
+        """Queue a copy of the status word to pinned memory behind the work that is on the stream
+        now.  The engine looks at it when it reads the step's tokens, so a kernel that met a bad
+        index or gave up a wait is noticed at the step it happened in, without an extra stall."""
+        slot = self._status_ring[self._status_turn]
+        self._status_turn = (self._status_turn + 1) % len(self._status_ring)
+        if slot[1] is not None:
+            slot[1].synchronize()
+        else:
+            slot[1] = torch.cuda.Event()
+        slot[0].copy_(self.status, non_blocking=True)
+        slot[1].record()
+        return StatusRead(slot[0], slot[1])
+
+    def clear_status(self) -> None:
+        self.status.zero_()
 
     # ------------------------------------------------------------------------------
     META_RING = 4     # pinned metadata buffers in rotation

@@ -12,6 +12,7 @@ import torch
 
 from ..config.base import ModelSpec
 from ..parts import Runtime, build_part, part_class
+from ..parts.base import declared
 from ..weights.loader import WeightSpec
 
 
@@ -26,8 +27,7 @@ class DecoderModel:
         self.final_norm = build_part("norm", spec.final_norm, rt)
         self.head = build_part("head", spec.head, rt)
         self.schedule = spec.resolved_schedule()
-        import inspect
-        self._forward_params = [set(inspect.signature(b.forward).parameters) for b in self.blocks]
+        self._takes_next_norm = [declared(b, "takes_next_norm") for b in self.blocks]
         self.bound = False
 
     # -- weights ------------------------------------------------------------------
@@ -41,6 +41,17 @@ class DecoderModel:
                 if w.name in seen and seen[w.name].shape != w.shape:
                     raise ValueError(f"tensor '{w.name}' is declared twice with different shapes")
                 seen.setdefault(w.name, w)
+        return list(seen.values())
+
+    def fused_specs(self, dtype_of) -> list:
+        """The fused tensors the parts want (``Part.fused_layout``), each once."""
+        parts = [self.embedding, *self.blocks, self.final_norm, self.head]
+        if self.embedding_position is not None:
+            parts.append(self.embedding_position)
+        seen = {}
+        for p in parts:
+            for f in (p.fused_layout(dtype_of) if hasattr(p, "fused_layout") else ()):
+                seen.setdefault(f.name, f)
         return list(seen.values())
 
     def bind(self, tensors: Mapping[str, torch.Tensor]) -> None:
@@ -82,8 +93,8 @@ class DecoderModel:
             block = self.blocks[layer]
             # the norm that follows this run, for a last product that can fold it in
             nxt = self.blocks[runs[i + 1][0]] if i + 1 < len(runs) else None
-            next_norm = nxt.first_norm() if nxt is not None and hasattr(nxt, "first_norm") else None
-            if "next_norm" in self._forward_params[layer]:
+            if self._takes_next_norm[layer]:
+                next_norm = nxt.first_norm() if nxt is not None and hasattr(nxt, "first_norm") else None
                 residual, pending = block.forward(residual, pending, ctx, slot, write, next_norm=next_norm)
             else:
                 residual, pending = block.forward(residual, pending, ctx, slot, write)

@@ -93,13 +93,34 @@ def _headers() -> Sequence[str]:
     return [os.path.join(CSRC, f) for f in sorted(os.listdir(CSRC)) if f.endswith((".cuh", ".h"))]
 
 
+def _included_sources(src: str) -> Sequence[str]:
+    """Files of ``csrc/`` that ``src`` pulls in with ``#include "..."``, followed through (a module may
+    include another module's ``.cu`` to share its kernels); they are part of what the object is made of."""
+    seen, todo = [], [src]
+    while todo:
+        path = todo.pop()
+        try:
+            with open(path, "r", encoding="utf-8", errors="replace") as fh:
+                lines = fh.read().splitlines()
+        except OSError:
+            continue
+        for line in lines:
+            line = line.strip()
+            if line.startswith("#include \""):
+                inc = os.path.join(CSRC, line.split('"')[1])
+                if os.path.isfile(inc) and inc not in seen and inc != src:
+                    seen.append(inc)
+                    todo.append(inc)
+    return seen
+
+
 def library_path(source: str, defines: Optional[Mapping[str, object]] = None) -> Tuple[str, Sequence[str]]:
     src = os.path.join(CSRC, source)
     if not os.path.isfile(src):
         raise KernelBuildError(f"kernel source missing: {src}")
     dflags = [f"-D{k}={v}" for k, v in sorted((defines or {}).items())]
     flags = ARCH_FLAGS + BASE_FLAGS + dflags
-    tag = _hash([src, *_headers()], flags)
+    tag = _hash(sorted({src, *_headers(), *_included_sources(src)}), flags)
     stem = os.path.splitext(source)[0]
     suffix = "".join(f"_{k.lower()}{v}" for k, v in sorted((defines or {}).items()))
     return os.path.join(build_dir(), f"ff_{stem}{suffix}-{tag}.so"), flags

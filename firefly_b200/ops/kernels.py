@@ -76,6 +76,7 @@ _MODULES = {
     "attention_simt": ("attention_simt.cu", None),
     "sampling": ("sampling.cu", None),
     "gemm_tcgen05": ("gemm_tcgen05.cu", None),
+    "weights": ("weights.cu", None),
 }
 
 
@@ -236,7 +237,7 @@ def sample(logits: torch.Tensor, out: torch.Tensor, temperature: Optional[torch.
         assert temperature.dtype == torch.float32 and seeds.dtype == torch.int64 \
             and counters.dtype == torch.int64
     # a row is split over several blocks so that few rows still fill the GPU
-    chunks = max(1, min(64, _SM_TARGET_CTAS // 2 // max(rows, 1), V // 2048))
+    chunks = max(1, min(64, _sm_target_ctas() // 2 // max(rows, 1), V // 2048))
     pv = pi = None
     if chunks > 1:
         key = logits.device
@@ -271,6 +272,7 @@ def linear(x: torch.Tensor, weight: torch.Tensor, out: torch.Tensor) -> None:
 
 
 EPI_BF16, EPI_F32, EPI_RESIDUAL_ADD, EPI_SWIGLU = 0, 1, 2, 3
+GEMM_TC_MAX_TOKENS = 64    # up to here the tcgen05 product is at least as fast as the library's
 USE_TCGEN05_GEMM = True    # tests flip this to compare with the library route
 FOLD_NORM = True           # fold the RMSNorm between two tcgen05 products into their epilogues
 
@@ -347,8 +349,20 @@ def set_exact_matmul() -> None:
 
 
 _ATTN_FORCE_SIMT = False      # tests flip this to compare the two kernels
-_SM_TARGET_CTAS = 592         # 148 SMs x 4: scratch of the decode attention is sized for this many blocks
-_SM_COUNT = 148
+
+
+@functools.lru_cache(maxsize=None)
+def sm_count(device_index: Optional[int] = None) -> int:
+    """Streaming multiprocessors of the device (the current one by default), asked of the driver
+    once.  Grid sizes, K splits and scratch extents are derived from it; no file holds the figure."""
+    if device_index is None:
+        device_index = torch.cuda.current_device()
+    return int(torch.cuda.get_device_properties(device_index).multi_processor_count)
+
+
+def _sm_target_ctas() -> int:
+    """Blocks that the decode attention's scratch memory is sized for: four per SM."""
+    return 4 * sm_count()
 
 
 def _attn_lib(d: int) -> ctypes.CDLL:
@@ -360,26 +374,28 @@ def mma_attention_supported(dtype: torch.dtype, d: int) -> bool:
 
 
 def attn_tiled(q, q_stride, pages, table, cu_q, ctx_lens, n_seqs, total_tiles, out, nq, nkv, d, scale,
-               window) -> None:
-    """Tensor-core attention for any mix of sequences (bfloat16)."""
-    _need_cuda(pages, table, cu_q, ctx_lens, out)
+               window, status: Optional[torch.Tensor] = None) -> None:
+    """Tensor-core attention for any mix of sequences (bfloat16).  ``status`` (int32 [1]) is set to 4
+    when a key that must be read has no valid page in the block table."""
+    _need_cuda(pages, table, cu_q, ctx_lens, out, status)
     num_blocks, _, _, block_size, _ = pages.shape
     _check(_attn_lib(d).ff_attn_tiled(
         _p(q), c_int(q_stride), _p(pages), _p(table), c_int(table.shape[1]), _p(cu_q), _p(ctx_lens),
         c_int(n_seqs), c_int(total_tiles), _p(out), c_int(out.shape[1]), c_int(nq), c_int(nkv),
-        c_int(block_size), c_int(num_blocks), c_float(scale), c_int(window), _stream()), "attn_tiled")
+        c_int(block_size), c_int(num_blocks), c_float(scale), c_int(window), _p(status), _stream()), "attn_tiled")
 
 
 def attn_decode(q, q_stride, pages, table, cu_q, ctx_lens, n_seqs, out, part_o, part_ml, nq, nkv, d,
-                scale, window, num_splits) -> None:
-    """Split-KV tensor-core attention when every sequence has one token (bfloat16)."""
-    _need_cuda(pages, table, cu_q, ctx_lens, out, part_o, part_ml)
+                scale, window, num_splits, status: Optional[torch.Tensor] = None) -> None:
+    """Split-KV tensor-core attention when every sequence has one token (bfloat16).  ``status`` as
+    for `attn_tiled`."""
+    _need_cuda(pages, table, cu_q, ctx_lens, out, part_o, part_ml, status)
     num_blocks, _, _, block_size, _ = pages.shape
     _check(_attn_lib(d).ff_attn_decode(
         _p(q), c_int(q_stride), _p(pages), _p(table), c_int(table.shape[1]), _p(cu_q), _p(ctx_lens),
         c_int(n_seqs), _p(out), c_int(out.shape[1]), _p(part_o), _p(part_ml), c_int(nq), c_int(nkv),
         c_int(block_size), c_int(num_blocks), c_float(scale), c_int(window), c_int(num_splits),
-        _stream()), "attn_decode")
+        _p(status), _stream()), "attn_decode")
     global LAUNCHES
     if num_splits > 1:
         LAUNCHES += 1     # the kernel that joins the splits
@@ -456,7 +472,7 @@ def decode_splits(n_seqs: int, nkv: int, max_kv_len: int) -> int:
     8 3.70 (6) against 3.83 (8), 16 4.18 (3) against 4.39 (8), 32 5.43 (3) against 5.70 (8),
     64 8.08 (3) against 8.34 (8)."""
     tiles = max(1, -(-max_kv_len // 64))
-    places = 3 * _SM_COUNT
+    places = 3 * sm_count()
     want = max(3, min(places // max(1, n_seqs * nkv), 20))
     return max(1, min(want, tiles, 64))
 
@@ -467,7 +483,7 @@ DECODE_MAX_RANGES = 24      # a sequence is cut into at most this many ranges (b
 
 @functools.lru_cache(maxsize=None)
 def _decode_places_per_kv_head(nkv: int, d: int) -> int:
-    return _SM_COUNT * int(_attn_lib(d).ff_attn_decode_blocks_per_sm()) // nkv
+    return sm_count() * int(_attn_lib(d).ff_attn_decode_blocks_per_sm()) // nkv
 
 
 def lengths_differ_much(ctx_lens) -> bool:
@@ -501,7 +517,7 @@ def _decode_scratch(ws, n: int, nq: int, nkv: int, d: int, splits: int):
     number of ranges per sequence.  The extent never shrinks as the batch grows (captured graphs
     of every batch size share the buffers that the largest one sized)."""
     units = _decode_places_per_kv_head(nkv, d) if DECODE_BY_UNITS else 0
-    cap = max(n * nq * splits, (nq // nkv) * _SM_TARGET_CTAS + n * nq, nq * units * (units // 2))
+    cap = max(n * nq * splits, (nq // nkv) * _sm_target_ctas() + n * nq, nq * units * (units // 2))
     return (ws.get("attn.part_o", (cap * d,), torch.float32), ws.get("attn.part_ml", (cap * 2,), torch.float32),
             ws.get("attn.seq_ranges", (max(n, 128),), torch.int32))
 
@@ -547,10 +563,10 @@ def paged_attention(q: torch.Tensor, q_stride: int, pages: torch.Tensor, table: 
         part_o, part_ml, seq_ranges = _decode_scratch(ctx.workspace, n_dec, nq, nkv, d, splits)
         if units:
             attn_decode_units(q, q_stride, pages, table, ctx.cu_q, ctx.ctx_lens, n_dec, out, part_o, part_ml,
-                              seq_ranges, nq, nkv, d, scale, window, units, DECODE_MAX_RANGES)
+                              seq_ranges, nq, nkv, d, scale, window, units, DECODE_MAX_RANGES, status=ctx.status)
         else:
             attn_decode(q, q_stride, pages, table, ctx.cu_q, ctx.ctx_lens, n_dec, out, part_o, part_ml, nq, nkv,
-                        d, scale, window, splits)
+                        d, scale, window, splits, ctx.status)
     if n_dec < n:
         # portions of prompts: tiled kernel over the remaining sequences (token offsets in cu_q are absolute)
         if USE_TC_ATTENTION and tc_attention_supported(q.dtype, d, pages.shape[3], ctx.max_kv_len):
@@ -560,4 +576,4 @@ def paged_attention(q: torch.Tensor, q_stride: int, pages: torch.Tensor, table: 
         else:
             tiles = sum(-(-(ql * G) // 64) for ql in ctx.q_lens[n_dec:])
             attn_tiled(q, q_stride, pages, table[n_dec:], ctx.cu_q[n_dec:], ctx.ctx_lens[n_dec:], n - n_dec,
-                       tiles, out, nq, nkv, d, scale, window)
+                       tiles, out, nq, nkv, d, scale, window, ctx.status)

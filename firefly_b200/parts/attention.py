@@ -27,12 +27,15 @@ import torch
 
 from ..cache.spec import PagedKVSpec
 from ..ops import kernels as K
+from ..weights.arena import FusedSpec, Piece
 from ..weights.loader import WeightSpec
 from .base import Part, register_part
 from .linear import apply_linear, linear_into_residual
 
 
 class GQAttention(Part):
+    adds_into_residual = True        # forward(accumulate_into=...)
+    folds_next_norm = True           # forward(then_norm=...)
     accepts_folded_norm = True       # its first operation is a product that can finish a folded norm
 
     def __init__(self, spec, rt, position=None):
@@ -68,19 +71,33 @@ class GQAttention(Part):
                     WeightSpec(self.name("v_proj.weight"), (self.nkv * self.d, self.hidden))]
         out.append(WeightSpec(self.name("o_proj.weight"), (self.hidden, self.nq * self.d)))
         if self.qk_norm:
-            out.append(WeightSpec(self.name("q_norm.weight"), (self.d,), init="norm"))
+            out.append(WeightSpec(self.name("q_norm.weight"), (self.d,), init="norm", as_float32=True))
             if self.has_kv:
-                out.append(WeightSpec(self.name("k_norm.weight"), (self.d,), init="norm"))
+                out.append(WeightSpec(self.name("k_norm.weight"), (self.d,), init="norm", as_float32=True))
         return out
 
+    def fused_layout(self, dtype_of) -> List[FusedSpec]:
+        """q, k and v stacked into one matrix [(nq + 2 nkv) d, hidden], the three projections' rows
+        in this order."""
+        if not self.has_kv:
+            return []
+        q_rows, kv_rows = self.nq * self.d, self.nkv * self.d
+        return [FusedSpec(self.name("qkv_proj.weight"), (q_rows + 2 * kv_rows, self.hidden),
+                          (Piece(self.name("q_proj.weight"), 0), Piece(self.name("k_proj.weight"), q_rows),
+                           Piece(self.name("v_proj.weight"), q_rows + kv_rows)))]
+
     def bind(self, tensors: Mapping[str, torch.Tensor]) -> None:
-        mats = [self._matrix(tensors[self.name("q_proj.weight")])]
-        if self.has_kv:
-            mats += [self._matrix(tensors[self.name("k_proj.weight")]),
-                     self._matrix(tensors[self.name("v_proj.weight")])]
-        if len({m.dtype for m in mats}) != 1:
-            mats = [m.to(torch.float32) for m in mats]
-        self.w_qkv = torch.cat(mats, dim=0).contiguous() if len(mats) > 1 else mats[0]
+        fused = self.name("qkv_proj.weight")
+        if fused in tensors:
+            self.w_qkv = self._matrix(tensors[fused])
+        else:
+            mats = [self._matrix(tensors[self.name("q_proj.weight")])]
+            if self.has_kv:
+                mats += [self._matrix(tensors[self.name("k_proj.weight")]),
+                         self._matrix(tensors[self.name("v_proj.weight")])]
+            if len({m.dtype for m in mats}) != 1:
+                mats = [m.to(torch.float32) for m in mats]
+            self.w_qkv = torch.cat(mats, dim=0).contiguous() if len(mats) > 1 else mats[0]
         self.w_o = self._matrix(tensors[self.name("o_proj.weight")])
         if self.qk_norm:
             self.q_norm_w = self._vector32(tensors[self.name("q_norm.weight")])

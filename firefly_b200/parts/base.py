@@ -24,9 +24,28 @@ Categories and what each must offer (beyond ``weight_specs`` and ``bind``):
 
 Registering a new kind: ``register_part("mixer", "my_mixer", MyMixer)``; a
 ``PartSpec("my_mixer", {...})`` in a layer then builds it.
+
+Optional abilities are *declared* as class attributes and checked when a block or a model is
+built (``declared``): a flag without its keyword, or a keyword without its flag, is an error then,
+not a fusion that is silently lost.
+
+=====================  ==========================  ==============================================
+flag (class attribute)  keyword / method it needs   meaning
+=====================  ==========================  ==============================================
+adds_into_residual      forward(accumulate_into=)   mixer / feed_forward may add its output into the
+                                                    32-bit residual itself and return None
+folds_next_norm         forward(then_norm=)         ... and, told which norm follows, may leave that
+                                                    norm folded (a ``FoldedNorm``) for its consumer
+accepts_folded_norm     (none)                      its first operation can finish a ``FoldedNorm``
+takes_next_norm         forward(next_norm=)         arrangement: hands the next block's first norm
+                                                    to its last part
+foldable                fold_buffers, size, eps     norm: can be folded into the products around it
+=====================  ==========================  ==============================================
+A part that declares nothing simply runs unfused; it need not derive from ``Part``.
 """
 from __future__ import annotations
 
+import inspect
 from dataclasses import dataclass, field
 from typing import Any, Dict, List, Mapping
 
@@ -55,6 +74,31 @@ def part_class(category: str, kind: str) -> type:
                           f"{', '.join(sorted(_REGISTRY.get(category, {}))) or '(none)'}") from None
 
 
+_FLAG_KEYWORD = {"adds_into_residual": "accumulate_into", "folds_next_norm": "then_norm",
+                 "takes_next_norm": "next_norm"}
+_FLAG_MEMBERS = {"foldable": ("fold_buffers", "size", "eps")}
+
+
+def declared(part, flag: str) -> bool:
+    """Does ``part`` declare the optional ability ``flag``?  Checks the declaration against what the
+    part really offers, both ways, and raises ``ConfigError`` when they disagree."""
+    has = bool(getattr(part, flag, False))
+    who = type(part).__name__
+    kw = _FLAG_KEYWORD.get(flag)
+    if kw is not None:
+        takes = kw in inspect.signature(part.forward).parameters
+        if has and not takes:
+            raise ConfigError(f"{who} declares {flag} = True but its forward() has no '{kw}' keyword")
+        if takes and not has:
+            raise ConfigError(f"{who}.forward() takes '{kw}' but the class does not declare {flag} = True")
+    for member in _FLAG_MEMBERS.get(flag, ()):
+        if has and not hasattr(part, member):
+            raise ConfigError(f"{who} declares {flag} = True but has no '{member}'")
+    if flag == "folds_next_norm" and has and not getattr(part, "adds_into_residual", False):
+        raise ConfigError(f"{who} declares folds_next_norm without adds_into_residual")
+    return has
+
+
 @dataclass
 class Runtime:
     """The surroundings a part may use: where it runs and in which type."""
@@ -70,6 +114,12 @@ def build_part(category: str, spec: PartSpec, rt: Runtime, **extra):
 
 class Part:
     """Base: parameters from the spec, tensors bound by full name."""
+
+    # optional abilities (see the module's table); a subclass that has one sets it to True
+    adds_into_residual = False
+    folds_next_norm = False
+    accepts_folded_norm = False
+    foldable = False
 
     def __init__(self, spec: PartSpec, rt: Runtime):
         self.spec = spec
@@ -88,6 +138,14 @@ class Part:
         return f"{self.prefix}.{leaf}" if self.prefix else leaf
 
     def weight_specs(self) -> List[WeightSpec]:
+        return []
+
+    def fused_layout(self, dtype_of) -> list:
+        """Tensors this part wants put together from several of its source tensors when the weights
+        are loaded: a list of ``weights.arena.FusedSpec``.  ``dtype_of(source name)`` is the element
+        type that source will have on the device.  The loader then keeps only the fused tensor and
+        hands it to ``bind`` under its name; a part must still be able to bind from the plain
+        sources (tensors made by hand)."""
         return []
 
     def bind(self, tensors: Mapping[str, torch.Tensor]) -> None:

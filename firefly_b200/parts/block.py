@@ -8,13 +8,12 @@ each sum is done once, in 32-bit, without a pass of its own.
 """
 from __future__ import annotations
 
-import inspect
 from typing import List, Mapping
 
 import torch
 
 from ..weights.loader import WeightSpec
-from .base import Part, Runtime, build_part, register_part
+from .base import Part, Runtime, build_part, declared, register_part
 
 
 class Block:
@@ -32,19 +31,19 @@ class Block:
             raise ValueError(f"arrangement '{layer_spec.arrangement}' needs {self.n_norms} norms, "
                              f"got {len(layer_spec.norms)}")
         self.norms = [build_part("norm", n, rt) for n in layer_spec.norms]
-        # a part whose forward takes ``accumulate_into`` may add its output into the 32-bit
-        # residual itself (and return None); others return a delta
-        self._mixer_fuses = "accumulate_into" in inspect.signature(self.mixer.forward).parameters
-        self._ffn_fuses = "accumulate_into" in inspect.signature(self.feed_forward.forward).parameters
-        # ... and, told which norm follows (``then_norm``), may fold that norm into its last product
-        self._mixer_folds = "then_norm" in inspect.signature(self.mixer.forward).parameters
-        self._ffn_folds = "then_norm" in inspect.signature(self.feed_forward.forward).parameters
-        # a part that declares ``accepts_folded_norm`` may be handed a FoldedNorm as its input
-        self._mixer_defers = bool(getattr(self.mixer, "accepts_folded_norm", False))
-        self._ffn_defers = bool(getattr(self.feed_forward, "accepts_folded_norm", False))
+        # the parts' declared abilities (parts/base.py), checked here against their signatures:
+        # adding into the 32-bit residual themselves, folding the norm that follows into their last
+        # product, taking a folded norm as input
+        self._mixer_fuses = declared(self.mixer, "adds_into_residual")
+        self._ffn_fuses = declared(self.feed_forward, "adds_into_residual")
+        self._mixer_folds = declared(self.mixer, "folds_next_norm")
+        self._ffn_folds = declared(self.feed_forward, "folds_next_norm")
+        self._mixer_defers = declared(self.mixer, "accepts_folded_norm")
+        self._ffn_defers = declared(self.feed_forward, "accepts_folded_norm")
+        self._norm_folds = [declared(nrm, "foldable") for nrm in self.norms]
         for k, nrm in enumerate(self.norms):
-            if hasattr(nrm, "fold_tag"):
-                nrm.fold_tag = f"fold.{k}"
+            if self._norm_folds[k]:
+                nrm.fold_tag = f"fold.{k}"      # scratch of the folded form, one per norm of the block
 
     def parts(self) -> List[Part]:
         out = [self.mixer, self.feed_forward, *self.norms]
@@ -55,6 +54,16 @@ class Block:
     def weight_specs(self) -> List[WeightSpec]:
         return [w for p in self.parts() for w in p.weight_specs()]
 
+    takes_next_norm = False      # an arrangement whose forward takes ``next_norm`` sets this
+
+    def first_norm(self):
+        """The norm a block in front of this one may fold into its last product (None: none)."""
+        return None
+
+    def fused_layout(self, dtype_of) -> list:
+        # a part need not derive from ``Part``: one without the method wants nothing fused
+        return [f for p in self.parts() if hasattr(p, "fused_layout") for f in p.fused_layout(dtype_of)]
+
     def bind(self, tensors: Mapping[str, torch.Tensor]) -> None:
         for p in self.parts():
             p.bind(tensors)
@@ -64,19 +73,24 @@ class Block:
 
 
 class PreNormBlock(Block):
+    takes_next_norm = True
+
     def first_norm(self):
         """The norm a block in front of this one may fold into its last product."""
         return self.norms[0]
 
     def forward(self, residual: torch.Tensor, pending, ctx, slot: int, write_cache: bool, next_norm=None):
-        x = self.norms[0].forward(residual, pending, ctx, may_defer=self._mixer_defers)
+        # only a foldable norm knows ``may_defer`` (hand a folded norm on to a consumer that finishes it)
+        defer0 = {"may_defer": True} if self._norm_folds[0] and self._mixer_defers else {}
+        defer1 = {"may_defer": True} if self._norm_folds[1] and self._ffn_defers else {}
+        x = self.norms[0].forward(residual, pending, ctx, **defer0)
         kw = {}
         if self._mixer_fuses:
             kw["accumulate_into"] = residual
             if self._mixer_folds:
                 kw["then_norm"] = self.norms[1]
         a = self.mixer.forward(x, ctx, slot, write_cache, **kw)
-        x = self.norms[1].forward(residual, a, ctx, may_defer=self._ffn_defers)
+        x = self.norms[1].forward(residual, a, ctx, **defer1)
         kw = {}
         if self._ffn_fuses:
             kw["accumulate_into"] = residual

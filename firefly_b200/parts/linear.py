@@ -19,13 +19,11 @@ import torch
 
 from ..ops import kernels as K
 
-TC_MAX_TOKENS = 64        # up to here the tcgen05 kernel is at least as fast as the library
-_SM_COUNT = 148
 
 
 def tc_usable(x: torch.Tensor, weight: torch.Tensor) -> bool:
     return (K.USE_TCGEN05_GEMM and x.dtype == torch.bfloat16 and weight.dtype == torch.bfloat16
-            and x.shape[0] <= TC_MAX_TOKENS and weight.shape[1] % 8 == 0)
+            and x.shape[0] <= K.GEMM_TC_MAX_TOKENS and weight.shape[1] % 8 == 0)
 
 
 def _splits(N: int, Kd: int) -> int:
@@ -36,7 +34,7 @@ def _splits(N: int, Kd: int) -> int:
     SMs that hold two blocks of this product make up for the ones that finish early."""
     tiles = -(-N // 128)
     kb = -(-Kd // 64)
-    want = (13 * _SM_COUNT + 5 * tiles) // (10 * tiles)          # round(1.3 * SMs / tiles)
+    want = (13 * K.sm_count() + 5 * tiles) // (10 * tiles)       # round(1.3 * SMs / tiles)
     return max(1, min(want, 8, kb // 4))
 
 
@@ -92,8 +90,8 @@ def linear_into_residual(x: torch.Tensor, weight: torch.Tensor, residual: Option
     returned for the next norm to add."""
     x = _resolve(x, weight)
     if residual is not None and tc_usable(x, weight):
-        if then_norm is not None and K.FOLD_NORM and getattr(then_norm, "size", None) == weight.shape[0] \
-                and hasattr(then_norm, "fold_buffers"):
+        if then_norm is not None and K.FOLD_NORM and getattr(then_norm, "foldable", False) \
+                and then_norm.size == weight.shape[0]:
             from .norm import FoldedNorm
             xw, nw, ssq = then_norm.fold_buffers(x.shape[0], ctx)
             _tc(x, weight, residual, K.EPI_RESIDUAL_ADD, ctx, norm_out=(xw, nw, ssq))

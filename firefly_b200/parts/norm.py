@@ -32,6 +32,8 @@ class FoldedNorm:
 
 
 class RMSNorm(Part):
+    foldable = True                      # fold_buffers / size / eps: the products around it can take it in
+
     def __init__(self, spec, rt):
         super().__init__(spec, rt)
         self.size = int(self.p("size"))
@@ -40,7 +42,7 @@ class RMSNorm(Part):
         self.fold_tag = "fold.0"          # scratch of the folded form; a block gives its norms different tags
 
     def weight_specs(self) -> List[WeightSpec]:
-        return [WeightSpec(self.name("weight"), (self.size,), init="norm")]
+        return [WeightSpec(self.name("weight"), (self.size,), init="norm", as_float32=True)]
 
     def bind(self, tensors: Mapping[str, torch.Tensor]) -> None:
         self.weight = self._vector32(tensors[self.name("weight")])

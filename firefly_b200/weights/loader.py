@@ -7,8 +7,16 @@ shapes against that list and returns ``{name: tensor}`` on the device.
 Storage policy.  16-bit floating tensors are kept in bfloat16 (a BF16 tensor is
 copied bit for bit; the reference instead converts BF16 to FP16 element by
 element on the host, include/firefly/model_loader.h:79-92).  A tensor stored in
-32-bit floating point stays 32-bit.  Integer tensors of any width become int32.
-With ``dtype=float32`` every floating tensor is widened to 32-bit (exact).
+32-bit floating point stays 32-bit (``weight_dtype="keep"``, the default: its
+products then run in true 32-bit also inside a bfloat16 engine) or is narrowed
+to the engine's type on the device (``weight_dtype="engine"``).  Integer tensors
+of any width become int32.  With ``dtype=float32`` every floating tensor is
+widened to 32-bit (exact).  Tensors that a part reads in 32-bit arithmetic
+(norm weights) are declared ``as_float32`` and converted once, on the way in.
+
+All tensors lie in one device arena (``weights/arena.py``) and are copied from a
+pinned mapping of the file straight into their final places; tensors that parts
+want fused (q|k|v, gate|up) exist only in their fused form.
 The reference binds with ``unordered_map::at`` (src/model/qwen_model.cu:58-92),
 so a missing tensor surfaces as a bare ``std::out_of_range``; here all missing,
 unexpected and mis-shaped tensors are listed in one ``WeightError``.
@@ -56,6 +64,7 @@ class WeightSpec:
               "norm" (1 + N(0, 0.01)), "zeros", "ones", or "int:<high>" for a
               table of integers in [0, high).
     ``optional``  may be absent from the file (e.g. a tied head stored anyway).
+    ``as_float32``  kept in 32-bit on the device whatever the file and the engine use.
     """
 
     name: str
@@ -63,14 +72,20 @@ class WeightSpec:
     kind: str = "float"
     init: str = "linear"
     optional: bool = False
+    as_float32: bool = False
 
 
-def storage_dtype(stored: torch.dtype, mode: torch.dtype) -> torch.dtype:
+WEIGHT_DTYPES = ("keep", "engine")
+
+
+def storage_dtype(stored: torch.dtype, mode: torch.dtype, weight_dtype: str = "keep") -> torch.dtype:
     """The dtype a stored tensor has on the device under engine dtype ``mode``."""
+    if weight_dtype not in WEIGHT_DTYPES:
+        raise ValueError(f"weight_dtype must be one of {WEIGHT_DTYPES}, got {weight_dtype!r}")
     if stored.is_floating_point:
         if mode == torch.float32:
             return torch.float32
-        if stored in (torch.float32, torch.float64):
+        if stored in (torch.float32, torch.float64) and weight_dtype == "keep":
             return torch.float32
         return torch.bfloat16
     return torch.int32
@@ -96,33 +111,56 @@ def check_and_collect(where: str, available: Dict[str, Tuple[Tuple[int, ...], to
         raise WeightError(where, missing, unexpected, wrong_shape, wrong_kind)
 
 
-def load_weights(model_dir: str, expected: Iterable[WeightSpec], *, dtype: torch.dtype,
-                 device: torch.device | str, ignore: Iterable[str] = ()) -> Dict[str, torch.Tensor]:
+def read_weights(model_dir: str, expected: Iterable[WeightSpec], *, dtype: torch.dtype,
+                 ignore: Iterable[str] = (), weight_dtype: str = "keep") -> Dict[str, torch.Tensor]:
+    """The folder's tensors in host memory, checked and converted by the same rules as the device
+    loader (for tools and tests; the engine itself loads through ``load_weights``)."""
+    from .arena import FileSource
     expected = list(expected)
-    files = open_model_files(model_dir)
+    source = FileSource(model_dir, register=False)
     try:
-        where: Dict[str, object] = {}
-        available: Dict[str, Tuple[Tuple[int, ...], torch.dtype]] = {}
-        for f in files:
-            for name, ent in f.entries.items():
-                if name in available:
-                    raise SafetensorsError(f"tensor '{name}' appears in more than one shard")
-                available[name] = (ent.shape, ent.dtype)
-                where[name] = f
-        check_and_collect(model_dir, available, expected, ignore)
+        check_and_collect(model_dir, source.available, expected, ignore)
         out: Dict[str, torch.Tensor] = {}
         for w in expected:
-            if w.name not in available:
-                continue
-            t = where[w.name].tensor(w.name)
-            target = storage_dtype(t.dtype, dtype)
-            # one copy to the device in the stored dtype, conversion there
-            if t.dtype == torch.float64:
-                t = t.to(torch.float32)
-            if not t.dtype.is_floating_point and t.dtype != torch.int32:
-                t = t.to(torch.int32)
-            out[w.name] = t.to(device=device).to(target).contiguous()
+            if w.name in source.available:
+                t = source.where[w.name].tensor(w.name)
+                target = torch.float32 if (w.as_float32 and w.kind == "float") \
+                    else storage_dtype(t.dtype, dtype, weight_dtype)
+                out[w.name] = t.to(target).clone()
         return out
     finally:
-        for f in files:
-            f.close()
+        source.close()
+
+
+def plan_arena(model, available: Dict[str, Tuple[Tuple[int, ...], torch.dtype]], *, dtype: torch.dtype,
+               weight_dtype: str = "keep"):
+    """The arena plan of ``model`` for tensors stored as ``available`` says, and the names to load."""
+    from .arena import ArenaPlan
+    sources = {}
+    for w in model.weight_specs():
+        if w.name not in available:
+            continue
+        _, stored = available[w.name]
+        dev_dt = torch.float32 if (w.as_float32 and w.kind == "float") else storage_dtype(stored, dtype, weight_dtype)
+        sources[w.name] = (tuple(w.shape), dev_dt)
+    fused = model.fused_specs(lambda name: sources[name][1]) if hasattr(model, "fused_specs") else []
+    fused = [f for f in fused if all(p.source in sources for p in f.pieces)]
+    return ArenaPlan(sources, fused), list(sources)
+
+
+def load_weights(model_dir: str, model, *, dtype: torch.dtype, device: torch.device | str,
+                 ignore: Iterable[str] = (), weight_dtype: str = "keep", register: bool = True):
+    """Check the folder's tensors against what ``model`` expects (one error for everything wrong),
+    make the arena and fill it.  Returns (name -> tensor for ``model.bind``, the arena, load facts)."""
+    from .arena import FileSource, WeightArena
+    source = FileSource(model_dir, register=register)
+    try:
+        check_and_collect(model_dir, source.available, model.weight_specs(), ignore)
+        plan, names = plan_arena(model, source.available, dtype=dtype, weight_dtype=weight_dtype)
+        arena = WeightArena(plan, device)
+        source.fill(arena, names)
+        facts = {"arena_bytes": plan.total_bytes, "file_bytes": source.bytes_copied,
+                 "pinned_files": source.pinned_files, "files": len(source.files)}
+        return arena.tensors(), arena, facts
+    finally:
+        source.close()

@@ -10,7 +10,7 @@ import plain_qwen3 as P
 from firefly_b200.config import ConfigError, Qwen3Config, ScheduleEntry
 from firefly_b200.models import (config_from_dict, expected_weights, known_architectures, load_config,
                                  spec_for)
-from firefly_b200.weights import (SafetensorsError, SafetensorsFile, WeightError, load_weights,
+from firefly_b200.weights import (SafetensorsError, SafetensorsFile, WeightError, read_weights,
                                   save_safetensors, write_random_model)
 from firefly_b200.weights.loader import storage_dtype
 
@@ -142,7 +142,7 @@ def test_load_weights_reports_everything_at_once(tmp_path):
     d = _folder(tmp_path, raw, w)
     spec = spec_for(load_config(d))
     with pytest.raises(WeightError) as ei:
-        load_weights(d, expected_weights(spec), dtype=torch.float32, device="cpu")
+        read_weights(d, expected_weights(spec), dtype=torch.float32)
     e = ei.value
     assert set(e.missing) == {"model.layers.1.mlp.up_proj.weight", "model.norm.weight"}
     assert e.unexpected == ["extra.tensor"]
@@ -160,11 +160,11 @@ def test_load_weights_dtype_policy(tmp_path):
     w["lm_head.weight"] = torch.zeros(256, 64)          # a tied head stored anyway is ignored
     d = _folder(tmp_path, raw, w)
     spec = spec_for(load_config(d))
-    got = load_weights(d, expected_weights(spec), dtype=torch.bfloat16, device="cpu")
+    got = read_weights(d, expected_weights(spec), dtype=torch.bfloat16)
     assert got["model.layers.0.mlp.up_proj.weight"].dtype == torch.bfloat16      # kept in bfloat16
     assert got["model.layers.0.self_attn.q_proj.weight"].dtype == torch.float32  # stored 32-bit stays
     assert torch.equal(got["model.layers.0.self_attn.q_proj.weight"], w["model.layers.0.self_attn.q_proj.weight"])
-    got32 = load_weights(d, expected_weights(spec), dtype=torch.float32, device="cpu")
+    got32 = read_weights(d, expected_weights(spec), dtype=torch.float32)
     assert all(t.dtype == torch.float32 for t in got32.values())
     assert storage_dtype(torch.int64, torch.bfloat16) == torch.int32
     assert storage_dtype(torch.uint8, torch.float32) == torch.int32
@@ -190,7 +190,7 @@ def test_missing_files(tmp_path):
     (tmp_path / "config.json").write_text(json.dumps(P.TINY_A))
     spec = spec_for(load_config(str(tmp_path)))
     with pytest.raises(SafetensorsError, match="model.safetensors"):
-        load_weights(str(tmp_path), expected_weights(spec), dtype=torch.float32, device="cpu")
+        read_weights(str(tmp_path), expected_weights(spec), dtype=torch.float32)
 
 
 def test_random_model_folder(tmp_path):
@@ -198,14 +198,15 @@ def test_random_model_folder(tmp_path):
     d = write_random_model(cfg, 7, str(tmp_path / "r"), dtype=torch.bfloat16)
     assert load_config(d) == cfg
     spec = spec_for(cfg)
-    a = load_weights(d, expected_weights(spec), dtype=torch.bfloat16, device="cpu")
+    a = read_weights(d, expected_weights(spec), dtype=torch.bfloat16)
     d2 = write_random_model(cfg, 7, str(tmp_path / "r2"), dtype=torch.bfloat16)
-    b = load_weights(d2, expected_weights(spec), dtype=torch.bfloat16, device="cpu")
+    b = read_weights(d2, expected_weights(spec), dtype=torch.bfloat16)
     d3 = write_random_model(cfg, 8, str(tmp_path / "r3"), dtype=torch.bfloat16)
-    c = load_weights(d3, expected_weights(spec), dtype=torch.bfloat16, device="cpu")
+    c = read_weights(d3, expected_weights(spec), dtype=torch.bfloat16)
     assert all(torch.equal(a[k], b[k]) for k in a)                 # same seed, same weights
     assert not torch.equal(a["lm_head.weight"], c["lm_head.weight"])
-    assert all(v.dtype == torch.bfloat16 for v in a.values())
+    # matrices stay bfloat16; norm weights are read in 32-bit arithmetic and are widened once, on the way in
+    assert all(v.dtype == (torch.float32 if v.dim() == 1 else torch.bfloat16) for v in a.values())
     q = a["model.layers.0.self_attn.q_proj.weight"].float()
     n = a["model.norm.weight"].float()
     assert abs(q.std().item() - 0.02) < 0.002 and abs(n.mean().item() - 1.0) < 0.01
@@ -213,10 +214,10 @@ def test_random_model_folder(tmp_path):
     os.remove(os.path.join(d, "model.safetensors"))
     names = sorted(a)
     half = len(names) // 2
-    save_safetensors(os.path.join(d, "s1.safetensors"), {k: a[k] for k in names[:half]})
-    save_safetensors(os.path.join(d, "s2.safetensors"), {k: a[k] for k in names[half:]})
+    save_safetensors(os.path.join(d, "s1.safetensors"), {k: a[k].to(torch.bfloat16) for k in names[:half]})
+    save_safetensors(os.path.join(d, "s2.safetensors"), {k: a[k].to(torch.bfloat16) for k in names[half:]})
     wm = {k: ("s1.safetensors" if i < half else "s2.safetensors") for i, k in enumerate(names)}
     with open(os.path.join(d, "model.safetensors.index.json"), "w") as fh:
         json.dump({"weight_map": wm}, fh)
-    s = load_weights(d, expected_weights(spec), dtype=torch.bfloat16, device="cpu")
+    s = read_weights(d, expected_weights(spec), dtype=torch.bfloat16)
     assert all(torch.equal(a[k], s[k]) for k in a)
