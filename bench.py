@@ -45,7 +45,7 @@ SHAPES = {   # BASELINE.json configs[2] (the metric), configs[3] and configs[4]
 def load_shape(name: str = "8b"):
     """Layer sizes of a BASELINE.json shape (default configs[2], Qwen3-8B-shaped), as config.json keys."""
     base = dict(architectures=["Qwen3ForCausalLM"], head_dim=128, vocab_size=151936,
-                max_position_embeddings=4096, rms_norm_eps=1e-6, rope_theta=1e6)
+                max_position_embeddings=40960, rms_norm_eps=1e-6, rope_theta=1e6)
     base.update(SHAPES[name])
     return base
 
@@ -197,7 +197,7 @@ def main() -> int:
         ctx = args.context if steps is None else min(args.context, P + 1 + W + 2 * steps + 6 + max(B, 64))
         opts = EngineOptions(max_prefill_chunk_size=P, max_batch_size_limit=max(B, 1),
                              max_num_batched_tokens=max(P, B), kv_block_size=16,
-                             num_kv_blocks=B * (-(-ctx // 16)), max_model_len=args.context,
+                             num_kv_blocks=B * (-(-ctx // 16)),      # max_model_len: the configuration's
                              eos_token_ids=[], graph_batch_sizes=(1, 2, 4, 8, 16, 32, 64))
         return Engine(model, cfg, options=opts)
 
@@ -221,13 +221,20 @@ def main() -> int:
         for r in reqs:
             assert eng.cache.grow(r.cache, r.cache.num_tokens + steps + 1)
         entries = [StepEntry(r.cache, [r.generated_tokens[-1]], [0]) for r in reqs]
-        staged_h = torch.empty((steps, lay.size), dtype=torch.int32).pin_memory()
+        # every step's metadata is made beforehand and parked on the device: the head of the buffer
+        # (tokens, positions, lengths, table updates) per step; the block tables themselves, which
+        # hold all the pages of the run already, go up once in front of the timed region
+        head = lay.head_size
+        staged_h = torch.empty((steps, head), dtype=torch.int32).pin_memory()
         base = [r.cache.num_tokens for r in reqs]
         for s in range(steps):
             for r, c in zip(reqs, base):
                 r.cache.num_tokens = c + s          # positions of this step
             g._fill(b, entries)
-            staged_h[s].copy_(b.meta_host)
+            if not g._write_updates(b):
+                assert s == 0, "only the first step may change more table entries than the update list holds"
+                b.meta_dev.copy_(b.meta_host)
+            staged_h[s].copy_(b.meta_host[:head])
         for r, c in zip(reqs, base):
             r.cache.num_tokens = c
         staged = staged_h.to(dev, non_blocking=True)
@@ -236,7 +243,7 @@ def main() -> int:
         torch.cuda.synchronize()
         ev0.record()
         for s in range(steps):
-            b.meta_dev.copy_(staged[s], non_blocking=True)
+            b.meta_dev[:head].copy_(staged[s], non_blocking=True)
             if s:
                 b.meta_dev[lay.token_ids: lay.token_ids + n].copy_(toks[s - 1], non_blocking=True)
             b.graph.replay()
@@ -253,8 +260,8 @@ def main() -> int:
 
     def e2e_decode(eng, reqs, steps):
         n = len(reqs)
-        b = eng.graphs._bucket_for(n)
         torch.cuda.synchronize()
+        h2d0, replays0 = eng.graphs.h2d_bytes, eng.graphs.replays
         t = time.perf_counter()
         produced = 0
         for _ in range(steps):
@@ -264,7 +271,10 @@ def main() -> int:
         produced += len(eng.drain())                # a step launched ahead belongs to the timed work
         torch.cuda.synchronize()
         dt = time.perf_counter() - t
-        return dt, produced, b.layout.size * 4, n * 4
+        # bytes of metadata the replays of this region uploaded (counted from the copies), per replay;
+        # tokens and the status word come back
+        h2d = (eng.graphs.h2d_bytes - h2d0) / max(1, eng.graphs.replays - replays0)
+        return dt, produced, h2d, n * 4 + 4
 
     def decode_point(B, steps, with_e2e):
         eng = make_engine(B, steps)
@@ -346,6 +356,7 @@ def main() -> int:
                    "parallelism": "single GPU", "layers": L, "layers_of_config": full_layers, "hidden": H,
                    "q_heads": nq, "kv_heads": nkv, "head_dim": d, "intermediate": I, "vocab": V,
                    "prompt_len": P, "new_tokens": need_new, "kv_block": 16, "cuda_graphs": True,
+                   "max_positions": cfg.max_position_embeddings,
                    "l2": (f"inputs>L2: each step streams {step_bytes / 1e9:.1f} GB of weights, keys and values"
                           if step_bytes > 2 * 126e6 else
                           f"step reads {step_bytes / 1e6:.0f} MB, not larger than L2; no flush between steps"),

@@ -177,6 +177,19 @@ __global__ void add_kernel(float* __restrict__ res, const TD* __restrict__ delta
     if (i < n) res[i] += to_float(delta[i]);
 }
 
+// ----------------------------------------------------------- metadata updates --
+// buf[upd[1 + 2i]] = upd[2 + 2i] for i < min(upd[0], cap): a step's few changed block-table
+// entries are written into the table that stays on the device, so that the host uploads what
+// changed and not the table.  Indices outside [0, len) are skipped.
+__global__ void scatter_int_kernel(int* __restrict__ buf, const int* __restrict__ upd, int cap, int len) {
+    pdl_prologue();
+    const int n = min(upd[0], cap);
+    for (int i = blockIdx.x * blockDim.x + threadIdx.x; i < n; i += gridDim.x * blockDim.x) {
+        const int idx = upd[1 + 2 * i];
+        if (idx >= 0 && idx < len) buf[idx] = upd[2 + 2 * i];
+    }
+}
+
 static inline int norm_threads(int H) {
     int t = (H + 7) / 8;
     t = ((t + 31) / 32) * 32;
@@ -190,6 +203,13 @@ static inline int norm_threads(int H) {
 using namespace ff;
 
 // dtype codes: 0 = float32, 1 = bfloat16
+FF_EXPORT int ff_scatter_int(int* buf, const int* upd, int cap, int len, cudaStream_t stream) {
+    if (cap <= 0) return 0;
+    const unsigned blocks = (unsigned)((cap + 255) / 256);
+    FF_LAUNCH((scatter_int_kernel), blocks, 256, 0, stream, buf, upd, cap, len);
+    FF_LAUNCH_CHECK();
+    return 0;
+}
 FF_EXPORT int ff_embedding(const int* ids, const void* table, int table_dtype, float* out, int T,
                            int H, int V, int* status, cudaStream_t stream) {
     if (T <= 0) return 0;

@@ -77,15 +77,19 @@ __device__ __forceinline__ float random_normal_value(uint64_t key, uint64_t inde
     return __fadd_rn(__fmul_rn(__ll2float_rn(fixed), scale), shift);
 }
 
+// via_bf16: the value is first rounded to bfloat16, the type a checkpoint of this model would store
+// it in, and then widened (a tensor that is kept in 32-bit on the device, like a norm weight)
 template <typename TD>
 __global__ void random_rows_kernel(TD* __restrict__ dst, long long rows, long long cols, long long dst_row0,
                                    long long group, long long group_stride, uint64_t key,
-                                   const int* __restrict__ table, float scale, float shift) {
+                                   const int* __restrict__ table, float scale, float shift, int via_bf16) {
     const long long n = rows * cols;
     for (long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x; i < n; i += (long long)gridDim.x * blockDim.x) {
         const long long r = i / cols, c = i - r * cols;
         const long long dr = dst_row0 + (r / group) * group_stride + r % group;
-        dst[dr * cols + c] = from_float<TD>(random_normal_value(key, (uint64_t)i, table, scale, shift));
+        float v = random_normal_value(key, (uint64_t)i, table, scale, shift);
+        if (via_bf16) v = __bfloat162float(__float2bfloat16_rn(v));
+        dst[dr * cols + c] = from_float<TD>(v);
     }
 }
 
@@ -182,19 +186,20 @@ FF_EXPORT int ff_weights_convert_rows(const void* src, int src_type, void* dst, 
     }
 }
 
-// Draw a tensor of rows x cols values N(shift, scale) (see above) into its places.
+// Draw a tensor of rows x cols values N(shift, scale) (see above) into its places; via_bf16: rounded to
+// bfloat16 on the way, whatever the destination type.
 FF_EXPORT int ff_weights_random_rows(void* dst, int dst_type, long long rows, long long cols, long long dst_row0,
                                      long long group, long long group_stride, unsigned long long key,
-                                     const int* table, float scale, float shift, cudaStream_t stream) {
+                                     const int* table, float scale, float shift, int via_bf16, cudaStream_t stream) {
     if (rows <= 0 || cols <= 0) return 0;
     if (group <= 0 || dst_row0 < 0 || table == nullptr) return FF_ERR_BAD_ARG;
     const int g = grid_for(rows * cols);
     if (dst_type == WT_F32)
         random_rows_kernel<float><<<g, 256, 0, stream>>>((float*)dst, rows, cols, dst_row0, group, group_stride, key, table,
-                                                         scale, shift);
+                                                         scale, shift, via_bf16);
     else if (dst_type == WT_BF16)
         random_rows_kernel<bf16><<<g, 256, 0, stream>>>((bf16*)dst, rows, cols, dst_row0, group, group_stride, key, table,
-                                                        scale, shift);
+                                                        scale, shift, via_bf16);
     else
         return FF_ERR_UNSUPPORTED;
     FF_LAUNCH_CHECK();

@@ -30,7 +30,7 @@ from typing import Dict, List, Optional, Sequence
 
 import torch
 
-from ..cache.manager import CacheManager
+from ..cache.manager import CacheManager, plan_groups
 from ..config.base import ModelConfig
 from ..models.decoder import DecoderModel
 from ..sampling.params import SamplingParams
@@ -107,24 +107,12 @@ class Engine:
         max_len = opts.max_model_len or model.spec.max_positions
         max_len = min(max_len, model.spec.max_positions)
         slot_specs = model.cache_slot_specs()
-        probe = CacheManager(slot_specs, block_size=opts.kv_block_size, num_blocks=0, max_requests=1)
-        per_block = max(1, probe.bytes_per_block(model.rt.dtype))
-        if opts.num_kv_blocks is not None:
-            num_blocks = opts.num_kv_blocks
-        else:
-            free, _ = torch.cuda.mem_get_info(self.device)
-            reserve = 4 << 30       # scratch memory of the largest step and the library's own
-            num_blocks = int(max(0, free - reserve) * opts.memory_fraction) // per_block
-            # no request can use more than max_model_len tokens
-            num_blocks = min(num_blocks, opts.max_batch_size_limit * (-(-max_len // opts.kv_block_size)))
-        if num_blocks < 1:
-            raise RuntimeError("no memory left for cache pages")
-        self.cache = CacheManager(slot_specs, block_size=opts.kv_block_size, num_blocks=num_blocks,
+        counts, capacity = self._size_cache_groups(slot_specs, opts, max_len)
+        self.cache = CacheManager(slot_specs, block_size=opts.kv_block_size, num_blocks=counts,
                                   max_requests=opts.max_batch_size_limit)
         self.cache.allocate_storage(model.rt.dtype, self.device)
-        self.max_model_len = min(max_len, num_blocks * opts.kv_block_size) \
-            if not all(g.spec.window is not None for g in self.cache.groups) or not self.cache.groups \
-            else max_len
+        # no request can be longer than what the groups that keep every key can hold
+        self.max_model_len = max_len if capacity is None else min(max_len, capacity)
         self.runner = runner if runner is not None else ModelRunner(
             model, self.cache, max_model_len=self.max_model_len,
             max_batched_tokens=opts.max_num_batched_tokens, max_seqs=opts.max_batch_size_limit)
@@ -149,6 +137,54 @@ class Engine:
                       "dropped_tokens": 0, "device_errors": 0}
         self._inflight: Optional[_InFlight] = None
         self._loop_error: Optional[BaseException] = None
+
+    def _size_cache_groups(self, slot_specs, opts: EngineOptions, max_len: int):
+        """Pages per cache group.  Groups that keep every key get room for the same number of tokens:
+        ``num_kv_blocks`` pages of ``kv_block_size`` if given, else what ``memory_fraction`` of the free
+        device memory holds (after the step's scratch memory), at most ``max_batch_size_limit`` requests
+        of ``max_len`` tokens.  A group whose layers read a window only needs, per request, the pages of
+        its window plus one portion; it gets no more than that.  Returns (counts, tokens the
+        every-key groups hold, or None if there is no such group)."""
+        groups = plan_groups(slot_specs, opts.kv_block_size)
+        if not groups:
+            return [], None
+        es = torch.empty((), dtype=self.model.rt.dtype).element_size()
+        per_token = [len(slots) * 2 * sp.num_kv_heads * sp.head_dim * es for sp, slots, _ in groups]
+        most = opts.max_batch_size_limit * max_len
+
+        def window_pages(sp, bs):
+            per_request = -(-(sp.window + opts.max_prefill_chunk_size) // bs) + 2
+            return opts.max_batch_size_limit * min(per_request, -(-max_len // bs) + 1)
+        if opts.num_kv_blocks is not None:
+            tokens = opts.num_kv_blocks * opts.kv_block_size
+        else:
+            free, _ = torch.cuda.mem_get_info(self.device)
+            budget = int(max(0, free - self._scratch_estimate(opts)) * opts.memory_fraction)
+            for (sp, _, bs), pt in zip(groups, per_token):
+                if sp.window is not None:
+                    budget -= window_pages(sp, bs) * bs * pt
+            full = sum(pt for (sp, _, _), pt in zip(groups, per_token) if sp.window is None)
+            tokens = min(most, max(0, budget) // max(1, full)) if full else most
+        counts = []
+        for sp, _, bs in groups:
+            n = tokens // bs
+            if sp.window is not None:
+                n = min(n, window_pages(sp, bs))
+            counts.append(int(n))
+        if min(counts) < 1:
+            raise RuntimeError("no memory left for cache pages")
+        has_full = any(sp.window is None for sp, _, _ in groups)
+        capacity = min(c * bs for c, (sp, _, bs) in zip(counts, groups) if sp.window is None) if has_full else None
+        return counts, capacity
+
+    def _scratch_estimate(self, opts: EngineOptions) -> int:
+        """Bytes to leave for the scratch memory of the largest step and the library's own: activations
+        of ``max_num_batched_tokens`` tokens (about 64 bytes per token and hidden unit covers the
+        residual, the projections and a feed-forward four times as wide), logits of every request in
+        32-bit twice (eager and captured), and half a gigabyte for the matrix library's workspaces."""
+        spec = self.model.spec
+        return (opts.max_num_batched_tokens * spec.hidden_size * 64
+                + 2 * opts.max_batch_size_limit * spec.vocab_size * 4 + (512 << 20))
 
     # ---- the reference's interface ----------------------------------------------
     def async_generate(self, id: str, input_ids: Sequence[int], max_tokens: int = 512,

@@ -13,6 +13,16 @@ Unused lanes of a bucket decode a dummy token at
 position 0 into the reserved scratch page, so they never touch a live page.
 Unlike the reference, the block-table rows are bounded by the model length, not
 by the size of the whole pool, and nothing is allocated inside the capture.
+
+The block tables of a bucket stay on the device.  A step uploads only the head of
+the metadata (tokens, positions, lengths: a few hundred bytes) and a short list
+of (index, value) pairs, the table entries that changed since the last replay (a
+lane's new page, a new request's row); a small kernel at the front of the graph
+writes them into the tables.  When more entries changed than the list holds (a
+bucket's first use, many new requests at once) the whole buffer is uploaded that
+once.  So the bytes a decode step moves do not grow with the model's longest
+context (the reference copies a table as wide as the whole pool every step,
+src/engine.cc:96,126,321).
 """
 from __future__ import annotations
 
@@ -29,7 +39,8 @@ from .runner import MetaLayout, ModelRunner, StepEntry
 
 class _Bucket:
     __slots__ = ("size", "layout", "meta_host", "meta_stage", "meta_dev", "graph", "logits", "tokens", "h_tokens",
-                 "events", "launches", "lanes", "turn", "by_length", "samp_stage", "samp_dev", "samp_greedy", "h_status")
+                 "events", "launches", "lanes", "turn", "by_length", "samp_stage", "samp_dev", "samp_greedy", "h_status",
+                 "changes", "full_upload")
 
 
 class LaunchedStep:
@@ -47,6 +58,8 @@ class DecodeGraphs:
         self.replays = 0
         self.replays_by_length = 0
         self.kernel_launches = 0
+        self.h2d_bytes = 0            # metadata bytes uploaded by all replays so far
+        self.full_uploads = 0
 
     def supports(self, n: int) -> bool:
         return bool(self.sizes) and n <= self.sizes[-1]
@@ -65,11 +78,11 @@ class DecodeGraphs:
     def _fill(self, b: _Bucket, entries: Sequence[StepEntry]) -> None:
         """Write the step's metadata into the bucket's pinned buffer.  A lane that holds the same
         request as in the step before only gets what changed: its token, position and any new
-        page; block-table rows are rewritten only for lanes whose request changed."""
+        page.  Every write into a block table is also noted in ``b.changes`` (offset, values), from
+        which the step's update list is made."""
         r, lay = self.runner, b.layout
         h = b.meta_host.numpy()
         n = len(entries)
-        mb = r.max_blocks_per_seq
         if b.lanes is None:
             # constant parts, and every lane as padding: a dummy token at position 0 in the scratch page
             h[lay.token_ids: lay.token_ids + b.size] = 0
@@ -80,11 +93,16 @@ class DecodeGraphs:
             h[lay.state_slots: lay.state_slots + b.size] = 0
             h[lay.seq_fresh: lay.seq_fresh + b.size] = 0
             h[lay.logits_rows: lay.logits_rows + b.size] = np.arange(b.size)
-            for off in lay.tables:
-                tab = h[off: off + b.size * mb].reshape(b.size, mb)
+            for off, w in zip(lay.tables, lay.widths):
+                tab = h[off: off + b.size * w].reshape(b.size, w)
                 tab[:, 0] = SCRATCH_PAGE
                 tab[:, 1:] = -1
             b.lanes = [None] * b.size
+            b.full_upload = True
+
+        def put(off, values):
+            h[off: off + len(values)] = values
+            b.changes.append((off, values))
         for i in range(n, b.size):                 # lanes that fell out of use become padding again
             if b.lanes[i] is not None:
                 h[lay.token_ids + i] = 0
@@ -92,9 +110,8 @@ class DecodeGraphs:
                 h[lay.ctx_lens + i] = 0
                 h[lay.state_slots + i] = 0
                 h[lay.seq_fresh + i] = 0
-                for off in lay.tables:
-                    h[off + i * mb] = SCRATCH_PAGE
-                    h[off + i * mb + 1: off + (i + 1) * mb] = -1
+                for off, w in zip(lay.tables, lay.widths):
+                    put(off + i * w, [SCRATCH_PAGE])        # position 0 reads and writes the first entry only
                 b.lanes[i] = None
         for i, e in enumerate(entries):
             rc = e.cache
@@ -114,21 +131,42 @@ class DecodeGraphs:
                 h[lay.state_slots + i] = rc.state_slot
             lens = []
             for g, table in enumerate(rc.tables):
-                row = lay.tables[g] + i * mb
+                row = lay.tables[g] + i * lay.widths[g]
                 if same and old[2][g] == rc.first_live[g] and old[1][g] <= len(table):
                     if old[1][g] < len(table):
-                        h[row + old[1][g]: row + len(table)] = table[old[1][g]:]
+                        put(row + old[1][g], table[old[1][g]:])
                 else:
-                    h[row: row + len(table)] = table
-                    h[row + len(table): row + mb] = -1
+                    # entries behind the request's pages are never read (a key's page index is below its
+                    # count of pages), so what an earlier request left there may stay
+                    put(row, list(table))
                 lens.append(len(table))
             b.lanes[i] = (rc.serial, lens, list(rc.first_live))
+
+    def _write_updates(self, b: _Bucket) -> bool:
+        """The step's table changes as (index, value) pairs in the buffer's update list.  False if
+        they do not fit: then the whole buffer has to be uploaded."""
+        lay = b.layout
+        h = b.meta_host.numpy()
+        count = sum(len(v) for _, v in b.changes)
+        fits = count <= lay.update_cap and not b.full_upload
+        if fits:
+            k = lay.updates + 1
+            for off, values in b.changes:
+                m = len(values)
+                h[k: k + 2 * m: 2] = np.arange(off, off + m)
+                h[k + 1: k + 1 + 2 * m: 2] = values
+                k += 2 * m
+        h[lay.updates] = count if fits else 0
+        b.changes = []
+        b.full_upload = False
+        return fits
 
     def _prepare(self, size: int, capture: bool) -> _Bucket:
         r = self.runner
         b = _Bucket()
         b.size = size
-        b.layout = MetaLayout(size, size, size, len(r.cache.groups), r.max_blocks_per_seq)
+        b.layout = MetaLayout(size, size, size, r.max_blocks, update_cap=max(64, 4 * size))
+        b.changes, b.full_upload = [], True
         b.meta_host = torch.zeros(b.layout.size, dtype=torch.int32).pin_memory()
         # two of everything the host touches while a replay may still be using the other
         b.meta_stage = [torch.zeros(b.layout.size, dtype=torch.int32).pin_memory() for _ in range(2)]
@@ -145,6 +183,8 @@ class DecodeGraphs:
         b.turn = 0
         b.lanes = None
         self._fill(b, [])
+        self._write_updates(b)
+        b.full_upload = True                  # the first replay uploads everything once more
         b.meta_dev.copy_(b.meta_host)
         ctx = r.context_from_layout(b.layout, b.meta_dev, [1] * size, [0] * size)
         ctx.workspace = self.workspace
@@ -154,6 +194,7 @@ class DecodeGraphs:
         side = torch.cuda.Stream(device=r.device)
         side.wait_stream(torch.cuda.current_stream())
         with torch.cuda.stream(side):
+            self._apply_updates(b)
             logits = r.model.forward(ctx)     # warm-up: library handles, lazy module loads
             self._sample(b, logits)
         torch.cuda.current_stream().wait_stream(side)
@@ -163,6 +204,7 @@ class DecodeGraphs:
         b.graph = torch.cuda.CUDAGraph()
         before = K.LAUNCHES
         with torch.cuda.graph(b.graph):
+            self._apply_updates(b)
             b.logits = r.model.forward(ctx)
             self._sample(b, b.logits)
         b.launches = K.LAUNCHES - before      # own kernels in one replay
@@ -180,10 +222,17 @@ class DecodeGraphs:
             g2 = torch.cuda.CUDAGraph()
             before = K.LAUNCHES
             with torch.cuda.graph(g2):
+                self._apply_updates(b)
                 logits2 = r.model.forward(ctx)
                 self._sample(b, logits2)
             b.by_length = (g2, logits2, K.LAUNCHES - before)
         return b
+
+    def _apply_updates(self, b: _Bucket) -> None:
+        """First kernel of a replay: the uploaded (index, value) pairs go into the block tables."""
+        lay = b.layout
+        if lay.tables:
+            K.scatter_int(b.meta_dev, b.meta_dev[lay.updates:], lay.update_cap)
 
     def _sample(self, b: _Bucket, logits: torch.Tensor) -> None:
         d, n = b.samp_dev, b.size
@@ -222,8 +271,13 @@ class DecodeGraphs:
         b.turn ^= 1
         self._upload_sampling(b, k, sampling)
         stage = b.meta_stage[k]
-        stage.copy_(b.meta_host)
-        b.meta_dev.copy_(stage, non_blocking=True)
+        # the head (tokens, positions, lengths, the update list) always; the tables only when more of
+        # them changed than the list holds
+        upto = b.layout.head_size if self._write_updates(b) else b.layout.size
+        self.full_uploads += upto == b.layout.size
+        stage[:upto].copy_(b.meta_host[:upto])
+        b.meta_dev[:upto].copy_(stage[:upto], non_blocking=True)
+        self.h2d_bytes += 4 * upto
         if tokens_from_last_replay:
             lay = b.layout
             b.meta_dev[lay.token_ids: lay.token_ids + n].copy_(b.tokens[:n], non_blocking=True)

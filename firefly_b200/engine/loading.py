@@ -87,7 +87,7 @@ def random_model(config: ModelConfig, seed: int, *, dtype="bfloat16", device="cu
     available = {w.name: (tuple(w.shape), stored if w.kind == "float" else torch.int32) for w in specs}
     plan, names = plan_arena(model, available, dtype=dt)
     arena = WeightArena(plan, dev)
-    RandomSource(specs, seed).fill(arena, names)
+    RandomSource(specs, seed, stored).fill(arena, names)
     model.bind(arena.tensors())
     model.weight_arena, model.load_facts = arena, {"arena_bytes": plan.total_bytes}
     return model

@@ -10,7 +10,10 @@ rectangular ``forward(input_ids[B,S], context_lens[B], ...)``
 
 Per step the host packs all integer metadata (token ids, positions, the token ->
 sequence map, block tables, wanted rows) into one pinned buffer and uploads it
-with one copy.
+with one copy.  The block tables of a step are as wide as the longest table among
+its requests, not as wide as the model's longest context, so the copy grows with
+the pages that are live (the reference uploads a table as wide as the whole pool
+every step, src/engine.cc:96,126,321).
 """
 from __future__ import annotations
 
@@ -72,8 +75,12 @@ class StatusRead:
 class MetaLayout:
     """Where each integer array of a step lies in the packed metadata buffer."""
 
-    def __init__(self, T: int, n: int, r: int, n_groups: int, max_blocks: int):
-        self.T, self.n, self.r, self.n_groups, self.max_blocks = T, n, r, n_groups, max_blocks
+    def __init__(self, T: int, n: int, r: int, widths: Sequence[int], update_cap: int = 0):
+        """``widths``: entries per row of each cache group's block table.  ``update_cap`` > 0 reserves
+        room for that many (index, value) pairs in front of the tables: changes to tables that stay
+        on the device (see ``DecodeGraphs``)."""
+        self.T, self.n, self.r, self.widths = T, n, r, [int(w) for w in widths]
+        self.update_cap = update_cap
         off = 0
 
         def take(count):
@@ -89,7 +96,9 @@ class MetaLayout:
         self.state_slots = take(n)
         self.seq_fresh = take(n)
         self.logits_rows = take(r)
-        self.tables = [take(n * max_blocks) for _ in range(n_groups)]
+        self.updates = take(1 + 2 * update_cap) if update_cap else off
+        self.head_size = off                   # everything in front of the block tables
+        self.tables = [take(n * w) for w in self.widths]
         self.size = off
 
 
@@ -102,16 +111,15 @@ class ModelRunner:
         self.dtype = model.rt.dtype
         self.vocab_size = model.spec.vocab_size
         self.max_model_len = max_model_len
-        self.block_size = cache.block_size
-        self.max_blocks_per_seq = -(-max_model_len // cache.block_size)
+        # widest block table a request can have, per cache group (each group has its own page size)
+        self.max_blocks = [-(-max_model_len // g.block_size) for g in cache.groups]
         self.workspace = Workspace(self.device)
         self.status = torch.zeros(1, dtype=torch.int32, device=self.device)
         self._meta_cap = 0
         self._meta_ring: List[list] = []      # [pinned buffer, event of its last upload]
         self._meta_turn = 0
         self._meta_dev: Optional[torch.Tensor] = None
-        self._ensure_meta(MetaLayout(max_batched_tokens, max_seqs, max_seqs, len(cache.groups),
-                                     self.max_blocks_per_seq).size)
+        self._ensure_meta(MetaLayout(max_batched_tokens, max_seqs, max_seqs, self.max_blocks).size)
         self._status_ring = [[torch.zeros(1, dtype=torch.int32).pin_memory(), None] for _ in range(self.META_RING)]
         self._status_turn = 0
         self.steps_run = 0
@@ -180,7 +188,10 @@ class ModelRunner:
                     raise StepError(f"request {e.cache.request_id!r}: wanted place {w} is outside its "
                                     f"{ql} tokens of this step")
                 wants.append(starts[id(e)] + w)
-        lay = MetaLayout(T, n, len(wants), len(self.cache.groups), self.max_blocks_per_seq)
+        # tables as wide as this step's longest (in steps of four entries), not as the longest possible
+        widths = [min(cap, max(4, -(-max(len(e.cache.tables[g]) for e in entries) // 4) * 4))
+                  for g, cap in enumerate(self.max_blocks)]
+        lay = MetaLayout(T, n, len(wants), widths)
         slot = None
         if meta_host is None:
             self._ensure_meta(lay.size)
@@ -204,14 +215,15 @@ class ModelRunner:
             h[lay.ctx_lens + i] = cl
             h[lay.state_slots + i] = e.cache.state_slot
             h[lay.seq_fresh + i] = 1 if e.cache.fresh else 0
-            need_pages = -(-(cl + ql) // self.block_size)
             for g, table in enumerate(e.cache.tables):
+                need_pages = -(-(cl + ql) // self.cache.groups[g].block_size)
                 if len(table) < need_pages:
                     raise OutOfPages(f"request {e.cache.request_id!r} has {len(table)} pages in group "
                                      f"{g}, this step needs {need_pages}")
-                row = lay.tables[g] + i * self.max_blocks_per_seq
+                w = lay.widths[g]
+                row = lay.tables[g] + i * w
                 h[row: row + len(table)] = table
-                h[row + len(table): row + self.max_blocks_per_seq] = -1
+                h[row + len(table): row + w] = -1
             pos += ql
         h[lay.cu_q + n] = pos
         if wants:
@@ -236,7 +248,7 @@ class ModelRunner:
             token_seq=sl(lay.token_seq, lay.T), cu_q=sl(lay.cu_q, lay.n + 1),
             ctx_lens=sl(lay.ctx_lens, lay.n), state_slots=sl(lay.state_slots, lay.n),
             seq_fresh=sl(lay.seq_fresh, lay.n), logits_rows=sl(lay.logits_rows, lay.r),
-            block_tables=[sl(o, lay.n * lay.max_blocks).view(lay.n, lay.max_blocks) for o in lay.tables],
+            block_tables=[sl(o, lay.n * w).view(lay.n, w) for o, w in zip(lay.tables, lay.widths)],
             q_lens=list(q_lens), ctx_lens_host=list(ctx_lens),
             max_q_len=max(q_lens, default=0),
             max_kv_len=max((c + q for c, q in zip(ctx_lens, q_lens)), default=0),

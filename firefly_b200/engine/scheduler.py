@@ -152,11 +152,10 @@ class Scheduler:
             req = self.pending_requests[0]
             total = req.get_total_len()
             n = min(total, self.max_prefill_chunk_size, budget)
-            pages_for_all = -(-total // self.cache.block_size)
-            if pages_for_all > self.cache.num_blocks and not self._windowed_only():
+            why = self.cache.why_it_cannot_fit(total, self.max_prefill_chunk_size)
+            if why is not None:
                 self.pending_requests.popleft()
-                self._fail(req, f"its {total} tokens need {pages_for_all} pages, the pool has "
-                                f"{self.cache.num_blocks}", batch)
+                self._fail(req, why, batch)
                 continue
             rc = self.cache.admit(req.id)
             if not self.cache.grow(rc, n):
@@ -169,9 +168,6 @@ class Scheduler:
             batch.items.append(ScheduledItem(req, 0, n, n == total))
             budget -= n
         return batch
-
-    def _windowed_only(self) -> bool:
-        return bool(self.cache.groups) and all(g.spec.window is not None for g in self.cache.groups)
 
     # ---- after the step -------------------------------------------------------------
     def append_token(self, req: GenerationRequest, token: int) -> bool:

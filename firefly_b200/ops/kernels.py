@@ -126,6 +126,14 @@ def embedding(ids: torch.Tensor, table: torch.Tensor, out: torch.Tensor, status:
                                            c_int(H), c_int(V), _p(status), _stream()), "embedding")
 
 
+def scatter_int(buf: torch.Tensor, updates: torch.Tensor, cap: int) -> None:
+    """buf[updates[1 + 2i]] = updates[2 + 2i] for i < min(updates[0], cap); all int32."""
+    _need_cuda(buf, updates)
+    assert buf.dtype == torch.int32 and updates.dtype == torch.int32 and updates.numel() >= 1 + 2 * cap
+    _check(_lib("elementwise").ff_scatter_int(_p(buf), _p(updates), c_int(cap), c_int(buf.numel()), _stream()),
+           "scatter_int")
+
+
 def add_rms_norm(residual: torch.Tensor, delta: Optional[torch.Tensor], weight: torch.Tensor,
                  eps: float, out: torch.Tensor, row_idx: Optional[torch.Tensor] = None) -> None:
     """residual (+= delta), out = rms_norm(residual) * weight.

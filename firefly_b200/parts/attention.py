@@ -16,7 +16,8 @@ Unlike the reference, whose prefill attends only inside the portion it is given
 Parameters: hidden_size, num_heads, num_kv_heads, head_dim, qk_norm (bool),
 qk_norm_eps, window (None = all keys, W = the last W keys including the query's
 own), scale (None = 1/sqrt(head_dim)), has_kv (False: the layer has no k/v
-projections and only ever reads another run's cache).
+projections and only ever reads another run's cache), cache_block_size (tokens per
+cache page if this layer wants a page size of its own; None: the engine's).
 """
 from __future__ import annotations
 
@@ -50,6 +51,7 @@ class GQAttention(Part):
         scale = self.p("scale", None)
         self.scale = 1.0 / math.sqrt(self.d) if scale is None else float(scale)
         self.has_kv = bool(self.p("has_kv", True))
+        self.cache_block_size = self.p("cache_block_size", None)
         self.position = position
         if self.nq % self.nkv:
             raise ValueError(f"num_heads {self.nq} is not a multiple of num_kv_heads {self.nkv}")
@@ -61,7 +63,8 @@ class GQAttention(Part):
 
     # -- cache ------------------------------------------------------------------
     def cache_spec(self):
-        return PagedKVSpec(self.nkv, self.d, None if self.window is None else int(self.window))
+        return PagedKVSpec(self.nkv, self.d, None if self.window is None else int(self.window),
+                           None if self.cache_block_size is None else int(self.cache_block_size))
 
     # -- weights ------------------------------------------------------------------
     def weight_specs(self) -> List[WeightSpec]:

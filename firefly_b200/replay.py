@@ -23,7 +23,7 @@ from typing import Dict, Optional
 import numpy as np
 import torch
 
-from .cache.manager import CacheManager, OutOfPages, RequestCache
+from .cache.manager import CacheManager, OutOfPages, RequestCache, plan_groups
 from .engine.loading import load_model
 from .engine.runner import ModelRunner, StepEntry, StepError
 
@@ -56,11 +56,16 @@ class ReplaySession:
         else:
             self.model, self.config = model, None
         self.max_tokens = max_tokens
-        num_blocks = -(-max_tokens // block_size)
-        self.cache = CacheManager(self.model.cache_slot_specs(), block_size=block_size,
-                                  num_blocks=num_blocks, max_requests=max_requests)
+        # every cache group holds max_tokens tokens in pages of its own size
+        slot_specs = self.model.cache_slot_specs()
+        counts = []
+        for spec, _, bs in plan_groups(slot_specs, block_size):
+            if PAGE_ROUNDING % bs:
+                raise ValueError(f"a cache group's page size {bs} does not divide {PAGE_ROUNDING}")
+            counts.append(-(-max_tokens // bs))
+        self.cache = CacheManager(slot_specs, block_size=block_size, num_blocks=counts, max_requests=max_requests)
         self.cache.allocate_storage(self.model.rt.dtype, self.model.rt.device)
-        max_len = min(self.model.spec.max_positions, num_blocks * block_size)
+        max_len = min(self.model.spec.max_positions, -(-max_tokens // block_size) * block_size)
         if self.cache.groups and all(g.spec.window is not None for g in self.cache.groups):
             max_len = self.model.spec.max_positions     # windows give pages back: length is not bounded by the pool
         self.runner = ModelRunner(self.model, self.cache, max_model_len=max_len)

@@ -313,9 +313,12 @@ class FileSource:
 class RandomSource:
     """Seeded random tensors drawn on the device into their places (see ``random_init``)."""
 
-    def __init__(self, specs, seed: int):
+    def __init__(self, specs, seed: int, stored: torch.dtype = torch.float32):
+        """``stored``: the type a checkpoint of these weights would hold them in; a value is rounded to
+        it once, also where the device keeps the tensor in a wider type."""
         self.specs = {w.name: w for w in specs}
         self.seed = seed
+        self.stored = stored
 
     def fill(self, arena: WeightArena, names: Iterable[str]) -> None:
         from . import random_init as R
@@ -341,6 +344,7 @@ class RandomSource:
                 _check(lib.ff_weights_random_rows(c_void_p(dst.data_ptr()), c_int(_WT[dst.dtype]), c_longlong(rows),
                                                   c_longlong(cols), c_longlong(pl.row0), c_longlong(pl.group),
                                                   c_longlong(pl.group_stride), c_ulonglong(key),
-                                                  c_void_p(table.data_ptr()), c_float(scale), c_float(shift), sp),
+                                                  c_void_p(table.data_ptr()), c_float(scale), c_float(shift),
+                                                  c_int(1 if self.stored == torch.bfloat16 else 0), sp),
                        f"random '{name}'")
             torch.cuda.synchronize(dev)

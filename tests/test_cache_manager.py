@@ -3,6 +3,7 @@ twice, under random orders of requests; windows give pages back."""
 import random
 
 import pytest
+import torch
 
 from firefly_b200.cache import (BlockAllocator, CacheManager, OutOfPages, PageError, PagedKVSpec,
                                 StateSpec)
@@ -141,3 +142,93 @@ def test_random_orders_keep_invariants(seed):
         m.free(rc)
     m.check()
     assert all(g.allocator.num_free == m.num_blocks for g in m.groups)
+
+
+def test_groups_have_their_own_page_size_and_count():
+    """A windowed group with small pages and few of them beside a group that keeps every key."""
+    from firefly_b200.cache import plan_groups
+    specs = {0: PagedKVSpec(2, 16, None), 1: PagedKVSpec(2, 16, 8, block_size=2), 2: PagedKVSpec(2, 16, None),
+             3: PagedKVSpec(1, 32, None, block_size=8)}
+    planned = plan_groups(specs, 4)
+    assert [(sl, bs) for _, sl, bs in planned] == [([0, 2], 4), ([1], 2), ([3], 8)]
+    m = CacheManager(specs, block_size=4, num_blocks=[20, 12, 10], max_requests=3)
+    assert [(g.block_size, g.num_blocks) for g in m.groups] == [(4, 20), (2, 12), (8, 10)]
+    assert m.num_blocks == 10 and m.bytes_per_block(torch.float32) == (2 * 2 * 2 * 16 * 4 + 2 * 2 * 16 * 2 + 2 * 32 * 8) * 4
+    r = m.admit("r")
+    n = 0
+    for step in (5, 3, 9, 1, 1, 7, 13, 2):
+        assert m.grow(r, n + step), (n, step)
+        m.advance(r, step)
+        n += step
+        assert len(r.tables[0]) == -(-n // 4) and len(r.tables[2]) == -(-n // 8)
+        live = [b for b in r.tables[1] if b >= 0]
+        # the windowed group holds the pages of its window only: at most ceil(8 / 2) + 1
+        assert len(live) <= 5 and len(r.tables[1]) == -(-n // 2)
+        m.check()
+    assert n == 41 and m.groups[1].allocator.num_free >= 7
+    # what runs out first decides: group 0 has 20 pages of 4 = 80 tokens, group 2 10 of 8 = 80
+    assert not m.grow(r, 80)                       # 39 tokens at once are more than the windowed group's 12 pages of 2
+    while n < 80:
+        step = min(8, 80 - n)
+        assert m.grow(r, n + step)
+        m.advance(r, step)
+        n += step
+    assert not m.grow(r, 81)
+    assert m.why_it_cannot_fit(80, 8) is None
+    assert "cache group 0" in m.why_it_cannot_fit(81, 8)
+    # the windowed group refuses a portion that does not fit its pages: 8 + 16 tokens need 13 pages of 2
+    assert m.why_it_cannot_fit(60, 12) is None and "cache group 1" in m.why_it_cannot_fit(60, 16)
+    m.free(r)
+    m.check()
+    assert [g.allocator.num_free for g in m.groups] == [20, 12, 10]
+    with pytest.raises(ValueError, match="page counts"):
+        CacheManager(specs, block_size=4, num_blocks=[20, 9], max_requests=3)
+
+
+@pytest.mark.parametrize("seed", range(4))
+def test_random_orders_with_unequal_groups(seed):
+    rng = random.Random(100 + seed)
+    specs = {0: PagedKVSpec(2, 16, None), 1: PagedKVSpec(2, 16, rng.choice([3, 9]), block_size=rng.choice([1, 2, 4])),
+             2: StateSpec((2, 2))}
+    m = CacheManager(specs, block_size=rng.choice([4, 8]), num_blocks=[rng.choice([10, 30]), rng.choice([12, 25])],
+                     max_requests=4)
+    live = {}
+    nid = 0
+    for _ in range(500):
+        op = rng.random()
+        if op < 0.25 and m.can_admit():
+            live[nid] = m.admit(nid)
+            nid += 1
+        elif op < 0.8 and live:
+            rc = live[rng.choice(list(live))]
+            n = rng.choice([1, 1, 2, 3])
+            before = [list(t) for t in rc.tables]
+            if m.grow(rc, rc.num_tokens + n):
+                m.advance(rc, n)
+            else:
+                assert [list(t) for t in rc.tables] == before
+        elif live:
+            m.free(live.pop(rng.choice(list(live))))
+        m.check()
+    for rc in list(live.values()):
+        m.free(rc)
+    m.check()
+    assert all(g.allocator.num_free == g.num_blocks for g in m.groups)
+
+
+def test_engine_gives_a_windowed_group_far_fewer_pages():
+    """The engine sizes each group from what it needs: every-key groups share the token capacity, a
+    windowed group gets its window plus a portion per request and no more."""
+    from types import SimpleNamespace
+    from firefly_b200.engine.engine import Engine, EngineOptions
+    model = SimpleNamespace(rt=SimpleNamespace(device=torch.device("cpu"), dtype=torch.bfloat16),
+                            spec=SimpleNamespace(max_positions=4096, vocab_size=8),
+                            cache_slot_specs=lambda: {0: PagedKVSpec(2, 16, None), 1: PagedKVSpec(2, 16, 64),
+                                                      2: PagedKVSpec(2, 16, None)})
+    opts = EngineOptions(num_kv_blocks=4096, kv_block_size=16, max_batch_size_limit=4, max_prefill_chunk_size=32,
+                         use_cuda_graphs=False)
+    eng = Engine(model, options=opts, runner=object(), sampler=object())
+    full, win = eng.cache.groups
+    assert full.num_blocks == 4096 and win.spec.window == 64
+    assert win.num_blocks == 4 * ((64 + 32) // 16 + 2) == 32          # 128 times fewer than the full group
+    assert eng.max_model_len == 4096

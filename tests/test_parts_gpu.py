@@ -143,6 +143,59 @@ def test_assembly_is_data(dtype, case):
         assert not sess.cache.live
 
 
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+def test_groups_with_their_own_page_sizes_and_counts_through_the_engine(dtype):
+    """Three cache groups: every key in pages of 8, a window of 21 in pages of 4, a window of 5 in pages
+    of 16.  The engine gives the windowed groups the pages of their windows only; logits and generated
+    tokens are the plain implementation's."""
+    from firefly_b200.engine.engine import Engine, EngineOptions
+    from firefly_b200.engine.request import GenerationRequest
+    from firefly_b200.sampling import SamplingParams
+    cfg = P.TINY_B
+    tdt = torch.float32 if dtype == "float32" else torch.bfloat16
+    w = P.random_weights(cfg, 6, dtype=tdt, scale=0.05)
+    windows, pages = [None, 21, 5], [None, 4, 16]
+
+    def edit(spec):
+        layers = [dataclasses.replace(ls, mixer=ls.mixer.with_params(window=win, cache_block_size=bs))
+                  for ls, win, bs in zip(spec.layers, windows, pages)]
+        return dataclasses.replace(spec, layers=tuple(layers))
+    model = _bound_model(cfg, w, tdt, edit)
+    # replay: whole, and mixed with pages used again
+    reqs = U.make_requests(cfg["vocab_size"], [90, 33, 140, 7, 61], 3)
+    plain = {rid: P.forward(cfg, w, toks, windows=windows).numpy() for rid, toks in reqs.items()}
+    for steps in (U.trace_whole(reqs), U.trace_mixed(reqs, seed=2, max_live=3)):
+        sess = _session(model, U.peak_tokens(steps), 8)
+        assert [g.block_size for g in sess.cache.groups] == [8, 4, 16]
+        U.compare(U.run_trace(sess, steps), plain, U.TOL[dtype], f"own page sizes/{dtype}")
+        sess.cache.check()
+    # the engine: sizes per group, generation equal to the plain implementation's
+    opts = EngineOptions(num_kv_blocks=64, kv_block_size=8, max_batch_size_limit=4, max_prefill_chunk_size=16)
+    eng = Engine(model, options=opts)
+    full, w21, w5 = eng.cache.groups
+    assert (full.num_blocks, full.block_size) == (64, 8)
+    assert (w21.num_blocks, w21.block_size) == (4 * (-(-(21 + 16) // 4) + 2), 4)
+    assert (w5.num_blocks, w5.block_size) == (4 * (-(-(5 + 16) // 16) + 2), 16)
+    assert w5.num_blocks * w5.block_size < full.num_blocks * full.block_size // 2
+    prompts = [reqs["r0"][:50], reqs["r1"][:20], reqs["r2"][:77]]
+    rs = [GenerationRequest(f"g{i}", list(p), SamplingParams(max_tokens=12)) for i, p in enumerate(prompts)]
+    for r in rs:
+        eng.add_request(r)
+    while eng.has_unfinished_requests():
+        eng.step()
+    eng.runner.check_status()
+    eng.cache.check()
+    for r, prompt in zip(rs, prompts):
+        assert len(r.generated_tokens) == 12
+        rows = P.forward(cfg, {k: v.double() for k, v in w.items()}, list(prompt) + r.generated_tokens[:-1], windows=windows)
+        for i, tok in enumerate(r.generated_tokens):
+            row = rows[len(prompt) - 1 + i]
+            if dtype == "float32":
+                assert tok == P.greedy_pick(row), (r.id, i)
+            else:
+                assert float(row.max() - row[tok]) <= U.TOL[dtype] * float(row.abs().max())
+
+
 def test_window_pages_are_given_back_while_the_request_lives():
     cfg = P.TINY_A
     w = P.random_weights(cfg, 8, scale=0.05)
