@@ -10,7 +10,11 @@ JSON line per request.  ``--max-tokens`` defaults to the reference's 512
 
     firefly MODEL_DIR --prompt-ids 1,2,3 --max-tokens 16
     firefly MODEL_DIR --prompts-file prompts.jsonl --temperature 0.8 --seed 1
+    firefly --random config.json --seed 0 --prompt-len 64 --num-prompts 4 --max-tokens 16
     firefly --write-random-model OUT_DIR --config config.json --seed 0
+
+A fault of the input or of the machine (no CUDA device, a folder without weights, tensors that do
+not fit the configuration) ends with one line on stderr and exit code 1, not with a traceback.
 """
 from __future__ import annotations
 
@@ -29,6 +33,11 @@ def build_parser() -> argparse.ArgumentParser:
     ap.add_argument("--prompt-ids", action="append", default=[],
                     help="a prompt as comma-separated token ids; may be given several times")
     ap.add_argument("--prompts-file", help="file with one JSON list of token ids per line")
+    ap.add_argument("--prompt-len", type=int, default=None,
+                    help="make --num-prompts prompts of this many seeded random token ids")
+    ap.add_argument("--num-prompts", type=int, default=1, help="how many prompts --prompt-len makes (default 1)")
+    ap.add_argument("--random", metavar="CONFIG.json", default=None,
+                    help="no model folder: a model of this configuration with seeded random weights (--seed)")
     ap.add_argument("--max-tokens", type=int, default=512, help="new tokens per request (default 512)")
     ap.add_argument("--temperature", type=float, default=0.0, help="0 = greedy (default)")
     ap.add_argument("--seed", type=int, default=0, help="seed of temperature sampling / random weights")
@@ -75,18 +84,39 @@ def main(argv=None) -> int:
                 line = line.strip()
                 if line:
                     prompts.append([int(x) for x in json.loads(line)])
-    if not prompts:
-        print("firefly: no prompt given (--prompt-ids or --prompts-file)", file=sys.stderr)
-        return 2
-
-    from .entry import LLM
-    llm = LLM(args.model_dir, dtype=args.dtype, max_prefill_chunk_size=args.max_prefill_chunk_size,
-              max_batch_size_limit=args.max_batch_size, max_num_batched_tokens=args.max_num_batched_tokens,
-              kv_block_size=args.kv_block_size, num_kv_blocks=args.num_kv_blocks,
-              max_model_len=args.max_model_len, eos_token_ids=args.eos_token_id,
-              use_cuda_graphs=not args.no_cuda_graphs, overlap_decode=not args.no_overlap_decode)
-    outs = llm.generate(prompts, max_tokens=args.max_tokens, temperature=args.temperature, seed=args.seed,
-                        ignore_eos=args.ignore_eos)
+    try:
+        model = args.model_dir
+        if args.random:
+            from .models import config_from_dict
+            with open(args.random) as fh:
+                model = config_from_dict(json.load(fh))
+        if args.prompt_len:
+            import random
+            if args.random:
+                vocab = model.vocab_size
+            else:
+                from .models import load_config
+                vocab = load_config(args.model_dir).vocab_size
+            rng = random.Random(args.seed)
+            prompts += [[rng.randrange(vocab) for _ in range(args.prompt_len)] for _ in range(args.num_prompts)]
+        if not prompts:
+            print("firefly: no prompt given (--prompt-ids, --prompts-file or --prompt-len)", file=sys.stderr)
+            return 2
+        from .entry import LLM
+        llm = LLM(model, dtype=args.dtype, seed=args.seed, max_prefill_chunk_size=args.max_prefill_chunk_size,
+                  max_batch_size_limit=args.max_batch_size, max_num_batched_tokens=args.max_num_batched_tokens,
+                  kv_block_size=args.kv_block_size, num_kv_blocks=args.num_kv_blocks,
+                  max_model_len=args.max_model_len, eos_token_ids=args.eos_token_id,
+                  use_cuda_graphs=not args.no_cuda_graphs, overlap_decode=not args.no_overlap_decode)
+        outs = llm.generate(prompts, max_tokens=args.max_tokens, temperature=args.temperature, seed=args.seed,
+                            ignore_eos=args.ignore_eos)
+    except (RuntimeError, OSError, ValueError) as e:
+        # ConfigError, WeightError, SafetensorsError and StepError are among these
+        first = str(e).strip().splitlines()
+        print(f"firefly: {first[0] if first else type(e).__name__}", file=sys.stderr)
+        for line in first[1:]:
+            print(f"  {line.strip()}", file=sys.stderr)
+        return 1
     for i, (p, o) in enumerate(zip(prompts, outs)):
         print(json.dumps({"request": i, "prompt_tokens": len(p), "tokens": o}))
     return 0

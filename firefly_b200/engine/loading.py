@@ -64,9 +64,9 @@ def load_model(model_dir: str, *, dtype="bfloat16", device="cuda:0", weight_dtyp
     ``model.load_facts`` tells its size and whether the file could be pinned.  ``weight_dtype``:
     "keep" leaves tensors stored in 32-bit as they are, "engine" narrows them to the engine's type."""
     dt = parse_dtype(dtype)
+    config = load_config_with_file_hints(model_dir)          # a folder's faults are told before the machine's
     dev = require_cuda(device)
     K.set_exact_matmul()
-    config = load_config_with_file_hints(model_dir)
     model = DecoderModel(spec_for(config), Runtime(dev, dt))
     tensors, arena, facts = load_weights(model_dir, model, dtype=dt, device=dev, weight_dtype=weight_dtype)
     model.bind(tensors)

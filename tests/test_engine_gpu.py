@@ -54,6 +54,30 @@ def test_few_pages_preempt_and_still_match(models):
         assert g == P.greedy_generate(cfg, w, p, 14)
 
 
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+def test_more_decoding_requests_than_the_largest_graph(models, dtype):
+    """70 requests decode together: more than the largest captured batch (64), so those steps run
+    without a graph (one-token sequences, the split-KV attention at a batch of 70)."""
+    path, cfg, w = models["B"]
+    rng = np.random.RandomState(11)
+    prompts = [list(map(int, rng.randint(0, cfg["vocab_size"], size=int(n)))) for n in rng.randint(1, 12, size=70)]
+    llm = _llm(path, dtype=dtype, kv_block_size=8, num_kv_blocks=70 * 4, max_batch_size_limit=80,
+               max_prefill_chunk_size=64, max_num_batched_tokens=1024)
+    got = llm.generate(prompts, max_tokens=5)
+    st = llm.engine.stats
+    assert st["steps"] > st["graph_steps"] and len(llm.engine.scheduler.active_requests) == 0
+    wd = {k: v.double() for k, v in w.items()}
+    for p, g in zip(prompts, got):
+        if dtype == "float32":
+            assert g == P.greedy_generate(cfg, w, p, 5)
+        else:
+            rows = P.forward(cfg, wd, list(p) + g[:-1])
+            for i, tok in enumerate(g):
+                row = rows[len(p) - 1 + i]
+                assert float(row.max() - row[tok]) <= U.TOL[dtype] * float(row.abs().max())
+    llm.engine.cache.check()
+
+
 def test_long_decoding_and_first_tokens(models):
     path, cfg, w = models["A"]
     llm = _llm(path, dtype="float32", num_kv_blocks=16)
@@ -323,9 +347,10 @@ def test_sampled_requests_survive_preemption_with_the_same_draws(models):
 def test_host_may_run_steps_ahead_of_the_device(tmp_path):
     """Steps without wanted logits are never waited for, so the host can queue several of them while
     the device is still busy; each must run with its own metadata.  The device is held up by a
-    spinning kernel while a prompt is queued in more portions than there are metadata buffers; the
-    model allows long sequences, so that a step's block table is tens of kilobytes (a copy that
-    small enough may be taken at the time it is queued and would hide the fault)."""
+    spinning kernel while a prompt is queued in more portions than there are metadata buffers.  A second
+    request that holds thousands of pages rides along, so that a step's block tables are tens of
+    kilobytes (a copy that is small enough may be taken at the time it is queued and would hide the
+    fault)."""
     from firefly_b200.engine.runner import StepEntry
     from firefly_b200.replay import ReplaySession
     cfg = dict(P.TINY_B, max_position_embeddings=65536)
@@ -336,19 +361,22 @@ def test_host_may_run_steps_ahead_of_the_device(tmp_path):
     want = P.forward(cfg, w, toks)[-1].numpy()
     for hold in (False, True):
         s = ReplaySession(path, dtype="float32", max_tokens=65536, block_size=8)
-        assert s.runner.max_blocks_per_seq == 8192
+        assert s.runner.max_blocks == [8192]
         warm = s.cache.admit("warm")                    # scratch buffers get their sizes before the hold
         assert s.cache.grow(warm, 13)
         s.runner.step([StepEntry(warm, toks[:13], [])])
         torch.cuda.synchronize()
         s.cache.free(warm)
         rc = s.cache.admit("a")
+        big = s.cache.admit("big")                      # its table is as wide as 40000 tokens need
+        assert s.cache.grow(big, 40000) and len(big.tables[0]) == 5000
         if hold:
             torch.cuda._sleep(int(3e8))                 # some tenths of a second
         p = 0
-        for n in (7, 2, 13, 5, 9, 11, 3, 10):
+        for k, n in enumerate((7, 2, 13, 5, 9, 11, 3, 10)):
             assert s.cache.grow(rc, p + n)
-            last = s.runner.step([StepEntry(rc, toks[p:p + n], [n - 1] if p + n == len(toks) else [])])
+            last = s.runner.step([StepEntry(rc, toks[p:p + n], [n - 1] if p + n == len(toks) else []),
+                                  StepEntry(big, [toks[k]], [])])
             p += n
         got = last[0].cpu().numpy()
         s.runner.check_status()

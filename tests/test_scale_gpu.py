@@ -42,22 +42,36 @@ def test_generated_tokens_are_the_replays_best_at_real_layer_sizes(options):
         del sess
 
 
-def test_replay_matches_the_plain_implementation_at_real_layer_sizes(tmp_path):
-    """The plain implementation (32-bit, on the CPU) against the replay at these sizes: a request
-    whole, its last tokens one by one, and mixed with two others of very different lengths."""
+@pytest.fixture(scope="module")
+def real_size_case(tmp_path_factory):
+    """A model folder at the real layer sizes (bfloat16 values), three requests and the plain
+    implementation's logits for them (32-bit, on the CPU), made once for the tests below."""
     import plain_qwen3 as P
     import replay_util as U
-    from firefly_b200.replay import ReplaySession
+    tmp = tmp_path_factory.mktemp("real_sizes")
     cfg = dict(REAL_SIZES, tie_word_embeddings=True)       # one matrix of 151936 x 4096 less to draw on the CPU
     w = P.random_weights(cfg, 3, dtype=torch.bfloat16, scale=0.02)
-    U.write_model_dir(str(tmp_path), cfg, w, torch.bfloat16)
+    U.write_model_dir(str(tmp), cfg, w, torch.bfloat16)
     reqs = U.make_requests(cfg["vocab_size"], [150, 20, 330], 5)
     w32 = {k: v.float() for k, v in w.items()}
     plain = {rid: P.forward(cfg, w32, toks, dtype=torch.float32).numpy() for rid, toks in reqs.items()}
-    del w32
-    for family in ("whole", "tail", "mixed"):
-        steps = {"whole": U.trace_whole, "tail": U.trace_tail_decode, "mixed": U.trace_mixed}[family](reqs)
-        sess = ReplaySession(str(tmp_path), dtype="bfloat16", max_tokens=U.peak_tokens(steps))
-        U.compare(U.run_trace(sess, steps), plain, U.TOL["bfloat16"], f"real sizes/{family}")
+    return str(tmp), reqs, plain
+
+
+@pytest.mark.parametrize("dtype", ["bfloat16", "float32"])
+def test_replay_matches_the_plain_implementation_at_real_layer_sizes(real_size_case, dtype):
+    """The plain implementation against the replay at these sizes, in bfloat16 and in true 32-bit (the
+    folder's bfloat16 values widened exactly): a request whole, its last tokens one by one, in portions
+    of changing size, and mixed with two others of very different lengths."""
+    import replay_util as U
+    from firefly_b200.replay import ReplaySession
+    path, reqs, plain = real_size_case
+    tol = U.TOL[dtype]
+    for family in ("whole", "tail", "portions", "mixed"):
+        steps = {"whole": U.trace_whole, "tail": U.trace_tail_decode, "portions": U.trace_portions,
+                 "mixed": U.trace_mixed}[family](reqs)
+        sess = ReplaySession(path, dtype=dtype, max_tokens=U.peak_tokens(steps))
+        U.compare(U.run_trace(sess, steps), plain, tol, f"real sizes/{dtype}/{family}")
         sess.cache.check()
         del sess
+        torch.cuda.empty_cache()
