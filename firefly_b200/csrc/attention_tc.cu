@@ -149,12 +149,14 @@ __device__ __forceinline__ float fast_exp2(float x) {   // 2^x; -inf -> 0
     asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
     return y;
 }
-// 2^x for two values at once on the special-function unit, result rounded to bfloat16 (the form P
-// is stored in): half as many special-function operations as two 32-bit exponentials
+// 2^x for two values, each exponential in 32-bit and only the result rounded to bfloat16 (the form
+// P is stored in).  The argument must not be rounded to bfloat16 first: the reference max trails the
+// true max by up to 8, so the heaviest keys have arguments in [4, 8), where bfloat16 is 2^-5 apart,
+// about 1 % in the weight; that is several times the rounding of P itself.
 __device__ __forceinline__ uint32_t exp2_bf16x2(float x0, float x1) {
-    uint32_t packed, y;
-    asm("cvt.rn.bf16x2.f32 %0, %1, %2;" : "=r"(packed) : "f"(x1), "f"(x0));   // low half = x0
-    asm("ex2.approx.ftz.bf16x2 %0, %1;" : "=r"(y) : "r"(packed));
+    uint32_t y;
+    const float p0 = fast_exp2(x0), p1 = fast_exp2(x1);
+    asm("cvt.rn.bf16x2.f32 %0, %1, %2;" : "=r"(y) : "f"(p1), "f"(p0));        // low half = p0
     return y;
 }
 __device__ __forceinline__ void tm_st16(uint32_t taddr, const float (&v)[16]) {
@@ -369,8 +371,8 @@ attn_tc_kernel(const __grid_constant__ TensorMapArg kv_map, const bf16* __restri
                 m = m_new;
             }
             const float neg_m = m == -CUDART_INF_F ? 0.f : -m;
-            // p = 2^(s*scale - m), two at a time in bfloat16; the row sum adds the rounded values, the
-            // same numbers the P V product sees
+            // p = 2^(s*scale - m) in 32-bit, rounded to bfloat16 in pairs; the row sum adds the rounded
+            // values, the same numbers the P V product sees
             uint32_t w[BN / 2];
             float sum4[4] = {0.f, 0.f, 0.f, 0.f};
 #pragma unroll

@@ -39,8 +39,17 @@ constexpr int BN = 128;          // weight rows per tile (MMA M)
 constexpr int BK = 64;           // k per stage: 128 bytes of bfloat16, one swizzle span
 constexpr int UMMA_K = 16;
 constexpr int GEMM_THREADS = 192;
-constexpr int NUM_SMS = 148;
-constexpr unsigned long long WAIT_LIMIT_CYCLES = 2000000000ull;   // about a second
+#ifndef FF_GEMM_WAIT_LIMIT_CYCLES
+#define FF_GEMM_WAIT_LIMIT_CYCLES 2000000000ull                    // about a second
+#endif
+constexpr unsigned long long WAIT_LIMIT_CYCLES = FF_GEMM_WAIT_LIMIT_CYCLES;
+// Test builds only (-DFF_GEMM_TEST_DROP_KBLOCK=i): the loads of a block's i-th k block are never
+// issued, so the wait for that stage runs out; the test checks that the kernel gives up cleanly.
+#ifdef FF_GEMM_TEST_DROP_KBLOCK
+#define FF_GEMM_LOADS(it) ((it) != FF_GEMM_TEST_DROP_KBLOCK)
+#else
+#define FF_GEMM_LOADS(it) true
+#endif
 
 enum Epilogue { EPI_BF16 = 0, EPI_F32 = 1, EPI_RESIDUAL_ADD = 2, EPI_SWIGLU = 3 };
 
@@ -226,12 +235,13 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant_
         for (int it = 0; it < pre; ++it) {
             const uint32_t full = smem_addr(&bars[it]);
             mbar_expect_tx(issue, full, Cfg::STAGE_BYTES);
-            tma_load_2d(issue, smem_addr(tiles + (size_t)it * Cfg::STAGE_BYTES), &map_w, (kb0 + it) * BK, n0, full);
+            tma_load_2d(issue && FF_GEMM_LOADS(it), smem_addr(tiles + (size_t)it * Cfg::STAGE_BYTES), &map_w, (kb0 + it) * BK,
+                        n0, full);
         }
         grid_dependency_wait();
         for (int it = 0; it < pre; ++it) {
-            tma_load_2d(issue, smem_addr(tiles + (size_t)it * Cfg::STAGE_BYTES + Cfg::A_BYTES), &map_x, (kb0 + it) * BK, t0,
-                        smem_addr(&bars[it]));
+            tma_load_2d(issue && FF_GEMM_LOADS(it), smem_addr(tiles + (size_t)it * Cfg::STAGE_BYTES + Cfg::A_BYTES), &map_x,
+                        (kb0 + it) * BK, t0, smem_addr(&bars[it]));
             issued = it + 1;
         }
         for (int it = pre; it < n_iters; ++it) {
@@ -241,8 +251,8 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant_
             const uint32_t full = smem_addr(&bars[s]);
             mbar_expect_tx(issue, full, Cfg::STAGE_BYTES);
             unsigned char* st = tiles + (size_t)s * Cfg::STAGE_BYTES;
-            tma_load_2d(issue, smem_addr(st), &map_w, (kb0 + it) * BK, n0, full);
-            tma_load_2d(issue, smem_addr(st + Cfg::A_BYTES), &map_x, (kb0 + it) * BK, t0, full);
+            tma_load_2d(issue && FF_GEMM_LOADS(it), smem_addr(st), &map_w, (kb0 + it) * BK, n0, full);
+            tma_load_2d(issue && FF_GEMM_LOADS(it), smem_addr(st + Cfg::A_BYTES), &map_x, (kb0 + it) * BK, t0, full);
             issued = it + 1;
         }
         if (*abort_flag) {

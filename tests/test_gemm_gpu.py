@@ -115,3 +115,37 @@ def test_refuses_what_it_cannot_do():
     st = torch.zeros(1, dtype=torch.int32, device="cuda")
     with pytest.raises(k.KernelError, match="bad argument"):
         k.gemm_tc(x, w, out, k.EPI_BF16, 1, st)      # K not a multiple of 8
+
+
+def test_a_wait_that_runs_out_ends_the_kernel_with_a_status_and_leaves_the_device_usable():
+    """A test build of the product in which the loads of one k block are never issued and waits give
+    up after a few milliseconds: the kernel must return, say which wait ran out (102: a loaded stage,
+    or 103: the accumulator), store nothing, and the next ordinary launch must be right.  One block,
+    no cluster (a block that gives up never leaves a peer waiting at a cluster barrier this way)."""
+    import ctypes
+    from ctypes import c_float, c_int, c_void_p
+    from firefly_b200.ops.build import load_module
+    k = K()
+    lib = load_module("gemm_tcgen05.cu", {"FF_GEMM_TEST_DROP_KBLOCK": 1, "FF_GEMM_WAIT_LIMIT_CYCLES": "8000000ull"})
+    g = torch.Generator().manual_seed(3)
+    T, N, Kd = 16, 128, 256                                   # one tile of 128 rows, four k blocks
+    x = torch.randn(T, Kd, generator=g).to(torch.bfloat16).cuda()
+    w = (torch.randn(N, Kd, generator=g) / 16).to(torch.bfloat16).cuda()
+    out = torch.full((T, N), 7.0, dtype=torch.float32, device="cuda")
+    status = torch.zeros(1, dtype=torch.int32, device="cuda")
+    null = c_void_p(0)
+    rc = lib.ff_gemm_tc(c_void_p(x.data_ptr()), c_void_p(w.data_ptr()), c_void_p(out.data_ptr()), c_int(N), c_int(T),
+                        c_int(N), c_int(Kd), c_int(k.EPI_F32), c_int(1), c_int(0), null, null, null, null, c_int(0),
+                        c_int(0), c_float(0.0), c_void_p(status.data_ptr()),
+                        c_void_p(torch.cuda.current_stream().cuda_stream))
+    assert rc == 0
+    torch.cuda.synchronize()                                   # the kernel came back
+    assert int(status) in (102, 103)
+    assert bool((out == 7.0).all())                            # a block that gave up stores nothing
+    status.zero_()
+    good = torch.zeros(T, N, dtype=torch.float32, device="cuda")
+    k.gemm_tc(x, w, good, k.EPI_F32, 1, status)
+    torch.cuda.synchronize()
+    assert int(status) == 0
+    ref = x.double() @ w.double().T
+    assert float((good.double() - ref).abs().max()) < 2e-3 * float(ref.abs().max())

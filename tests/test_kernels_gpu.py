@@ -250,6 +250,56 @@ def test_attention_tcgen05(d, nq, nkv, block, window):
     assert float(err) < 2e-2, float(err)
 
 
+@pytest.mark.parametrize("d", [64, 128])
+def test_attention_tcgen05_weights_of_late_large_scores(d):
+    """Two heavy keys come late and stand 4.5 and 6 powers of two above everything before them: not
+    far enough for the kernel to move its reference maximum (it does so beyond 8), so their softmax
+    arguments are large.  The keys are tuned so that rounding those arguments to bfloat16 (spacing
+    2^-5 there) would move one weight up and the other down by 0.9 %; their values are opposite, so
+    the output is their weighted difference and shows it: 1.7 % against the 64-bit result.  The kernel
+    must stay within 5e-3 (rounding of P, V and the output to bfloat16 costs up to about 4e-3)."""
+    nq, nkv, block, T = 2, 1, 16, 192
+    log2e = 1.4426950408889634
+    g = torch.Generator().manual_seed(17)
+    u = torch.randn(d, generator=g)
+    u = u / u.norm()
+    qv = (u * 4.0).to(torch.bfloat16)
+
+    def key_for(target):                 # a key along u whose score, in powers of two, is `target`
+        lo, hi, best = 0.0, 40.0, None
+        for _ in range(60):
+            mid = (lo + hi) / 2
+            kv = (u * mid).to(torch.bfloat16)
+            x = float(qv.double() @ kv.double()) / math.sqrt(d) * log2e
+            if best is None or abs(x - target) < abs(best[1] - target):
+                best = (kv, x)
+            lo, hi = (mid, hi) if x < target else (lo, mid)
+        return best
+    h = 2.0 ** -5
+    (k1, x1), (k2, x2) = key_for(6.0 + 0.4 * h), key_for(4.5 + 0.6 * h)
+    assert abs((x1 - 6.0) / h - 0.4) < 0.05 and abs((x2 - 4.5) / h - 0.6) < 0.05
+    q = qv.repeat(T, nq, 1)                                   # every query the same: every other score is 0
+    k = torch.zeros(T, nkv, d, dtype=torch.bfloat16)
+    v = torch.zeros(T, nkv, d, dtype=torch.bfloat16)
+    w = torch.randn(d, generator=g).to(torch.bfloat16)
+    k[130, 0], k[150, 0] = k1, k2
+    v[130, 0], v[150, 0] = w, -w
+    want = P.attention(q.double(), k.double(), v.double()).reshape(T, nq * d)
+    pages, order = _paged(k, v, block, seed=2)
+    table = torch.tensor([order + [-1]], dtype=torch.int32)
+    out = torch.zeros(T, nq * d, dtype=torch.bfloat16, device="cuda")
+    status = torch.zeros(1, dtype=torch.int32, device="cuda")
+    tiles = -(-(T * (nq // nkv)) // 128)
+    K().attn_tc(dev(q.reshape(T, nq * d).contiguous()), nq * d, dev(pages), dev(table),
+                dev(torch.tensor([0, T], dtype=torch.int32)), dev(torch.tensor([0], dtype=torch.int32)), 1, tiles, out,
+                nq, nkv, d, 1 / math.sqrt(d), 0, status)
+    torch.cuda.synchronize()
+    assert int(status) == 0
+    late = slice(160, T)                     # queries that see both heavy keys
+    err = (out.cpu().double()[late] - want[late]).abs().max() / want[late].abs().max()
+    assert float(err) < 5e-3, float(err)
+
+
 @pytest.mark.parametrize("d,nq,nkv,block", ATT_SHAPES)
 @pytest.mark.parametrize("window", [None, 100])
 @pytest.mark.parametrize("splits", [1, 2, 5])

