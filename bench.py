@@ -119,14 +119,138 @@ class ClockSampler:
                 "samples": len(sm)}
 
 
-def reference_arm():
-    # The reference is a CMake/C++/CUDA server with no Python package: there is nothing pip can
-    # install from it, its build fetches CUTLASS/mdspan/json/googletest over the network and needs
-    # gRPC, and it has no sm_100 kernels.
-    print(json.dumps({"impl": "reference",
-                      "unavailable": "gallnut/firefly is a C++/CMake gRPC server without a Python package "
-                                     "(pip install finds no setup.py/pyproject.toml); its build needs network "
-                                     "fetches (CPM: CUTLASS, mdspan, json) and gRPC, none available offline"}))
+REF_BIN = os.path.join(ROOT, "baseline", "_ref", "ref_bench")
+
+
+def write_reference_model(folder: str, shape: dict, seed: int = 0) -> float:
+    """A model folder the reference can load: config.json, model.safetensors (FP16, the only type its
+    kernels run; matrices N(0, 0.02), norm weights 1 + N(0, 0.01), drawn tensor by tensor and written
+    as they come, so the host never holds the model) and a tokenizer.json that gives every id a text
+    (the reference's engine reports a token only when it has text for it).  Returns gigabytes written."""
+    import struct
+
+    import torch
+    H, I, L, V = shape["hidden_size"], shape["intermediate_size"], shape["num_hidden_layers"], shape["vocab_size"]
+    nq, nkv, d = shape["num_attention_heads"], shape["num_key_value_heads"], shape["head_dim"]
+    tensors = [("model.embed_tokens.weight", (V, H)), ("model.norm.weight", (H,)), ("lm_head.weight", (V, H))]
+    for i in range(L):
+        p = f"model.layers.{i}"
+        tensors += [(f"{p}.input_layernorm.weight", (H,)), (f"{p}.post_attention_layernorm.weight", (H,)),
+                    (f"{p}.self_attn.q_proj.weight", (nq * d, H)), (f"{p}.self_attn.k_proj.weight", (nkv * d, H)),
+                    (f"{p}.self_attn.v_proj.weight", (nkv * d, H)), (f"{p}.self_attn.o_proj.weight", (H, nq * d)),
+                    (f"{p}.self_attn.q_norm.weight", (d,)), (f"{p}.self_attn.k_norm.weight", (d,)),
+                    (f"{p}.mlp.gate_proj.weight", (I, H)), (f"{p}.mlp.up_proj.weight", (I, H)),
+                    (f"{p}.mlp.down_proj.weight", (H, I))]
+    header, off = {}, 0
+    for name, shp in tensors:
+        n = 2
+        for x in shp:
+            n *= x
+        header[name] = {"dtype": "F16", "shape": list(shp), "data_offsets": [off, off + n]}
+        off += n
+    blob = json.dumps(header, separators=(",", ":")).encode()
+    blob += b" " * ((8 - len(blob) % 8) % 8)
+    gen = torch.Generator(device="cuda").manual_seed(seed)
+    with open(os.path.join(folder, "model.safetensors"), "wb") as fh:
+        fh.write(struct.pack("<Q", len(blob)))
+        fh.write(blob)
+        for name, shp in tensors:
+            x = torch.randn(shp, generator=gen, device="cuda", dtype=torch.float32)
+            x = (1.0 + 0.01 * x) if len(shp) == 1 else 0.02 * x
+            fh.write(x.to(torch.float16).cpu().numpy().tobytes())
+    cfg = {k: shape[k] for k in ("architectures", "hidden_size", "intermediate_size", "num_hidden_layers",
+                                 "num_attention_heads", "num_key_value_heads", "head_dim", "vocab_size",
+                                 "max_position_embeddings", "rms_norm_eps", "rope_theta")}
+    with open(os.path.join(folder, "config.json"), "w") as fh:
+        json.dump(cfg, fh)
+    with open(os.path.join(folder, "tokenizer.json"), "w") as fh:
+        json.dump({"model": {"vocab": {f"a{i}": i for i in range(V)}, "merges": []}}, fh)
+    return off / 1e9
+
+
+def reference_arm(args) -> int:
+    """The reference's own engine (built unmodified by baseline/build_reference.py into
+    baseline/_ref/ref_bench) on the same shape and batch, fed through Engine::async_generate and timed
+    from outside by the arrival of its tokens."""
+    def unavailable(why: str) -> int:
+        print(json.dumps({"impl": "reference", "unavailable": why}))
+        return 0
+    if args.gpus != 1:
+        return unavailable("the reference runs on one GPU only (it has no multi-GPU path)")
+    if not os.path.isfile(REF_BIN):
+        src = os.environ.get("FIREFLY_REFERENCE", "/root/reference")
+        if not os.path.isdir(os.path.join(src, "src", "kernels")):
+            return unavailable("baseline/_ref/ref_bench is not built and the reference's sources are not on this "
+                               "machine (python baseline/build_reference.py builds it where they are)")
+        try:
+            subprocess.run([sys.executable, os.path.join(ROOT, "baseline", "build_reference.py"), src], check=True,
+                           stdout=subprocess.DEVNULL, stderr=subprocess.PIPE, text=True, timeout=1500)
+        except Exception as e:  # noqa: BLE001
+            tail = (getattr(e, "stderr", "") or str(e)).strip().splitlines()[-1:] or [str(e)]
+            return unavailable(f"the reference's sources do not build here: {tail[0][:200]}")
+    if args.dtype != "bfloat16":
+        return unavailable("the reference has one element type (FP16 with FP16 accumulation)")
+    if args.prompt_len % 16:
+        return unavailable("the reference's prefill kernel reads past prompts that are no multiple of 16 tokens "
+                           "(src/kernels/attention.cu:78,240); not run")
+    import shutil
+
+    import torch
+    if not torch.cuda.is_available():
+        return unavailable("no CUDA device on this machine")
+    shape = load_shape(args.shape)
+    full_layers = shape["num_hidden_layers"]
+    if args.layers:
+        shape["num_hidden_layers"] = args.layers
+    K_steps, W = args.steps, max(args.warmup, 3)
+    pk = peaks()
+    folder = tempfile.mkdtemp(prefix="firefly_ref_model_")
+    clocks = ClockSampler()
+    try:
+        t0 = time.time()
+        gb = write_reference_model(folder, shape)
+        torch.cuda.synchronize()
+        torch.cuda.empty_cache()
+        write_s = time.time() - t0
+        if not os.environ.get("FF_NO_CLOCKS"):
+            clocks.start()
+        proc = subprocess.run([REF_BIN, folder, "--batch", str(args.batch), "--prompt-len", str(args.prompt_len),
+                               "--steps", str(K_steps), "--warmup", str(W)], capture_output=True, text=True,
+                              timeout=1500)
+        clock_info = clocks.stop()
+        line = next((x for x in proc.stdout.splitlines() if x.startswith("REF_RESULT ")), None)
+        if proc.returncode != 0 or line is None:
+            tail = (proc.stderr.strip().splitlines() or proc.stdout.strip().splitlines() or ["no output"])[-1]
+            return unavailable(f"the reference's engine ended with code {proc.returncode} on this machine: {tail[:300]}")
+        r = json.loads(line[len("REF_RESULT "):])
+    except subprocess.TimeoutExpired:
+        clocks.stop()
+        return unavailable("the reference's engine did not finish within 25 minutes")
+    finally:
+        shutil.rmtree(folder, ignore_errors=True)
+    L, H, I, V = shape["num_hidden_layers"], shape["hidden_size"], shape["intermediate_size"], shape["vocab_size"]
+    nq, nkv, d = shape["num_attention_heads"], shape["num_key_value_heads"], shape["head_dim"]
+    out = {
+        "metric": f"decode tok/s at batch {args.batch} (Qwen3-{args.shape.upper()}-shaped float16, {args.prompt_len}-token prompts)",
+        "value": r["tok_s"], "unit": "tok/s", "n_gpus": 1, "steps": K_steps, "warmup": W,
+        "ms_per_step": r["ms_per_step"], "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
+        "dtype": "fp16", "data": "synthetic", "impl": "reference",
+        "config": {"model": f"Qwen3-{args.shape.upper()}-shaped random weights", "global_batch": args.batch,
+                   "seq_len": args.context, "parallelism": "single GPU", "layers": L, "layers_of_config": full_layers,
+                   "hidden": H, "q_heads": nq, "kv_heads": nkv, "head_dim": d, "intermediate": I, "vocab": V,
+                   "prompt_len": args.prompt_len, "new_tokens": 1 + W + K_steps, "kv_block": 16, "cuda_graphs": True,
+                   "l2": "inputs>L2: each step streams the weights", "peaks": pk["source"],
+                   "model_write_s": round(write_s, 1), "model_gb": round(gb, 2)},
+        "clocks": clock_info,
+        # the reference is timed through its public API already (tokens counted as its result queue
+        # delivers them), so this is the end-to-end figure too
+        "e2e": {"value": r["tok_s"], "unit": "tok/s", "steps": K_steps, "h2d_bytes_per_step": None,
+                "d2h_bytes_per_step": args.batch * 4},
+        "gpu_launches": 0,
+        "reference": {"decode_tokens_timed": r["decode_tokens_timed"], "requests_ended_early": r["requests_ended_early"],
+                      "load_seconds": r["load_seconds"], "total_seconds": r["total_seconds"]},
+    }
+    print(json.dumps(out))
     return 0
 
 
@@ -147,7 +271,7 @@ def main() -> int:
     ap.add_argument("--shape", default="8b", choices=sorted(SHAPES), help="model shape (default: the metric's 8b)")
     args = ap.parse_args()
     if args.impl == "reference":
-        return reference_arm()
+        return reference_arm(args)
     if args.gpus != 1:
         print(f"bench.py: this engine runs on one GPU; --gpus {args.gpus} is not supported")
         return 2
