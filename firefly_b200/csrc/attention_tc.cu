@@ -47,7 +47,14 @@ constexpr int BN = 64;                  // keys per tile
 constexpr int PANELS = D / 64;          // 64-column (128-byte) panels of a row
 constexpr int KV_STAGES = 2;
 constexpr int ATC_THREADS = 192;        // warps 0-3 softmax, warp 4 loads, warp 5 MMAs
-constexpr int MAX_PAGE_LIST = 1024;     // page ids of a block's tiles kept in shared memory
+// Page ids of a block's tiles kept in shared memory: a ring of two halves.  The softmax warps fill
+// what the first tiles need; the load warp refills a half whenever its tiles move into it, so a
+// context of any length is walked through the same few kilobytes.  (A test build makes it tiny.)
+#ifndef FF_ATC_PAGE_LIST
+#define FF_ATC_PAGE_LIST 1024
+#endif
+constexpr int MAX_PAGE_LIST = FF_ATC_PAGE_LIST;
+static_assert(MAX_PAGE_LIST >= 16 && MAX_PAGE_LIST % 16 == 0, "two halves of whole tiles (up to 8 pages each)");
 constexpr float LOG2E = 1.4426950408889634f;
 constexpr unsigned long long WAIT_LIMIT_CYCLES = 2000000000ull;
 
@@ -280,9 +287,23 @@ attn_tc_kernel(const __grid_constant__ TensorMapArg kv_map, const bf16* __restri
         n_tiles = (kv_hi + BN - 1) / BN - t_begin;
     }
     const int pages_per_tile = BN / block_size;
-    const bool list_fits = n_tiles * pages_per_tile <= MAX_PAGE_LIST;
-    if (!list_fits && threadIdx.x == 0) atomicExch(status, 108);
-    if (seq < 0 || !list_fits) n_tiles = 0;
+    const int tiles_per_half = (MAX_PAGE_LIST / 2) / pages_per_tile;      // tiles whose page ids one half of the ring holds
+    if (seq < 0) n_tiles = 0;
+    // Page ids of tiles [first, first + count) of this block into their places of the ring, by the
+    // threads `who` of `nthreads`.  A page that should be there and is not raises status 4.
+    const int* bt = block_table + (size_t)max(seq, 0) * max_blocks;
+    const int last_page = (kv_hi - 1) / block_size, first_page = kv_lo / block_size;
+    auto fill_pages = [&](int first, int count, int who, int nthreads) {
+        for (int i = who; i < count * pages_per_tile; i += nthreads) {
+            const int tile = first + i / pages_per_tile;
+            const int pi = (t_begin + tile) * pages_per_tile + i % pages_per_tile;
+            const bool wanted = pi >= first_page && pi <= last_page;
+            int page = (wanted && pi < max_blocks) ? bt[pi] : -1;
+            if (page >= num_blocks) page = -1;
+            if (wanted && page < 0) atomicExch(status, 4);      // a key's page is missing: the bookkeeping is at fault
+            s_pages[(tile % (2 * tiles_per_half)) * pages_per_tile + i % pages_per_tile] = page;
+        }
+    };
 
     if (warp < 4) {
         // ------------------------------------------------ set-up by the softmax warps --
@@ -298,17 +319,8 @@ attn_tc_kernel(const __grid_constant__ TensorMapArg kv_map, const bf16* __restri
 #pragma unroll
             for (int ch = 0; ch < D / 8; ++ch) qv[ch] = valid ? __ldg(src + ch) : make_uint4(0u, 0u, 0u, 0u);
         }
-        // page ids of all tiles
-        const int* bt = block_table + (size_t)max(seq, 0) * max_blocks;
-        const int last_page = (kv_hi - 1) / block_size, first_page = kv_lo / block_size;
-        for (int i = threadIdx.x; i < n_tiles * pages_per_tile; i += 128) {
-            const int pi = t_begin * pages_per_tile + i;
-            const bool wanted = pi >= first_page && pi <= last_page;
-            int page = (wanted && pi < max_blocks) ? bt[pi] : -1;
-            if (page >= num_blocks) page = -1;
-            if (wanted && page < 0) atomicExch(status, 4);      // a key's page is missing: the bookkeeping is at fault
-            s_pages[i] = page;
-        }
+        // page ids of the first tiles (both halves of the ring)
+        fill_pages(0, min(n_tiles, 2 * tiles_per_half), threadIdx.x, 128);
         // zero the K/V stages once: parts no page is loaded into must hold finite numbers
         for (int i = threadIdx.x; i < KV_STAGES * 2 * KV_TILE_BYTES / 16; i += 128)
             reinterpret_cast<uint4*>(Ks)[i] = make_uint4(0u, 0u, 0u, 0u);
@@ -447,9 +459,15 @@ attn_tc_kernel(const __grid_constant__ TensorMapArg kv_map, const bf16* __restri
         const int p = lane / PANELS, h = lane % PANELS;                  // this lane's page and panel of a tile
         auto load_tile = [&](int j, int kv) -> bool {
             const int s = j % KV_STAGES;
+            if (kv == 0 && j >= 2 * tiles_per_half && j % tiles_per_half == 0) {
+                // the K loads run ahead of the V loads by one tile and have reached a half of the ring whose
+                // tiles are all behind both: refill it with the next tiles' page ids
+                fill_pages(j, min(tiles_per_half, n_tiles - j), lane, 32);
+                __syncwarp();
+            }
             bool fine = mb_wait(sa(&bars[(kv ? B_V_EMPTY : B_K_EMPTY) + s]), ((j / KV_STAGES) & 1) ^ 1, status, abort_flag);
             if (!__all_sync(0xffffffffu, fine)) return false;
-            const int page = p < pages_per_tile ? s_pages[j * pages_per_tile + p] : -1;
+            const int page = p < pages_per_tile ? s_pages[(j % (2 * tiles_per_half)) * pages_per_tile + p] : -1;
             const unsigned boxes = __ballot_sync(0xffffffffu, page >= 0);
             const uint32_t bar = sa(&bars[(kv ? B_V_FULL : B_K_FULL) + s]);
             if (lane == 0) mb_expect_tx(bar, (uint32_t)(__popc(boxes) * block_size * 128));

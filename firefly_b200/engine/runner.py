@@ -50,8 +50,7 @@ _STATUS = {1: "a token id outside the vocabulary reached the embedding kernel",
            101: "matrix product: the loader's wait for a free stage ran out",
            102: "matrix product: the wait for a loaded stage ran out",
            103: "matrix product: the wait for the accumulator ran out",
-           107: "attention (tcgen05): a bounded wait ran out",
-           108: "attention (tcgen05): a sequence's page list does not fit the kernel's shared memory"}
+           107: "attention (tcgen05): a bounded wait ran out"}
 
 
 def status_text(code: int) -> str:

@@ -451,23 +451,25 @@ def attn_decode_heads(qkv, pages, table, ctx, out, nq, nkv, d, scale, window, q_
 USE_TC_ATTENTION = True     # tcgen05 attention for prompt portions where the sizes allow
 
 
-def _attn_tc_lib(d: int) -> ctypes.CDLL:
-    return _configured(load_module("attention_tc.cu", {"FF_HEAD_DIM": d}))
+def _attn_tc_lib(d: int, page_list: Optional[int] = None) -> ctypes.CDLL:
+    defs = {"FF_HEAD_DIM": d}
+    if page_list is not None:
+        defs["FF_ATC_PAGE_LIST"] = int(page_list)       # a test build with a tiny ring of page ids
+    return _configured(load_module("attention_tc.cu", defs))
 
 
-def tc_attention_supported(dtype: torch.dtype, d: int, block_size: int, max_kv_len: int) -> bool:
-    """The tcgen05 attention kernel takes head sizes 64..256 in steps of 64, pages of 8..64 tokens
-    that divide 64, and contexts whose page list fits its shared memory."""
-    return (dtype == torch.bfloat16 and d % 64 == 0 and 64 <= d <= 256 and block_size in (8, 16, 32, 64)
-            and -(-max_kv_len // 64) * (64 // block_size) <= 1024)
+def tc_attention_supported(dtype: torch.dtype, d: int, block_size: int, max_kv_len: int = 0) -> bool:
+    """The tcgen05 attention kernel takes head sizes 64..256 in steps of 64 and pages of 8..64 tokens
+    that divide 64; contexts of any length (it walks the block table in pieces)."""
+    return dtype == torch.bfloat16 and d % 64 == 0 and 64 <= d <= 256 and block_size in (8, 16, 32, 64)
 
 
 def attn_tc(q, q_stride, pages, table, cu_q, ctx_lens, n_seqs, total_tiles, out, nq, nkv, d, scale, window,
-            status) -> None:
+            status, page_list: Optional[int] = None) -> None:
     """tcgen05 flash attention over the paged cache (bfloat16); total_tiles counts row tiles of 128."""
     _need_cuda(pages, table, cu_q, ctx_lens, out, status)
     num_blocks, _, _, block_size, _ = pages.shape
-    _check(_attn_tc_lib(d).ff_attn_tc(
+    _check(_attn_tc_lib(d, page_list).ff_attn_tc(
         _p(q), c_int(q_stride), _p(pages), _p(table), c_int(table.shape[1]), _p(cu_q), _p(ctx_lens),
         c_int(n_seqs), c_int(total_tiles), _p(out), c_int(out.shape[1]), c_int(nq), c_int(nkv),
         c_int(block_size), c_int(num_blocks), c_float(scale), c_int(window), _p(status), _stream()), "attn_tc")

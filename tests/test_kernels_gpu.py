@@ -250,6 +250,61 @@ def test_attention_tcgen05(d, nq, nkv, block, window):
     assert float(err) < 2e-2, float(err)
 
 
+@pytest.mark.parametrize("d,nq,nkv,block,page_list", [(64, 4, 1, 16, 16), (128, 8, 2, 8, 16), (128, 4, 4, 64, 16),
+                                                      (64, 6, 2, 32, 32)])
+@pytest.mark.parametrize("window", [None, 150])
+def test_attention_tcgen05_walks_long_block_tables_in_pieces(d, nq, nkv, block, page_list, window):
+    """A build whose ring of page ids holds 16 or 32 entries (1024 in the product): contexts of a
+    thousand tokens then need it refilled many times, as contexts beyond 16 k tokens do in the
+    product.  One far key stands out for the last query of each sequence, so a page read from the wrong
+    place of the ring shows."""
+    seqs = [(0, 1000), (700, 300), (1100, 2), (64 * 7, 129), (5, 17)]
+    c = _attention_case(d, nq, nkv, block, seqs, window, torch.bfloat16, seed=9)
+    G = nq // nkv
+    out = torch.zeros(c["q"].shape, dtype=torch.bfloat16, device="cuda")
+    status = torch.zeros(1, dtype=torch.int32, device="cuda")
+    tiles = sum(-(-(ql * G) // 128) for ql in c["q_lens"])
+    K().attn_tc(dev(c["q"]), nq * d, dev(c["pages"]), dev(c["table"]), dev(c["cu_q"]), dev(c["ctx_lens"]),
+                len(seqs), tiles, out, nq, nkv, d, 1 / math.sqrt(d), window or 0, status, page_list=page_list)
+    torch.cuda.synchronize()
+    assert int(status) == 0
+    err = (out.cpu().double() - c["want"]).abs().max() / c["want"].abs().max()
+    assert float(err) < 2e-2, float(err)
+
+
+def test_attention_tcgen05_context_beyond_one_ring_of_page_ids():
+    """The product build at a context of 17 000 tokens in pages of 16: 1 066 page ids a block, more than
+    its ring of 1 024 holds.  Only the portion's 200 queries are compared (softmax over keys 0..position
+    in 64-bit, written out here: the whole-sequence plain function would need the full score matrix)."""
+    d, nq, nkv, block, ctx_len, q_len = 128, 4, 1, 16, 17000, 200
+    g = torch.Generator().manual_seed(21)
+    T = ctx_len + q_len
+    q = torch.randn(q_len, nq, d, generator=g)
+    k = torch.randn(T, nkv, d, generator=g)
+    v = torch.randn(T, nkv, d, generator=g)
+    k[3] = k[3] * 0.1 + 3.0 * q[-1, 0] / math.sqrt(d) * 4                 # far keys that stand out for late queries,
+    k[16500] = k[16500] * 0.1 + 3.0 * q[-2, 1] / math.sqrt(d) * 4          # one on each side of the ring's refill
+    q, k, v = q.to(torch.bfloat16), k.to(torch.bfloat16), v.to(torch.bfloat16)
+    want = torch.empty(q_len, nq, d, dtype=torch.float64)
+    kd, vd = k.double()[:, 0], v.double()[:, 0]
+    for i in range(q_len):
+        n = ctx_len + i + 1
+        sc = (q[i].double() @ kd[:n].T) / math.sqrt(d)                     # [nq, n]
+        want[i] = torch.softmax(sc, dim=-1) @ vd[:n]
+    pages, order = _paged(k, v, block, seed=4)
+    table = torch.tensor([order + [-1]], dtype=torch.int32)
+    out = torch.zeros(q_len, nq * d, dtype=torch.bfloat16, device="cuda")
+    status = torch.zeros(1, dtype=torch.int32, device="cuda")
+    tiles = -(-(q_len * nq) // 128)
+    K().attn_tc(dev(q.reshape(q_len, nq * d).contiguous()), nq * d, dev(pages), dev(table),
+                dev(torch.tensor([0, q_len], dtype=torch.int32)), dev(torch.tensor([ctx_len], dtype=torch.int32)), 1,
+                tiles, out, nq, nkv, d, 1 / math.sqrt(d), 0, status)
+    torch.cuda.synchronize()
+    assert int(status) == 0
+    err = (out.cpu().double() - want.reshape(q_len, nq * d)).abs().max() / want.abs().max()
+    assert float(err) < 2e-2, float(err)
+
+
 @pytest.mark.parametrize("d", [64, 128])
 def test_attention_tcgen05_weights_of_late_large_scores(d):
     """Two heavy keys come late and stand 4.5 and 6 powers of two above everything before them: not
