@@ -452,8 +452,37 @@ def main() -> int:
                 "frac": flops / (ms / 1e3) / (pk["bf16_tflops_sustained" if False else "bf16_tflops"] * 1e12),
                 "tflops": flops / (ms / 1e3) / 1e12}
 
+    def prefill_chunked_point(chunk=256):
+        """The prompt of P tokens fed through ``Engine.step`` in portions of ``chunk`` tokens (256: the
+        reference's --max-prefill-chunk-size; None: the engine's default, which does not cut a prompt
+        while no request is decoding): wall time from the first step to the first sampled token on the
+        host, median of five prompts."""
+        opts = EngineOptions(max_prefill_chunk_size=chunk, max_batch_size_limit=1, max_num_batched_tokens=8192,
+                             kv_block_size=16, num_kv_blocks=-(-(P + 64) // 16), eos_token_ids=[])
+        eng = Engine(model, cfg, options=opts)
+        times = []
+        for it in range(2 + 5):
+            ids = torch.randint(0, V, (P,), generator=gen).tolist()
+            req = GenerationRequest(f"c{it}", ids, SamplingParams(max_tokens=1, ignore_eos=True))
+            eng.add_request(req)
+            torch.cuda.synchronize()
+            t = time.perf_counter()
+            steps = 0
+            while eng.has_unfinished_requests():
+                eng.step()
+                steps += 1
+            torch.cuda.synchronize()
+            if it >= 2:
+                times.append((time.perf_counter() - t) * 1e3)
+        eng.runner.check_status()
+        del eng
+        torch.cuda.empty_cache()
+        ms = statistics.median(times)
+        return {"value": P / (ms / 1e3), "tokens": P, "chunk": chunk, "steps": steps, "ms": ms}
+
     if args.no_decode:
-        print(json.dumps({"prefill": prefill_point(), "config": {"layers": L}}))
+        print(json.dumps({"prefill": prefill_point(), "prefill_chunked": prefill_chunked_point(),
+                          "prefill_engine_default": prefill_chunked_point(None), "config": {"layers": L}}))
         return 0
     clocks = ClockSampler()
     if not os.environ.get("FF_NO_CLOCKS"):
@@ -461,6 +490,10 @@ def main() -> int:
     main_res = decode_point(args.batch, K_steps, with_e2e=True)
     clock_info = clocks.stop()
     prefill = None if args.no_prefill else prefill_point()
+    prefill_chunked = None if args.no_prefill else prefill_chunked_point()
+    if prefill_chunked is not None:
+        d = prefill_chunked_point(None)
+        prefill_chunked["engine_default_ms"], prefill_chunked["engine_default_steps"] = d["ms"], d["steps"]
     points = {}
     if not args.no_points:
         for B in (1, 64):
@@ -489,6 +522,7 @@ def main() -> int:
         "e2e": main_res["e2e"],
         "gpu_launches": main_res["launches"],
         "prefill": prefill,
+        "prefill_chunked": prefill_chunked,
         "roofline": {"bound": "hbm", "achieved": achieved, "peak": pk["hbm_gbs"], "unit": "GB/s",
                      "frac": achieved / pk["hbm_gbs"]},
         "points": points,

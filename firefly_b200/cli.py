@@ -2,8 +2,8 @@
 
 In the manner of the reference's ``firefly_server [model_dir] [--max-prefill-chunk-size N]``
 (src/server.cu:83-97): the model folder is the positional argument (default
-``qwen3``) and ``--max-prefill-chunk-size`` has the same meaning and default
-(256).  The reference then serves chat completions over gRPC; this program
+``qwen3``) and ``--max-prefill-chunk-size`` has the same meaning (its default, 256, holds
+while requests are decoding; while none is, a prompt is not cut).  The reference then serves chat completions over gRPC; this program
 generates from token ids given on the command line or in a file and prints one
 JSON line per request.  ``--max-tokens`` defaults to the reference's 512
 (src/server.cu:189).
@@ -28,8 +28,9 @@ def build_parser() -> argparse.ArgumentParser:
     ap = argparse.ArgumentParser(prog="firefly", description="Qwen3 dense inference on one B200")
     ap.add_argument("model_dir", nargs="?", default="qwen3",
                     help="folder with config.json and model.safetensors (default: qwen3)")
-    ap.add_argument("--max-prefill-chunk-size", type=int, default=256,
-                    help="most prompt tokens of one request in one step (default 256)")
+    ap.add_argument("--max-prefill-chunk-size", type=int, default=None,
+                    help="most prompt tokens of one request in one step (default: 256 while requests are "
+                         "decoding, whole prompts while none is)")
     ap.add_argument("--prompt-ids", action="append", default=[],
                     help="a prompt as comma-separated token ids; may be given several times")
     ap.add_argument("--prompts-file", help="file with one JSON list of token ids per line")

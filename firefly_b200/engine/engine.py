@@ -5,7 +5,8 @@ src/engine.cc): ``async_generate(id, input_ids, max_tokens)`` queues a request
 from any thread, ``start()`` / ``stop()`` run the loop in a background thread and
 results arrive on a ``ResultQueue`` as (request id, new token ids, is_finished)
 — token ids where the reference pushes text, since text is outside this engine.
-``max_prefill_chunk_size`` has the reference's meaning and default (256).
+``max_prefill_chunk_size`` has the reference's meaning; left unset it is the reference's 256 while
+some request is decoding and the step's whole token budget while none is.
 One iteration is ``Engine.step()``: the scheduler picks portions and decode
 tokens, the step function runs them as one batch, the sampler picks next tokens.
 
@@ -74,9 +75,15 @@ class _InFlight:
     dropped: List[bool]                     # per lane: the request ended before this step's token
 
 
+DEFAULT_PREFILL_CHUNK = 256      # the reference's default (include/firefly/engine.h:20, src/server.cu:84)
+
+
 @dataclass
 class EngineOptions:
-    max_prefill_chunk_size: int = 256       # the reference's --max-prefill-chunk-size
+    # the reference's --max-prefill-chunk-size: most prompt tokens of one request in one step.  None: the
+    # reference's 256 while some request is decoding (a portion bounds what a prompt adds to their steps),
+    # and as much as the step's token budget allows while none is (then portions only cost)
+    max_prefill_chunk_size: Optional[int] = None
     max_batch_size_limit: int = 64          # most active requests (reference: 64)
     max_num_batched_tokens: int = 8192      # tokens of one step, all requests together
     kv_block_size: int = 16                 # tokens per cache page (reference: 16)
@@ -91,7 +98,7 @@ class EngineOptions:
 
 class Engine:
     def __init__(self, model: DecoderModel, config: Optional[ModelConfig] = None,
-                 result_queue: Optional[ResultQueue] = None, max_prefill_chunk_size: int = 256,
+                 result_queue: Optional[ResultQueue] = None, max_prefill_chunk_size: Optional[int] = None,
                  options: Optional[EngineOptions] = None, raw_config: Optional[dict] = None,
                  runner=None, sampler=None):
         """``runner`` / ``sampler``: stand-ins for the step function and the sampler (tests of the
@@ -100,6 +107,7 @@ class Engine:
         if options is None:
             opts.max_prefill_chunk_size = max_prefill_chunk_size
         self.options = opts
+        self.prefill_chunk = opts.max_prefill_chunk_size or DEFAULT_PREFILL_CHUNK
         self.model = model
         self.config = config
         self.result_queue = result_queue
@@ -121,9 +129,11 @@ class Engine:
             e = (raw_config or {}).get("eos_token_id")
             eos = [] if e is None else ([int(x) for x in e] if isinstance(e, list) else [int(e)])
         self.scheduler = Scheduler(self.cache, max_batch_size_limit=opts.max_batch_size_limit,
-                                   max_prefill_chunk_size=opts.max_prefill_chunk_size,
+                                   max_prefill_chunk_size=self.prefill_chunk,
                                    max_num_batched_tokens=opts.max_num_batched_tokens,
-                                   max_model_len=self.max_model_len, eos_token_ids=eos)
+                                   max_model_len=self.max_model_len, eos_token_ids=eos,
+                                   whole_prompts_when_idle=opts.max_prefill_chunk_size is None
+                                   and not any(g.spec.window is not None for g in self.cache.groups))
         self.sampler = sampler if sampler is not None else Sampler(self.device, opts.max_batch_size_limit)
         self.graphs = None
         if opts.use_cuda_graphs:
@@ -153,7 +163,7 @@ class Engine:
         most = opts.max_batch_size_limit * max_len
 
         def window_pages(sp, bs):
-            per_request = -(-(sp.window + opts.max_prefill_chunk_size) // bs) + 2
+            per_request = -(-(sp.window + self.prefill_chunk) // bs) + 2
             return opts.max_batch_size_limit * min(per_request, -(-max_len // bs) + 1)
         if opts.num_kv_blocks is not None:
             tokens = opts.num_kv_blocks * opts.kv_block_size
@@ -431,7 +441,7 @@ class LLM:
     """
 
     def __init__(self, model, *, dtype="bfloat16", device="cuda:0", seed: int = 0,
-                 max_prefill_chunk_size: int = 256, **options):
+                 max_prefill_chunk_size: Optional[int] = None, **options):
         """``model``: a folder with config.json and model.safetensors, or a typed
         configuration (random weights drawn from ``seed``)."""
         raw = None

@@ -81,6 +81,35 @@ def test_prompt_is_cut_into_portions_then_decoded():
     assert r.status is RequestStatus.FINISHED and cache.num_free_blocks == 8 and not cache.live
 
 
+def test_prompts_are_not_cut_while_nobody_decodes():
+    """With ``whole_prompts_when_idle`` a portion may fill the step's token budget as long as no
+    request is decoding; as soon as one is, later prompts come in portions of the configured size.
+    The tokens produced do not depend on it."""
+    for idle_whole in (False, True):
+        sched, cache = make(chunk=64, budget=1000, num_blocks=256)
+        sched.whole_prompts_when_idle = idle_whole
+        a, b = req(0, 700, max_tokens=20), req(1, 500, max_tokens=3)
+        sched.add_request(a)
+        first = sched.step()
+        assert [(it.request.id, it.num_tokens) for it in first.items] == [("r0", 700 if idle_whole else 64)]
+        for it in first.items:
+            cache.advance(it.request.cache, it.num_tokens)
+            if it.samples:
+                sched.append_token(a, next_token(a.prompt_tokens))
+        sched.add_request(b)                        # arrives while (or before) r0 decodes
+        steps = run(sched, cache)
+        portions_b = [n for step in steps for (rid, _, n, _) in step if rid == "r1"]
+        if idle_whole:
+            # r0 was decoding when r1 came in: r1 is cut into portions of 64
+            assert portions_b[:7] == [64] * 7 and max(portions_b) == 64
+        assert a.generated_tokens == alone(a.prompt_tokens, 20) and b.generated_tokens == alone(b.prompt_tokens, 3)
+    # the budget still bounds a whole prompt
+    sched, cache = make(chunk=64, budget=300, num_blocks=256)
+    sched.whole_prompts_when_idle = True
+    sched.add_request(req(2, 700, max_tokens=1))
+    assert [it.num_tokens for it in sched.step().items] == [300]
+
+
 def test_token_budget_and_limits_hold():
     sched, cache = make(chunk=64, budget=100, limit=3, num_blocks=200)
     rs = [req(i, 150 + 10 * i, max_tokens=5) for i in range(6)]
