@@ -208,7 +208,12 @@ __global__ void __launch_bounds__(ATC_THREADS)
 attn_tc_kernel(const __grid_constant__ TensorMapArg kv_map, const bf16* __restrict__ q, int q_stride,
                const int* __restrict__ block_table, int max_blocks, const int* __restrict__ cu_q,
                const int* __restrict__ ctx_lens, int n_seqs, bf16* __restrict__ out, int out_stride, int nq,
-               int nkv, int block_size, int num_blocks, float scale_log2, int window, int* __restrict__ status) {
+               int nkv, int block_size, int num_blocks, float scale_log2, int window, int* __restrict__ status,
+               int num_splits, float* __restrict__ part_o, float* __restrict__ part_ml) {
+    // num_splits > 1: the grid holds every (row tile, kv head) num_splits times; each copy walks its share
+    // of the tile's keys and leaves an unnormalised result with its (reference max, sum) for the join
+    // kernel.  For prompts so short that their row tiles would leave most SMs idle while each block
+    // walks a long chain of key tiles alone.
     asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
     extern __shared__ unsigned char smem_raw[];
     unsigned char* base = reinterpret_cast<unsigned char*>(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
@@ -220,7 +225,10 @@ attn_tc_kernel(const __grid_constant__ TensorMapArg kv_map, const bf16* __restri
     __shared__ int s_seq, s_tile, s_abort, s_tok0, s_qlen, s_ctx;
     __shared__ uint32_t s_tmem;
     const int G = nq / nkv;
-    const int kh = (int)(blockIdx.x % (unsigned)nkv);
+    const unsigned units = gridDim.x / (unsigned)num_splits;          // (row tile, kv head) pairs
+    const unsigned unit = blockIdx.x % units;
+    const int split = (int)(blockIdx.x / units);
+    const int kh = (int)(unit % (unsigned)nkv);
     // the warp index through a shuffle, so that the compiler knows it to be the same in the whole warp and
     // keeps the address arithmetic of the single-thread roles in uniform registers
     const int warp = __shfl_sync(0xffffffffu, (int)(threadIdx.x >> 5), 0), lane = threadIdx.x & 31;
@@ -239,7 +247,7 @@ attn_tc_kernel(const __grid_constant__ TensorMapArg kv_map, const bf16* __restri
     asm volatile("griddepcontrol.wait;" ::: "memory");
     // Row tiles are handed out last first, for all kv heads before the next tile: in a prompt the
     // late tiles see the most keys, and the long blocks should not be the ones that start last.
-    const int vtile = (int)(gridDim.x / (unsigned)nkv) - 1 - (int)(blockIdx.x / (unsigned)nkv);
+    const int vtile = (int)(units / (unsigned)nkv) - 1 - (int)(unit / (unsigned)nkv);
     if (warp == 0) {   // which sequence owns row tile vtile
         int cum = 0, found_seq = -1, found_tile = 0;
         for (int s0 = 0; s0 < n_seqs && found_seq < 0; s0 += 32) {
@@ -285,6 +293,12 @@ attn_tc_kernel(const __grid_constant__ TensorMapArg kv_map, const bf16* __restri
         kv_lo = window > 0 ? max(0, ctx + first_tok - window + 1) : 0;
         t_begin = kv_lo / BN;
         n_tiles = (kv_hi + BN - 1) / BN - t_begin;
+        if (num_splits > 1) {                    // this copy's share of the key tiles (it may be empty)
+            const int per = (n_tiles + num_splits - 1) / num_splits;
+            const int mine = min(per, max(0, n_tiles - split * per));
+            t_begin += split * per;
+            n_tiles = mine;
+        }
     }
     const int pages_per_tile = BN / block_size;
     const int tiles_per_half = (MAX_PAGE_LIST / 2) / pages_per_tile;      // tiles whose page ids one half of the ring holds
@@ -428,7 +442,29 @@ attn_tc_kernel(const __grid_constant__ TensorMapArg kv_map, const bf16* __restri
             ok = mb_wait(sa(&bars[B_PV_DONE]), (n_tiles - 1) & 1, status, abort_flag);
             ok = __all_sync(0xffffffffu, ok);
         }
-        if (n_tiles > 0 && ok) {
+        if (num_splits > 1) {
+            // the partial result of this share of the keys: O unnormalised in 32-bit, its reference max
+            // (in powers of two) and sum; a share without keys says so with max = -inf
+            if (n_tiles > 0 && ok) tc_after();
+            const size_t p = ((size_t)(tok0 + token) * nq + head) * num_splits + split;
+            const bool any = n_tiles > 0 && ok && l > 0.f;
+            if (valid && seq >= 0) {
+                part_ml[p * 2] = any ? m : -CUDART_INF_F;
+                part_ml[p * 2 + 1] = any ? l : 0.f;
+            }
+            if (n_tiles > 0 && ok) {
+#pragma unroll 1
+                for (int c = 0; c < D / 16; ++c) {
+                    float v[16];
+                    tm_ld16(tm_O + lane_base + c * 16, v);
+                    if (valid) {
+                        float4* dst4 = reinterpret_cast<float4*>(part_o + p * D + c * 16);
+#pragma unroll
+                        for (int i = 0; i < 4; ++i) dst4[i] = make_float4(v[4 * i], v[4 * i + 1], v[4 * i + 2], v[4 * i + 3]);
+                    }
+                }
+            }
+        } else if (n_tiles > 0 && ok) {
             tc_after();
             const float inv = 1.0f / l;
             bf16* dst = out + (size_t)(tok0 + token) * out_stride + (size_t)head * D;
@@ -543,6 +579,28 @@ attn_tc_kernel(const __grid_constant__ TensorMapArg kv_map, const bf16* __restri
     }
 }
 
+// Join of the shares: out[token, head, :] = sum_s w_s O_s / sum_s w_s l_s, w_s = 2^(m_s - max m), in
+// the order of the shares.  grid (tokens, heads); token t of the grid is row tok_base + t.
+__global__ void attn_tc_join_kernel(const float* __restrict__ part_o, const float* __restrict__ part_ml,
+                                    bf16* __restrict__ out, int out_stride, int nq, int num_splits, int tok_base) {
+    asm volatile("griddepcontrol.launch_dependents;\n\tgriddepcontrol.wait;" ::: "memory");
+    const int tok = tok_base + blockIdx.x, head = blockIdx.y;
+    const size_t base = ((size_t)tok * nq + head) * num_splits;
+    float M = -CUDART_INF_F;
+    for (int s = 0; s < num_splits; ++s) M = fmaxf(M, part_ml[(base + s) * 2]);
+    for (int col = threadIdx.x; col < D; col += blockDim.x) {
+        float L = 0.f, O = 0.f;
+        for (int s = 0; s < num_splits; ++s) {
+            const float ms = part_ml[(base + s) * 2];
+            if (ms == -CUDART_INF_F) continue;
+            const float w = exp2f(ms - M);
+            L += w * part_ml[(base + s) * 2 + 1];
+            O += w * part_o[(base + s) * D + col];
+        }
+        out[(size_t)tok * out_stride + (size_t)head * D + col] = __float2bfloat16_rn(L > 0.f ? O / L : 0.f);
+    }
+}
+
 // ------------------------------------------------------------------ host side --
 typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
                                   const cuuint64_t*, const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave,
@@ -595,12 +653,18 @@ FF_EXPORT int ff_attn_tc_block_m() { return BM; }
 
 // total_tiles = sum over sequences of ceil(q_len * G / 128).  Needs a block size that divides 64
 // (8, 16, 32 or 64), a 128-byte aligned cache and q rows aligned to 16 bytes.
+// num_splits > 1: every row tile's keys are shared out over that many blocks, which leave partial
+// results in part_o (float [tokens * nq * num_splits * D]) and part_ml (float [tokens * nq * num_splits * 2]),
+// indexed by the token's row in q/out; a second kernel joins them for the n_tokens rows from tok_base on
+// (the rows of the sequences given here).
 FF_EXPORT int ff_attn_tc(const void* q, int q_stride, const void* cache, const int* block_table, int max_blocks,
                          const int* cu_q, const int* ctx_lens, int n_seqs, int total_tiles, void* out,
                          int out_stride, int nq, int nkv, int block_size, int num_blocks, float scale, int window,
-                         int* status, cudaStream_t stream) {
+                         int* status, int num_splits, float* part_o, float* part_ml, int tok_base, int n_tokens,
+                         cudaStream_t stream) {
     if (n_seqs <= 0 || total_tiles <= 0) return 0;
     if (nkv <= 0 || nq % nkv) return FF_ERR_BAD_ARG;
+    if (num_splits < 1 || (num_splits > 1 && (!part_o || !part_ml || n_tokens <= 0 || tok_base < 0))) return FF_ERR_BAD_ARG;
     if (block_size < 8 || BN % block_size) return FF_ERR_UNSUPPORTED;
     if (((uintptr_t)cache & 127) || ((uintptr_t)q & 15) || (q_stride % 8) || ((uintptr_t)out & 15) || (out_stride % 8))
         return FF_ERR_UNSUPPORTED;
@@ -612,9 +676,14 @@ FF_EXPORT int ff_attn_tc(const void* q, int q_stride, const void* cache, const i
     if (rc) return rc;
     TensorMapArg arg;
     std::memcpy(arg.bytes, &map, sizeof(map));
-    if ((long long)total_tiles * nkv >= (1ll << 31)) return FF_ERR_UNSUPPORTED;
-    FF_LAUNCH((attn_tc_kernel), dim3((unsigned)(total_tiles * nkv)), ATC_THREADS, ATC_SMEM, stream, arg, (const bf16*)q, q_stride,
-              block_table, max_blocks, cu_q, ctx_lens, n_seqs, (bf16*)out, out_stride, nq, nkv, block_size, num_blocks,
-              scale * LOG2E, window, status);
+    if ((long long)total_tiles * nkv * num_splits >= (1ll << 31)) return FF_ERR_UNSUPPORTED;
+    FF_LAUNCH((attn_tc_kernel), dim3((unsigned)(total_tiles * nkv * num_splits)), ATC_THREADS, ATC_SMEM, stream, arg,
+              (const bf16*)q, q_stride, block_table, max_blocks, cu_q, ctx_lens, n_seqs, (bf16*)out, out_stride, nq, nkv,
+              block_size, num_blocks, scale * LOG2E, window, status, num_splits, part_o, part_ml);
+    if (num_splits > 1) {
+        FF_LAUNCH((attn_tc_join_kernel), dim3((unsigned)n_tokens, (unsigned)nq), D >= 128 ? 128 : 64, 0, stream,
+                  (const float*)part_o, (const float*)part_ml, (bf16*)out, out_stride, nq, num_splits, tok_base);
+        FF_LAUNCH_CHECK();
+    }
     return 0;
 }

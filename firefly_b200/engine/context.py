@@ -23,6 +23,7 @@ class Workspace:
         self.device = torch.device(device)
         self._bufs: Dict[Tuple[str, torch.dtype], torch.Tensor] = {}
         self.frozen = False
+        self.version = 0          # counts (re)allocations: graphs that captured an address note it
 
     def get(self, tag: str, shape: Sequence[int], dtype: torch.dtype) -> torch.Tensor:
         n = 1
@@ -36,6 +37,7 @@ class Workspace:
                                    "while a captured graph uses it")
             buf = torch.empty(max(n, 1), dtype=dtype, device=self.device)
             self._bufs[key] = buf
+            self.version += 1
         return buf[:n].view(*shape)
 
     def get_zeroed(self, tag: str, numel: int, dtype: torch.dtype) -> torch.Tensor:
@@ -48,6 +50,7 @@ class Workspace:
                 raise RuntimeError(f"workspace buffer '{tag}' would have to grow while a captured graph uses it")
             buf = torch.zeros(max(numel, 1), dtype=dtype, device=self.device)
             self._bufs[key] = buf
+            self.version += 1
         return buf[:numel]
 
     def zero(self, tag: str, dtype: torch.dtype) -> None:

@@ -92,6 +92,7 @@ class EngineOptions:
     max_model_len: Optional[int] = None     # None: the model's max positions
     eos_token_ids: Optional[Sequence[int]] = None   # None: config.json's eos_token_id, if any
     use_cuda_graphs: bool = True
+    capture_repeating_steps: bool = True    # steps of other shapes (prompt portions) are captured when their shape comes again
     overlap_decode: bool = True             # launch the next greedy decode step before this one's tokens are read
     graph_batch_sizes: Sequence[int] = (1, 2, 4, 8, 16, 32, 64)   # reference: engine.h:72
 
@@ -392,6 +393,7 @@ class Engine:
         params = [it.request.sampling for it in sampling_items]
         counters = [len(it.request.generated_tokens) for it in sampling_items]
         tokens = None
+        code = 0
         if (self.graphs is not None and len(sampling_items) == len(batch.items)
                 and all(it.num_tokens == 1 for it in batch.items)
                 and self.graphs.supports(len(entries))):
@@ -403,16 +405,27 @@ class Engine:
                                            reqs, [False] * len(entries))
                 return outputs + self._finish_inflight()
             logits, tokens = self.graphs.run(entries, want_tokens=True, sampling=lanes)
-        else:
-            logits = self.runner.step(entries)
-        # the status word is copied behind the step; reading the tokens (below) waits past it
-        status = self.runner.queue_status_read()
-        if tokens is None:
-            tokens = self.sampler.sample(logits, params, counters)
-        if sampling_items or self._status_due():
+            status = self.runner.queue_status_read()
             code = status.code()
-            if code:
-                return outputs + self._device_error(code, [it.request for it in batch.items])
+        else:
+            plan = self.graphs.shape_ready(entries) \
+                if self.graphs is not None and self.options.capture_repeating_steps else None
+            if plan is not None:
+                # a shape that came before: one replay instead of some hundred launches
+                lanes = None if all(p.temperature <= 0 for p in params) else \
+                    [(p.temperature, p.seed, c) for p, c in zip(params, counters)]
+                tokens, code = self.graphs.run_shape(plan, entries, lanes)
+                tokens = tokens or []
+                self.stats["graph_steps"] += 1
+            else:
+                logits = self.runner.step(entries)
+                # the status word is copied behind the step; reading the tokens (below) waits past it
+                status = self.runner.queue_status_read()
+                tokens = self.sampler.sample(logits, params, counters)
+                if sampling_items or self._status_due():
+                    code = status.code()
+        if code:
+            return outputs + self._device_error(code, [it.request for it in batch.items])
         self.stats["steps"] += 1
         self.stats["tokens"] += batch.num_tokens
         for it, tok in zip(sampling_items, tokens):

@@ -31,7 +31,9 @@ from typing import Dict, List, Optional, Sequence, Tuple
 import numpy as np
 import torch
 
-from ..cache.manager import SCRATCH_PAGE
+from collections import OrderedDict
+
+from ..cache.manager import SCRATCH_PAGE, OutOfPages
 from ..ops import kernels as K
 from .context import Workspace
 from .runner import MetaLayout, ModelRunner, StepEntry
@@ -40,7 +42,7 @@ from .runner import MetaLayout, ModelRunner, StepEntry
 class _Bucket:
     __slots__ = ("size", "layout", "meta_host", "meta_stage", "meta_dev", "graph", "logits", "tokens", "h_tokens",
                  "events", "launches", "lanes", "turn", "by_length", "samp_stage", "samp_dev", "samp_greedy", "h_status",
-                 "changes", "full_upload")
+                 "changes", "full_upload", "q_lens", "rows", "starts", "stage_events")
 
 
 class LaunchedStep:
@@ -60,6 +62,12 @@ class DecodeGraphs:
         self.kernel_launches = 0
         self.h2d_bytes = 0            # metadata bytes uploaded by all replays so far
         self.full_uploads = 0
+        # steps of other shapes (prompt portions, alone or beside decode tokens) whose shape came again
+        self.shapes: "OrderedDict[tuple, _Bucket]" = OrderedDict()
+        self.shape_seen: Dict[tuple, int] = {}
+        self.shape_workspace = Workspace(runner.device)
+        self.shape_replays = 0
+        self.shape_captures = 0
 
     def supports(self, n: int) -> bool:
         return bool(self.sizes) and n <= self.sizes[-1]
@@ -302,6 +310,204 @@ class DecodeGraphs:
             self.runner.cache.advance(e.cache, 1)
         self.runner.steps_run += 1
         return step
+
+    # ------------------------------------------------------------------------------------------
+    # Steps of any shape.  The launches of a step depend on its shape alone: how many tokens each
+    # sequence brings (one-token sequences first) and which rows' logits are wanted.  While a long
+    # prompt comes in in portions, or a set of requests decodes beside it, that shape repeats step
+    # after step; queueing its ~330 launches from the host costs about as long as the device needs for
+    # a 256-token step of the 8B shape and many times longer for small models.  So a shape that comes a
+    # second time is captured (over metadata of its own, like a decode bucket: the head is uploaded
+    # every step, block-table entries through the update list) and replayed from then on.
+    MAX_SHAPES = 24            # captured shapes kept (the least recently used one goes)
+    SHAPE_MAX_TOKENS = 1024    # longer steps are bound by the device, not by the host
+    CAPTURE_AT = 2             # a shape is captured when it is seen this many times
+
+    @staticmethod
+    def shape_of(entries: Sequence[StepEntry]):
+        """(order, key): the entries' order in the step (one-token sequences first, as the step function
+        sorts them) and the shape key (tokens per sequence, wanted rows among the step's tokens)."""
+        order = sorted(range(len(entries)), key=lambda i: 0 if len(entries[i].tokens) == 1 else 1)
+        q_lens = tuple(len(entries[i].tokens) for i in order)
+        start, starts = 0, {}
+        for i, ql in zip(order, q_lens):
+            starts[i] = start
+            start += ql
+        rows = tuple(starts[i] + w for i, e in enumerate(entries) for w in e.want)
+        return order, (q_lens, rows)
+
+    def shape_ready(self, entries: Sequence[StepEntry]):
+        """The plan of a step that should run from a graph: (order, key), or None if its shape has not
+        come often enough yet (it is counted), is too long, or the entries are not fit for it."""
+        if not entries or len(entries) > self.runner.cache.max_requests:
+            return None
+        order, key = self.shape_of(entries)
+        q_lens, rows = key
+        if sum(q_lens) > self.SHAPE_MAX_TOKENS or any(ql < 1 for ql in q_lens):
+            return None
+        if key not in self.shapes:
+            seen = self.shape_seen.get(key, 0) + 1
+            if len(self.shape_seen) > 4096:
+                self.shape_seen.clear()
+            self.shape_seen[key] = seen
+            if seen < self.CAPTURE_AT:
+                return None
+        return order, key
+
+    def _prepare_shape(self, key) -> _Bucket:
+        """Capture one forward (and the sampler) for steps of shape ``key``, over metadata in which every
+        sequence lies in the scratch page and the scratch state slot: the capture and the run before it
+        write no live page and no request's state."""
+        r = self.runner
+        q_lens, rows = key
+        n, T, nr = len(q_lens), sum(q_lens), len(rows)
+        b = _Bucket()
+        b.size, b.q_lens, b.rows = n, list(q_lens), list(rows)
+        b.layout = lay = MetaLayout(T, n, max(nr, 1), r.max_blocks, update_cap=max(64, 4 * n))
+        b.changes, b.full_upload = [], True
+        b.meta_host = torch.zeros(lay.size, dtype=torch.int32).pin_memory()
+        b.meta_stage = [torch.zeros(lay.size, dtype=torch.int32).pin_memory() for _ in range(2)]
+        b.stage_events = [None, None]
+        b.meta_dev = torch.zeros(lay.size, dtype=torch.int32, device=r.device)
+        b.tokens = torch.zeros(max(nr, 1), dtype=torch.int32, device=r.device)
+        b.samp_stage = [torch.zeros(5 * max(nr, 1), dtype=torch.int32).pin_memory() for _ in range(2)]
+        b.samp_dev = torch.zeros(5 * max(nr, 1), dtype=torch.int32, device=r.device)
+        b.samp_greedy = True
+        b.h_tokens = [torch.zeros(max(nr, 1), dtype=torch.int32).pin_memory() for _ in range(2)]
+        b.h_status = [torch.zeros(1, dtype=torch.int32).pin_memory() for _ in range(2)]
+        b.events = [torch.cuda.Event() for _ in range(2)]
+        b.turn, b.by_length = 0, None
+        b.lanes = [None] * n
+        h = b.meta_host.numpy()
+        b.starts = []
+        pos = 0
+        for i, ql in enumerate(q_lens):
+            b.starts.append(pos)
+            h[lay.positions + pos: lay.positions + pos + ql] = np.arange(ql)
+            h[lay.token_seq + pos: lay.token_seq + pos + ql] = i
+            h[lay.cu_q + i] = pos
+            pos += ql
+        h[lay.cu_q + n] = pos
+        h[lay.seq_fresh: lay.seq_fresh + n] = 1            # the scratch state slot starts from zero, like a new request's
+        h[lay.logits_rows: lay.logits_rows + nr] = rows
+        # every table entry names the scratch page: whatever position is looked up, the page exists
+        for off, w in zip(lay.tables, lay.widths):
+            h[off: off + n * w] = SCRATCH_PAGE
+        h[lay.updates] = 0
+        b.meta_dev.copy_(b.meta_host)
+        ctx = r.context_from_layout(lay, b.meta_dev, list(q_lens), [0] * n)
+        ctx.logits_rows = ctx.logits_rows[:nr]
+        ctx.workspace = self.shape_workspace
+        ctx.max_kv_len = r.max_model_len      # launch shapes must not depend on the requests
+        ctx.captured = True
+        ws_before = self.shape_workspace.version
+        side = torch.cuda.Stream(device=r.device)
+        side.wait_stream(torch.cuda.current_stream())
+        with torch.cuda.stream(side):
+            self._apply_updates(b)
+            logits = r.model.forward(ctx)     # sizes the scratch buffers; nothing may be allocated while capturing
+            if nr:
+                self._sample_rows(b, logits, nr)
+        torch.cuda.current_stream().wait_stream(side)
+        torch.cuda.synchronize(r.device)
+        if self.shape_workspace.version != ws_before and self.shapes:
+            self.shapes.clear()               # a scratch buffer moved: graphs that hold its old address are void
+        b.graph = torch.cuda.CUDAGraph()
+        before = K.LAUNCHES
+        with torch.cuda.graph(b.graph):
+            self._apply_updates(b)
+            b.logits = r.model.forward(ctx)
+            if nr:
+                self._sample_rows(b, b.logits, nr)
+        b.launches = K.LAUNCHES - before
+        self.shape_captures += 1
+        return b
+
+    def _sample_rows(self, b: _Bucket, logits: torch.Tensor, nr: int) -> None:
+        d = b.samp_dev
+        K.sample(logits, b.tokens[:nr], d[4 * nr:].view(torch.float32), d[:2 * nr].view(torch.int64),
+                 d[2 * nr: 4 * nr].view(torch.int64))
+
+    def _fill_shape(self, b: _Bucket, entries: Sequence[StepEntry]) -> None:
+        r, lay = self.runner, b.layout
+        h = b.meta_host.numpy()
+
+        def put(off, values):
+            h[off: off + len(values)] = values
+            b.changes.append((off, values))
+        for i, e in enumerate(entries):
+            rc, ql, at = e.cache, b.q_lens[i], b.starts[i]
+            cl = rc.num_tokens
+            toks = np.asarray(e.tokens, dtype=np.int64)
+            if toks.min() < 0 or toks.max() >= r.vocab_size:
+                raise ValueError(f"request {rc.request_id!r}: token id outside the vocabulary")
+            if cl + ql > r.max_model_len:
+                raise ValueError(f"request {rc.request_id!r} exceeds max_model_len")
+            h[lay.token_ids + at: lay.token_ids + at + ql] = toks
+            h[lay.positions + at: lay.positions + at + ql] = np.arange(cl, cl + ql)
+            h[lay.ctx_lens + i] = cl
+            h[lay.seq_fresh + i] = 1 if rc.fresh else 0
+            h[lay.state_slots + i] = rc.state_slot
+            old = b.lanes[i]
+            same = old is not None and old[0] == rc.serial
+            lens = []
+            for g, table in enumerate(rc.tables):
+                if len(table) < -(-(cl + ql) // r.cache.groups[g].block_size):
+                    raise OutOfPages(f"request {rc.request_id!r} lacks pages in group {g} for this step")
+                row = lay.tables[g] + i * lay.widths[g]
+                if same and old[2][g] == rc.first_live[g] and old[1][g] <= len(table):
+                    if old[1][g] < len(table):
+                        put(row + old[1][g], table[old[1][g]:])
+                else:
+                    put(row, list(table))
+                lens.append(len(table))
+            b.lanes[i] = (rc.serial, lens, list(rc.first_live))
+
+    def run_shape(self, plan, entries: Sequence[StepEntry], sampling=None):
+        """Run one step of a captured shape (capturing it first if need be).  ``sampling``: per wanted
+        row (temperature, seed, counter) or None for arg-max everywhere.  Returns (tokens sampled at the
+        wanted rows in the caller's order, device status), or (None, 0) without a wait when nothing is
+        wanted."""
+        order, key = plan
+        b = self.shapes.get(key)
+        if b is None:
+            if len(self.shapes) >= self.MAX_SHAPES:
+                self.shapes.popitem(last=False)
+            b = self.shapes[key] = self._prepare_shape(key)
+        self.shapes.move_to_end(key)
+        ordered = [entries[i] for i in order]
+        self._fill_shape(b, ordered)
+        nr = len(b.rows)
+        k = b.turn
+        b.turn ^= 1
+        if b.stage_events[k] is not None:
+            b.stage_events[k].synchronize()        # the upload that last read this pinned buffer has happened
+        else:
+            b.stage_events[k] = torch.cuda.Event()
+        if nr:
+            size_was, b.size = b.size, nr          # the sampling buffer has one lane per wanted row
+            self._upload_sampling(b, k, sampling)
+            b.size = size_was
+        stage = b.meta_stage[k]
+        upto = b.layout.head_size if self._write_updates(b) else b.layout.size
+        self.full_uploads += upto == b.layout.size
+        stage[:upto].copy_(b.meta_host[:upto])
+        b.meta_dev[:upto].copy_(stage[:upto], non_blocking=True)
+        b.stage_events[k].record()
+        self.h2d_bytes += 4 * upto
+        b.graph.replay()
+        self.shape_replays += 1
+        self.kernel_launches += b.launches
+        for e in ordered:
+            self.runner.cache.advance(e.cache, len(e.tokens))
+        self.runner.steps_run += 1
+        if not nr:
+            return None, 0
+        b.h_tokens[k][:nr].copy_(b.tokens[:nr], non_blocking=True)
+        b.h_status[k].copy_(self.runner.status, non_blocking=True)
+        b.events[k].record()
+        b.events[k].synchronize()
+        return b.h_tokens[k][:nr].tolist(), int(b.h_status[k][0])
 
     @staticmethod
     def collect(step: LaunchedStep) -> Optional[List[int]]:

@@ -465,14 +465,38 @@ def tc_attention_supported(dtype: torch.dtype, d: int, block_size: int, max_kv_l
 
 
 def attn_tc(q, q_stride, pages, table, cu_q, ctx_lens, n_seqs, total_tiles, out, nq, nkv, d, scale, window,
-            status, page_list: Optional[int] = None) -> None:
-    """tcgen05 flash attention over the paged cache (bfloat16); total_tiles counts row tiles of 128."""
+            status, page_list: Optional[int] = None, shares=None) -> None:
+    """tcgen05 flash attention over the paged cache (bfloat16); total_tiles counts row tiles of 128.
+    ``shares`` = (count, part_o, part_ml, first row, rows): every row tile's keys are shared out over
+    ``count`` blocks and a second kernel joins their partial results (for prompts so short that their
+    row tiles alone would leave most SMs idle); the scratch tensors are float32 with at least
+    (first row + rows) * nq * count * d and ... * 2 elements."""
     _need_cuda(pages, table, cu_q, ctx_lens, out, status)
     num_blocks, _, _, block_size, _ = pages.shape
+    count, part_o, part_ml, row0, rows = shares if shares is not None else (1, None, None, 0, 0)
+    if count > 1:
+        _need_cuda(part_o, part_ml)
+        need = (row0 + rows) * nq * count
+        assert part_o.dtype == part_ml.dtype == torch.float32 and part_o.numel() >= need * d and part_ml.numel() >= need * 2
     _check(_attn_tc_lib(d, page_list).ff_attn_tc(
         _p(q), c_int(q_stride), _p(pages), _p(table), c_int(table.shape[1]), _p(cu_q), _p(ctx_lens),
         c_int(n_seqs), c_int(total_tiles), _p(out), c_int(out.shape[1]), c_int(nq), c_int(nkv),
-        c_int(block_size), c_int(num_blocks), c_float(scale), c_int(window), _p(status), _stream()), "attn_tc")
+        c_int(block_size), c_int(num_blocks), c_float(scale), c_int(window), _p(status), c_int(count), _p(part_o),
+        _p(part_ml), c_int(row0), c_int(rows), _stream()), "attn_tc")
+    if count > 1:
+        global LAUNCHES
+        LAUNCHES += 1     # the kernel that joins the shares
+
+
+def attn_tc_shares(total_tiles: int, nkv: int, max_key_tiles: int) -> int:
+    """Over how many blocks a row tile's keys are shared out: 1 unless the row tiles alone would fill
+    less than three quarters of the places (two per SM) and each would walk at least eight tiles of
+    keys; then as many as fill the places once, each share at least four key tiles long, at most 8."""
+    places = 2 * sm_count()
+    units = total_tiles * nkv
+    if units * 4 >= places * 3 or max_key_tiles < 8:
+        return 1
+    return max(1, min(8, places // units, max_key_tiles // 4))
 
 
 def decode_splits(n_seqs: int, nkv: int, max_kv_len: int) -> int:
@@ -581,8 +605,16 @@ def paged_attention(q: torch.Tensor, q_stride: int, pages: torch.Tensor, table: 
         # portions of prompts: tiled kernel over the remaining sequences (token offsets in cu_q are absolute)
         if USE_TC_ATTENTION and tc_attention_supported(q.dtype, d, pages.shape[3], ctx.max_kv_len):
             tiles = sum(-(-(ql * G) // 128) for ql in ctx.q_lens[n_dec:])
+            shares = None
+            count = 1 if ctx.captured else attn_tc_shares(
+                tiles, nkv, max(-(-(c + ql) // 64) for c, ql in zip(ctx.ctx_lens_host[n_dec:], ctx.q_lens[n_dec:])))
+            if count > 1:
+                row0, rows = sum(ctx.q_lens[:n_dec]), sum(ctx.q_lens[n_dec:])
+                cells = (row0 + rows) * nq * count
+                shares = (count, ctx.workspace.get("attn.tc_part_o", (cells * d,), torch.float32),
+                          ctx.workspace.get("attn.tc_part_ml", (cells * 2,), torch.float32), row0, rows)
             attn_tc(q, q_stride, pages, table[n_dec:], ctx.cu_q[n_dec:], ctx.ctx_lens[n_dec:], n - n_dec, tiles,
-                    out, nq, nkv, d, scale, window, ctx.status)
+                    out, nq, nkv, d, scale, window, ctx.status, shares=shares)
         else:
             tiles = sum(-(-(ql * G) // 64) for ql in ctx.q_lens[n_dec:])
             attn_tiled(q, q_stride, pages, table[n_dec:], ctx.cu_q[n_dec:], ctx.ctx_lens[n_dec:], n - n_dec,

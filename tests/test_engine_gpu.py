@@ -78,6 +78,37 @@ def test_more_decoding_requests_than_the_largest_graph(models, dtype):
     llm.engine.cache.check()
 
 
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+def test_steps_whose_shape_repeats_run_from_graphs_with_the_same_tokens(models, dtype):
+    """Long prompts come in in portions of 16 while other requests decode: the same step shapes repeat
+    and are captured at their second coming.  Tokens (greedy and sampled) must not depend on it."""
+    path, cfg, w = models["B"]
+    rng = np.random.RandomState(21)
+    prompts = [list(map(int, rng.randint(0, cfg["vocab_size"], size=n))) for n in (150, 9, 131, 40, 200)]
+    from firefly_b200.sampling import SamplingParams
+    sp = [SamplingParams(temperature=0.0 if i % 2 == 0 else 0.8, seed=5 + i, max_tokens=10) for i in range(len(prompts))]
+    got = {}
+    for capture in (False, True):
+        llm = _llm(path, dtype=dtype, kv_block_size=8, num_kv_blocks=128, max_prefill_chunk_size=16,
+                   max_batch_size_limit=3, capture_repeating_steps=capture)
+        got[capture] = llm.generate(prompts, sampling=sp)
+        g = llm.engine.graphs
+        if capture:
+            assert g.shape_captures > 0 and g.shape_replays > g.shape_captures
+        else:
+            assert g.shape_captures == 0
+        llm.engine.cache.check()
+        assert not llm.engine.cache.live
+    if dtype == "float32":
+        assert got[True] == got[False]
+        for p, g, s in zip(prompts, got[True], sp):
+            if s.temperature == 0:
+                assert g == P.greedy_generate(cfg, w, p, 10)
+    else:
+        same = sum(a == b for a, b in zip(got[True], got[False]))
+        assert same >= len(prompts) - 1          # bfloat16: the same kernels and order, so all but a rare near-tie
+
+
 def test_long_decoding_and_first_tokens(models):
     path, cfg, w = models["A"]
     llm = _llm(path, dtype="float32", num_kv_blocks=16)

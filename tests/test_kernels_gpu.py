@@ -250,6 +250,38 @@ def test_attention_tcgen05(d, nq, nkv, block, window):
     assert float(err) < 2e-2, float(err)
 
 
+@pytest.mark.parametrize("d,nq,nkv,block", [(64, 8, 1, 16), (128, 8, 2, 16), (128, 4, 4, 32), (192, 5, 1, 8)])
+@pytest.mark.parametrize("window", [None, 200])
+@pytest.mark.parametrize("count", [2, 3, 8])
+def test_attention_tcgen05_keys_shared_out_over_blocks(d, nq, nkv, block, window, count):
+    """Every row tile's keys shared out over `count` blocks and joined by the second kernel: the same
+    result as one block per row tile.  Sequences with fewer key tiles than shares (empty shares), one
+    key, and a far key that stands out are among them; sequences in front of the compared ones shift
+    the rows' indices in the scratch memory."""
+    seqs = [(0, 1), (5, 17), (700, 300), (0, 1000), (63, 2), (1200, 130)]
+    c = _attention_case(d, nq, nkv, block, seqs, window, torch.bfloat16, seed=11)
+    G = nq // nkv
+    T = sum(c["q_lens"])
+    first = 2                                  # the first two sequences are left to another launch
+    row0 = sum(c["q_lens"][:first])
+    out = torch.zeros(c["q"].shape, dtype=torch.bfloat16, device="cuda")
+    status = torch.zeros(1, dtype=torch.int32, device="cuda")
+    tiles = sum(-(-(ql * G) // 128) for ql in c["q_lens"][first:])
+    cells = T * nq * count
+    part_o = torch.full((cells * d,), float("nan"), device="cuda")
+    part_ml = torch.full((cells * 2,), float("nan"), device="cuda")
+    K().attn_tc(dev(c["q"]), nq * d, dev(c["pages"]), dev(c["table"][first:]), dev(c["cu_q"][first:]),
+                dev(c["ctx_lens"][first:]), len(seqs) - first, tiles, out, nq, nkv, d, 1 / math.sqrt(d), window or 0,
+                status, shares=(count, part_o, part_ml, row0, T - row0))
+    torch.cuda.synchronize()
+    assert int(status) == 0
+    got, want = out.cpu().double()[row0:], c["want"][row0:]
+    assert float((got - want).abs().max() / want.abs().max()) < 2e-2
+    assert bool((out[:row0] == 0).all())       # rows of the sequences left out are not touched
+    from firefly_b200.ops.kernels import attn_tc_shares
+    assert attn_tc_shares(64, 8, 32) == 1 and attn_tc_shares(8, 8, 36) >= 2 and attn_tc_shares(8, 8, 5) == 1
+
+
 @pytest.mark.parametrize("d,nq,nkv,block,page_list", [(64, 4, 1, 16, 16), (128, 8, 2, 8, 16), (128, 4, 4, 64, 16),
                                                       (64, 6, 2, 32, 32)])
 @pytest.mark.parametrize("window", [None, 150])
