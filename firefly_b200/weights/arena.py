@@ -189,7 +189,8 @@ class MappedFile:
             raise OSError(err.value, f"cannot map '{path}': {os.strerror(err.value)}")
         self.address = addr.value or 0
         self.size = size.value
-        self.pinned = bool(pinned.value)
+        self.pinned = pinned.value == 1
+        self.refusal = -pinned.value if pinned.value < 0 else 0     # the driver's error code when it would not pin
 
     def close(self) -> None:
         if self._handle:
