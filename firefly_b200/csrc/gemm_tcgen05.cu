@@ -25,24 +25,12 @@
 // Every wait on an mbarrier is bounded: after about a second the kernel records an
 // error code, stops issuing work, lets its copies land, frees its tensor memory
 // and returns.
-#include "common.cuh"
-
-#include <cuda.h>
-#include <cudaTypedefs.h>
-
-#include <mutex>
-#include <unordered_map>
+#include "tcgen05.cuh"
 
 namespace ff {
 
 constexpr int BN = 128;          // weight rows per tile (MMA M)
-constexpr int BK = 64;           // k per stage: 128 bytes of bfloat16, one swizzle span
-constexpr int UMMA_K = 16;
 constexpr int GEMM_THREADS = 192;
-#ifndef FF_GEMM_WAIT_LIMIT_CYCLES
-#define FF_GEMM_WAIT_LIMIT_CYCLES 2000000000ull                    // about a second
-#endif
-constexpr unsigned long long WAIT_LIMIT_CYCLES = FF_GEMM_WAIT_LIMIT_CYCLES;
 // Test builds only (-DFF_GEMM_TEST_DROP_KBLOCK=i): the loads of a block's i-th k block are never
 // issued, so the wait for that stage runs out; the test checks that the kernel gives up cleanly.
 #ifdef FF_GEMM_TEST_DROP_KBLOCK
@@ -70,89 +58,6 @@ template <int TOK> struct TileCfg {
     }
 };
 
-// ---------------------------------------------------------------- PTX helpers --
-__device__ __forceinline__ uint32_t smem_addr(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }
-
-__device__ __forceinline__ void mbar_init(uint32_t bar, uint32_t count) {
-    asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(bar), "r"(count));
-}
-// The producer and MMA warps run their loops with all lanes, so that addresses and descriptors are
-// warp-uniform values (kept in uniform registers); `issue` is true in the one lane that acts.
-__device__ __forceinline__ void mbar_expect_tx(bool issue, uint32_t bar, uint32_t bytes) {
-    asm volatile("{\n\t.reg .pred q;\n\tsetp.ne.b32 q, %2, 0;\n\t"
-                 "@q mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;\n\t}"
-                 ::"r"(bar), "r"(bytes), "r"((uint32_t)issue) : "memory");
-}
-__device__ __forceinline__ bool mbar_try_wait(uint32_t bar, uint32_t parity) {
-    uint32_t ok;
-    asm volatile("{\n\t.reg .pred P1;\n\tmbarrier.try_wait.parity.shared::cta.b64 P1, [%1], %2;\n\t"
-                 "selp.b32 %0, 1, 0, P1;\n\t}" : "=r"(ok) : "r"(bar), "r"(parity) : "memory");
-    return ok != 0;
-}
-// Bounded wait.  false: gave up (code recorded in *status, *abort set).
-__device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, int* status, volatile int* abort_flag,
-                                          int code) {
-    const unsigned long long start = clock64();
-    uint32_t spins = 0;
-    while (!mbar_try_wait(bar, parity)) {
-        __nanosleep(20);                     // waiting warps should not burn issue slots and power
-        if (((++spins) & 1023u) == 0) {
-            if (*abort_flag) return false;
-            if (clock64() - start > WAIT_LIMIT_CYCLES) {
-                atomicExch(status, code);
-                *abort_flag = 1;
-                return false;
-            }
-        }
-    }
-    return true;
-}
-__device__ __forceinline__ void tma_load_2d(bool issue, uint32_t dst, const CUtensorMap* map, int x, int y, uint32_t bar) {
-    asm volatile("{\n\t.reg .pred q;\n\tsetp.ne.b32 q, %5, 0;\n\t"
-                 "@q cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4}], [%2];\n\t}"
-                 ::"r"(dst), "l"(map), "r"(bar), "r"(x), "r"(y), "r"((uint32_t)issue) : "memory");
-}
-__device__ __forceinline__ void tc_fence_before() { asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory"); }
-__device__ __forceinline__ void tc_fence_after() { asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory"); }
-__device__ __forceinline__ void tc_commit(bool issue, uint32_t bar) {
-    asm volatile("{\n\t.reg .pred q;\n\tsetp.ne.b32 q, %1, 0;\n\t"
-                 "@q tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];\n\t}"
-                 ::"r"(bar), "r"((uint32_t)issue) : "memory");
-}
-__device__ __forceinline__ void tc_mma_bf16(bool issue, uint32_t tmem_d, uint64_t desc_a, uint64_t desc_b, uint32_t idesc,
-                                            uint32_t accumulate) {
-    asm volatile("{\n\t.reg .pred p, q;\n\tsetp.ne.b32 p, %4, 0;\n\tsetp.ne.b32 q, %5, 0;\n\t"
-                 "@q tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n\t}"
-                 ::"r"(tmem_d), "l"(desc_a), "l"(desc_b), "r"(idesc), "r"(accumulate), "r"((uint32_t)issue) : "memory");
-}
-// 16 consecutive accumulator columns of this warp's 32 lanes
-__device__ __forceinline__ void tc_ld16(uint32_t taddr, float (&v)[16]) {
-    uint32_t r[16];
-    asm volatile("tcgen05.ld.sync.aligned.32x32b.x16.b32 {%0,%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15}, [%16];"
-                 : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]),
-                   "=r"(r[8]), "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15])
-                 : "r"(taddr));
-    asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
-#pragma unroll
-    for (int i = 0; i < 16; ++i) v[i] = __uint_as_float(r[i]);
-}
-
-// Programmatic dependent launch: let the next kernel in the stream begin its prologue, and wait
-// for the previous kernel's results.  Both do nothing in a launch without the attribute.
-__device__ __forceinline__ void grid_launch_dependents() { asm volatile("griddepcontrol.launch_dependents;" ::: "memory"); }
-__device__ __forceinline__ void grid_dependency_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
-
-// Shared-memory operand descriptor: K-major tile, rows of 128 bytes, 128-byte swizzle;
-// groups of 8 rows are 1024 bytes apart.
-__device__ __forceinline__ uint64_t smem_desc_sw128(uint32_t addr) {
-    uint64_t d = 0;
-    d |= (uint64_t)((addr & 0x3FFFFu) >> 4);          // start address
-    d |= (uint64_t)1 << 16;                            // leading byte offset (unused for swizzled K-major): 1
-    d |= (uint64_t)(1024 >> 4) << 32;                  // stride byte offset between 8-row groups
-    d |= (uint64_t)1 << 46;                            // descriptor version of this architecture
-    d |= (uint64_t)2 << 61;                            // 128-byte swizzle
-    return d;
-}
 // Instruction descriptor: bfloat16 x bfloat16 -> float32, both operands K-major, M = 128, N = TOK
 __device__ __forceinline__ uint32_t instr_desc(int tok) {
     return (1u << 4) | (1u << 7) | (1u << 10) | ((uint32_t)(tok >> 3) << 17) | ((uint32_t)(BN >> 4) << 24);
@@ -476,58 +381,6 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant_
         tc_fence_after();
         asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"((uint32_t)Cfg::TMEM_COLS) : "memory");
     }
-}
-
-// ------------------------------------------------------------------ host side --
-typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
-                                  const cuuint64_t*, const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave,
-                                  CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
-
-static EncodeTiledFn encode_fn() {
-    static EncodeTiledFn fn = nullptr;
-    static std::once_flag once;
-    std::call_once(once, [] {
-        void* p = nullptr;
-        cudaDriverEntryPointQueryResult q;
-        if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &p, cudaEnableDefault, &q) == cudaSuccess &&
-            q == cudaDriverEntryPointSuccess)
-            fn = reinterpret_cast<EncodeTiledFn>(p);
-    });
-    return fn;
-}
-
-struct MapKey {
-    const void* ptr; int rows, cols, box_rows;
-    bool operator==(const MapKey& o) const { return ptr == o.ptr && rows == o.rows && cols == o.cols && box_rows == o.box_rows; }
-};
-struct MapKeyHash {
-    size_t operator()(const MapKey& k) const {
-        return std::hash<const void*>()(k.ptr) ^ ((size_t)k.rows * 1000003u) ^ ((size_t)k.cols * 7919u) ^ (size_t)k.box_rows;
-    }
-};
-
-// Tensor map of a row-major bfloat16 matrix [rows, cols]: boxes of box_rows x 64, 128-byte swizzle,
-// zeros outside the matrix.
-static int make_map(const void* ptr, int rows, int cols, int box_rows, CUtensorMap* out) {
-    static std::mutex mu;
-    static std::unordered_map<MapKey, CUtensorMap, MapKeyHash> cache;
-    std::lock_guard<std::mutex> lock(mu);
-    const MapKey key{ptr, rows, cols, box_rows};
-    auto it = cache.find(key);
-    if (it != cache.end()) { *out = it->second; return 0; }
-    EncodeTiledFn fn = encode_fn();
-    if (!fn) return FF_ERR_UNSUPPORTED;
-    cuuint64_t dims[2] = {(cuuint64_t)cols, (cuuint64_t)rows};
-    cuuint64_t strides[1] = {(cuuint64_t)cols * 2};
-    cuuint32_t box[2] = {(cuuint32_t)BK, (cuuint32_t)box_rows};
-    cuuint32_t estr[2] = {1, 1};
-    CUresult r = fn(out, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, const_cast<void*>(ptr), dims, strides, box, estr,
-                    CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
-                    CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
-    if (r != CUDA_SUCCESS) return FF_ERR_BAD_ARG;
-    if (cache.size() > 8192) cache.clear();
-    cache.emplace(key, *out);
-    return 0;
 }
 
 template <int TOK>

@@ -76,6 +76,7 @@ _MODULES = {
     "attention_simt": ("attention_simt.cu", None),
     "sampling": ("sampling.cu", None),
     "gemm_tcgen05": ("gemm_tcgen05.cu", None),
+    "gemm_pair": ("gemm_pair.cu", None),
     "weights": ("weights.cu", None),
 }
 
@@ -333,6 +334,47 @@ def gemm_tc(x: torch.Tensor, weight: torch.Tensor, out: torch.Tensor, epilogue: 
         _p(x), _p(weight), _p(out), c_int(out.stride(0)), c_int(T), c_int(N), c_int(Kd), c_int(epilogue),
         c_int(want_splits), c_int(1 if USE_PDL else 0), _p(xw), _p(xw_w), _p(ssq_out), _p(ssq_in),
         c_int(parts), c_int(dim), c_float(eps), _p(status), _stream()), "gemm_tc")
+
+
+def gemm_pair_plan(T: int, N: int, K: int, want_ranges: int):
+    """(tokens per tile, K ranges) the two-SM product would use."""
+    tok, ranges = c_int(), c_int()
+    _lib("gemm_pair").ff_gemm_pair_plan(c_int(T), c_int(N), c_int(K), c_int(want_ranges), ctypes.byref(tok),
+                                        ctypes.byref(ranges))
+    return tok.value, ranges.value
+
+
+def gemm_pair(x: torch.Tensor, weight: torch.Tensor, out: torch.Tensor, epilogue: int, want_ranges: int,
+              status: torch.Tensor, *, norm_out: Optional[tuple] = None, norm_in: Optional[tuple] = None) -> None:
+    """out (op)= x @ weight^T on pairs of SMs (tcgen05 with cta_group::2), for steps of about a hundred to
+    a few hundred tokens.  Arguments as `gemm_tc`; ``want_ranges`` K ranges (at most 4)."""
+    _need_cuda(x, weight, status)
+    if not out.is_cuda or out.dim() != 2 or out.stride(1) != 1:
+        raise KernelError("gemm_pair: the output must be a CUDA matrix with contiguous rows")
+    assert x.dtype == torch.bfloat16 and weight.dtype == torch.bfloat16
+    T, Kd = x.shape
+    N = weight.shape[0]
+    assert weight.shape[1] == Kd
+    assert out.dtype == (torch.bfloat16 if epilogue in (EPI_BF16, EPI_SWIGLU) else torch.float32)
+    assert out.shape[0] == T and out.shape[1] == (N // 2 if epilogue == EPI_SWIGLU else N)
+    xw = xw_w = ssq_out = ssq_in = None
+    parts = dim = 0
+    eps = 0.0
+    if norm_out is not None:
+        xw, xw_w, ssq_out = norm_out
+        _need_cuda(xw, xw_w, ssq_out)
+        assert epilogue == EPI_RESIDUAL_ADD and xw.dtype == torch.bfloat16 and xw.shape == (T, N)
+        assert xw_w.dtype == torch.float32 and xw_w.numel() == N
+        assert ssq_out.dtype == torch.float32 and ssq_out.numel() >= -(-N // 128) * T
+    if norm_in is not None:
+        ssq_in, dim, eps = norm_in
+        _need_cuda(ssq_in)
+        assert ssq_in.dtype == torch.float32 and ssq_in.dim() == 2 and ssq_in.shape[1] == T
+        parts = ssq_in.shape[0]
+    _check(_lib("gemm_pair").ff_gemm_pair(
+        _p(x), _p(weight), _p(out), c_int(out.stride(0)), c_int(T), c_int(N), c_int(Kd), c_int(epilogue),
+        c_int(want_ranges), c_int(1 if USE_PDL else 0), _p(xw), _p(xw_w), _p(ssq_out), _p(ssq_in),
+        c_int(parts), c_int(dim), c_float(eps), _p(status), _stream()), "gemm_pair")
 
 
 def interleave_gate_up(gate: torch.Tensor, up: torch.Tensor) -> torch.Tensor:
