@@ -33,11 +33,17 @@ template <int NTOK> struct PairCfg {
     static constexpr int A_BYTES = PM * BK * 2;                 // 16 KB
     static constexpr int B_BYTES = (NTOK / 2) * BK * 2;         // this block's half of the tokens
     static constexpr int STAGE_BYTES = A_BYTES + B_BYTES;
-    static constexpr int STAGES = (int)((200 * 1024) / STAGE_BYTES) > 8 ? 8 : (int)((200 * 1024) / STAGE_BYTES);
+    // pipeline depth: nearly all of an SM's shared memory (DEEP: one block per SM, what every launch
+    // uses) or half of it (SHALLOW: two blocks per SM, which made a product with between one and two
+    // blocks per SM 10 % faster when it ran alone, but two pairs on one pair of SMs both allocate tensor
+    // memory across the two SMs, and inside the model's step, where blocks arrive one by one behind the
+    // kernel in front, such launches now and then never came back: not used)
+    static constexpr int DEEP = (int)((200 * 1024) / STAGE_BYTES) > 8 ? 8 : (int)((200 * 1024) / STAGE_BYTES);
+    static constexpr int SHALLOW = (int)((100 * 1024) / STAGE_BYTES);
     static constexpr int TMEM_COLS = NTOK < 32 ? 32 : NTOK;
-    // the partial tile of a K range (float [NTOK][PM]) reuses the stages' memory
-    static_assert((size_t)STAGES * STAGE_BYTES >= (size_t)NTOK * PM * 4, "a partial tile fits the pipeline's memory");
-    static constexpr size_t SMEM = (size_t)STAGES * STAGE_BYTES + 1024 + 256;
+    // the partial tile of a K range (float [NTOK][PM]) and the epilogue's staging buffer reuse the stages' memory
+    static constexpr bool can_split(int stages) { return (size_t)stages * STAGE_BYTES >= (size_t)NTOK * PM * 4 + 32 * PM * 4; }
+    static constexpr size_t smem(int stages) { return (size_t)stages * STAGE_BYTES + 1024 + 256; }
 };
 
 __device__ __forceinline__ uint32_t cluster_ctarank() {
@@ -78,6 +84,7 @@ struct PairArgs {
     int epilogue;
     int ranges;           // K ranges = pairs per cluster (cluster = 2 * ranges blocks)
     int kb_per_range;
+    int stages;           // depth of the load pipeline
     int* status;
     bf16* xw_out;         // norm folded in, producing side (see gemm_tcgen05.cu)
     const float* xw_w;
@@ -94,7 +101,7 @@ template <int NTOK>
 __global__ void __launch_bounds__(PAIR_THREADS)
 gemm_pair_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant__ CUtensorMap map_x, const PairArgs a) {
     using Cfg = PairCfg<NTOK>;
-    constexpr int STAGES = Cfg::STAGES;
+    const int STAGES = a.stages;
     extern __shared__ unsigned char smem_raw[];
     unsigned char* tiles = reinterpret_cast<unsigned char*>(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
     uint64_t* bars = reinterpret_cast<uint64_t*>(tiles + (size_t)STAGES * Cfg::STAGE_BYTES);
@@ -102,7 +109,6 @@ gemm_pair_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constan
     __shared__ uint32_t s_tmem_base;
     __shared__ int s_abort;
     __shared__ float s_inv[NTOK];
-    __shared__ float s_red[4][16];
 
     const int warp = __shfl_sync(0xffffffffu, (int)(threadIdx.x >> 5), 0), lane = threadIdx.x & 31;
     const bool issue = lane == 0;
@@ -118,6 +124,10 @@ gemm_pair_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constan
     const int kb0 = range * a.kb_per_range;
     const int kb1 = min(num_kb, kb0 + a.kb_per_range);
     const int n_iters = max(0, kb1 - kb0);
+    // Every row tile walks its K range from another starting point (and wraps around): all tiles read the
+    // same token tile, and in step they would all ask the same few L2 lines of it at the same moment.
+    const int rot = n_iters > 0 ? (int)((blockIdx.y * 11u + blockIdx.z * 5u) % (unsigned)n_iters) : 0;
+    auto kb_of = [&](int it) { const int k = it + rot; return kb0 + (k >= n_iters ? k - n_iters : k); };
 
     if (threadIdx.x == 0) {
         s_abort = 0;
@@ -146,11 +156,11 @@ gemm_pair_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constan
         for (int it = 0; it < pre; ++it) {
             const uint32_t full = smem_addr(&bars[it]);
             if (leader) mbar_expect_tx(issue, full, 2 * Cfg::STAGE_BYTES);          // both blocks' bytes
-            tma_load_2d_pair(issue, smem_addr(tiles + (size_t)it * Cfg::STAGE_BYTES), &map_w, (kb0 + it) * BK, n0, full);
+            tma_load_2d_pair(issue, smem_addr(tiles + (size_t)it * Cfg::STAGE_BYTES), &map_w, kb_of(it) * BK, n0, full);
         }
         grid_dependency_wait();
         for (int it = 0; it < pre; ++it) {
-            tma_load_2d_pair(issue, smem_addr(tiles + (size_t)it * Cfg::STAGE_BYTES + Cfg::A_BYTES), &map_x, (kb0 + it) * BK, tb,
+            tma_load_2d_pair(issue, smem_addr(tiles + (size_t)it * Cfg::STAGE_BYTES + Cfg::A_BYTES), &map_x, kb_of(it) * BK, tb,
                              smem_addr(&bars[it]));
             issued = it + 1;
         }
@@ -161,8 +171,8 @@ gemm_pair_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constan
             const uint32_t full = smem_addr(&bars[s]);
             if (leader) mbar_expect_tx(issue, full, 2 * Cfg::STAGE_BYTES);
             unsigned char* st = tiles + (size_t)s * Cfg::STAGE_BYTES;
-            tma_load_2d_pair(issue, smem_addr(st), &map_w, (kb0 + it) * BK, n0, full);
-            tma_load_2d_pair(issue, smem_addr(st + Cfg::A_BYTES), &map_x, (kb0 + it) * BK, tb, full);
+            tma_load_2d_pair(issue, smem_addr(st), &map_w, kb_of(it) * BK, n0, full);
+            tma_load_2d_pair(issue, smem_addr(st + Cfg::A_BYTES), &map_x, kb_of(it) * BK, tb, full);
             issued = it + 1;
         }
         (void)issued;
@@ -257,90 +267,163 @@ gemm_pair_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constan
             c_end = min(NTOK, c_begin + per);
         }
         const uint32_t mine_addr = smem_addr(tiles);
+        // The accumulator has a weight row per thread and a token per register, the output a token per row
+        // of memory: written from the registers, a warp's store would be 32 two-byte pieces 64 bytes apart
+        // in time (at 256 tokens that alone took as long as the whole main loop).  So the tile passes
+        // through shared memory 32 tokens at a time, float [32][SROW], and leaves it with a thread writing
+        // 32 consecutive rows of one token: whole 16-byte vectors, four threads to a token's 128 rows.
+        constexpr int CH = 32, SROW = PM;                  // rows swizzled by the token: see below
+        float* stage = reinterpret_cast<float*>(tiles + (a.ranges > 1 ? (size_t)NTOK * PM * 4 : 0));
+        const int et = threadIdx.x - 64;                   // 0..127
+        const int o_tok = et >> 2, o_rg = et & 3;          // this thread's token of the chunk and group of 32 rows on the way out
+        const int o_n = n0 + o_rg * 32;
+        (void)res_pre; (void)wn_pre; (void)n;
 #pragma unroll 1
-        for (int c0 = c_begin; c0 < c_end; c0 += 16) {
-            float v[16];
-            const int cn = min(16, c_end - c0);
-            if (a.ranges == 1) {
-                if (n_iters > 0 && ok) tc_ld16(tmem_base + ((uint32_t)(quad * 32) << 16) + c0, v);
-                else {
+        for (int c0 = c_begin; c0 < c_end; c0 += CH) {
+            // ---- in: this thread's row, 32 tokens ----
+#pragma unroll
+            for (int h = 0; h < 2; ++h) {
+                const int cc = c0 + h * 16;
+                float v[16];
+                const int cn = max(0, min(16, c_end - cc));
+                if (a.ranges == 1) {
+                    if (n_iters > 0 && ok && cn > 0) tc_ld16(tmem_base + ((uint32_t)(quad * 32) << 16) + cc, v);
+                    else {
+#pragma unroll
+                        for (int i = 0; i < 16; ++i) v[i] = 0.f;
+                    }
+                } else {
 #pragma unroll
                     for (int i = 0; i < 16; ++i) v[i] = 0.f;
-                }
-            } else {
+                    // the same half of every pair of the cluster, in the order of the K ranges
+                    for (int z = 0; z < a.ranges; z += 2) {
+                        float p0[16], p1[16];
+                        const bool two = z + 1 < a.ranges;
 #pragma unroll
-                for (int i = 0; i < 16; ++i) v[i] = 0.f;
-                // the same half of every pair of the cluster, in the order of the K ranges
-                for (int z = 0; z < a.ranges; z += 2) {
-                    float p0[16], p1[16];
-                    const bool two = z + 1 < a.ranges;
+                        for (int i = 0; i < 16; ++i) {
+                            const uint32_t addr = mine_addr + (uint32_t)((cc + i) * PM + row) * 4u;
+                            p0[i] = i < cn ? ld_peer_smem(addr, (uint32_t)(2 * z + half)) : 0.f;
+                            p1[i] = (two && i < cn) ? ld_peer_smem(addr, (uint32_t)(2 * (z + 1) + half)) : 0.f;
+                        }
 #pragma unroll
-                    for (int i = 0; i < 16; ++i) {
-                        const uint32_t addr = mine_addr + (uint32_t)((c0 + i) * PM + row) * 4u;
-                        p0[i] = i < cn ? ld_peer_smem(addr, (uint32_t)(2 * z + half)) : 0.f;
-                        p1[i] = (two && i < cn) ? ld_peer_smem(addr, (uint32_t)(2 * (z + 1) + half)) : 0.f;
-                    }
-#pragma unroll
-                    for (int i = 0; i < 16; ++i) {
-                        v[i] += p0[i];
-                        if (two) v[i] += p1[i];
+                        for (int i = 0; i < 16; ++i) {
+                            v[i] += p0[i];
+                            if (two) v[i] += p1[i];
+                        }
                     }
                 }
-            }
-            if (!ok) continue;
-            if (a.ssq_in) {
+                if (a.ssq_in) {
 #pragma unroll
-                for (int i = 0; i < 16; ++i) v[i] *= s_inv[min(c0 + i, NTOK - 1)];
-            }
-            if (a.epilogue == P_SWIGLU) {
+                    for (int i = 0; i < 16; ++i) v[i] *= s_inv[min(cc + i, NTOK - 1)];
+                }
 #pragma unroll
-                for (int i = 0; i < 16; ++i) {
-                    const float other = __shfl_xor_sync(0xffffffffu, v[i], 16);
-                    const int t = t0 + c0 + i;
-                    const int col = (n0 + quad * 32) / 2 + lane;
-                    if (i < cn && lane < 16 && t < a.T && col < a.N / 2) {
-                        const float g = v[i];
-                        reinterpret_cast<bf16*>(a.out)[(size_t)t * a.ldo + col] =
-                            __float2bfloat16_rn(g / (1.0f + expf(-g)) * other);
+                for (int i = 0; i < 16; ++i) stage[(h * 16 + i) * SROW + (row ^ (((h * 16 + i) & 7) << 2))] = v[i];
+            }
+            asm volatile("bar.sync 1, 128;" ::: "memory");
+            // ---- out: one token, 32 consecutive rows ----
+            const int c = c0 + o_tok, t = t0 + c;
+            if (ok && c < c_end && t < a.T) {
+                float r[32];
+#pragma unroll
+                for (int j = 0; j < 8; ++j) {
+                    // groups of four rows sit at (group ^ token % 8): a warp's 32 reads of 16 bytes then spread
+                    // evenly over the banks, and so did the writes above
+                    const float4 q = *reinterpret_cast<const float4*>(stage + o_tok * SROW + ((o_rg * 32 + j * 4) ^ ((o_tok & 7) << 2)));
+                    r[j * 4] = q.x; r[j * 4 + 1] = q.y; r[j * 4 + 2] = q.z; r[j * 4 + 3] = q.w;
+                }
+#ifdef FF_PAIR_NO_STORE
+                if (r[0] == 123.456f)
+#endif
+                if (a.epilogue == P_SWIGLU) {
+                    // the 32 rows are 16 gate rows and the 16 up rows of the same columns
+                    const int col = o_n / 2;
+                    if (col < a.N / 2) {
+                        uint32_t w[8];
+#pragma unroll
+                        for (int i = 0; i < 8; ++i) {
+                            const float g0 = r[2 * i], g1 = r[2 * i + 1];
+                            __nv_bfloat162 pk = __floats2bfloat162_rn(g0 / (1.0f + expf(-g0)) * r[16 + 2 * i],
+                                                                      g1 / (1.0f + expf(-g1)) * r[17 + 2 * i]);
+                            w[i] = *reinterpret_cast<uint32_t*>(&pk);
+                        }
+                        bf16* dst = reinterpret_cast<bf16*>(a.out) + (size_t)t * a.ldo + col;
+                        if (col + 16 <= a.N / 2 && (((uintptr_t)dst) & 15) == 0) {
+                            reinterpret_cast<uint4*>(dst)[0] = make_uint4(w[0], w[1], w[2], w[3]);
+                            reinterpret_cast<uint4*>(dst)[1] = make_uint4(w[4], w[5], w[6], w[7]);
+                        } else {
+#pragma unroll
+                            for (int i = 0; i < 16; ++i)
+                                if (col + i < a.N / 2) dst[i] = __ushort_as_bfloat16((unsigned short)(w[i >> 1] >> ((i & 1) * 16)));
+                        }
+                    }
+                } else if (a.epilogue == P_BF16) {
+                    bf16* dst = reinterpret_cast<bf16*>(a.out) + (size_t)t * a.ldo + o_n;
+                    if (o_n + 32 <= a.N && (((uintptr_t)dst) & 15) == 0) {
+#pragma unroll
+                        for (int j = 0; j < 4; ++j) {
+                            uint32_t w[4];
+#pragma unroll
+                            for (int i = 0; i < 4; ++i) {
+                                __nv_bfloat162 pk = __floats2bfloat162_rn(r[j * 8 + 2 * i], r[j * 8 + 2 * i + 1]);
+                                w[i] = *reinterpret_cast<uint32_t*>(&pk);
+                            }
+                            reinterpret_cast<uint4*>(dst)[j] = make_uint4(w[0], w[1], w[2], w[3]);
+                        }
+                    } else {
+#pragma unroll
+                        for (int i = 0; i < 32; ++i)
+                            if (o_n + i < a.N) dst[i] = __float2bfloat16_rn(r[i]);
+                    }
+                } else {
+                    // float32 out: store, or add into the residual (and prepare the norm that follows)
+                    float* dst = reinterpret_cast<float*>(a.out) + (size_t)t * a.ldo + o_n;
+                    const bool whole = o_n + 32 <= a.N && (((uintptr_t)dst) & 15) == 0;
+                    float sq = 0.f;
+                    if (a.epilogue == P_RESIDUAL_ADD) {
+                        if (whole) {
+#pragma unroll
+                            for (int j = 0; j < 8; ++j) {
+                                const float4 q = __ldcg(reinterpret_cast<const float4*>(dst) + j);
+                                r[j * 4] += q.x; r[j * 4 + 1] += q.y; r[j * 4 + 2] += q.z; r[j * 4 + 3] += q.w;
+                            }
+                        } else {
+#pragma unroll
+                            for (int i = 0; i < 32; ++i)
+                                if (o_n + i < a.N) r[i] += dst[i];
+                        }
+                    }
+                    if (whole) {
+#pragma unroll
+                        for (int j = 0; j < 8; ++j)
+                            reinterpret_cast<float4*>(dst)[j] = make_float4(r[j * 4], r[j * 4 + 1], r[j * 4 + 2], r[j * 4 + 3]);
+                    } else {
+#pragma unroll
+                        for (int i = 0; i < 32; ++i)
+                            if (o_n + i < a.N) dst[i] = r[i];
+                    }
+                    if (a.xw_out) {
+                        bf16* xd = a.xw_out + (size_t)t * a.N + o_n;
+#pragma unroll
+                        for (int i = 0; i < 32; ++i) {
+                            if (o_n + i < a.N) {
+                                xd[i] = __float2bfloat16_rn(r[i] * __ldg(a.xw_w + o_n + i));
+                                sq += r[i] * r[i];
+                            }
+                        }
+                    }
+                    if (a.xw_out) {
+                        // the four threads of a token hold its 128 rows: one row of sums per 128 weight rows
+                        sq += __shfl_xor_sync(0xffffffffu, sq, 1);
+                        sq += __shfl_xor_sync(0xffffffffu, sq, 2);
+                        if (o_rg == 0) a.ssq_out[(size_t)(n0 / PM) * a.T + t] = sq;
                     }
                 }
-            } else if (a.epilogue == P_RESIDUAL_ADD && a.xw_out) {
-                const float wn = wn_pre;
-                const bool first = c0 == c_begin;
-                float sq[16];
-#pragma unroll
-                for (int i = 0; i < 16; ++i) {
-                    const int t = t0 + c0 + i;
-                    sq[i] = 0.f;
-                    if (i >= cn || t >= a.T || n >= a.N) continue;
-                    const size_t o = (size_t)t * a.ldo + n;
-                    const float r = (first ? res_pre[i] : reinterpret_cast<float*>(a.out)[o]) + v[i];
-                    reinterpret_cast<float*>(a.out)[o] = r;
-                    a.xw_out[(size_t)t * a.N + n] = __float2bfloat16_rn(r * wn);
-                    sq[i] = r * r;
-                }
-#pragma unroll
-                for (int i = 0; i < 16; ++i) {
-                    const float w_sum = warp_sum(sq[i]);
-                    if (lane == 0) s_red[quad][i] = w_sum;
-                }
-                asm volatile("bar.sync 1, 128;" ::: "memory");
-                const int et = threadIdx.x - 64;
-                if (et < cn && t0 + c0 + et < a.T)     // one row of sums per 128 weight rows, as the consumer expects
-                    a.ssq_out[(size_t)(n0 / PM) * a.T + t0 + c0 + et] =
-                        s_red[0][et] + s_red[1][et] + s_red[2][et] + s_red[3][et];
-                asm volatile("bar.sync 1, 128;" ::: "memory");
-            } else if (n < a.N) {
-#pragma unroll
-                for (int i = 0; i < 16; ++i) {
-                    const int t = t0 + c0 + i;
-                    if (i >= cn || t >= a.T) continue;
-                    const size_t o = (size_t)t * a.ldo + n;
-                    if (a.epilogue == P_BF16) reinterpret_cast<bf16*>(a.out)[o] = __float2bfloat16_rn(v[i]);
-                    else if (a.epilogue == P_F32) reinterpret_cast<float*>(a.out)[o] = v[i];
-                    else reinterpret_cast<float*>(a.out)[o] = (c0 == c_begin ? res_pre[i] : reinterpret_cast<float*>(a.out)[o]) + v[i];
-                }
+            } else if (a.xw_out && a.epilogue == P_RESIDUAL_ADD) {
+                float sq = 0.f;                            // keep the shuffles of the branch above warp-wide
+                sq += __shfl_xor_sync(0xffffffffu, sq, 1);
+                sq += __shfl_xor_sync(0xffffffffu, sq, 2);
             }
+            asm volatile("bar.sync 1, 128;" ::: "memory");
         }
     }
     // peers may still be reading this block's partial tile, and the pair's tensor memory is freed together
@@ -355,14 +438,25 @@ gemm_pair_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constan
 }
 
 template <int NTOK>
-static int launch_pair(const CUtensorMap& mw, const CUtensorMap& mx, const PairArgs& a, int row_tiles, int t_tiles, int pdl,
+static int launch_pair(const CUtensorMap& mw, const CUtensorMap& mx, const PairArgs& a_in, int row_tiles, int t_tiles, int pdl,
                        cudaStream_t stream) {
     using Cfg = PairCfg<NTOK>;
-    FF_SMEM_LIMIT(gemm_pair_kernel<NTOK>, Cfg::SMEM);
+    PairArgs a = a_in;
+    // one wave of blocks at one per SM -> deep pipelines; more blocks than SMs (and no K ranges, whose
+    // partial tiles need the room) -> two per SM
+    int sms = 0, dev = 0;
+    cudaGetDevice(&dev);
+    cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
+    const long long blocks = 2ll * a.ranges * row_tiles * t_tiles;
+    (void)blocks;
+    a.stages = Cfg::DEEP;
+    if (a.stages < 2) a.stages = 2;
+    if (a.ranges > 1 && !Cfg::can_split(a.stages)) return FF_ERR_UNSUPPORTED;
+    FF_SMEM_LIMIT(gemm_pair_kernel<NTOK>, Cfg::smem(Cfg::DEEP));
     cudaLaunchConfig_t cfg = {};
     cfg.gridDim = dim3(2 * a.ranges, row_tiles, t_tiles);
     cfg.blockDim = dim3(PAIR_THREADS);
-    cfg.dynamicSmemBytes = Cfg::SMEM;
+    cfg.dynamicSmemBytes = Cfg::smem(a.stages);
     cfg.stream = stream;
     cudaLaunchAttribute attrs[2];
     int na = 0;

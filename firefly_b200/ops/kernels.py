@@ -281,7 +281,14 @@ def linear(x: torch.Tensor, weight: torch.Tensor, out: torch.Tensor) -> None:
 
 
 EPI_BF16, EPI_F32, EPI_RESIDUAL_ADD, EPI_SWIGLU = 0, 1, 2, 3
-GEMM_TC_MAX_TOKENS = 64    # up to here the tcgen05 product is at least as fast as the library's
+GEMM_TC_MAX_TOKENS = 64    # up to here the one-block tcgen05 product runs
+# From there to GEMM_PAIR_MAX_TOKENS the two-SM product (cta_group::2, csrc/gemm_pair.cu) can take over,
+# with the same fused epilogues.  Off: alone it reaches 0.7 to 1.0 of the library's speed at 128 to 512
+# tokens (the gate|up product at 128 tokens: 41 us against 41), but inside a step its blocks, one per SM
+# with nearly all of the shared memory, leave no room for the next kernel to move in early, and a
+# 256-token step of the 8B shape takes 8.2 ms with it against 5.9 ms with the library's products.
+USE_PAIR_GEMM = False
+GEMM_PAIR_MAX_TOKENS = 512
 USE_TCGEN05_GEMM = True    # tests flip this to compare with the library route
 FOLD_NORM = True           # fold the RMSNorm between two tcgen05 products into their epilogues
 

@@ -22,8 +22,27 @@ from ..ops import kernels as K
 
 
 def tc_usable(x: torch.Tensor, weight: torch.Tensor) -> bool:
-    return (K.USE_TCGEN05_GEMM and x.dtype == torch.bfloat16 and weight.dtype == torch.bfloat16
-            and x.shape[0] <= K.GEMM_TC_MAX_TOKENS and weight.shape[1] % 8 == 0)
+    """True if one of the package's tcgen05 products takes this size: the one-block kernel up to
+    `GEMM_TC_MAX_TOKENS` tokens, the two-SM kernel from there to `GEMM_PAIR_MAX_TOKENS`."""
+    if not (K.USE_TCGEN05_GEMM and x.dtype == torch.bfloat16 and weight.dtype == torch.bfloat16
+            and weight.shape[1] % 8 == 0):
+        return False
+    return x.shape[0] <= K.GEMM_TC_MAX_TOKENS or (K.USE_PAIR_GEMM and x.shape[0] <= K.GEMM_PAIR_MAX_TOKENS)
+
+
+def _pair_ranges(T: int, N: int, Kd: int) -> int:
+    """K ranges of the two-SM product.  A tile of 256 rows x up to 256 tokens is one pair of blocks; the
+    K range is cut in two or three while that still leaves the blocks fewer than the SMs (clusters of
+    four pack the GPU well, clusters of six only when they are few; clusters of eight were slower)."""
+    tok, _ = K.gemm_pair_plan(T, N, Kd, 1)
+    pairs = -(-N // 256) * -(-T // tok)
+    sms = K.sm_count()
+    kb = -(-Kd // 64)
+    if 6 * pairs <= 0.7 * sms and kb >= 12:
+        return 3
+    if 4 * pairs <= sms and kb >= 8:
+        return 2
+    return 1
 
 
 def _splits(N: int, Kd: int) -> int:
@@ -49,11 +68,14 @@ def _resolve(x, weight):
 def _tc(x, weight, out, epilogue, ctx, norm_out=None) -> None:
     from .norm import FoldedNorm
     N, Kd = weight.shape
+    kw = {}
     if isinstance(x, FoldedNorm):
-        K.gemm_tc(x.xw, weight, out, epilogue, _splits(N, Kd), ctx.status, norm_out=norm_out,
-                  norm_in=(x.ssq, x.norm.size, x.norm.eps))
+        kw["norm_in"] = (x.ssq, x.norm.size, x.norm.eps)
+        x = x.xw
+    if x.shape[0] > K.GEMM_TC_MAX_TOKENS:
+        K.gemm_pair(x, weight, out, epilogue, _pair_ranges(x.shape[0], N, Kd), ctx.status, norm_out=norm_out, **kw)
     else:
-        K.gemm_tc(x, weight, out, epilogue, _splits(N, Kd), ctx.status, norm_out=norm_out)
+        K.gemm_tc(x, weight, out, epilogue, _splits(N, Kd), ctx.status, norm_out=norm_out, **kw)
 
 
 def apply_linear(x: torch.Tensor, weight: torch.Tensor, out: torch.Tensor, ctx, tag: str) -> torch.Tensor:
