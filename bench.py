@@ -492,8 +492,9 @@ def main() -> int:
     prefill = None if args.no_prefill else prefill_point()
     prefill_chunked = None if args.no_prefill else prefill_chunked_point()
     if prefill_chunked is not None:
-        d = prefill_chunked_point(None)
-        prefill_chunked["engine_default_ms"], prefill_chunked["engine_default_steps"] = d["ms"], d["steps"]
+        by_default = prefill_chunked_point(None)
+        prefill_chunked["engine_default_ms"] = by_default["ms"]
+        prefill_chunked["engine_default_steps"] = by_default["steps"]
     points = {}
     if not args.no_points:
         for B in (1, 64):
