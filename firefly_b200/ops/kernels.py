@@ -280,6 +280,19 @@ def linear(x: torch.Tensor, weight: torch.Tensor, out: torch.Tensor) -> None:
         raise KernelError(f"linear: cannot write {out.dtype} from {x.dtype}")
 
 
+def linear_add(x: torch.Tensor, weight: torch.Tensor, residual: torch.Tensor) -> None:
+    """residual (float32) += x @ weight^T through the library, the sum formed in 32-bit: the product
+    never exists rounded to the operands' type, and the norm behind it has one tensor less to read."""
+    _need_cuda(x, weight, residual)
+    if x.dtype != weight.dtype or residual.dtype != torch.float32:
+        raise KernelError(f"linear_add: {x.dtype} x {weight.dtype} into {residual.dtype}")
+    if x.dtype == torch.float32:
+        torch.addmm(residual, x, weight.t(), out=residual)
+    else:
+        torch.addmm(residual, x, weight.t(), out_dtype=torch.float32, out=residual)
+
+
+LIBRARY_ADDS_INTO_RESIDUAL = True   # products of more than GEMM_TC_MAX_TOKENS tokens add into the 32-bit residual themselves
 EPI_BF16, EPI_F32, EPI_RESIDUAL_ADD, EPI_SWIGLU = 0, 1, 2, 3
 GEMM_TC_MAX_TOKENS = 64    # up to here the one-block tcgen05 product runs
 # From there to GEMM_PAIR_MAX_TOKENS the two-SM product (cta_group::2, csrc/gemm_pair.cu) can take over,

@@ -108,8 +108,9 @@ def linear_into_residual(x: torch.Tensor, weight: torch.Tensor, residual: Option
     """The product as a delta for the residual stream.  When it can be fused it is
     added into ``residual`` (float32) in the product's epilogue; then None is
     returned, or, when the norm that follows is given as ``then_norm`` and can be
-    folded, a FoldedNorm that the norm's consumer finishes.  Else the delta is
-    returned for the next norm to add."""
+    folded, a FoldedNorm that the norm's consumer finishes.  Larger bfloat16 products
+    let the library add into the residual (32-bit sum), None again.  Else the delta
+    is returned for the next norm to add."""
     x = _resolve(x, weight)
     if residual is not None and tc_usable(x, weight):
         if then_norm is not None and K.FOLD_NORM and getattr(then_norm, "foldable", False) \
@@ -119,6 +120,10 @@ def linear_into_residual(x: torch.Tensor, weight: torch.Tensor, residual: Option
             _tc(x, weight, residual, K.EPI_RESIDUAL_ADD, ctx, norm_out=(xw, nw, ssq))
             return FoldedNorm(then_norm, residual, xw, ssq, ctx)
         _tc(x, weight, residual, K.EPI_RESIDUAL_ADD, ctx)
+        return None
+    if residual is not None and K.LIBRARY_ADDS_INTO_RESIDUAL and x.dtype == weight.dtype == torch.bfloat16 \
+            and residual.dtype == torch.float32 and residual.is_contiguous():
+        K.linear_add(x, weight, residual)
         return None
     out = ctx.workspace.get(tag, (x.shape[0], weight.shape[0]), ctx.dtype)
     return apply_linear(x, weight, out, ctx, tag)
