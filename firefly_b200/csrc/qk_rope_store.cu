@@ -188,10 +188,12 @@ __global__ void qk_norm_rope_store_vec_kernel(
     }
 }
 
-// The same for long portions of prompts: a warp takes HPW consecutive heads of one token, so the
-// token's position, page, cosines and sines are fetched once for all of them and the loads of the
-// HPW heads are in flight together.
-template <int C, int HPW>
+// The same for long portions of prompts, where the kernel is a stream over the projection's output:
+// a lane owns eight consecutive elements of a head's lower half and the eight that rotate with them in
+// the upper half (16-byte loads and stores), LPH = head size / 16 lanes make up a head, a warp takes
+// HPW consecutive heads of one token in passes of 32 / LPH heads, with all its loads in flight
+// together.  The token's position, page, cosines and sines are fetched once for all of them.
+template <int LPH, int HPW>
 __global__ void qk_norm_rope_store_rows_kernel(
     bf16* __restrict__ qkv, int row_width, int T_tokens, int nq, int nkv,
     const float* __restrict__ q_norm_w, const float* __restrict__ k_norm_w, float eps,
@@ -200,30 +202,27 @@ __global__ void qk_norm_rope_store_rows_kernel(
     const int* __restrict__ block_table, int max_blocks, int block_size, int num_blocks,
     bf16* __restrict__ cache, int* __restrict__ status) {
     asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
-    constexpr int HALF = 32 * C, d = 64 * C;
-    using Vec = typename std::conditional<C == 2, uint32_t, uint2>::type;
+    constexpr int d = LPH * 16, HALF = d / 2, HPP = 32 / LPH, PASSES = HPW / HPP;
+    static_assert(HPW % HPP == 0, "a warp's heads come in whole passes");
     const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+    const int sub = lane % LPH, hsel = lane / LPH;
     const int heads = nq + 2 * nkv;
     const int chunks = (heads + HPW - 1) / HPW;
     const long long item = (long long)blockIdx.x * QKR_WARPS + warp;
     const bool active = item < (long long)T_tokens * chunks;
     const int t = active ? (int)(item / chunks) : 0, h0 = active ? (int)(item % chunks) * HPW : 0;
     const int pos = positions[t];
-    const int e0 = lane * C;
-    float wq_l[C], wq_h[C], wk_l[C], wk_h[C], cs_c[C], cs_s[C];
+    const int e0 = sub * 8;
     const bool pos_ok = pos >= 0 && pos < max_positions;
+    float cs_c[8], cs_s[8];
 #pragma unroll
-    for (int j = 0; j < C; ++j) {
-        wq_l[j] = q_norm_w ? q_norm_w[e0 + j] : 1.f;
-        wq_h[j] = q_norm_w ? q_norm_w[HALF + e0 + j] : 1.f;
-        wk_l[j] = k_norm_w ? k_norm_w[e0 + j] : 1.f;
-        wk_h[j] = k_norm_w ? k_norm_w[HALF + e0 + j] : 1.f;
-        cs_c[j] = 1.f;
-        cs_s[j] = 0.f;
-        if (cos_sin && pos_ok) {
-            const float* cs = cos_sin + (size_t)pos * d + 2 * (e0 + j);  // [half][2]
-            cs_c[j] = cs[0];
-            cs_s[j] = cs[1];
+    for (int j = 0; j < 8; ++j) { cs_c[j] = 1.f; cs_s[j] = 0.f; }
+    if (cos_sin && pos_ok) {
+        const float4* cs = reinterpret_cast<const float4*>(cos_sin + (size_t)pos * d + 2 * e0);   // [half][2]
+#pragma unroll
+        for (int j = 0; j < 4; ++j) {
+            const float4 v = __ldg(cs + j);
+            cs_c[2 * j] = v.x; cs_s[2 * j] = v.y; cs_c[2 * j + 1] = v.z; cs_s[2 * j + 1] = v.w;
         }
     }
     const bool has_kv = h0 + HPW > nq;
@@ -240,55 +239,61 @@ __global__ void qk_norm_rope_store_rows_kernel(
         return;
     }
     bf16* row = qkv + (size_t)t * row_width;
-    Vec a[HPW], b[HPW];
+    uint4 a[PASSES], b[PASSES];
 #pragma unroll
-    for (int u = 0; u < HPW; ++u) {
-        const int hh = min(h0 + u, heads - 1);
-        a[u] = *reinterpret_cast<const Vec*>(row + (size_t)hh * d + e0);
-        b[u] = *reinterpret_cast<const Vec*>(row + (size_t)hh * d + HALF + e0);
+    for (int p = 0; p < PASSES; ++p) {
+        const int hh = min(h0 + p * HPP + hsel, heads - 1);
+        a[p] = *reinterpret_cast<const uint4*>(row + (size_t)hh * d + e0);
+        b[p] = *reinterpret_cast<const uint4*>(row + (size_t)hh * d + HALF + e0);
     }
 #pragma unroll
-    for (int u = 0; u < HPW; ++u) {
-        const int hh = h0 + u;
-        if (hh >= heads) break;
+    for (int p = 0; p < PASSES; ++p) {
+        const int hh = h0 + p * HPP + hsel;
+        const bool valid = hh < heads;
         const int kind = hh < nq ? 0 : (hh < nq + nkv ? 1 : 2);  // q, k, v
-        float lo[C], hi[C];
-        const bf16* pa = reinterpret_cast<const bf16*>(&a[u]);
-        const bf16* pb = reinterpret_cast<const bf16*>(&b[u]);
+        float lo[8], hi[8];
+        const bf16* pa = reinterpret_cast<const bf16*>(&a[p]);
+        const bf16* pb = reinterpret_cast<const bf16*>(&b[p]);
 #pragma unroll
-        for (int j = 0; j < C; ++j) { lo[j] = __bfloat162float(pa[j]); hi[j] = __bfloat162float(pb[j]); }
-        if ((kind == 0 && q_norm_w) || (kind == 1 && k_norm_w)) {
-            float ss = 0.f;
+        for (int j = 0; j < 8; ++j) { lo[j] = __bfloat162float(pa[j]); hi[j] = __bfloat162float(pb[j]); }
+        const float* nw = kind == 0 ? q_norm_w : (kind == 1 ? k_norm_w : nullptr);
+        float ss = 0.f;
 #pragma unroll
-            for (int j = 0; j < C; ++j) ss += lo[j] * lo[j] + hi[j] * hi[j];
-            ss = warp_sum(ss);
+        for (int j = 0; j < 8; ++j) ss += lo[j] * lo[j] + hi[j] * hi[j];
+#pragma unroll
+        for (int o = LPH / 2; o > 0; o >>= 1) ss += __shfl_xor_sync(0xffffffffu, ss, o);   // over the head's lanes
+        if (nw) {
             const float inv = 1.0f / sqrtf(ss / (float)d + eps);
+            const float4* wl = reinterpret_cast<const float4*>(nw + e0);
+            const float4* wh = reinterpret_cast<const float4*>(nw + HALF + e0);
 #pragma unroll
-            for (int j = 0; j < C; ++j) {
-                lo[j] = lo[j] * inv * (kind == 0 ? wq_l[j] : wk_l[j]);
-                hi[j] = hi[j] * inv * (kind == 0 ? wq_h[j] : wk_h[j]);
+            for (int j = 0; j < 2; ++j) {
+                const float4 l = __ldg(wl + j), h = __ldg(wh + j);
+                lo[4 * j] *= inv * l.x; lo[4 * j + 1] *= inv * l.y; lo[4 * j + 2] *= inv * l.z; lo[4 * j + 3] *= inv * l.w;
+                hi[4 * j] *= inv * h.x; hi[4 * j + 1] *= inv * h.y; hi[4 * j + 2] *= inv * h.z; hi[4 * j + 3] *= inv * h.w;
             }
         }
         if (kind != 2 && cos_sin) {
 #pragma unroll
-            for (int j = 0; j < C; ++j) {
+            for (int j = 0; j < 8; ++j) {
                 const float x = lo[j], y = hi[j];
                 lo[j] = x * cs_c[j] - y * cs_s[j];
                 hi[j] = y * cs_c[j] + x * cs_s[j];
             }
         }
+        if (!valid) continue;
         bf16* dst = row + (size_t)hh * d;
         if (kind != 0) {
             const int kh = kind == 1 ? hh - nq : hh - nq - nkv;
             dst = cache + ((((size_t)page * 2 + (kind == 2)) * nkv + kh) * block_size + pos % block_size) * d;
         }
-        Vec oa, ob;
+        uint4 oa, ob;
         bf16* qa = reinterpret_cast<bf16*>(&oa);
         bf16* qb = reinterpret_cast<bf16*>(&ob);
 #pragma unroll
-        for (int j = 0; j < C; ++j) { qa[j] = __float2bfloat16_rn(lo[j]); qb[j] = __float2bfloat16_rn(hi[j]); }
-        *reinterpret_cast<Vec*>(dst + e0) = oa;
-        *reinterpret_cast<Vec*>(dst + HALF + e0) = ob;
+        for (int j = 0; j < 8; ++j) { qa[j] = __float2bfloat16_rn(lo[j]); qb[j] = __float2bfloat16_rn(hi[j]); }
+        *reinterpret_cast<uint4*>(dst + e0) = oa;
+        *reinterpret_cast<uint4*>(dst + HALF + e0) = ob;
     }
 }
 
@@ -312,16 +317,18 @@ FF_EXPORT int ff_qk_norm_rope_store(void* qkv, int dtype, int row_width, int T, 
     // whole-head rotation of a 128- or 256-wide bfloat16 head with aligned rows: the register form
     if (dtype == 1 && (d == 128 || d == 256) && (!cos_sin || rotary_dim == d) && row_width % 4 == 0 &&
         ((uintptr_t)qkv & 7) == 0 && ((uintptr_t)cache & 7) == 0) {
-        if (T >= 256) {   // long portions: a warp per (token, 8 heads)
+        const bool wide_ok = row_width % 8 == 0 && ((uintptr_t)qkv & 15) == 0 && ((uintptr_t)cache & 15) == 0 &&
+                             ((uintptr_t)cos_sin & 15) == 0 && ((uintptr_t)q_norm_w & 15) == 0 && ((uintptr_t)k_norm_w & 15) == 0;
+        if (T >= 256 && wide_ok) {   // long portions: a warp per (token, 8 heads), 16 bytes a lane
             constexpr int HPW = 8;
             const long long ritems = (long long)T * ((nq + 2 * nkv + HPW - 1) / HPW);
             const unsigned rblocks = (unsigned)((ritems + QKR_WARPS - 1) / QKR_WARPS);
             if (d == 128)
-                FF_LAUNCH((qk_norm_rope_store_rows_kernel<2, HPW>), rblocks, QKR_WARPS * 32, 0, stream, (bf16*)qkv,
+                FF_LAUNCH((qk_norm_rope_store_rows_kernel<8, HPW>), rblocks, QKR_WARPS * 32, 0, stream, (bf16*)qkv,
                           row_width, T, nq, nkv, q_norm_w, k_norm_w, eps, cos_sin, max_positions, positions, token_seq,
                           block_table, max_blocks, block_size, num_blocks, (bf16*)cache, status);
             else
-                FF_LAUNCH((qk_norm_rope_store_rows_kernel<4, HPW>), rblocks, QKR_WARPS * 32, 0, stream, (bf16*)qkv,
+                FF_LAUNCH((qk_norm_rope_store_rows_kernel<16, HPW>), rblocks, QKR_WARPS * 32, 0, stream, (bf16*)qkv,
                           row_width, T, nq, nkv, q_norm_w, k_norm_w, eps, cos_sin, max_positions, positions, token_seq,
                           block_table, max_blocks, block_size, num_blocks, (bf16*)cache, status);
             FF_LAUNCH_CHECK();

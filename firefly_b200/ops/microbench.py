@@ -6,6 +6,10 @@
         one step of a prompt portion of that many tokens (context 1024): queued by the host launch by
         launch, and replayed from a CUDA graph
 
+    python -m firefly_b200.ops.microbench timeline [--tokens 2048] [--context 0] [--batch 1] [--layers 4] [--shape 8b]
+        the kernels of one replayed step in order with their device times (a CUPTI timeline through
+        torch.profiler): ``--batch`` requests with ``--tokens`` new tokens each behind ``--context`` tokens
+
 CUDA events around 20 (gemm) or 40 (step) repetitions after warm-up; weights are rotated through more
 than 400 MB in the gemm case so that they come from HBM, not from L2.
 """
@@ -123,19 +127,97 @@ def step(args) -> None:
         del eng, graph
 
 
+def timeline(args) -> None:
+    """One step replayed from a CUDA graph under the profiler.  With programmatic dependent launch a
+    kernel's recorded start lies before its real work, so beside each kernel's own time the step from
+    the end of the kernel before to its own end is printed: those add up to the step."""
+    import collections
+    from torch.profiler import ProfilerActivity, profile
+    from ..config.qwen3 import Qwen3Config
+    from ..engine.engine import Engine, EngineOptions
+    from ..engine.loading import random_model
+    from ..engine.runner import StepEntry
+    H, I, nq, nkv, d, L, V = SHAPES[args.shape]
+    layers = args.layers or 4
+    cfg = Qwen3Config.from_dict(dict(
+        architectures=["Qwen3ForCausalLM"], hidden_size=H, intermediate_size=I, num_hidden_layers=layers,
+        num_attention_heads=nq, num_key_value_heads=nkv, head_dim=d, vocab_size=V, max_position_embeddings=40960,
+        rms_norm_eps=1e-6, rope_theta=1e6, tie_word_embeddings=args.shape == "0.6b"))
+    model = random_model(cfg, 0)
+    T, B, C = args.tokens[0], args.batch, args.context
+    ids = torch.randint(0, V, (C + T,), generator=torch.Generator().manual_seed(0)).tolist()
+    eng = Engine(model, cfg, options=EngineOptions(
+        max_prefill_chunk_size=max(T, C, 1), max_num_batched_tokens=max(B * T, C, 1), max_batch_size_limit=max(B, 1),
+        num_kv_blocks=B * (-(-(C + T) // 16) + 1) + 8, max_model_len=C + T + 16, use_cuda_graphs=False))
+    caches = []
+    for r in range(B):
+        rc = eng.cache.admit(f"r{r}")
+        if C:
+            assert eng.cache.grow(rc, C)
+            eng.runner.step([StepEntry(rc, ids[:C], [])])
+        assert eng.cache.grow(rc, C + T)
+        caches.append(rc)
+    ctx = eng.runner.build_context([StepEntry(rc, ids[C:C + T], [T - 1]) for rc in caches])
+    for _ in range(2):
+        model.forward(ctx)
+    torch.cuda.synchronize()
+    side = torch.cuda.Stream()
+    side.wait_stream(torch.cuda.current_stream())
+    with torch.cuda.stream(side):
+        model.forward(ctx)
+    torch.cuda.current_stream().wait_stream(side)
+    torch.cuda.synchronize()
+    graph = torch.cuda.CUDAGraph()
+    with torch.cuda.graph(graph):
+        model.forward(ctx)
+    for _ in range(3):
+        graph.replay()
+    torch.cuda.synchronize()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e0.record()
+    for _ in range(20):
+        graph.replay()
+    e1.record()
+    torch.cuda.synchronize()
+    print(f"{args.shape}, {layers} layers, {B} x {T} tokens behind {C}: {e0.elapsed_time(e1) / 20 * 1000:.1f} us a replayed step")
+    with profile(activities=[ProfilerActivity.CUDA]) as prof:
+        graph.replay()
+        torch.cuda.synchronize()
+    evs = sorted((e for e in prof.events() if e.device_type == torch.autograd.DeviceType.CUDA),
+                 key=lambda e: e.time_range.start)
+    eng.runner.check_status()
+    total = collections.OrderedDict()
+    prev_end = None
+    print("   step us   own us  kernel (in launch order)")
+    for e in evs:
+        own = e.time_range.end - e.time_range.start
+        step_us = e.time_range.end - (prev_end if prev_end is not None else e.time_range.start)
+        prev_end = max(prev_end or 0, e.time_range.end)
+        print(f"  {step_us:8.1f} {own:8.1f}  {e.name[:100]}")
+        t = total.setdefault(e.name[:100], [0, 0.0])
+        t[0] += 1
+        t[1] += step_us
+    print("sums by kernel:")
+    for name, (n, us) in sorted(total.items(), key=lambda kv: -kv[1][1]):
+        print(f"  {us:9.1f} us  {n:4d} x  {name}")
+
+
 def main(argv=None) -> int:
     ap = argparse.ArgumentParser(prog="python -m firefly_b200.ops.microbench")
-    ap.add_argument("what", choices=["gemm", "step"])
+    ap.add_argument("what", choices=["gemm", "step", "timeline"])
     ap.add_argument("--tokens", default=None)
     ap.add_argument("--shape", default="8b", choices=sorted(SHAPES))
     ap.add_argument("--layers", type=int, default=None)
+    ap.add_argument("--context", type=int, default=0, help="timeline: tokens already in the cache")
+    ap.add_argument("--batch", type=int, default=1, help="timeline: requests in the step")
     ap.add_argument("--pair", action="store_true", help="route products of 65 to 512 tokens to the two-SM kernel")
     args = ap.parse_args(argv)
-    args.tokens = [int(t) for t in (args.tokens or ("128,256,512" if args.what == "gemm" else "96,128,256,512")).split(",")]
+    default = {"gemm": "128,256,512", "step": "96,128,256,512", "timeline": "2048"}[args.what]
+    args.tokens = [int(t) for t in (args.tokens or default).split(",")]
     if not torch.cuda.is_available():
         print("microbench: needs a CUDA device")
         return 1
-    {"gemm": gemm, "step": step}[args.what](args)
+    {"gemm": gemm, "step": step, "timeline": timeline}[args.what](args)
     return 0
 
 
