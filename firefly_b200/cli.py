@@ -46,6 +46,8 @@ def build_parser() -> argparse.ArgumentParser:
     ap.add_argument("--eos-token-id", type=int, action="append", default=None,
                     help="end-of-sequence id (default: config.json's eos_token_id)")
     ap.add_argument("--dtype", default="bfloat16", choices=["bfloat16", "float32"])
+    ap.add_argument("--weight-dtype", default="keep", choices=["keep", "engine"],
+                    help="tensors stored in 32-bit: keep them (default) or narrow them to --dtype on the device")
     ap.add_argument("--kv-block-size", type=int, default=16)
     ap.add_argument("--num-kv-blocks", type=int, default=None)
     ap.add_argument("--max-batch-size", type=int, default=64, help="most active requests (default 64)")
@@ -104,7 +106,8 @@ def main(argv=None) -> int:
             print("firefly: no prompt given (--prompt-ids, --prompts-file or --prompt-len)", file=sys.stderr)
             return 2
         from .entry import LLM
-        llm = LLM(model, dtype=args.dtype, seed=args.seed, max_prefill_chunk_size=args.max_prefill_chunk_size,
+        llm = LLM(model, dtype=args.dtype, seed=args.seed, weight_dtype=args.weight_dtype,
+                  max_prefill_chunk_size=args.max_prefill_chunk_size,
                   max_batch_size_limit=args.max_batch_size, max_num_batched_tokens=args.max_num_batched_tokens,
                   kv_block_size=args.kv_block_size, num_kv_blocks=args.num_kv_blocks,
                   max_model_len=args.max_model_len, eos_token_ids=args.eos_token_id,

@@ -453,13 +453,14 @@ class LLM:
         outs = llm.generate([[1, 2, 3], [4, 5]], max_tokens=16)
     """
 
-    def __init__(self, model, *, dtype="bfloat16", device="cuda:0", seed: int = 0,
+    def __init__(self, model, *, dtype="bfloat16", device="cuda:0", seed: int = 0, weight_dtype: str = "keep",
                  max_prefill_chunk_size: Optional[int] = None, **options):
         """``model``: a folder with config.json and model.safetensors, or a typed
-        configuration (random weights drawn from ``seed``)."""
+        configuration (random weights drawn from ``seed``).  ``weight_dtype``: "keep" leaves a
+        tensor stored in 32-bit as it is, "engine" narrows it to the engine's type on the device."""
         raw = None
         if isinstance(model, (str, os.PathLike)):
-            self.model, self.config = load_model(str(model), dtype=dtype, device=device)
+            self.model, self.config = load_model(str(model), dtype=dtype, device=device, weight_dtype=weight_dtype)
             with open(os.path.join(str(model), "config.json")) as fh:
                 raw = json.load(fh)
         elif isinstance(model, ModelConfig):

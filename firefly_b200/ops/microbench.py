@@ -10,6 +10,10 @@
         the kernels of one replayed step in order with their device times (a CUPTI timeline through
         torch.profiler): ``--batch`` requests with ``--tokens`` new tokens each behind ``--context`` tokens
 
+    python -m firefly_b200.ops.microbench load [--shape 8b]
+        a bfloat16 model folder of that shape written to a temporary folder, then loaded twice through
+        the engine's loader: seconds, GB/s, the arena's size and the peak of device memory
+
 CUDA events around 20 (gemm) or 40 (step) repetitions after warm-up; weights are rotated through more
 than 400 MB in the gemm case so that they come from HBM, not from L2.
 """
@@ -202,9 +206,71 @@ def timeline(args) -> None:
         print(f"  {us:9.1f} us  {n:4d} x  {name}")
 
 
+def load(args) -> None:
+    import json
+    import os
+    import shutil
+    import struct
+    import tempfile
+    from ..config.qwen3 import Qwen3Config
+    from ..engine.loading import load_model, random_model
+    from ..models import expected_weights, spec_for
+    H, I, nq, nkv, d, L, V = SHAPES[args.shape]
+    cfg = Qwen3Config.from_dict(dict(
+        architectures=["Qwen3ForCausalLM"], hidden_size=H, intermediate_size=I, num_hidden_layers=args.layers or L,
+        num_attention_heads=nq, num_key_value_heads=nkv, head_dim=d, vocab_size=V, max_position_embeddings=40960,
+        rms_norm_eps=1e-6, rope_theta=1e6, tie_word_embeddings=args.shape == "0.6b"))
+    folder = tempfile.mkdtemp(prefix="firefly_b200_load_")
+    try:
+        specs = [w for w in expected_weights(spec_for(cfg)) if not w.optional]
+        header, off = {}, 0
+        for w in specs:
+            n = 2
+            for x in w.shape:
+                n *= x
+            header[w.name] = {"dtype": "BF16", "shape": list(w.shape), "data_offsets": [off, off + n]}
+            off += n
+        blob = json.dumps(header, separators=(",", ":")).encode()
+        blob += b" " * ((8 - len(blob) % 8) % 8)
+        g = torch.Generator(device="cuda").manual_seed(0)
+        with open(os.path.join(folder, "model.safetensors"), "wb") as fh:
+            fh.write(struct.pack("<Q", len(blob)))
+            fh.write(blob)
+            for w in specs:
+                x = torch.randn(w.shape, generator=g, device="cuda", dtype=torch.float32)
+                x = (1 + 0.01 * x) if len(w.shape) == 1 else 0.02 * x
+                fh.write(x.to(torch.bfloat16).view(torch.int16).cpu().numpy().tobytes())
+        with open(os.path.join(folder, "config.json"), "w") as fh:
+            json.dump(cfg.to_dict(), fh)
+        del x
+        torch.cuda.empty_cache()
+        torch.cuda.synchronize()
+        print(f"{args.shape}: a folder of {off / 1e9:.1f} GB", flush=True)
+        for attempt in ("first load (the file is in the page cache)", "second load"):
+            torch.cuda.reset_peak_memory_stats()
+            base = torch.cuda.memory_allocated()
+            t0 = time.perf_counter()
+            model, _ = load_model(folder, dtype="bfloat16")
+            torch.cuda.synchronize()
+            dt = time.perf_counter() - t0
+            f = model.load_facts
+            print(f"{args.shape} {attempt}: {dt:.2f} s ({f['file_bytes'] / dt / 1e9:.1f} GB/s), arena "
+                  f"{f['arena_bytes'] / 1e9:.2f} GB, peak device memory "
+                  f"{(torch.cuda.max_memory_allocated() - base) / 1e9:.2f} GB, files registered with the driver "
+                  f"{f['pinned_files']} of {f['files']}", flush=True)
+            del model
+            torch.cuda.empty_cache()
+        t0 = time.perf_counter()
+        model = random_model(cfg, 0)
+        torch.cuda.synchronize()
+        print(f"{args.shape} random weights drawn on the device: {time.perf_counter() - t0:.2f} s")
+    finally:
+        shutil.rmtree(folder, ignore_errors=True)
+
+
 def main(argv=None) -> int:
     ap = argparse.ArgumentParser(prog="python -m firefly_b200.ops.microbench")
-    ap.add_argument("what", choices=["gemm", "step", "timeline"])
+    ap.add_argument("what", choices=["gemm", "step", "timeline", "load"])
     ap.add_argument("--tokens", default=None)
     ap.add_argument("--shape", default="8b", choices=sorted(SHAPES))
     ap.add_argument("--layers", type=int, default=None)
@@ -212,12 +278,12 @@ def main(argv=None) -> int:
     ap.add_argument("--batch", type=int, default=1, help="timeline: requests in the step")
     ap.add_argument("--pair", action="store_true", help="route products of 65 to 512 tokens to the two-SM kernel")
     args = ap.parse_args(argv)
-    default = {"gemm": "128,256,512", "step": "96,128,256,512", "timeline": "2048"}[args.what]
+    default = {"gemm": "128,256,512", "step": "96,128,256,512", "timeline": "2048", "load": "0"}[args.what]
     args.tokens = [int(t) for t in (args.tokens or default).split(",")]
     if not torch.cuda.is_available():
         print("microbench: needs a CUDA device")
         return 1
-    {"gemm": gemm, "step": step, "timeline": timeline}[args.what](args)
+    {"gemm": gemm, "step": step, "timeline": timeline, "load": load}[args.what](args)
     return 0
 
 
