@@ -137,7 +137,8 @@ class Engine:
                                    and not any(g.spec.window is not None for g in self.cache.groups))
         self.sampler = sampler if sampler is not None else Sampler(self.device, opts.max_batch_size_limit)
         self.graphs = None
-        if opts.use_cuda_graphs:
+        # a model with a part that reads device values on the host runs launch by launch
+        if opts.use_cuda_graphs and not getattr(model, "host_synchronous", False):
             from .graphs import DecodeGraphs
             self.graphs = DecodeGraphs(self.runner, opts.graph_batch_sizes)
         self._inbox: "queue.Queue[GenerationRequest]" = queue.Queue()

@@ -36,7 +36,7 @@ from collections import OrderedDict
 from ..cache.manager import SCRATCH_PAGE, OutOfPages
 from ..ops import kernels as K
 from .context import Workspace
-from .runner import MetaLayout, ModelRunner, StepEntry
+from .runner import MetaLayout, ModelRunner, StepEntry, StepError
 
 
 class _Bucket:
@@ -49,6 +49,31 @@ class LaunchedStep:
     """A replay that has been put on the stream: its tokens arrive in ``h_tokens`` once
     ``event`` has passed."""
     __slots__ = ("bucket", "n", "h_tokens", "event", "logits", "h_status", "status_code")
+
+
+class _Capture:
+    """``torch.cuda.graph`` with the one failure a model of foreign parts can cause turned into words:
+    an operation that synchronises with the host (``.item()``, an index taken from a device tensor,
+    ``bool(t.any())``) ends the capture with an error."""
+
+    def __init__(self, graph):
+        self._cm = torch.cuda.graph(graph)
+
+    def __enter__(self):
+        return self._cm.__enter__()
+
+    def __exit__(self, et, ev, tb):
+        try:
+            self._cm.__exit__(et, ev, tb)
+        except RuntimeError as e:
+            raise StepError("the model's step could not be captured into a CUDA graph: some part read a device "
+                            "value on the host. Declare host_synchronous = True on that part (parts/base.py) "
+                            f"or run with use_cuda_graphs=False. ({str(e).splitlines()[0]})") from e
+        if et is not None and issubclass(et, RuntimeError) and "capture" in str(ev):
+            raise StepError("the model's step could not be captured into a CUDA graph: some part read a device "
+                            "value on the host. Declare host_synchronous = True on that part (parts/base.py) "
+                            f"or run with use_cuda_graphs=False. ({str(ev).splitlines()[0]})") from ev
+        return False
 
 
 class DecodeGraphs:
@@ -211,7 +236,7 @@ class DecodeGraphs:
             return b
         b.graph = torch.cuda.CUDAGraph()
         before = K.LAUNCHES
-        with torch.cuda.graph(b.graph):
+        with _Capture(b.graph):
             self._apply_updates(b)
             b.logits = r.model.forward(ctx)
             self._sample(b, b.logits)
@@ -229,7 +254,7 @@ class DecodeGraphs:
         if K.BY_LENGTH_CALLS != calls:
             g2 = torch.cuda.CUDAGraph()
             before = K.LAUNCHES
-            with torch.cuda.graph(g2):
+            with _Capture(g2):
                 self._apply_updates(b)
                 logits2 = r.model.forward(ctx)
                 self._sample(b, logits2)
@@ -414,7 +439,7 @@ class DecodeGraphs:
             self.shapes.clear()               # a scratch buffer moved: graphs that hold its old address are void
         b.graph = torch.cuda.CUDAGraph()
         before = K.LAUNCHES
-        with torch.cuda.graph(b.graph):
+        with _Capture(b.graph):
             self._apply_updates(b)
             b.logits = r.model.forward(ctx)
             if nr:

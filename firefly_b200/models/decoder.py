@@ -12,7 +12,7 @@ import torch
 
 from ..config.base import ModelSpec
 from ..parts import Runtime, build_part, part_class
-from ..parts.base import declared
+from ..parts.base import declared, host_synchronous
 from ..weights.loader import WeightSpec
 
 
@@ -28,6 +28,9 @@ class DecoderModel:
         self.head = build_part("head", spec.head, rt)
         self.schedule = spec.resolved_schedule()
         self._takes_next_norm = [declared(b, "takes_next_norm") for b in self.blocks]
+        # a part that reads device values on the host keeps the whole model's steps out of CUDA graphs
+        self.host_synchronous = any(host_synchronous(p) for p in (
+            self.embedding, self.embedding_position, *self.blocks, self.final_norm, self.head) if p is not None)
         self.bound = False
 
     # -- weights ------------------------------------------------------------------

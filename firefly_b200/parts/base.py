@@ -40,8 +40,14 @@ accepts_folded_norm     (none)                      its first operation can fini
 takes_next_norm         forward(next_norm=)         arrangement: hands the next block's first norm
                                                     to its last part
 foldable                fold_buffers, size, eps     norm: can be folded into the products around it
+host_synchronous        (none)                      any part: its forward() reads device values on the
+                                                    host (``.item()``, ``bool(t.any())``, shapes that
+                                                    depend on data), so the steps of a model that holds
+                                                    it cannot be captured into CUDA graphs and run
+                                                    launch by launch
 =====================  ==========================  ==============================================
-A part that declares nothing simply runs unfused; it need not derive from ``Part``.
+A part that declares nothing simply runs unfused; it need not derive from ``Part``.  A part that
+holds other parts (an arrangement) lists them in ``parts()``.
 """
 from __future__ import annotations
 
@@ -97,6 +103,14 @@ def declared(part, flag: str) -> bool:
     if flag == "folds_next_norm" and has and not getattr(part, "adds_into_residual", False):
         raise ConfigError(f"{who} declares folds_next_norm without adds_into_residual")
     return has
+
+
+def host_synchronous(part) -> bool:
+    """True if ``part`` or a part it holds (``parts()``) declares that it synchronises with the host."""
+    if bool(getattr(part, "host_synchronous", False)):
+        return True
+    inner = getattr(part, "parts", None)
+    return any(host_synchronous(p) for p in inner()) if callable(inner) else False
 
 
 @dataclass

@@ -79,6 +79,10 @@ class PreNormBlock(Block):
         """The norm a block in front of this one may fold into its last product."""
         return self.norms[0]
 
+    def parts(self) -> list:
+        """The parts this block holds."""
+        return [p for p in (self.mixer, self.feed_forward, *self.norms, getattr(self, "position", None)) if p is not None]
+
     def forward(self, residual: torch.Tensor, pending, ctx, slot: int, write_cache: bool, next_norm=None):
         # only a foldable norm knows ``may_defer`` (hand a folded norm on to a consumer that finishes it)
         defer0 = {"may_defer": True} if self._norm_folds[0] and self._mixer_defers else {}

@@ -249,12 +249,14 @@ class ToyDecayMixer:
         out = torch.empty(x.shape[0], self.hidden, device=x.device)
         start = 0
         for i, n in enumerate(ctx.q_lens):
-            sl = ctx.state_slots[i].long()
-            s = st[sl] * (1 - ctx.seq_fresh[i]).float()        # a fresh request starts from zero
+            # the slot is a value on the device: it is used as an index tensor, never read by the host,
+            # so that the step can be captured into a CUDA graph
+            sl = ctx.state_slots[i:i + 1].long()
+            s = st.index_select(0, sl)[0] * (1 - ctx.seq_fresh[i]).float()   # a fresh request starts from zero
             for t in range(start, start + n):
                 s = self.decay * s + u[t]
                 out[t] = s @ self.w_out.T
-            st[sl] = s
+            st.index_copy_(0, sl, s[None])
             start += n
         return out.to(ctx.dtype)
 
@@ -313,10 +315,95 @@ def test_toy_mixer_with_state_is_registered_built_and_stepped():
         sess.cache.check()
 
 
+def _generate(model, prompts, n_new, **options):
+    """Greedy generation through the engine's own loop for a model built by hand."""
+    from firefly_b200.engine.engine import Engine, EngineOptions
+    from firefly_b200.engine.request import GenerationRequest
+    from firefly_b200.sampling import SamplingParams
+    eng = Engine(model, options=EngineOptions(kv_block_size=8, num_kv_blocks=64, max_batch_size_limit=4,
+                                              eos_token_ids=[], **options))
+    reqs = [GenerationRequest(f"g{i}", list(p), SamplingParams(max_tokens=n_new, ignore_eos=True)) for i, p in enumerate(prompts)]
+    for r in reqs:
+        eng.add_request(r)
+    while eng.has_unfinished_requests():
+        eng.step()
+    eng.runner.check_status()
+    eng.cache.check()
+    return [list(r.generated_tokens) for r in reqs], eng
+
+
+def test_toy_mixer_with_state_generates_from_cuda_graphs():
+    """The toy mixer's state lives in the cache manager's slots, so captured decode steps and captured
+    prompt portions find it like any page: tokens with graphs equal tokens without, and the plain ones."""
+    from firefly_b200.config import PartSpec
+    from firefly_b200.models import DecoderModel, config_from_dict, spec_for
+    from firefly_b200.parts import register_part
+    register_part("mixer", "toy_decay", ToyDecayMixer, replace=True)
+    cfg, decay = P.TINY_A, 0.9
+    spec = spec_for(config_from_dict(cfg))
+    toy = PartSpec("toy_decay", dict(hidden_size=cfg["hidden_size"], state_size=24, decay=decay), prefix="toy")
+    spec = dataclasses.replace(spec, layers=(spec.layers[0], dataclasses.replace(spec.layers[1], mixer=toy, position=None)))
+    model = DecoderModel(spec, _runtime(torch.float32))
+    assert not model.host_synchronous
+    names = {ws.name for ws in model.weight_specs()}
+    w = P.random_weights(cfg, 2, scale=0.05)
+    g = torch.Generator().manual_seed(5)
+    w["toy.in.weight"] = torch.randn(24, cfg["hidden_size"], generator=g) * 0.1
+    w["toy.out.weight"] = torch.randn(cfg["hidden_size"], 24, generator=g) * 0.1
+    model.bind({k: v.cuda() for k, v in w.items() if k in names})
+    rng = np.random.RandomState(3)
+    prompts = [list(map(int, rng.randint(0, cfg["vocab_size"], size=n))) for n in (40, 7, 33)]
+    with_graphs, eng = _generate(model, prompts, 12, max_prefill_chunk_size=8)
+    assert eng.graphs is not None and eng.stats["graph_steps"] > 0 and eng.graphs.shape_replays > 0
+    without, eng2 = _generate(model, prompts, 12, max_prefill_chunk_size=8, use_cuda_graphs=False)
+    assert eng2.graphs is None
+    assert with_graphs == without
+    for p, got in zip(prompts, with_graphs):
+        toks = list(p)
+        for _ in range(12):
+            toks.append(int(np.argmax(_toy_plain(cfg, w, toks, decay)[-1])))
+        assert got == toks[len(p):]
+
+
+def test_an_undeclared_host_read_fails_the_capture_with_words():
+    """A part that reads the device on the host without declaring it: the first captured step says
+    what is wrong and what to do, instead of a bare CUDA error."""
+    from firefly_b200.config import PartSpec
+    from firefly_b200.engine.runner import StepError
+    from firefly_b200.models import DecoderModel, config_from_dict, spec_for
+    from firefly_b200.parts import register_part
+
+    class Peeking(ToyDecayMixer):
+        def forward(self, x, ctx, slot, write_cache):
+            float(x.float().abs().max())                       # a read-back in the middle of the step
+            return super().forward(x, ctx, slot, write_cache)
+    register_part("mixer", "toy_peeking", Peeking, replace=True)
+    cfg = P.TINY_A
+    spec = spec_for(config_from_dict(cfg))
+    toy = PartSpec("toy_peeking", dict(hidden_size=cfg["hidden_size"], state_size=24, decay=0.5), prefix="toy")
+    spec = dataclasses.replace(spec, layers=(spec.layers[0], dataclasses.replace(spec.layers[1], mixer=toy, position=None)))
+    model = DecoderModel(spec, _runtime(torch.float32))
+    names = {ws.name for ws in model.weight_specs()}
+    w = P.random_weights(cfg, 2, scale=0.05)
+    w["toy.in.weight"] = torch.zeros(24, cfg["hidden_size"])
+    w["toy.out.weight"] = torch.zeros(cfg["hidden_size"], 24)
+    model.bind({k: v.cuda() for k, v in w.items() if k in names})
+    with pytest.raises(StepError, match="host_synchronous"):
+        _generate(model, [[1, 2, 3]], 4)
+    torch.cuda.synchronize()                                   # the device is fine afterwards
+    Peeking.host_synchronous = True
+    model2 = DecoderModel(spec, _runtime(torch.float32))
+    model2.bind({k: v.cuda() for k, v in w.items() if k in names})
+    out, eng = _generate(model2, [[1, 2, 3]], 4)
+    assert eng.graphs is None and len(out[0]) == 4
+
+
 # ------------------------------------- a toy feed-forward with routing, a toy position encoding --
 class ToyRoutedFFN:
     """Two small experts and a router: every token goes to its top-1 expert, whose output is
     scaled by the router's softmax weight.  Written with torch operations in the test."""
+
+    host_synchronous = True      # forward() asks the device which experts have tokens: no CUDA graphs for this model
 
     def __init__(self, spec, rt):
         self.hidden = spec.params["hidden_size"]
@@ -426,6 +513,16 @@ def test_toy_routed_feed_forward_and_learned_positions():
         got = U.run_trace(sess, steps)
         # a token whose two best experts are within rounding may be routed differently: not with these weights
         U.compare(got, plain, 2e-4, "toy routed feed-forward and learned positions")
+    # the routed part reads the device on the host and says so: the engine then runs launch by launch
+    assert model.host_synchronous
+    prompts = [reqs["r1"][:20], reqs["r2"]]
+    got, eng = _generate(model, prompts, 6)
+    assert eng.graphs is None
+    for p, out in zip(prompts, got):
+        toks = list(p)
+        for _ in range(6):
+            toks.append(int(np.argmax(_toy2_plain(cfg, w, toks)[-1])))
+        assert out == toks[len(p):]
 
 
 # ------------------------------------- a toy norm, arrangement and architecture --

@@ -68,3 +68,31 @@ def test_the_engines_own_parts_declare_what_they_do():
     for cls in (GQAttention, SwiGLUMLP):
         assert cls.adds_into_residual and cls.folds_next_norm and cls.accepts_folded_norm
     assert RMSNorm.foldable and PreNormBlock.takes_next_norm
+
+
+def test_a_part_that_synchronises_with_the_host_is_found_through_the_parts_that_hold_it():
+    from firefly_b200.parts.base import host_synchronous
+
+    class Quiet:
+        pass
+
+    class Loud:
+        host_synchronous = True
+
+    class Holder:
+        def __init__(self, inner):
+            self.inner = inner
+
+        def parts(self):
+            return self.inner
+
+    assert not host_synchronous(Quiet())
+    assert host_synchronous(Loud())
+    assert not host_synchronous(Holder([Quiet(), Holder([Quiet()])]))
+    assert host_synchronous(Holder([Quiet(), Holder([Loud()])]))
+    # the package's own model has none, so its steps may be captured
+    import plain_qwen3 as P
+    from firefly_b200.models import DecoderModel, config_from_dict, spec_for
+    model = DecoderModel(spec_for(config_from_dict(P.TINY_A)), Runtime(torch.device("cpu"), torch.float32))
+    assert model.host_synchronous is False
+    assert len(model.blocks[0].parts()) >= 4
