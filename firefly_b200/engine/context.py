@@ -7,7 +7,7 @@ position; that is all the kernels need to find its keys, whatever the cut.
 """
 from __future__ import annotations
 
-from dataclasses import dataclass
+from dataclasses import dataclass, field
 from typing import Dict, List, Sequence, Tuple
 
 import torch
@@ -22,10 +22,17 @@ class Workspace:
     def __init__(self, device):
         self.device = torch.device(device)
         self._bufs: Dict[Tuple[str, torch.dtype], torch.Tensor] = {}
+        # the views handed out, by (tag, type, shape): a step asks for the same few hundred again and
+        # again, and making a view costs the host several microseconds
+        self._views: Dict[tuple, torch.Tensor] = {}
         self.frozen = False
         self.version = 0          # counts (re)allocations: graphs that captured an address note it
 
     def get(self, tag: str, shape: Sequence[int], dtype: torch.dtype) -> torch.Tensor:
+        vkey = (tag, dtype, tuple(shape))
+        view = self._views.get(vkey)
+        if view is not None:
+            return view
         n = 1
         for s in shape:
             n *= int(s)
@@ -38,7 +45,12 @@ class Workspace:
             buf = torch.empty(max(n, 1), dtype=dtype, device=self.device)
             self._bufs[key] = buf
             self.version += 1
-        return buf[:n].view(*shape)
+            self._views.clear()   # views of the buffer that was replaced must not be handed out again
+        if len(self._views) > 4096:
+            self._views.clear()
+        view = buf[:n].view(*shape)
+        self._views[vkey] = view
+        return view
 
     def get_zeroed(self, tag: str, numel: int, dtype: torch.dtype) -> torch.Tensor:
         """A buffer that is zero when first handed out (and after it grows); users
@@ -51,6 +63,7 @@ class Workspace:
             buf = torch.zeros(max(numel, 1), dtype=dtype, device=self.device)
             self._bufs[key] = buf
             self.version += 1
+            self._views.clear()
         return buf[:numel]
 
     def zero(self, tag: str, dtype: torch.dtype) -> None:
@@ -90,6 +103,7 @@ class StepContext:
     num_decode_seqs: int = 0           # the first this-many sequences have exactly one token
     captured: bool = False             # being captured into a CUDA graph: launch shapes must be static
     ranges_by_length: bool = False     # the decoding sequences differ much in length (a hint for the attention)
+    memo: Dict[tuple, object] = field(default_factory=dict)   # what layers work out alike for this step (slices, counts)
 
     def kv(self, slot: int) -> Tuple[torch.Tensor, torch.Tensor]:
         """Pages of cache slot ``slot`` and the block table of its group."""

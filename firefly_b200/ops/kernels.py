@@ -665,19 +665,32 @@ def paged_attention(q: torch.Tensor, q_stride: int, pages: torch.Tensor, table: 
                         d, scale, window, splits, ctx.status)
     if n_dec < n:
         # portions of prompts: tiled kernel over the remaining sequences (token offsets in cu_q are absolute)
+        # every layer of a step asks the same of the step's arrays: worked out once and kept with the step
+        memo = getattr(ctx, "memo", None)
+        tail = memo.get(("attn_tail", id(table), n_dec)) if memo is not None else None
+        if tail is None:
+            tail = (table[n_dec:], ctx.cu_q[n_dec:], ctx.ctx_lens[n_dec:])
+            if memo is not None:
+                memo[("attn_tail", id(table), n_dec)] = tail
+        table_t, cu_q_t, ctx_lens_t = tail
         if USE_TC_ATTENTION and tc_attention_supported(q.dtype, d, pages.shape[3], ctx.max_kv_len):
-            tiles = sum(-(-(ql * G) // 128) for ql in ctx.q_lens[n_dec:])
+            plan = memo.get(("attn_tc_plan", G, nkv, n_dec, ctx.captured)) if memo is not None else None
+            if plan is None:
+                tiles = sum(-(-(ql * G) // 128) for ql in ctx.q_lens[n_dec:])
+                count = 1 if ctx.captured else attn_tc_shares(
+                    tiles, nkv, max(-(-(c + ql) // 64) for c, ql in zip(ctx.ctx_lens_host[n_dec:], ctx.q_lens[n_dec:])))
+                plan = (tiles, count, sum(ctx.q_lens[:n_dec]), sum(ctx.q_lens[n_dec:]))
+                if memo is not None:
+                    memo[("attn_tc_plan", G, nkv, n_dec, ctx.captured)] = plan
+            tiles, count, row0, rows = plan
             shares = None
-            count = 1 if ctx.captured else attn_tc_shares(
-                tiles, nkv, max(-(-(c + ql) // 64) for c, ql in zip(ctx.ctx_lens_host[n_dec:], ctx.q_lens[n_dec:])))
             if count > 1:
-                row0, rows = sum(ctx.q_lens[:n_dec]), sum(ctx.q_lens[n_dec:])
                 cells = (row0 + rows) * nq * count
                 shares = (count, ctx.workspace.get("attn.tc_part_o", (cells * d,), torch.float32),
                           ctx.workspace.get("attn.tc_part_ml", (cells * 2,), torch.float32), row0, rows)
-            attn_tc(q, q_stride, pages, table[n_dec:], ctx.cu_q[n_dec:], ctx.ctx_lens[n_dec:], n - n_dec, tiles,
+            attn_tc(q, q_stride, pages, table_t, cu_q_t, ctx_lens_t, n - n_dec, tiles,
                     out, nq, nkv, d, scale, window, ctx.status, shares=shares)
         else:
             tiles = sum(-(-(ql * G) // 64) for ql in ctx.q_lens[n_dec:])
-            attn_tiled(q, q_stride, pages, table[n_dec:], ctx.cu_q[n_dec:], ctx.ctx_lens[n_dec:], n - n_dec,
+            attn_tiled(q, q_stride, pages, table_t, cu_q_t, ctx_lens_t, n - n_dec,
                        tiles, out, nq, nkv, d, scale, window, ctx.status)
