@@ -127,7 +127,8 @@ def build_parser() -> argparse.ArgumentParser:
     ap.add_argument("--temperature", type=float, default=0.0)
     ap.add_argument("--stop-at-eos", action="store_true", help="end requests at config.json's eos_token_id")
     ap.add_argument("--dtype", default="bfloat16", choices=["bfloat16", "float32"])
-    ap.add_argument("--max-prefill-chunk-size", type=int, default=256)
+    ap.add_argument("--max-prefill-chunk-size", type=int, default=None,
+                    help="most prompt tokens of one request in one step (default: the engine's own choice)")
     ap.add_argument("--max-batch-size", type=int, default=64)
     ap.add_argument("--max-num-batched-tokens", type=int, default=8192)
     ap.add_argument("--kv-block-size", type=int, default=16)
