@@ -580,25 +580,47 @@ attn_tc_kernel(const __grid_constant__ TensorMapArg kv_map, const bf16* __restri
 }
 
 // Join of the shares: out[token, head, :] = sum_s w_s O_s / sum_s w_s l_s, w_s = 2^(m_s - max m), in
-// the order of the shares.  grid (tokens, heads); token t of the grid is row tok_base + t.
-__global__ void attn_tc_join_kernel(const float* __restrict__ part_o, const float* __restrict__ part_ml,
-                                    bf16* __restrict__ out, int out_stride, int nq, int num_splits, int tok_base) {
+// the order of the shares.  D / 4 threads own one (token, head) and four columns each (16-byte loads,
+// all shares' loads in flight together); a block of JOIN_THREADS takes as many pairs as fit it.
+constexpr int JOIN_THREADS = 256;
+constexpr int JOIN_MAX_SPLITS = 8;
+__global__ void __launch_bounds__(JOIN_THREADS)
+attn_tc_join_kernel(const float* __restrict__ part_o, const float* __restrict__ part_ml,
+                    bf16* __restrict__ out, int out_stride, int nq, int num_splits, int tok_base, int n_pairs) {
     asm volatile("griddepcontrol.launch_dependents;\n\tgriddepcontrol.wait;" ::: "memory");
-    const int tok = tok_base + blockIdx.x, head = blockIdx.y;
+    constexpr int TPP = D / 4;                                  // threads per (token, head)
+    const int pair = blockIdx.x * (JOIN_THREADS / TPP) + threadIdx.x / TPP;
+    if (pair >= n_pairs) return;
+    const int col = (threadIdx.x % TPP) * 4;
+    const int tok = tok_base + pair / nq, head = pair % nq;
     const size_t base = ((size_t)tok * nq + head) * num_splits;
+    float ms[JOIN_MAX_SPLITS], ls[JOIN_MAX_SPLITS];
+    float4 o[JOIN_MAX_SPLITS];
     float M = -CUDART_INF_F;
-    for (int s = 0; s < num_splits; ++s) M = fmaxf(M, part_ml[(base + s) * 2]);
-    for (int col = threadIdx.x; col < D; col += blockDim.x) {
-        float L = 0.f, O = 0.f;
-        for (int s = 0; s < num_splits; ++s) {
-            const float ms = part_ml[(base + s) * 2];
-            if (ms == -CUDART_INF_F) continue;
-            const float w = exp2f(ms - M);
-            L += w * part_ml[(base + s) * 2 + 1];
-            O += w * part_o[(base + s) * D + col];
+#pragma unroll
+    for (int s = 0; s < JOIN_MAX_SPLITS; ++s) {
+        if (s < num_splits) {
+            const float2 ml = *reinterpret_cast<const float2*>(part_ml + (base + s) * 2);
+            ms[s] = ml.x;
+            ls[s] = ml.y;
+            o[s] = *reinterpret_cast<const float4*>(part_o + (base + s) * D + col);
+            M = fmaxf(M, ml.x);
         }
-        out[(size_t)tok * out_stride + (size_t)head * D + col] = __float2bfloat16_rn(L > 0.f ? O / L : 0.f);
     }
+    float L = 0.f;
+    float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
+#pragma unroll
+    for (int s = 0; s < JOIN_MAX_SPLITS; ++s) {
+        if (s < num_splits && ms[s] != -CUDART_INF_F) {
+            const float w = exp2f(ms[s] - M);
+            L += w * ls[s];
+            acc.x += w * o[s].x; acc.y += w * o[s].y; acc.z += w * o[s].z; acc.w += w * o[s].w;
+        }
+    }
+    const float inv = L > 0.f ? 1.0f / L : 0.f;
+    __align__(8) bf16 r[4] = {__float2bfloat16_rn(acc.x * inv), __float2bfloat16_rn(acc.y * inv),
+                              __float2bfloat16_rn(acc.z * inv), __float2bfloat16_rn(acc.w * inv)};
+    *reinterpret_cast<uint2*>(out + (size_t)tok * out_stride + (size_t)head * D + col) = *reinterpret_cast<const uint2*>(r);
 }
 
 // ------------------------------------------------------------------ host side --
@@ -665,6 +687,7 @@ FF_EXPORT int ff_attn_tc(const void* q, int q_stride, const void* cache, const i
     if (n_seqs <= 0 || total_tiles <= 0) return 0;
     if (nkv <= 0 || nq % nkv) return FF_ERR_BAD_ARG;
     if (num_splits < 1 || (num_splits > 1 && (!part_o || !part_ml || n_tokens <= 0 || tok_base < 0))) return FF_ERR_BAD_ARG;
+    if (num_splits > JOIN_MAX_SPLITS) return FF_ERR_UNSUPPORTED;
     if (block_size < 8 || BN % block_size) return FF_ERR_UNSUPPORTED;
     if (((uintptr_t)cache & 127) || ((uintptr_t)q & 15) || (q_stride % 8) || ((uintptr_t)out & 15) || (out_stride % 8))
         return FF_ERR_UNSUPPORTED;
@@ -681,8 +704,9 @@ FF_EXPORT int ff_attn_tc(const void* q, int q_stride, const void* cache, const i
               (const bf16*)q, q_stride, block_table, max_blocks, cu_q, ctx_lens, n_seqs, (bf16*)out, out_stride, nq, nkv,
               block_size, num_blocks, scale * LOG2E, window, status, num_splits, part_o, part_ml);
     if (num_splits > 1) {
-        FF_LAUNCH((attn_tc_join_kernel), dim3((unsigned)n_tokens, (unsigned)nq), D >= 128 ? 128 : 64, 0, stream,
-                  (const float*)part_o, (const float*)part_ml, (bf16*)out, out_stride, nq, num_splits, tok_base);
+        const int n_pairs = n_tokens * nq, per_block = JOIN_THREADS / (D / 4);
+        FF_LAUNCH((attn_tc_join_kernel), dim3((unsigned)((n_pairs + per_block - 1) / per_block)), JOIN_THREADS, 0, stream,
+                  (const float*)part_o, (const float*)part_ml, (bf16*)out, out_stride, nq, num_splits, tok_base, n_pairs);
         FF_LAUNCH_CHECK();
     }
     return 0;

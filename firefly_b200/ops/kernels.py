@@ -550,13 +550,16 @@ def attn_tc(q, q_stride, pages, table, cu_q, ctx_lens, n_seqs, total_tiles, out,
         LAUNCHES += 1     # the kernel that joins the shares
 
 
+USE_TC_SHARES = True       # short portions behind long contexts share their keys out over several blocks
+
+
 def attn_tc_shares(total_tiles: int, nkv: int, max_key_tiles: int) -> int:
     """Over how many blocks a row tile's keys are shared out: 1 unless the row tiles alone would fill
     less than three quarters of the places (two per SM) and each would walk at least eight tiles of
     keys; then as many as fill the places once, each share at least four key tiles long, at most 8."""
     places = 2 * sm_count()
     units = total_tiles * nkv
-    if units * 4 >= places * 3 or max_key_tiles < 8:
+    if not USE_TC_SHARES or units * 4 >= places * 3 or max_key_tiles < 8:
         return 1
     return max(1, min(8, places // units, max_key_tiles // 4))
 
