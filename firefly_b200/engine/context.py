@@ -103,6 +103,7 @@ class StepContext:
     num_decode_seqs: int = 0           # the first this-many sequences have exactly one token
     captured: bool = False             # being captured into a CUDA graph: launch shapes must be static
     ranges_by_length: bool = False     # the decoding sequences differ much in length (a hint for the attention)
+    key_share_level: int = 0           # captured steps: over how many blocks at most a portion's keys may be shared out
     memo: Dict[tuple, object] = field(default_factory=dict)   # what layers work out alike for this step (slices, counts)
 
     def kv(self, slot: int) -> Tuple[torch.Tensor, torch.Tensor]:

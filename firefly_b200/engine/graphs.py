@@ -351,7 +351,9 @@ class DecodeGraphs:
     @staticmethod
     def shape_of(entries: Sequence[StepEntry]):
         """(order, key): the entries' order in the step (one-token sequences first, as the step function
-        sorts them) and the shape key (tokens per sequence, wanted rows among the step's tokens)."""
+        sorts them) and the shape key: tokens per sequence, wanted rows among the step's tokens, and how
+        long the longest portion's context is in four coarse levels (a captured step fixes over how many
+        blocks a portion's keys are shared out, and what suits 500 keys does not suit 16 000)."""
         order = sorted(range(len(entries)), key=lambda i: 0 if len(entries[i].tokens) == 1 else 1)
         q_lens = tuple(len(entries[i].tokens) for i in order)
         start, starts = 0, {}
@@ -359,7 +361,9 @@ class DecodeGraphs:
             starts[i] = start
             start += ql
         rows = tuple(starts[i] + w for i, e in enumerate(entries) for w in e.want)
-        return order, (q_lens, rows)
+        key_tiles = max((-(-(e.cache.num_tokens + len(e.tokens)) // 64) for e in entries if len(e.tokens) > 1), default=0)
+        level = 0 if key_tiles < 8 else (2 if key_tiles < 16 else (4 if key_tiles < 32 else 8))
+        return order, (q_lens, rows, level)
 
     def shape_ready(self, entries: Sequence[StepEntry]):
         """The plan of a step that should run from a graph: (order, key), or None if its shape has not
@@ -367,7 +371,7 @@ class DecodeGraphs:
         if not entries or len(entries) > self.runner.cache.max_requests:
             return None
         order, key = self.shape_of(entries)
-        q_lens, rows = key
+        q_lens, rows, _ = key
         if sum(q_lens) > self.SHAPE_MAX_TOKENS or any(ql < 1 for ql in q_lens):
             return None
         if key not in self.shapes:
@@ -384,7 +388,7 @@ class DecodeGraphs:
         sequence lies in the scratch page and the scratch state slot: the capture and the run before it
         write no live page and no request's state."""
         r = self.runner
-        q_lens, rows = key
+        q_lens, rows, level = key
         n, T, nr = len(q_lens), sum(q_lens), len(rows)
         b = _Bucket()
         b.size, b.q_lens, b.rows = n, list(q_lens), list(rows)
@@ -425,6 +429,7 @@ class DecodeGraphs:
         ctx.workspace = self.shape_workspace
         ctx.max_kv_len = r.max_model_len      # launch shapes must not depend on the requests
         ctx.captured = True
+        ctx.key_share_level = level           # ... except by the context's coarse level, which is part of the key
         ws_before = self.shape_workspace.version
         side = torch.cuda.Stream(device=r.device)
         side.wait_stream(torch.cuda.current_stream())

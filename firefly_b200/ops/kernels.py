@@ -680,8 +680,10 @@ def paged_attention(q: torch.Tensor, q_stride: int, pages: torch.Tensor, table: 
             plan = memo.get(("attn_tc_plan", G, nkv, n_dec, ctx.captured)) if memo is not None else None
             if plan is None:
                 tiles = sum(-(-(ql * G) // 128) for ql in ctx.q_lens[n_dec:])
-                count = 1 if ctx.captured else attn_tc_shares(
-                    tiles, nkv, max(-(-(c + ql) // 64) for c, ql in zip(ctx.ctx_lens_host[n_dec:], ctx.q_lens[n_dec:])))
+                # a captured step does not know its requests' lengths: the level it was captured for stands in
+                key_tiles = 4 * getattr(ctx, "key_share_level", 0) if ctx.captured else \
+                    max(-(-(c + ql) // 64) for c, ql in zip(ctx.ctx_lens_host[n_dec:], ctx.q_lens[n_dec:]))
+                count = attn_tc_shares(tiles, nkv, key_tiles)
                 plan = (tiles, count, sum(ctx.q_lens[:n_dec]), sum(ctx.q_lens[n_dec:]))
                 if memo is not None:
                     memo[("attn_tc_plan", G, nkv, n_dec, ctx.captured)] = plan

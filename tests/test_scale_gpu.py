@@ -42,6 +42,37 @@ def test_generated_tokens_are_the_replays_best_at_real_layer_sizes(options):
         del sess
 
 
+def test_captured_portions_share_out_the_keys_of_long_contexts_like_uncaptured_ones():
+    """A prompt of 2700 tokens comes in portions of 128 (twice, so that the shapes repeat and are
+    captured at every level of context length).  Captured steps fix over how many blocks a portion's
+    keys are shared out; the logits of the last portion and the generated tokens must agree with the
+    run that launches every step kernel by kernel."""
+    from firefly_b200 import LLM
+    from firefly_b200.models import config_from_dict
+    cfg = config_from_dict(REAL_SIZES)
+    rng = np.random.RandomState(8)
+    prompts = [list(map(int, rng.randint(0, cfg.vocab_size, size=2700))) for _ in range(2)]
+    outs, captures = {}, {}
+    for capture in (True, False):
+        llm = LLM(cfg, seed=3, dtype="bfloat16", num_kv_blocks=512, max_prefill_chunk_size=128,
+                  capture_repeating_steps=capture)
+        got = []
+        for p in prompts:                                  # one after the other: the second meets captured shapes
+            got.append(llm.generate([p], max_tokens=4)[0])
+        llm.engine.runner.check_status()
+        outs[capture] = got
+        captures[capture] = (llm.engine.graphs.shape_captures, llm.engine.graphs.shape_replays,
+                             sorted({k[2] for k in llm.engine.graphs.shapes}))
+        del llm
+        torch.cuda.empty_cache()
+    # every level of context length got a graph of its own (a scratch buffer that grows voids the older ones)
+    assert captures[True][0] >= 4 and captures[True][1] >= 10 and captures[True][2][-1] == 8
+    assert captures[False][0] == 0
+    assert outs[True][0] == outs[False][0]                  # the first prompt ran launch by launch in both
+    same = sum(a == b for a, b in zip(outs[True][1], outs[False][1]))
+    assert same >= 3, (outs[True][1], outs[False][1])       # bfloat16: the same kernels, a near tie at most
+
+
 @pytest.fixture(scope="module")
 def real_size_case(tmp_path_factory):
     """A model folder at the real layer sizes (bfloat16 values), three requests and the plain
