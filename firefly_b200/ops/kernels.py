@@ -237,7 +237,11 @@ def sample(logits: torch.Tensor, out: torch.Tensor, temperature: Optional[torch.
            seeds: Optional[torch.Tensor] = None, counters: Optional[torch.Tensor] = None) -> None:
     """out[r] = arg-max of logits[r] (lowest index on ties), or, where
     temperature[r] > 0, a draw from softmax(logits[r] / temperature[r]) with the
-    random numbers of (seeds[r], counters[r])."""
+    random numbers of (seeds[r], counters[r]).
+
+    The one wrapper that keeps memory of its own: the partial results of rows split over several
+    blocks live in a scratch pair per device that grows when more rows come.  It never grows while
+    the stream is being captured (an error then: the run before the capture sizes it)."""
     global LAUNCHES
     _need_cuda(logits, out, temperature, seeds, counters)
     assert logits.dtype == torch.float32 and out.dtype == torch.int32 and logits.dim() == 2
@@ -252,6 +256,9 @@ def sample(logits: torch.Tensor, out: torch.Tensor, temperature: Optional[torch.
         key = logits.device
         buf = _sample_scratch.get(key)
         if buf is None or buf[0].numel() < rows * chunks:
+            if torch.cuda.is_current_stream_capturing():
+                raise KernelError("sample: its scratch memory would have to grow while a CUDA graph is being "
+                                  "captured; run the same step once before the capture")
             n = max(rows * chunks, 4096)
             buf = (torch.empty(n, dtype=torch.float32, device=key), torch.empty(n, dtype=torch.int32, device=key))
             _sample_scratch[key] = buf
