@@ -13,6 +13,7 @@ headers under ``baseline/shim`` (``mdspan/mdspan.hpp``, ``print``) and ``ref_dri
     python baseline/build_reference.py [/path/to/firefly]
 """
 import glob
+import json
 import os
 import subprocess
 import sys
@@ -63,4 +64,13 @@ def build(reference: str) -> str:
 
 
 if __name__ == "__main__":
-    print(build(sys.argv[1] if len(sys.argv) > 1 else "/root/reference"))
+    where = sys.argv[1] if len(sys.argv) > 1 else os.environ.get("FIREFLY_REFERENCE", "")
+    if not where:
+        try:
+            with open(os.path.join(HERE, "..", "BASELINE.json")) as fh:
+                where = json.load(fh).get("reference_path", "")
+        except (OSError, ValueError):
+            where = ""
+    if not where:
+        sys.exit("usage: python baseline/build_reference.py REFERENCE_SOURCES (or $FIREFLY_REFERENCE)")
+    print(build(where))

@@ -168,6 +168,15 @@ def write_reference_model(folder: str, shape: dict, seed: int = 0) -> float:
     return off / 1e9
 
 
+def _baseline_record() -> dict:
+    """BASELINE.json beside this file (it names where the reference's sources lie), or nothing."""
+    try:
+        with open(os.path.join(ROOT, "BASELINE.json")) as fh:
+            return json.load(fh)
+    except (OSError, ValueError):
+        return {}
+
+
 def reference_arm(args) -> int:
     """The reference's own engine (built unmodified by baseline/build_reference.py into
     baseline/_ref/ref_bench) on the same shape and batch, fed through Engine::async_generate and timed
@@ -178,8 +187,8 @@ def reference_arm(args) -> int:
     if args.gpus != 1:
         return unavailable("the reference runs on one GPU only (it has no multi-GPU path)")
     if not os.path.isfile(REF_BIN):
-        src = os.environ.get("FIREFLY_REFERENCE", "/root/reference")
-        if not os.path.isdir(os.path.join(src, "src", "kernels")):
+        src = os.environ.get("FIREFLY_REFERENCE") or _baseline_record().get("reference_path", "")
+        if not src or not os.path.isdir(os.path.join(src, "src", "kernels")):
             return unavailable("baseline/_ref/ref_bench is not built and the reference's sources are not on this "
                                "machine (python baseline/build_reference.py builds it where they are)")
         try:
