@@ -494,7 +494,8 @@ attn_decode_body(const bf16* __restrict__ q, int q_stride, const bf16* __restric
         if (i < n && unit >= u0 && unit < u1) {
             s_mine[0] = i;
             s_mine[1] = unit - u0;
-            s_mine[2] = min(min(u1 - u0, tiles), un.max_ranges);
+            // a range holds a tile and a half of keys at least: short sequences are not cut into crumbs
+            s_mine[2] = min(min(u1 - u0, max(1, tiles * 2 / 3)), un.max_ranges);
             s_mine[3] = p;
         }
         __syncthreads();
@@ -763,46 +764,73 @@ __device__ __forceinline__ void attn_combine_body(const float* __restrict__ part
                                                   int out_stride, int nq, int num_splits,
                                                   const int* __restrict__ seq_ranges, int part_stride) {
     pdl_prologue();
+    // D / 4 threads (four columns each, 16-byte loads) make a group; the block's groups take the
+    // partial results in turn (group g the ranges g, g + groups, ...), four loads in flight each, and
+    // group 0 then merges the groups' sums in their order: the result does not depend on timing.
+    constexpr int LPG = D / 4;
+    constexpr int MAXG = 8;
+    __shared__ float s_o[MAXG][D];
+    __shared__ float s_ml[MAXG][2];
     const int seq = blockIdx.x, head = blockIdx.y;
-    // The count of a sequence's partial results is asked for together with the first eight of them
-    // (which may lie beyond the count: they are read from the scratch memory and then ignored).
-    const int readable = seq_ranges != nullptr ? part_stride : num_splits;
+    const int groups = min(MAXG, (int)blockDim.x / LPG);
+    const int g = threadIdx.x / LPG, col = (threadIdx.x % LPG) * 4;
     if (seq_ranges != nullptr) num_splits = seq_ranges[seq];
+    if (seq_ranges != nullptr && num_splits <= 1) return;          // one range: the output is final already
     const size_t base = ((size_t)seq * nq + head) * part_stride;
     const int tok = cu_q[seq];
-    for (int col = threadIdx.x; col < D; col += blockDim.x) {
-        float M = -CUDART_INF_F, L = 0.f, O = 0.f;
-        for (int s0 = 0; s0 == 0 || s0 < num_splits; s0 += 8) {
-            float ms[8], ls[8], os[8];
+    float M = -CUDART_INF_F, L = 0.f;
+    float4 O = make_float4(0.f, 0.f, 0.f, 0.f);
+    if (g < groups) {
+        for (int s0 = g; s0 < num_splits; s0 += 4 * groups) {
+            float ms[4], ls[4];
+            float4 os[4];
 #pragma unroll
-            for (int k = 0; k < 8; ++k) {
-                const size_t p = base + min(s0 + k, readable - 1);
-                ms[k] = part_ml[p * 2];
-                ls[k] = part_ml[p * 2 + 1];
-                os[k] = part_o[p * D + col];
+            for (int k = 0; k < 4; ++k) {
+                const int sp = s0 + k * groups;
+                const size_t p = base + min(sp, num_splits - 1);
+                const float2 ml = *reinterpret_cast<const float2*>(part_ml + p * 2);
+                ms[k] = sp < num_splits ? ml.x : -CUDART_INF_F;
+                ls[k] = ml.y;
+                os[k] = *reinterpret_cast<const float4*>(part_o + p * D + col);
             }
-            if (seq_ranges != nullptr && num_splits <= 1) return;   // one range: the output is final already
-#pragma unroll
-            for (int k = 0; k < 8; ++k)
-                if (s0 + k >= num_splits) ms[k] = -CUDART_INF_F;
             float Mn = M;
 #pragma unroll
-            for (int k = 0; k < 8; ++k) Mn = fmaxf(Mn, ms[k]);
-            if (Mn == -CUDART_INF_F) continue;                     // no key in any split so far
+            for (int k = 0; k < 4; ++k) Mn = fmaxf(Mn, ms[k]);
+            if (Mn == -CUDART_INF_F) continue;                     // no key in any of these ranges
             const float r = M == -CUDART_INF_F ? 0.f : exp2f(M - Mn);
             L *= r;
-            O *= r;
+            O.x *= r; O.y *= r; O.z *= r; O.w *= r;
 #pragma unroll
-            for (int k = 0; k < 8; ++k) {
+            for (int k = 0; k < 4; ++k) {
                 if (ms[k] != -CUDART_INF_F) {
                     const float w = exp2f(ms[k] - Mn);
                     L += w * ls[k];
-                    O += w * os[k];
+                    O.x += w * os[k].x; O.y += w * os[k].y; O.z += w * os[k].z; O.w += w * os[k].w;
                 }
             }
             M = Mn;
         }
-        out[(size_t)tok * out_stride + (size_t)head * D + col] = __float2bfloat16_rn(O / L);
+        *reinterpret_cast<float4*>(&s_o[g][col]) = O;
+        if (col == 0) { s_ml[g][0] = M; s_ml[g][1] = L; }
+    }
+    __syncthreads();
+    if (g == 0) {
+        float Mt = -CUDART_INF_F;
+        for (int k = 0; k < groups; ++k) Mt = fmaxf(Mt, s_ml[k][0]);
+        float Lt = 0.f;
+        float4 Ot = make_float4(0.f, 0.f, 0.f, 0.f);
+        for (int k = 0; k < groups; ++k) {
+            const float mk = s_ml[k][0];
+            if (mk == -CUDART_INF_F) continue;
+            const float w = exp2f(mk - Mt);
+            const float4 o = *reinterpret_cast<const float4*>(&s_o[k][col]);
+            Lt += w * s_ml[k][1];
+            Ot.x += w * o.x; Ot.y += w * o.y; Ot.z += w * o.z; Ot.w += w * o.w;
+        }
+        const float inv = 1.0f / Lt;
+        __align__(8) bf16 r4[4] = {__float2bfloat16_rn(Ot.x * inv), __float2bfloat16_rn(Ot.y * inv),
+                                   __float2bfloat16_rn(Ot.z * inv), __float2bfloat16_rn(Ot.w * inv)};
+        *reinterpret_cast<uint2*>(out + (size_t)tok * out_stride + (size_t)head * D + col) = *reinterpret_cast<const uint2*>(r4);
     }
 }
 __global__ void attn_combine_kernel(const float* __restrict__ part_o, const float* __restrict__ part_ml,
@@ -816,6 +844,7 @@ __global__ void attn_combine_units_kernel(const float* __restrict__ part_o, cons
     attn_combine_body(part_o, part_ml, cu_q, out, out_stride, nq, 0, seq_ranges, part_stride);
 }
 
+constexpr int COMBINE_THREADS = D >= 256 ? 256 : 128;     // two to eight groups of D / 4 threads
 constexpr size_t TILED_SMEM = (size_t)(BM + 4 * BN) * KSTR * sizeof(bf16);
 constexpr size_t DECODE_KV_SMEM = (size_t)(4 * BN) * KSTR * sizeof(bf16);
 constexpr size_t DECODE_JOIN_SMEM = (size_t)(4 * 16 * (D + 8) + 2 * 4 * 16) * sizeof(float);
@@ -863,7 +892,7 @@ FF_EXPORT int ff_attn_decode(const void* q, int q_stride, const void* cache, con
     FF_LAUNCH_CHECK();
     if (num_splits > 1) {
         dim3 cgrid(n_seqs, nq);
-        FF_LAUNCH((attn_combine_kernel), cgrid, D >= 128 ? 128 : 64, 0, stream, part_o, part_ml, cu_q, (bf16*)out,
+        FF_LAUNCH((attn_combine_kernel), cgrid, COMBINE_THREADS, 0, stream, part_o, part_ml, cu_q, (bf16*)out,
                                                                      out_stride, nq, num_splits);
         FF_LAUNCH_CHECK();
     }
@@ -892,7 +921,7 @@ FF_EXPORT int ff_attn_decode_heads(const void* qkv, int row_width, void* cache, 
     FF_LAUNCH_CHECK();
     if (num_splits > 1) {
         dim3 cgrid(n_seqs, nq);
-        FF_LAUNCH((attn_combine_kernel), cgrid, D >= 128 ? 128 : 64, 0, stream, part_o, part_ml, cu_q, (bf16*)out,
+        FF_LAUNCH((attn_combine_kernel), cgrid, COMBINE_THREADS, 0, stream, part_o, part_ml, cu_q, (bf16*)out,
                                                                      out_stride, nq, num_splits);
         FF_LAUNCH_CHECK();
     }
@@ -935,7 +964,7 @@ FF_EXPORT int ff_attn_decode_units(const void* q, int q_stride, void* cache, con
     FF_LAUNCH_CHECK();
     if (units > n_seqs && max_ranges > 1) {
         dim3 cgrid(n_seqs, nq);
-        FF_LAUNCH((attn_combine_units_kernel), cgrid, D >= 128 ? 128 : 64, 0, stream, part_o, part_ml, cu_q,
+        FF_LAUNCH((attn_combine_units_kernel), cgrid, COMBINE_THREADS, 0, stream, part_o, part_ml, cu_q,
                   (bf16*)out, out_stride, nq, (const int*)seq_ranges, units);
         FF_LAUNCH_CHECK();
     }

@@ -584,7 +584,7 @@ def decode_splits(n_seqs: int, nkv: int, max_kv_len: int) -> int:
 
 
 DECODE_BY_UNITS = True      # few sequences: ranges of keys shared out by length so that the blocks fill the SMs once
-DECODE_MAX_RANGES = 24      # a sequence is cut into at most this many ranges (batch 1 measured best near it)
+DECODE_MAX_RANGES = 64      # a sequence is cut into at most this many ranges (and a range holds 1.5 tiles of keys at least)
 
 
 @functools.lru_cache(maxsize=None)
@@ -595,10 +595,14 @@ def _decode_places_per_kv_head(nkv: int, d: int) -> int:
 def lengths_differ_much(ctx_lens) -> bool:
     """True if the longest of these decoding sequences has a quarter more tiles of keys than the
     average: then a fixed number of ranges per sequence makes blocks of very different length, and
-    the attention shares its blocks out by length instead (`decode_units`)."""
-    if len(ctx_lens) < 2:
-        return False
+    the attention shares its blocks out by length instead (`decode_units`).  Also true for one or
+    two sequences of 3000 tokens or more."""
     tiles = [c // 64 + 1 for c in ctx_lens]
+    if len(tiles) <= 2:
+        # one or two long sequences: the fixed 20 ranges leave two thirds of the SMs' places empty and every
+        # block waits for its own tiles one after the other (batch 1 behind 32 000 tokens: 2.3 TB/s);
+        # shared out by length a sequence gets as many ranges as there are places
+        return bool(tiles) and max(tiles) >= 48
     return max(tiles) >= 4 and max(tiles) * len(tiles) >= 1.25 * sum(tiles)
 
 

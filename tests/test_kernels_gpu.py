@@ -432,6 +432,64 @@ def test_attention_decode_ranges_shared_out_by_length(d, nq, nkv, block, window,
         assert window or (got[5] == max(got) and got[5] > got[7] > got[4])       # by length
 
 
+@pytest.mark.parametrize("ctx_len,n", [(9000, 1), (6100, 2), (70, 1)])
+def test_attention_decode_one_or_two_long_sequences_take_all_the_places(ctx_len, n):
+    """Few long sequences: as many ranges as there are units (here 55 a kv head), each of a tile and a
+    half of keys at least; a short sequence is not cut into crumbs.  One far key carries nearly all the
+    weight of a row, so that a range that is lost or joined twice shows.  The plain result is written
+    out for the new token alone (the whole-sequence function would need the full score matrix)."""
+    d, nq, nkv, block = 128, 8, 2, 16
+    G = nq // nkv
+    g = torch.Generator().manual_seed(6)
+    qs, wants, tables, page_list, ctxs, base = [], [], [], [], [], 1
+    for si in range(n):
+        cl = ctx_len - 37 * si
+        T = cl + 1
+        q = torch.randn(nq, d, generator=g)
+        k = torch.randn(T, nkv, d, generator=g)
+        v = torch.randn(T, nkv, d, generator=g)
+        far = min(T - 1, 5 + 700 * si)
+        k[far] = k[far] * 0.1 + 3.0 * q[::G] / math.sqrt(d) * 4
+        q, k, v = q.to(torch.bfloat16), k.to(torch.bfloat16), v.to(torch.bfloat16)
+        want = torch.empty(nq, d, dtype=torch.float64)
+        for h in range(nq):
+            sc = (k.double()[:, h // G] @ q[h].double()) / math.sqrt(d)
+            want[h] = torch.softmax(sc, dim=0) @ v.double()[:, h // G]
+        pages, order = _paged(k, v, block, seed=30 + si)
+        page_list.append(pages[1:])
+        tables.append([o - 1 + base for o in order])
+        base += pages.shape[0] - 1
+        qs.append(q.reshape(1, nq * d))
+        wants.append(want.reshape(1, nq * d))
+        ctxs.append(cl)
+    all_pages = torch.cat([torch.zeros(1, *page_list[0].shape[1:], dtype=torch.bfloat16)] + page_list, 0)
+    mb = max(len(t) for t in tables) + 1
+    table = torch.full((n, mb), -1, dtype=torch.int32)
+    for i, t in enumerate(tables):
+        table[i, :len(t)] = torch.tensor(t, dtype=torch.int32)
+    want = torch.cat(wants, 0)
+    units, max_ranges = 55, 64
+    out = torch.zeros(n, nq * d, dtype=torch.bfloat16, device="cuda")
+    part_o = torch.full((n * nq * units * d,), float("nan"), device="cuda")
+    part_ml = torch.full((n * nq * units * 2,), float("nan"), device="cuda")
+    seq_ranges = torch.full((n,), -7, dtype=torch.int32, device="cuda")
+    K().attn_decode_units(dev(torch.cat(qs, 0).contiguous()), nq * d, dev(all_pages), dev(table),
+                          dev(torch.arange(n + 1, dtype=torch.int32)), dev(torch.tensor(ctxs, dtype=torch.int32)),
+                          n, out, part_o, part_ml, seq_ranges, nq, nkv, d, 1 / math.sqrt(d), 0, units, max_ranges)
+    torch.cuda.synchronize()
+    err = (out.cpu().double() - want).abs().max() / want.abs().max()
+    assert float(err) < 2e-2, float(err)
+    got = seq_ranges.cpu().tolist()
+    for r, cl in zip(got, ctxs):
+        tiles = (cl + 64) // 64
+        assert 1 <= r <= max(1, tiles * 2 // 3), (got, tiles)
+    if ctx_len >= 6000:
+        assert sum(got) >= units - n           # the long ones fill the units
+    from firefly_b200.ops import kernels as kern
+    assert kern.lengths_differ_much([ctx_len] * n) == (ctx_len >= 3072)
+    assert not kern.lengths_differ_much([2100] * 8) and kern.lengths_differ_much([200, 6000, 300, 250])
+
+
 class _Scratch:
     def __init__(self):
         self.bufs = {}
