@@ -80,7 +80,7 @@ int ff_attn_decode_static(const void* q, int q_stride, const void* cache, const 
     FF_LAUNCH_CHECK();
     if (num_splits > 1) {
         dim3 cgrid(n_seqs, nq);
-        attn_combine_kernel<<<cgrid, COMBINE_THREADS, 0, stream>>>(part_o, part_ml, cu_q, (bf16*)out,
+        attn_combine_kernel<<<cgrid, D >= 128 ? 128 : 64, 0, stream>>>(part_o, part_ml, cu_q, (bf16*)out,
                                                                      out_stride, nq, num_splits);
         FF_LAUNCH_CHECK();
     }

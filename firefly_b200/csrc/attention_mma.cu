@@ -764,6 +764,57 @@ __device__ __forceinline__ void attn_combine_body(const float* __restrict__ part
                                                   int out_stride, int nq, int num_splits,
                                                   const int* __restrict__ seq_ranges, int part_stride) {
     pdl_prologue();
+    const int seq = blockIdx.x, head = blockIdx.y;
+    // The count of a sequence's partial results is asked for together with the first eight of them
+    // (which may lie beyond the count: they are read from the scratch memory and then ignored).
+    const int readable = seq_ranges != nullptr ? part_stride : num_splits;
+    if (seq_ranges != nullptr) num_splits = seq_ranges[seq];
+    const size_t base = ((size_t)seq * nq + head) * part_stride;
+    const int tok = cu_q[seq];
+    for (int col = threadIdx.x; col < D; col += blockDim.x) {
+        float M = -CUDART_INF_F, L = 0.f, O = 0.f;
+        for (int s0 = 0; s0 == 0 || s0 < num_splits; s0 += 8) {
+            float ms[8], ls[8], os[8];
+#pragma unroll
+            for (int k = 0; k < 8; ++k) {
+                const size_t p = base + min(s0 + k, readable - 1);
+                ms[k] = part_ml[p * 2];
+                ls[k] = part_ml[p * 2 + 1];
+                os[k] = part_o[p * D + col];
+            }
+            if (seq_ranges != nullptr && num_splits <= 1) return;   // one range: the output is final already
+#pragma unroll
+            for (int k = 0; k < 8; ++k)
+                if (s0 + k >= num_splits) ms[k] = -CUDART_INF_F;
+            float Mn = M;
+#pragma unroll
+            for (int k = 0; k < 8; ++k) Mn = fmaxf(Mn, ms[k]);
+            if (Mn == -CUDART_INF_F) continue;                     // no key in any split so far
+            const float r = M == -CUDART_INF_F ? 0.f : exp2f(M - Mn);
+            L *= r;
+            O *= r;
+#pragma unroll
+            for (int k = 0; k < 8; ++k) {
+                if (ms[k] != -CUDART_INF_F) {
+                    const float w = exp2f(ms[k] - Mn);
+                    L += w * ls[k];
+                    O += w * os[k];
+                }
+            }
+            M = Mn;
+        }
+        out[(size_t)tok * out_stride + (size_t)head * D + col] = __float2bfloat16_rn(O / L);
+    }
+}
+__device__ __forceinline__ void attn_combine_many_body(const float* __restrict__ part_o,
+                                                  const float* __restrict__ part_ml,
+                                                  const int* __restrict__ cu_q, bf16* __restrict__ out,
+                                                  int out_stride, int nq, int num_splits,
+                                                  const int* __restrict__ seq_ranges, int part_stride) {
+    pdl_prologue();
+    // The form for many ranges (a long sequence cut into up to 64).  It holds shared memory, so its blocks
+    // cannot sit beside three blocks of the attention kernel and start only when those leave: the form
+    // above, which holds none, stays the one for the usual few ranges (0.9 us a layer at batch 8).
     // D / 4 threads (four columns each, 16-byte loads) make a group; the block's groups take the
     // partial results in turn (group g the ranges g, g + groups, ...), four loads in flight each, and
     // group 0 then merges the groups' sums in their order: the result does not depend on timing.
@@ -843,6 +894,16 @@ __global__ void attn_combine_units_kernel(const float* __restrict__ part_o, cons
                                           int nq, const int* __restrict__ seq_ranges, int part_stride) {
     attn_combine_body(part_o, part_ml, cu_q, out, out_stride, nq, 0, seq_ranges, part_stride);
 }
+__global__ void attn_combine_many_kernel(const float* __restrict__ part_o, const float* __restrict__ part_ml,
+                                         const int* __restrict__ cu_q, bf16* __restrict__ out, int out_stride,
+                                         int nq, int num_splits) {
+    attn_combine_many_body(part_o, part_ml, cu_q, out, out_stride, nq, num_splits, nullptr, num_splits);
+}
+__global__ void attn_combine_units_many_kernel(const float* __restrict__ part_o, const float* __restrict__ part_ml,
+                                               const int* __restrict__ cu_q, bf16* __restrict__ out, int out_stride,
+                                               int nq, const int* __restrict__ seq_ranges, int part_stride) {
+    attn_combine_many_body(part_o, part_ml, cu_q, out, out_stride, nq, 0, seq_ranges, part_stride);
+}
 
 constexpr int COMBINE_THREADS = D >= 256 ? 256 : 128;     // two to eight groups of D / 4 threads
 constexpr size_t TILED_SMEM = (size_t)(BM + 4 * BN) * KSTR * sizeof(bf16);
@@ -892,8 +953,12 @@ FF_EXPORT int ff_attn_decode(const void* q, int q_stride, const void* cache, con
     FF_LAUNCH_CHECK();
     if (num_splits > 1) {
         dim3 cgrid(n_seqs, nq);
-        FF_LAUNCH((attn_combine_kernel), cgrid, COMBINE_THREADS, 0, stream, part_o, part_ml, cu_q, (bf16*)out,
-                                                                     out_stride, nq, num_splits);
+        if (num_splits > 8)
+            FF_LAUNCH((attn_combine_many_kernel), cgrid, COMBINE_THREADS, 0, stream, part_o, part_ml, cu_q, (bf16*)out,
+                      out_stride, nq, num_splits);
+        else
+            FF_LAUNCH((attn_combine_kernel), cgrid, D >= 128 ? 128 : 64, 0, stream, part_o, part_ml, cu_q, (bf16*)out,
+                      out_stride, nq, num_splits);
         FF_LAUNCH_CHECK();
     }
     return 0;
@@ -921,8 +986,12 @@ FF_EXPORT int ff_attn_decode_heads(const void* qkv, int row_width, void* cache, 
     FF_LAUNCH_CHECK();
     if (num_splits > 1) {
         dim3 cgrid(n_seqs, nq);
-        FF_LAUNCH((attn_combine_kernel), cgrid, COMBINE_THREADS, 0, stream, part_o, part_ml, cu_q, (bf16*)out,
-                                                                     out_stride, nq, num_splits);
+        if (num_splits > 8)
+            FF_LAUNCH((attn_combine_many_kernel), cgrid, COMBINE_THREADS, 0, stream, part_o, part_ml, cu_q, (bf16*)out,
+                      out_stride, nq, num_splits);
+        else
+            FF_LAUNCH((attn_combine_kernel), cgrid, D >= 128 ? 128 : 64, 0, stream, part_o, part_ml, cu_q, (bf16*)out,
+                      out_stride, nq, num_splits);
         FF_LAUNCH_CHECK();
     }
     return 0;
@@ -964,8 +1033,14 @@ FF_EXPORT int ff_attn_decode_units(const void* q, int q_stride, void* cache, con
     FF_LAUNCH_CHECK();
     if (units > n_seqs && max_ranges > 1) {
         dim3 cgrid(n_seqs, nq);
-        FF_LAUNCH((attn_combine_units_kernel), cgrid, COMBINE_THREADS, 0, stream, part_o, part_ml, cu_q,
-                  (bf16*)out, out_stride, nq, (const int*)seq_ranges, units);
+        // a sequence gets at most this many ranges: many of them take the form that spreads them over warps
+        const int most = max_ranges < units - n_seqs + 1 ? max_ranges : units - n_seqs + 1;
+        if (most > 8)
+            FF_LAUNCH((attn_combine_units_many_kernel), cgrid, COMBINE_THREADS, 0, stream, part_o, part_ml, cu_q,
+                      (bf16*)out, out_stride, nq, (const int*)seq_ranges, units);
+        else
+            FF_LAUNCH((attn_combine_units_kernel), cgrid, D >= 128 ? 128 : 64, 0, stream, part_o, part_ml, cu_q,
+                      (bf16*)out, out_stride, nq, (const int*)seq_ranges, units);
         FF_LAUNCH_CHECK();
     }
     return 0;

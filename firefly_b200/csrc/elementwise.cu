@@ -187,8 +187,11 @@ __global__ void add_kernel(float* __restrict__ res, const TD* __restrict__ delta
 // buf[upd[1 + 2i]] = upd[2 + 2i] for i < min(upd[0], cap): a step's few changed block-table
 // entries are written into the table that stays on the device, so that the host uploads what
 // changed and not the table.  Indices outside [0, len) are skipped.
+// The kernels behind this one look pages up in the tables before they wait for the kernel in front of
+// them, so this one does not let its dependents start early: they are launched when it has ended,
+// with its writes in place.
 __global__ void scatter_int_kernel(int* __restrict__ buf, const int* __restrict__ upd, int cap, int len) {
-    pdl_prologue();
+    asm volatile("griddepcontrol.wait;" ::: "memory");
     const int n = min(upd[0], cap);
     for (int i = blockIdx.x * blockDim.x + threadIdx.x; i < n; i += gridDim.x * blockDim.x) {
         const int idx = upd[1 + 2 * i];
